@@ -1,0 +1,646 @@
+"""ctypes wrapper over libb200mat.so with the `cm` module surface of cudamat.
+
+Mirrors cudamat/cudamat.py: class CUDAMatrix (:126-1531), empty (:1533), sum (:1546),
+dot (:1579), vdot (:1596), sigmoid/exp/log_1_plus_exp (:1607-1700), cuda_set_device,
+cublas_init/shutdown, cuda_sync_threads, so deepnet's dbm.py / layer.py / edge.py /
+parameter.py run on it unchanged.  Matrices are float32, column-major; `.T` and
+`slice` are non-owning views.  Extra entry points (fused_gemm, momentum_update,
+split_tf32, dp_*) have no counterpart in the reference.
+
+There is no CPU fallback: importing works without a GPU (so the symbols can be
+inspected), but the first operation fails loudly if the library or a device is missing.
+"""
+import ctypes as ct
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libb200mat.so")
+
+MAX_PASS = 8
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            "libb200mat.so is missing: build it with `python -m deepnet_b200.build` "
+            "(nvcc, sm_100a); there is no CPU fallback")
+    return ct.CDLL(_LIB_PATH)
+
+
+_lib = _load()
+
+
+class cudamat(ct.Structure):
+    """struct cudamat of cudamat/cudamat.cuh:21-29."""
+    _fields_ = [("data_host", ct.POINTER(ct.c_float)), ("data_device", ct.POINTER(ct.c_float)),
+                ("on_device", ct.c_int), ("on_host", ct.c_int), ("size", ct.c_int * 2),
+                ("is_trans", ct.c_int), ("owns_data", ct.c_int)]
+
+
+class rnd_struct(ct.Structure):
+    _fields_ = [("seed", ct.c_ulonglong), ("calls", ct.c_ulonglong)]
+
+
+class _Pass(ct.Structure):
+    _fields_ = [("a", ct.POINTER(cudamat)), ("b", ct.POINTER(cudamat)), ("negate", ct.c_int)]
+
+
+class _FusedGemm(ct.Structure):
+    _fields_ = [("npass", ct.c_int), ("passes", _Pass * MAX_PASS), ("alpha", ct.c_float), ("beta", ct.c_float),
+                ("bias", ct.POINTER(cudamat)), ("col_scale", ct.POINTER(cudamat)), ("activation", ct.c_int),
+                ("out", ct.POINTER(cudamat)), ("out_hi", ct.POINTER(cudamat)), ("out_lo", ct.POINTER(cudamat)),
+                ("sample", ct.POINTER(cudamat))]
+
+
+_lib.get_last_cuda_error.restype = ct.c_char_p
+_lib.euclid_norm.restype = ct.c_float
+_lib.vdot.restype = ct.c_float
+_lib.sum_all.restype = ct.c_float
+_lib.b200_host_alloc.restype = ct.c_void_p
+_lib.b200_host_alloc.argtypes = [ct.c_size_t]
+_lib.b200_host_free.argtypes = [ct.c_void_p]
+_lib.b200_get_stream.restype = ct.c_void_p
+_lib.b200_set_stream.argtypes = [ct.c_void_p]
+_lib.copy_from_host_ptr.argtypes = [ct.POINTER(cudamat), ct.c_void_p, ct.c_size_t]
+_lib.init_from_array.restype = None
+_lib.set_transpose.restype = None
+_lib.cuda_sync_threads.restype = None
+
+
+class CUDAMatException(Exception):
+    pass
+
+
+_ERRORS = {
+    -1: "Incompatible matrix dimensions.",
+    -2: "CUBLAS error.",
+    -4: "Operation not supported on views.",
+    -5: "Operation not supported on transposed matrices.",
+    -6: "",
+    -7: "Incompatible transposedness.",
+    -8: "Matrix is not in device memory.",
+    -9: "Operation not supported.",
+    -11: "A device-side wait ran out of time.",
+}
+
+
+def generate_exception(err_code):
+    """Error-code mapping of cudamat/cudamat.py:101-123 (plus -10 NCCL, -11 device timeout)."""
+    if err_code in (-3, -10):
+        return CUDAMatException(("CUDA error: " if err_code == -3 else "NCCL error: ") +
+                                _lib.get_last_cuda_error().decode("utf-8", "replace"))
+    return CUDAMatException(_ERRORS.get(err_code, "error code %d" % err_code))
+
+
+def _check(err_code):
+    if err_code:
+        raise generate_exception(err_code)
+
+
+_device_checked = False
+
+
+def _require_device():
+    global _device_checked
+    if not _device_checked:
+        if _lib.b200_device_count() <= 0:
+            raise CUDAMatException("no CUDA device is visible; b200mat has no CPU fallback")
+        _check(_lib.cublas_init())
+        _device_checked = True
+
+
+class CUDAMatrix(object):
+    """A float32 column-major matrix in GPU memory (cudamat/cudamat.py:126)."""
+
+    rnd_state = rnd_struct()
+    rnd_state_p = ct.pointer(rnd_state)
+    ones = None
+
+    def __init__(self, array, copy_to_device=True, copy_on_host=True):
+        _require_device()
+        array = np.asarray(array)
+        if array.ndim == 1:
+            array = array.reshape(-1, 1)
+        # cudamat/cudamat.py:183-195 keeps a Fortran-order float32 host copy
+        self.numpy_array = np.array(array, dtype=np.float32, order="F") if copy_on_host else reformat(array)
+        self.mat = cudamat()
+        self.p_mat = ct.pointer(self.mat)
+        _lib.init_from_array(self.p_mat, self.numpy_array.ctypes.data_as(ct.POINTER(ct.c_float)),
+                             ct.c_int(self.numpy_array.shape[0]), ct.c_int(self.numpy_array.shape[1]))
+        if copy_to_device:
+            _check(_lib.copy_to_device(self.p_mat))
+
+    @classmethod
+    def _from_mat(cls, mat):
+        obj = cls.__new__(cls)
+        obj.mat = mat
+        obj.p_mat = ct.pointer(mat)
+        obj.numpy_array = None
+        return obj
+
+    @property
+    def T(self):
+        """cudamat/cudamat.py:139-146: a view of the same storage with is_trans = 1."""
+        t = TransposedCUDAMatrix(self.mat)
+        t._parent = self  # keep the owner (and its device memory) alive
+        return t
+
+    def __del__(self):
+        try:
+            if self.mat.owns_data and self.mat.on_device:
+                _lib.free_device_memory(self.p_mat)
+        except Exception:
+            pass
+
+    # -- random ------------------------------------------------------------
+    @staticmethod
+    def init_random(seed=0):
+        """cudamat/cudamat.py:209-224; here: Philox key = seed, call counter = 0."""
+        _check(_lib.init_random(CUDAMatrix.rnd_state_p, ct.c_int(seed), None))
+
+    # -- structure ---------------------------------------------------------
+    @property
+    def shape(self):
+        return (self.mat.size[0], self.mat.size[1])
+
+    def set_shape(self, shape):
+        _check(_lib.set_shape(self.p_mat, ct.c_uint(shape[0]), ct.c_uint(shape[1])))
+        return self
+
+    def reshape(self, shape):
+        _check(_lib.reshape(self.p_mat, ct.c_uint(shape[0]), ct.c_uint(shape[1])))
+        return self
+
+    def set_trans(self, is_trans):
+        _lib.set_transpose(self.p_mat, ct.c_int(1 if is_trans else 0))
+
+    def asarray(self):
+        self.copy_to_host()
+        return self.numpy_array
+
+    def copy_to_device(self):
+        _check(_lib.copy_to_device(self.p_mat))
+
+    def copy_to_host(self):
+        if not self.mat.on_host or self.numpy_array is None:
+            self.numpy_array = np.empty(self.shape, dtype=np.float32, order="F")
+            self.mat.data_host = self.numpy_array.ctypes.data_as(ct.POINTER(ct.c_float))
+            self.mat.on_host = 1
+        _check(_lib.copy_to_host(self.p_mat))
+
+    def overwrite(self, array):
+        """cudamat/cudamat.py:152-168: replace the contents from a host array of the same shape."""
+        array = np.asarray(array)
+        if array.ndim == 1:
+            array = array.reshape(-1, 1)
+        if tuple(array.shape) != tuple(self.shape):
+            raise CUDAMatException("Incompatible matrix dimensions.")
+        self.numpy_array = np.array(array, dtype=np.float32, order="F")
+        self.mat.data_host = self.numpy_array.ctypes.data_as(ct.POINTER(ct.c_float))
+        self.mat.on_host = 1
+        _check(_lib.copy_to_device(self.p_mat))
+
+    def overwrite_from_pinned(self, ptr, nbytes):
+        """Asynchronous host-to-device copy from a pinned buffer (see host_alloc)."""
+        _check(_lib.copy_from_host_ptr(self.p_mat, ct.c_void_p(ptr), ct.c_size_t(nbytes)))
+
+    def assign(self, val):
+        if isinstance(val, CUDAMatrix):
+            _check(_lib.copy_on_device(val.p_mat, self.p_mat))
+        elif isinstance(val, (int, float, np.floating, np.integer)):
+            _check(_lib.assign_scalar(self.p_mat, ct.c_float(val)))
+        else:
+            raise ValueError("Assigned value must be of type CUDAMatrix, int, or float.")
+        return self
+
+    def free_device_memory(self):
+        _check(_lib.free_device_memory(self.p_mat))
+
+    def slice(self, first_col, last_col):
+        mat = cudamat()
+        if self.mat.size[0] == 1 or self.mat.size[1] == 1:
+            _check(_lib.get_vector_slice(self.p_mat, ct.pointer(mat), ct.c_uint(int(first_col)), ct.c_uint(int(last_col))))
+        else:
+            _check(_lib.get_slice(self.p_mat, ct.pointer(mat), ct.c_uint(int(first_col)), ct.c_uint(int(last_col))))
+        new = CUDAMatrix._from_mat(mat)
+        new._parent = self  # keep the owner alive
+        return new
+
+    get_col_slice = slice
+
+    # -- random ops --------------------------------------------------------
+    def fill_with_rand(self):
+        _check(_lib.fill_with_rand(CUDAMatrix.rnd_state_p, self.p_mat))
+        return self
+
+    def fill_with_randn(self):
+        _check(_lib.fill_with_randn(CUDAMatrix.rnd_state_p, self.p_mat))
+        return self
+
+    def sample_bernoulli(self, target=None):
+        target = target or self
+        _check(_lib.sample_bernoulli(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat))
+        return target
+
+    def sample_bernoulli_tanh(self, target=None):
+        target = target or self
+        _check(_lib.sample_bernoulli_tanh(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat))
+        return target
+
+    def sample_gaussian(self, target=None, mult=1.0):
+        target = target or self
+        _check(_lib.sample_gaussian(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat, ct.c_float(mult)))
+        return target
+
+    def perturb_energy_for_softmax_sampling(self, target=None):
+        target = target or self
+        _check(_lib.perturb_energy(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat))
+        return target
+
+    def perturb_prob_for_softmax_sampling(self, target=None):
+        target = target or self
+        _check(_lib.perturb_prob(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat))
+        return target
+
+    def dropout(self, dropprob, val=0.0):
+        _check(_lib.dropout(CUDAMatrix.rnd_state_p, self.p_mat, ct.c_float(dropprob), ct.c_float(val)))
+        return self
+
+    # -- broadcasts --------------------------------------------------------
+    def _vec_op(self, fn, vec, target, *extra):
+        target = target or self
+        _check(fn(self.p_mat, vec.p_mat, target.p_mat, *extra))
+        return target
+
+    def add_col_vec(self, vec, target=None):
+        return self._vec_op(_lib.add_col_vec, vec, target)
+
+    def add_col_mult(self, vec, mult, target=None):
+        return self._vec_op(_lib.add_col_mult, vec, target, ct.c_float(mult))
+
+    def add_row_vec(self, vec, target=None):
+        return self._vec_op(_lib.add_row_vec, vec, target)
+
+    def add_row_mult(self, vec, mult, target=None):
+        return self._vec_op(_lib.add_row_mult, vec, target, ct.c_float(mult))
+
+    def mult_by_col(self, vec, target=None):
+        return self._vec_op(_lib.mult_by_col_vec, vec, target)
+
+    def mult_by_row(self, vec, target=None):
+        return self._vec_op(_lib.mult_by_row_vec, vec, target)
+
+    def div_by_col(self, vec, target=None):
+        return self._vec_op(_lib.div_by_col_vec, vec, target)
+
+    def div_by_row(self, vec, target=None):
+        return self._vec_op(_lib.div_by_row_vec, vec, target)
+
+    # -- reductions --------------------------------------------------------
+    def sum(self, axis=None, target=None):
+        if axis is None:
+            err = ct.c_int(0)
+            r = _lib.sum_all(self.p_mat, ct.byref(err))
+            _check(err.value)
+            return r
+        return sum(self, axis, target)
+
+    def add_sums(self, mat, axis, mult=1.0):
+        _check(_lib.add_sum_by_axis(mat.p_mat, self.p_mat, ct.c_int(axis), ct.c_float(mult)))
+        return self
+
+    def max(self, axis, target=None):
+        m, n = self.shape
+        if target is None:
+            target = empty((1, n)) if axis == 0 else empty((m, 1))
+        _check(_lib.max_by_axis(self.p_mat, target.p_mat, ct.c_int(axis)))
+        return target
+
+    def argmax(self, axis, target=None):
+        m, n = self.shape
+        if target is None:
+            target = empty((1, n)) if axis == 0 else empty((m, 1))
+        _check(_lib.argmax_by_axis(self.p_mat, target.p_mat, ct.c_int(axis)))
+        return target
+
+    def choose_max(self, axis, target=None):
+        target = target or self
+        _check(_lib.choose_max_by_axis(self.p_mat, target.p_mat, ct.c_int(axis)))
+        return target
+
+    def choose_max_and_accumulate(self, acc):
+        _check(_lib.choose_max_and_accumulate(self.p_mat, acc.p_mat))
+        return acc
+
+    def euclid_norm(self):
+        err = ct.c_int(0)
+        r = _lib.euclid_norm(self.p_mat, ct.byref(err))
+        _check(err.value)
+        return r
+
+    def apply_softmax(self, target=None):
+        target = target or self
+        _check(_lib.softmax(self.p_mat, target.p_mat))
+        return target
+
+    # -- elementwise -------------------------------------------------------
+    def _scalar_or_mat(self, val, target, fn_mat, fn_scalar):
+        target = target or self
+        if isinstance(val, CUDAMatrix):
+            _check(fn_mat(self.p_mat, val.p_mat, target.p_mat))
+        elif isinstance(val, (int, float, np.floating, np.integer)):
+            _check(fn_scalar(self.p_mat, ct.c_float(val), target.p_mat))
+        else:
+            raise ValueError("Value must be of type CUDAMatrix, int, or float.")
+        return target
+
+    def add(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.add_elementwise, _lib.add_scalar)
+
+    def subtract(self, val, target=None):
+        if isinstance(val, CUDAMatrix):
+            return self._scalar_or_mat(val, target, _lib.subtract_elementwise, None)
+        return self._scalar_or_mat(-val, target, None, _lib.add_scalar)
+
+    def mult(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.mult_elementwise, _lib.mult_by_scalar)
+
+    def divide(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.divide_elementwise, _lib.divide_by_scalar)
+
+    def less_than(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.less_than, _lib.less_than_scalar)
+
+    def less_than_eq(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.less_than_eq, _lib.less_than_eq_scalar)
+
+    def greater_than(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.greater_than, _lib.greater_than_scalar)
+
+    def greater_than_eq(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.greater_than_eq, _lib.greater_than_eq_scalar)
+
+    def upper_bound(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.upper_bound, _lib.upper_bound_scalar)
+
+    def lower_bound(self, val, target=None):
+        return self._scalar_or_mat(val, target, _lib.lower_bound, _lib.lower_bound_scalar)
+
+    def sign(self, target=None):
+        target = target or self
+        _check(_lib.sign(self.p_mat, target.p_mat))
+        return target
+
+    def apply_sigmoid(self, target=None):
+        return sigmoid(self, target)
+
+    def reciprocal(self, target=None):
+        target = target or self
+        _check(_lib.reciprocal(self.p_mat, target.p_mat))
+        return target
+
+    def apply_logistic_deriv(self, val, target=None):
+        target = target or self
+        _check(_lib.apply_logistic_deriv(self.p_mat, val.p_mat, target.p_mat))
+        return target
+
+    def add_mult(self, mat2, mult=1.0, alpha=None):
+        """self += mult * mat2 (cudamat names the scalar `mult`, eigenmat `alpha`)."""
+        _check(_lib.add_mult(self.p_mat, mat2.p_mat, ct.c_float(mult if alpha is None else alpha)))
+        return self
+
+    def subtract_mult(self, mat2, mult=1.0):
+        return self.add_mult(mat2, -mult)
+
+    def add_mult_sign(self, mat2, mult=1.0):
+        _check(_lib.add_mult_sign(self.p_mat, mat2.p_mat, ct.c_float(mult)))
+        return self
+
+    def dot(self, mat2, mult=1.0, target=None):
+        return dot(self, mat2, mult, target)
+
+    def add_dot(self, m1, m2, mult=1.0):
+        _check(_lib.dot(m1.p_mat, m2.p_mat, self.p_mat, ct.c_float(1.0), ct.c_float(mult)))
+        return self
+
+    def subtract_dot(self, m1, m2):
+        return self.add_dot(m1, m2, -1.0)
+
+    # -- fused entry points (no counterpart in the reference API) -------------
+    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_hi=None, w_lo=None):
+        """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter."""
+        _check(_lib.momentum_update(self.p_mat, delta.p_mat, grad.p_mat if grad is not None else None, suff.p_mat,
+                                    w_hi.p_mat if w_hi is not None else None,
+                                    w_lo.p_mat if w_lo is not None else None,
+                                    ct.c_float(inv_batch), ct.c_float(momentum), ct.c_float(eps), ct.c_float(l2),
+                                    ct.c_float(l1)))
+        return self
+
+    def split_tf32(self, hi, lo):
+        _check(_lib.split_tf32(self.p_mat, hi.p_mat, lo.p_mat))
+        return hi, lo
+
+
+class TransposedCUDAMatrix(CUDAMatrix):
+    """cudamat/cudamat.py:139-146: same storage, is_trans flipped, never owns the data."""
+
+    def __init__(self, mat):
+        self.mat = cudamat()
+        ct.memmove(ct.pointer(self.mat), ct.pointer(mat), ct.sizeof(self.mat))
+        self.mat.is_trans = 0 if mat.is_trans else 1
+        self.mat.owns_data = 0
+        self.p_mat = ct.pointer(self.mat)
+        self.numpy_array = None
+
+    @property
+    def shape(self):
+        return (self.mat.size[1], self.mat.size[0]) if self.mat.is_trans else (self.mat.size[0], self.mat.size[1])
+
+    def __del__(self):
+        pass
+
+
+def empty(shape):
+    """cudamat/cudamat.py:1533-1544; zero-filled like eigenmat's (eigenmat/eigenmat.py:1339-1343)."""
+    _require_device()
+    mat = cudamat()
+    _check(_lib.init_empty(ct.pointer(mat), ct.c_int(shape[0]), ct.c_int(shape[1])))
+    return CUDAMatrix._from_mat(mat)
+
+
+def reformat(array):
+    """cudamat/cudamat.py:1863-1868."""
+    return np.array(array, dtype=np.float32, order="F")
+
+
+def sum(mat, axis, target=None):
+    m = _lib.get_leading_dimension(mat.p_mat)
+    n = _lib.get_nonleading_dimension(mat.p_mat)
+    if target is None:
+        target = empty((1, n)) if axis == 0 else empty((m, 1))
+    _check(_lib.sum_by_axis(mat.p_mat, target.p_mat, ct.c_int(axis)))
+    return target
+
+
+def dot(m1, m2, mult=1.0, target=None):
+    if target is None:
+        m = _lib.get_leading_dimension(m1.p_mat)
+        n = _lib.get_nonleading_dimension(m2.p_mat)
+        target = empty((m, n))
+    _check(_lib.dot(m1.p_mat, m2.p_mat, target.p_mat, ct.c_float(0.0), ct.c_float(mult)))
+    return target
+
+
+def vdot(m1, m2):
+    err = ct.c_int(0)
+    r = _lib.vdot(m1.p_mat, m2.p_mat, ct.byref(err))
+    _check(err.value)
+    return r
+
+
+def _unary(fn):
+    def op(mat, target=None):
+        target = target or mat
+        _check(fn(mat.p_mat, target.p_mat))
+        return target
+    return op
+
+
+sigmoid = _unary(_lib.apply_sigmoid)
+tanh = _unary(_lib.apply_tanh)
+abs = _unary(_lib.apply_abs)
+log_1_plus_exp = _unary(_lib.apply_log_1_plus_exp)
+exp = _unary(_lib.apply_exp)
+sqrt = _unary(_lib.apply_sqrt)
+
+
+def log(mat, target=None, tiny=0.0):
+    target = target or mat
+    _check(_lib.apply_log(mat.p_mat, target.p_mat, ct.c_float(tiny)))
+    return target
+
+
+def pow(mat, p, target=None):
+    target = target or mat
+    _check(_lib.apply_pow(mat.p_mat, ct.c_float(p), target.p_mat))
+    return target
+
+
+def cross_entropy_bernoulli(mat, p, target=None, tiny=1e-10):
+    target = target or mat
+    _check(_lib.compute_cross_entropy_bernoulli(mat.p_mat, p.p_mat, target.p_mat, ct.c_float(tiny)))
+    return target
+
+
+def correct_preds(mat, p, target=None, cutoff=0.5):
+    target = target or mat
+    _check(_lib.correct_preds(mat.p_mat, p.p_mat, target.p_mat, ct.c_float(cutoff)))
+    return target
+
+
+def fused_gemm(passes, out=None, out_hi=None, out_lo=None, sample=None, bias=None, col_scale=None,
+               activation=0, alpha=1.0, beta=0.0):
+    """out = act(alpha * sum_p (+/-) a_p . b_p + beta * out + bias (x) col_scale) in one kernel.
+
+    `passes` is a list of (a, b) or (a, b, negate); a and b may be `.T` views.  Optional
+    outputs: the TF32 hi/lo split of the result and a Bernoulli draw of it (consumes one
+    sampling call of the global random state).  Replaces the dot / add_dot / add_col_vec /
+    sigmoid / sample_bernoulli group of deepnet/dbm.py:88-105.
+    """
+    f = _FusedGemm()
+    f.npass = len(passes)
+    if not 0 < f.npass <= MAX_PASS:
+        raise CUDAMatException("fused_gemm takes 1..%d passes" % MAX_PASS)
+    for i, p in enumerate(passes):
+        f.passes[i].a = p[0].p_mat
+        f.passes[i].b = p[1].p_mat
+        f.passes[i].negate = int(p[2]) if len(p) > 2 else 0
+    f.alpha, f.beta, f.activation = alpha, beta, activation
+    for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("out_hi", out_hi), ("out_lo", out_lo),
+                    ("sample", sample)):
+        if m is not None:
+            setattr(f, name, m.p_mat)
+    _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))
+
+
+# -- device / library control -----------------------------------------------------
+def cuda_set_device(dev_id):
+    _check(_lib.cuda_set_device(ct.c_int(dev_id)))
+
+
+def cublas_init():
+    _require_device()
+    CUDAMatrix.ones = None
+
+
+init = cublas_init
+
+
+def cublas_shutdown():
+    _lib.cublas_shutdown()
+
+
+shutdown = cublas_shutdown
+
+
+def cuda_sync_threads():
+    _lib.cuda_sync_threads()
+
+
+def set_gemm_path(path):
+    """0 auto, 1 tensor cores only, 2 CUDA cores only."""
+    _lib.b200_set_gemm_path(ct.c_int(path))
+
+
+def set_dot_precision(mode):
+    """0: fp32-grade split-TF32 `dot` (default); 1: one TF32 pass."""
+    _lib.b200_set_dot_precision(ct.c_int(mode))
+
+
+def set_rng_column_offset(col0):
+    _check(_lib.set_rng_column_offset(ct.c_int(col0)))
+
+
+def read_status():
+    """Non-zero if a kernel's bounded wait gave up since the last call (blocks)."""
+    return _lib.b200_read_status()
+
+
+def host_alloc(shape):
+    """Returns (array, ptr): a pinned float32 Fortran-order host array; free with host_free(ptr)."""
+    n = int(np.prod(shape))
+    ptr = _lib.b200_host_alloc(ct.c_size_t(n * 4))
+    if not ptr:
+        raise CUDAMatException("pinned host allocation failed")
+    buf = (ct.c_float * n).from_address(ptr)
+    arr = np.frombuffer(buf, dtype=np.float32).reshape(shape, order="F")
+    return arr, ptr
+
+
+def host_free(ptr):
+    _lib.b200_host_free(ct.c_void_p(ptr))
+
+
+# -- data parallelism ------------------------------------------------------------------
+def dp_unique_id():
+    buf = ct.create_string_buffer(128)
+    _check(_lib.dp_unique_id(buf))
+    return buf.raw
+
+
+def dp_init(unique_id, nranks, rank):
+    _check(_lib.dp_init(ct.c_char_p(unique_id), ct.c_int(nranks), ct.c_int(rank)))
+
+
+def dp_allreduce(mat):
+    _check(_lib.dp_allreduce(mat.p_mat))
+
+
+def dp_check():
+    _check(_lib.dp_check())
+
+
+def dp_destroy():
+    _lib.dp_destroy()

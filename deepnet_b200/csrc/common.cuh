@@ -1,0 +1,111 @@
+// Shared declarations of the b200mat library: the matrix handle, error codes, the
+// library stream, launch helpers and the counter-based random stream.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Error codes of the reference C ABI (cudamat/cudamat.cuh:1-9) plus two new ones.
+#define ERROR_INCOMPATIBLE_DIMENSIONS -1
+#define CUBLAS_ERROR -2
+#define CUDA_ERROR -3
+#define VIEW_ERROR -4
+#define ERROR_TRANSPOSED -5
+#define ERROR_GENERIC -6
+#define ERROR_TRANSPOSEDNESS -7
+#define ERROR_NOT_ON_DEVICE -8
+#define ERROR_UNSUPPORTED -9
+#define ERROR_NCCL -10
+#define ERROR_DEVICE_TIMEOUT -11
+
+// Matrix handle, binary-compatible with cudamat/cudamat.cuh:21-29: float32,
+// column-major, size[0] rows by size[1] columns, owned by the Python caller.
+struct cudamat {
+  float* data_host;
+  float* data_device;
+  int on_device;
+  int on_host;
+  int size[2];
+  int is_trans;  // 0 or 1
+  int owns_data;
+};
+
+// Random state.  Same size as the reference's two-pointer struct
+// (cudamat/cudamat.cuh:31-34) so an unmodified wrapper can allocate it; it holds the
+// Philox key and the number of sampling calls issued so far.
+struct rnd_struct {
+  unsigned long long seed;
+  unsigned long long calls;
+};
+
+namespace b200 {
+
+cudaStream_t stream();                 // the stream every operation of the library runs on
+int sm_count();                        // SMs of the current device
+int check_launch();                    // cudaGetLastError -> 0 or CUDA_ERROR (message kept)
+int set_error(const char* msg);        // records msg, returns CUDA_ERROR
+int rng_col0();                        // first global column of this process's minibatch shard
+void* workspace(int slot, size_t bytes);  // grow-only cached device scratch, slot 0..7
+int* status_word();                    // device int: non-zero after a bounded wait gave up
+
+inline long numel(const cudamat* m) { return (long)m->size[0] * m->size[1]; }
+inline bool same_shape(const cudamat* a, const cudamat* b) {
+  return a->size[0] == b->size[0] && a->size[1] == b->size[1];
+}
+
+// ---------------------------------------------------------------- Philox4x32-10
+// Element (row r, column c) of sampling call `call` under `seed` takes word (c & 3) of
+// philox(ctr = {r, c >> 2, call_lo, call_hi}, key = {seed_lo, seed_hi}); c is the global
+// column (local column + the shard's first column).  The layout depends on neither the
+// launch shape nor the number of GPUs.
+struct PhiloxKey {
+  uint32_t k0, k1, c2, c3;  // key words and the call counter words
+};
+
+__host__ __device__ inline PhiloxKey make_philox_key(unsigned long long seed, unsigned long long call) {
+  PhiloxKey k;
+  k.k0 = (uint32_t)seed;
+  k.k1 = (uint32_t)(seed >> 32);
+  k.c2 = (uint32_t)call;
+  k.c3 = (uint32_t)(call >> 32);
+  return k;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, const PhiloxKey& key) {
+  uint32_t c2 = key.c2, c3 = key.c3, k0 = key.k0, k1 = key.k1;
+#pragma unroll
+  for (int r = 0; r < 10; r++) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
+// Word -> uniform in (0, 1], the reference mapping (cudamat/cudamat_kernels.cu:120).
+__device__ __forceinline__ float word_to_uniform(uint32_t x) {
+  return __fmul_rn(__fadd_rn(__uint2float_rn(x), 1.0f), 2.3283064365386963e-10f);
+}
+
+__device__ __forceinline__ uint32_t pick_word(const uint4& w, int i) {
+  return i == 0 ? w.x : (i == 1 ? w.y : (i == 2 ? w.z : w.w));
+}
+
+// 1 / (1 + exp(-x)) with the accurate expf (the reference's fast __expf of
+// cudamat_kernels.cu:404 would miss the 1e-5 relative bound against libm).
+__device__ __forceinline__ float sigmoid_accurate(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// Split x = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits zero)
+// and lo = x - hi (exact in fp32).  The tensor core reads only the TF32 bits of lo.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  lo = (fabsf(hi) <= 3.4028234e38f) ? x - hi : 0.0f;  // inf/nan stay in hi alone
+}
+#endif
+
+}  // namespace b200

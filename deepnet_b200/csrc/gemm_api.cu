@@ -1,0 +1,308 @@
+// C entry points built on the fused matrix product: the reference `dot`
+// (cudamat/cudamat.cu:1671-1696) and the fused calls that replace whole groups of
+// reference operations on the contrastive-divergence path (deepnet/dbm.py:64-115,
+// deepnet/edge.py:222-246, deepnet/parameter.py:80-106).
+#include "gemm.cuh"
+
+using namespace b200;
+
+namespace {
+
+int g_path = 0;       // 0 auto, 1 tensor cores only, 2 CUDA cores only
+int g_dot_mode = 0;   // 0: fp32-grade (split TF32, 3 passes), 1: single TF32 pass
+constexpr long kTcMinWork = 1L << 21;  // below this many multiply-adds `dot` stays on CUDA cores
+
+inline int lead(const cudamat* m) { return m->is_trans ? m->size[1] : m->size[0]; }
+inline int nonlead(const cudamat* m) { return m->is_trans ? m->size[0] : m->size[1]; }
+inline GemmOperand operand(const cudamat* m, const float* ptr = nullptr) {
+  GemmOperand o;
+  o.ptr = ptr ? ptr : m->data_device;
+  o.ld = m->size[0];
+  o.trans = m->is_trans;
+  return o;
+}
+
+int run(const GemmProblem& g) {
+  if (g_path == 2) return gemm_simt(g);
+  if (gemm_tc_supported(g)) return gemm_tc(g);
+  if (g_path == 1) return ERROR_UNSUPPORTED;
+  return gemm_simt(g);
+}
+
+__global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float* lo, long n, bool vec) {
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  if (vec) {
+    const long n4 = n >> 2;
+    for (long i = tid; i < n4; i += nth) {
+      const float4 v = reinterpret_cast<const float4*>(x)[i];
+      float4 h, l;
+      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+      reinterpret_cast<float4*>(hi)[i] = h;
+      reinterpret_cast<float4*>(lo)[i] = l;
+    }
+    for (long i = (n4 << 2) + tid; i < n; i += nth) split_tf32(x[i], hi[i], lo[i]);
+  } else {
+    for (long i = tid; i < n; i += nth) split_tf32(x[i], hi[i], lo[i]);
+  }
+}
+
+int launch_split(const float* x, float* hi, float* lo, long n) {
+  if (n == 0) return 0;
+  const bool vec = (((uintptr_t)x | (uintptr_t)hi | (uintptr_t)lo) & 15) == 0;
+  long blocks = ((vec ? (n + 3) / 4 : n) + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  k_split<<<(int)blocks, 256, 0, stream()>>>(x, hi, lo, n, vec);
+  return check_launch();
+}
+
+// One pass of the parameter update, in the order the reference issues its calls
+// (deepnet/dbm.py:242,254 then deepnet/parameter.py:89-106).  Products and sums are
+// rounded separately (no fused multiply-add) so the result equals the call sequence's.
+__device__ __forceinline__ void update_one(float& w, float& d, float g, float suff, float ninv_batch, float momentum,
+                                           float neps, float l2, float l1) {
+  g = __fadd_rn(g, __fmul_rn(suff, ninv_batch));
+  d = __fmul_rn(d, momentum);
+  if (l2 != 0.0f) d = __fadd_rn(d, __fmul_rn(w, l2));
+  if (l1 != 0.0f) d = __fadd_rn(d, w == 0.0f ? 0.0f : (w > 0.0f ? l1 : -l1));
+  d = __fadd_rn(d, g);
+  w = __fadd_rn(w, __fmul_rn(d, neps));
+}
+
+template <bool kHasGrad, bool kSplit>
+__global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff, float* w_hi,
+                                                float* w_lo, long n, bool vec, float ninv_batch, float momentum,
+                                                float neps, float l2, float l1) {
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  if (vec) {
+    const long n4 = n >> 2;
+    for (long i = tid; i < n4; i += nth) {
+      float4 W = reinterpret_cast<float4*>(w)[i];
+      float4 D = reinterpret_cast<float4*>(delta)[i];
+      const float4 S = reinterpret_cast<const float4*>(suff)[i];
+      float4 G = make_float4(0, 0, 0, 0);
+      if (kHasGrad) G = reinterpret_cast<float4*>(grad)[i];
+      update_one(W.x, D.x, G.x, S.x, ninv_batch, momentum, neps, l2, l1);
+      update_one(W.y, D.y, G.y, S.y, ninv_batch, momentum, neps, l2, l1);
+      update_one(W.z, D.z, G.z, S.z, ninv_batch, momentum, neps, l2, l1);
+      update_one(W.w, D.w, G.w, S.w, ninv_batch, momentum, neps, l2, l1);
+      reinterpret_cast<float4*>(w)[i] = W;
+      reinterpret_cast<float4*>(delta)[i] = D;
+      if (kHasGrad) reinterpret_cast<float4*>(grad)[i] = make_float4(0, 0, 0, 0);
+      if (kSplit) {
+        float4 H, L;
+        split_tf32(W.x, H.x, L.x); split_tf32(W.y, H.y, L.y); split_tf32(W.z, H.z, L.z); split_tf32(W.w, H.w, L.w);
+        reinterpret_cast<float4*>(w_hi)[i] = H;
+        reinterpret_cast<float4*>(w_lo)[i] = L;
+      }
+    }
+    for (long i = (n4 << 2) + tid; i < n; i += nth) {
+      float W = w[i], D = delta[i];
+      update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
+      w[i] = W; delta[i] = D;
+      if (kHasGrad) grad[i] = 0.0f;
+      if (kSplit) split_tf32(W, w_hi[i], w_lo[i]);
+    }
+  } else {
+    for (long i = tid; i < n; i += nth) {
+      float W = w[i], D = delta[i];
+      update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
+      w[i] = W; delta[i] = D;
+      if (kHasGrad) grad[i] = 0.0f;
+      if (kSplit) split_tf32(W, w_hi[i], w_lo[i]);
+    }
+  }
+}
+
+}  // namespace
+
+// One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
+struct b200_pass {
+  cudamat* a;
+  cudamat* b;
+  int negate;
+};
+// out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale)
+struct b200_fused_gemm {
+  int npass;
+  b200_pass pass[kMaxPass];
+  float alpha, beta;
+  cudamat* bias;       // M x 1 or null
+  cudamat* col_scale;  // 1 x N or null
+  int activation;      // 0 identity, 1 logistic
+  cudamat* out;        // M x N or null
+  cudamat* out_hi;     // TF32-exact part of the result, or null
+  cudamat* out_lo;     // result - out_hi, or null
+  cudamat* sample;     // Bernoulli(result), or null
+};
+
+extern "C" {
+
+// 0 auto (tensor cores when the operands are TMA-addressable), 1 tensor cores only
+// (ERROR_UNSUPPORTED otherwise), 2 CUDA cores only.
+int b200_set_gemm_path(int path) {
+  g_path = path;
+  return 0;
+}
+// Precision of `dot`: 0 = fp32-grade (operands split into TF32 hi/lo, three passes),
+// 1 = one TF32 pass (about 1e-3 relative).
+int b200_set_dot_precision(int mode) {
+  g_dot_mode = mode;
+  return 0;
+}
+
+// hi = x with the low 13 mantissa bits cleared, lo = x - hi.
+int split_tf32(cudamat* x, cudamat* hi, cudamat* lo) {
+  if (!x->on_device || !hi->on_device || !lo->on_device) return ERROR_NOT_ON_DEVICE;
+  if (!same_shape(x, hi) || !same_shape(x, lo)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  return launch_split(x->data_device, hi->data_device, lo->data_device, numel(x));
+}
+
+int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
+  if (f->npass <= 0 || f->npass > kMaxPass) return ERROR_UNSUPPORTED;
+  GemmProblem g;
+  g.npass = f->npass;
+  g.M = lead(f->pass[0].a);
+  g.N = nonlead(f->pass[0].b);
+  for (int q = 0; q < f->npass; q++) {
+    const cudamat *a = f->pass[q].a, *b = f->pass[q].b;
+    if (!a->on_device || !b->on_device) return ERROR_NOT_ON_DEVICE;
+    if (lead(a) != g.M || nonlead(b) != g.N || nonlead(a) != lead(b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    g.pass[q].a = operand(a);
+    g.pass[q].b = operand(b);
+    g.pass[q].k = nonlead(a);
+    g.pass[q].negate = f->pass[q].negate;
+  }
+  GemmEpilogue& e = g.epi;
+  e.alpha = f->alpha;
+  e.beta = f->beta;
+  e.bias = nullptr;
+  e.col_scale = nullptr;
+  e.activation = f->activation;
+  e.out = e.out_hi = e.out_lo = e.sample = nullptr;
+  e.ldo = g.M;
+  e.col0 = rng_col0();
+  cudamat* outs[4] = {f->out, f->out_hi, f->out_lo, f->sample};
+  for (int i = 0; i < 4; i++) {
+    if (!outs[i]) continue;
+    if (!outs[i]->on_device) return ERROR_NOT_ON_DEVICE;
+    if (outs[i]->is_trans) return ERROR_TRANSPOSED;
+    if (outs[i]->size[0] != g.M || outs[i]->size[1] != g.N) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  }
+  if (f->out) e.out = f->out->data_device;
+  if (f->out_hi) e.out_hi = f->out_hi->data_device;
+  if (f->out_lo) e.out_lo = f->out_lo->data_device;
+  if (f->sample) e.sample = f->sample->data_device;
+  if (e.out_lo && !e.out_hi) return ERROR_UNSUPPORTED;
+  if (e.beta != 0.0f && !e.out) return ERROR_UNSUPPORTED;
+  if (f->bias) {
+    if (!f->bias->on_device) return ERROR_NOT_ON_DEVICE;
+    if (numel(f->bias) != g.M) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    e.bias = f->bias->data_device;
+  }
+  if (f->col_scale) {
+    if (!f->col_scale->on_device) return ERROR_NOT_ON_DEVICE;
+    if (numel(f->col_scale) != g.N || !f->bias) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    e.col_scale = f->col_scale->data_device;
+  }
+  e.key = make_philox_key(0, 0);
+  if (f->sample) {
+    if (!rnd_state) return ERROR_GENERIC;
+    e.key = make_philox_key(rnd_state->seed, rnd_state->calls);
+    rnd_state->calls += 1;
+  }
+  return run(g);
+}
+
+// cudamat/cudamat.cu:1671-1696: target = beta * target + alpha * op(mat1) . op(mat2).
+int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) {
+  if (!mat1->on_device || !mat2->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (lead(mat1) != lead(target) || nonlead(mat2) != nonlead(target) || nonlead(mat1) != lead(mat2))
+    return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (target->is_trans) return ERROR_TRANSPOSED;
+  const int m = lead(mat1), k = lead(mat2), n = nonlead(mat2);
+  GemmProblem g;
+  g.M = m;
+  g.N = n;
+  GemmEpilogue& e = g.epi;
+  e.alpha = alpha;
+  e.beta = beta;
+  e.bias = e.col_scale = nullptr;
+  e.activation = 0;
+  e.out = target->data_device;
+  e.out_hi = e.out_lo = e.sample = nullptr;
+  e.ldo = m;
+  e.col0 = 0;
+  e.key = make_philox_key(0, 0);
+  g.npass = 1;
+  g.pass[0].a = operand(mat1);
+  g.pass[0].b = operand(mat2);
+  g.pass[0].k = k;
+  g.pass[0].negate = 0;
+  if (m == 0 || n == 0) return 0;
+  if (k == 0) {  // empty inner dimension: target = beta * target
+    g.pass[0].k = 0;
+    return gemm_simt(g);
+  }
+  const bool tc = g_path != 2 && gemm_tc_supported(g) && (g_path == 1 || (long)m * n * k >= kTcMinWork);
+  if (!tc) {
+    if (g_path == 1) return ERROR_UNSUPPORTED;
+    return gemm_simt(g);
+  }
+  if (g_dot_mode == 1) return gemm_tc(g);
+  // fp32-grade: split both operands into scratch, then hi.hi + hi.lo + lo.hi
+  const long na = numel(mat1), nb = numel(mat2);
+  float* sa = (float*)workspace(2, (size_t)na * 2 * sizeof(float));
+  float* sb = (float*)workspace(3, (size_t)nb * 2 * sizeof(float));
+  if (!sa || !sb) return CUDA_ERROR;
+  int err = launch_split(mat1->data_device, sa, sa + na, na);
+  if (err) return err;
+  err = launch_split(mat2->data_device, sb, sb + nb, nb);
+  if (err) return err;
+  g.npass = 3;
+  const float* ap[3] = {sa + na, sa, sa};  // small terms first
+  const float* bp[3] = {sb, sb + nb, sb};
+  for (int q = 0; q < 3; q++) {
+    g.pass[q].a = operand(mat1, ap[q]);
+    g.pass[q].b = operand(mat2, bp[q]);
+    g.pass[q].k = k;
+    g.pass[q].negate = 0;
+  }
+  return gemm_tc(g);
+}
+
+// deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass over the parameter:
+//   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
+//   w -= eps * delta; grad = 0; and, when w_hi / w_lo are given, the TF32 split of the new w.
+// grad may be null (treated as zero and not written).  20 bytes of traffic per element
+// without grad and split, 36 with both.
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_hi, cudamat* w_lo,
+                    float inv_batch, float momentum, float eps, float l2, float l1) {
+  if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
+  if (!same_shape(w, delta) || !same_shape(w, suff)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (grad && (!grad->on_device || !same_shape(w, grad))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if ((w_hi == nullptr) != (w_lo == nullptr)) return ERROR_UNSUPPORTED;
+  if (w_hi && (!w_hi->on_device || !w_lo->on_device || !same_shape(w, w_hi) || !same_shape(w, w_lo)))
+    return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const long n = numel(w);
+  if (n == 0) return 0;
+  uintptr_t bits = (uintptr_t)w->data_device | (uintptr_t)delta->data_device | (uintptr_t)suff->data_device;
+  if (grad) bits |= (uintptr_t)grad->data_device;
+  if (w_hi) bits |= (uintptr_t)w_hi->data_device | (uintptr_t)w_lo->data_device;
+  const bool vec = (bits & 15) == 0;
+  long blocks = ((vec ? (n + 3) / 4 : n) + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  float* gp = grad ? grad->data_device : nullptr;
+  float* hp = w_hi ? w_hi->data_device : nullptr;
+  float* lp = w_lo ? w_lo->data_device : nullptr;
+#define LAUNCH_UPDATE(G, S)                                                                                       \
+  k_update<G, S><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, hp, \
+                                                    lp, n, vec, -inv_batch, momentum, -eps, l2, l1)
+  if (grad && w_hi) LAUNCH_UPDATE(true, true);
+  else if (grad) LAUNCH_UPDATE(true, false);
+  else if (w_hi) LAUNCH_UPDATE(false, true);
+  else LAUNCH_UPDATE(false, false);
+#undef LAUNCH_UPDATE
+  return check_launch();
+}
+
+}  // extern "C"

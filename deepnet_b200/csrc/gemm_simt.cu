@@ -1,0 +1,95 @@
+// fp32 CUDA-core product for operands the tensor-core path cannot address (leading
+// dimensions that are not multiples of 4 floats, unaligned views) and for tiny
+// problems.  64x64 output tile, 16-deep slices in shared memory, 4x4 outputs per
+// thread, every edge bounds-checked.  Same pass list and epilogue as the tcgen05 kernel.
+#include "gemm.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+__device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K) {
+  if (m >= M || k >= K) return 0.0f;
+  return a.trans ? a.ptr[(long)m * a.ld + k] : a.ptr[(long)k * a.ld + m];
+}
+__device__ __forceinline__ float load_b(const GemmOperand& b, int k, int n, int K, int N) {
+  if (n >= N || k >= K) return 0.0f;
+  return b.trans ? b.ptr[(long)k * b.ld + n] : b.ptr[(long)n * b.ld + k];
+}
+
+__global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmProblem g) {
+  __shared__ float As[TK][TM + 4];
+  __shared__ float Bs[TK][TN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+
+  for (int p = 0; p < g.npass; p++) {
+    const GemmPass& ps = g.pass[p];
+    const float sgn = ps.negate ? -1.0f : 1.0f;
+    for (int k0 = 0; k0 < ps.k; k0 += TK) {
+      // stage the slices; the thread->element map follows the contiguous direction
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int m, k;
+        if (ps.a.trans) { k = tid & 15; m = (tid >> 4) + 16 * i; }
+        else { m = tid & 63; k = (tid >> 6) + 4 * i; }
+        As[k][m] = sgn * load_a(ps.a, m0 + m, k0 + k, g.M, ps.k);
+        int n, kb;
+        if (ps.b.trans) { n = tid & 63; kb = (tid >> 6) + 4 * i; }
+        else { kb = tid & 15; n = (tid >> 4) + 16 * i; }
+        Bs[kb][n] = load_b(ps.b, k0 + kb, n0 + n, ps.k, g.N);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < TK; k++) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) a[i] = As[k][tx + 16 * i];
+#pragma unroll
+        for (int j = 0; j < 4; j++) b[j] = Bs[k][ty + 16 * j];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int n = n0 + ty + 16 * j;
+    if (n >= g.N) continue;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int m = m0 + tx + 16 * i;
+      if (m >= g.M) continue;
+      float u = 0.0f;
+      if (g.epi.sample) {
+        const int gc = n + g.epi.col0;
+        const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), g.epi.key);
+        u = word_to_uniform(pick_word(w, gc & 3));
+      }
+      epilogue_store(g.epi, acc[i][j], m, n, u);
+    }
+  }
+}
+
+}  // namespace
+
+int gemm_simt(const GemmProblem& g) {
+  if (g.M <= 0 || g.N <= 0) return 0;
+  dim3 grid((g.M + TM - 1) / TM, (g.N + TN - 1) / TN);
+  k_gemm_simt<<<grid, 256, 0, stream()>>>(g);
+  return check_launch();
+}
+
+}  // namespace b200

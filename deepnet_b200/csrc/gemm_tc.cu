@@ -1,0 +1,525 @@
+// Tensor-core matrix product for sm_100a: tcgen05.mma kind::tf32 with the accumulator
+// in tensor memory, operands staged in 128-byte-swizzled shared memory by TMA
+// (cp.async.bulk.tensor, one copy per CTA, never multicast), a fused epilogue read back
+// with tcgen05.ld.  It replaces the cublasSgemm behind `dot` (cudamat/cudamat.cu:1671-1696)
+// and the separate bias / sigmoid / Bernoulli passes that follow it in
+// deepnet/dbm.py:88-105 and deepnet/logistic_layer.py:11-15.
+//
+// fp32-grade accuracy comes from the caller's pass list: x = hi + lo with hi exact in
+// TF32, and hi*hi + hi*lo + lo*hi accumulate into ONE fp32 accumulator (a k-loop over
+// "passes x K").  A pass may be negated (instruction-descriptor bit), which folds
+// positive-minus-negative statistics into one kernel.
+//
+// Kernel shape: persistent, one CTA per SM, 192 threads:
+//   warp 0     : TMA producer (one lane)       -> ring of kStages {A tile, B tile}
+//   warp 1     : TMEM allocation + MMA issuer (one lane), tcgen05.commit frees stages
+//   warps 2..5 : epilogue, one TMEM lane quarter each; two accumulators in TMEM let the
+//                epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded; on expiry the kernel records a status word, drains
+// and frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // 32 floats = one 128-byte swizzle row
+constexpr int kThreadsTc = 192;
+constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
+
+struct TcPass {
+  int a_map, b_map;      // indices into TcParams::maps
+  int k_iters;           // ceil(k / BK)
+  uint32_t idesc;        // tcgen05 instruction descriptor of this pass
+  uint32_t a_desc_hi, b_desc_hi;  // upper 32 bits of the shared-memory descriptors
+  uint32_t a_desc_lo, b_desc_lo;  // leading byte offset field (bits 16-29 of the low word)
+  uint32_t a_adv, b_adv;          // descriptor advance per K=8 step, in 16-byte units
+  int a_mn, b_mn;        // 1: operand is MN-major (loaded as 32x32 boxes)
+};
+
+struct TcParams {
+  CUtensorMap maps[2 * kMaxPass];
+  TcPass pass[kMaxPass];
+  int npass;
+  int M, N, tiles_m, tiles_n;
+  GemmEpilogue epi;
+  int* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(40);
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Tile order: groups of 16 row tiles sweep the column tiles, so that one wave of
+// CTAs shares a compact set of A and B panels in L2.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GM = 16;
+  const int per_group = GM * tiles_n;
+  const int g = t / per_group;
+  const int first = g * GM;
+  const int gsize = min(GM, tiles_m - first);
+  const int r = t - g * per_group;
+  tm = first + r % gsize;
+  tn = r / gsize;
+}
+
+template <int BN>
+struct TcConfig {
+  static constexpr int kABytes = BM * BK * 4;
+  static constexpr int kBBytes = BN * BK * 4;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant__ TcParams p) {
+  using Cfg = TcConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + 2 + a); };
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < Cfg::kStages; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  int total_k_iters = 0;
+  for (int q = 0; q < p.npass; q++) total_k_iters += p.pass[q].k_iters;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int q = 0; q < p.npass && ok; q++) {
+          const TcPass& ps = p.pass[q];
+          const CUtensorMap* amap = &p.maps[ps.a_map];
+          const CUtensorMap* bmap = &p.maps[ps.b_map];
+          for (int kb = 0; kb < ps.k_iters; kb++, it++) {
+            const int s = it % Cfg::kStages;
+            const uint32_t ph = (it / Cfg::kStages) & 1u;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) {
+              ok = false;
+              if (!abort_flag) atomicCAS(p.status, 0, 1);
+              abort_flag = 1;
+              break;
+            }
+            const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
+            const uint32_t b_dst = a_dst + Cfg::kABytes;
+            mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+            const int k0 = kb * BK;
+            if (ps.a_mn) {
+#pragma unroll
+              for (int j = 0; j < BM / 32; j++) tma_load_2d(a_dst + j * 4096, amap, m0 + 32 * j, k0, full_bar(s));
+            } else {
+              tma_load_2d(a_dst, amap, k0, m0, full_bar(s));
+            }
+            if (ps.b_mn) {
+#pragma unroll
+              for (int j = 0; j < BN / 32; j++) tma_load_2d(b_dst + j * 4096, bmap, n0 + 32 * j, k0, full_bar(s));
+            } else {
+              tma_load_2d(b_dst, bmap, k0, n0, full_bar(s));
+            }
+          }
+        }
+      }
+      if (!ok) {
+        // let copies already issued land before the CTA leaves
+        for (int s = 0; s < Cfg::kStages; s++) {
+          for (uint32_t i = 0; i < 4096; i++) {
+            if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
+            __nanosleep(100);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tcount++) {
+        const int acc = tcount & 1;
+        const uint32_t acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, &abort_flag)) {
+          if (!abort_flag) atomicCAS(p.status, 0, 2);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t first = 1;
+        for (int q = 0; q < p.npass && ok; q++) {
+          const TcPass& ps = p.pass[q];
+          for (int kb = 0; kb < ps.k_iters; kb++, it++) {
+            const int s = it % Cfg::kStages;
+            const uint32_t ph = (it / Cfg::kStages) & 1u;
+            if (!mbar_wait(full_bar(s), ph, &abort_flag)) {
+              ok = false;
+              if (!abort_flag) atomicCAS(p.status, 0, 3);
+              abort_flag = 1;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+            const uint32_t b_addr = a_addr + Cfg::kABytes;
+            const uint64_t a_desc = ((uint64_t)ps.a_desc_hi << 32) | (uint64_t)(ps.a_desc_lo | ((a_addr >> 4) & 0x3fffu));
+            const uint64_t b_desc = ((uint64_t)ps.b_desc_hi << 32) | (uint64_t)(ps.b_desc_lo | ((b_addr >> 4) & 0x3fffu));
+#pragma unroll
+            for (int j = 0; j < BK / 8; j++) {
+              mma_tf32(d_tmem, a_desc + (uint64_t)(j * ps.a_adv), b_desc + (uint64_t)(j * ps.b_adv), ps.idesc,
+                       first ? 0u : 1u);
+              first = 0;
+            }
+            mma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+          }
+        }
+        if (ok) mma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int wq = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t tcount = 0;
+    const GemmEpilogue& e = p.epi;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, tcount++) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int acc = tcount & 1;
+      const uint32_t acc_ph = (tcount >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag)) {
+        if (!abort_flag) atomicCAS(p.status, 0, 4);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int m = tm * BM + wq * 32 + lane;
+      const int n0 = tn * BN;
+      const bool m_ok = m < p.M;
+      float bias = 0.0f;
+      if (e.bias && m_ok) bias = e.bias[m];
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ch++) {
+        float v[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * BN + ch * 32);
+        tmem_ld32(taddr, v);
+        tmem_ld_wait();
+        const int nc = n0 + ch * 32;
+        if (m_ok && nc < p.N) {
+#pragma unroll
+          for (int g4 = 0; g4 < 8; g4++) {
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (e.sample) w = philox4x32_10((uint32_t)m, (uint32_t)((nc + 4 * g4 + e.col0) >> 2), e.key);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int n = nc + 4 * g4 + j;
+              if (n < p.N) {
+                const long idx = (long)n * e.ldo + m;
+                float x = e.alpha * v[4 * g4 + j];
+                if (e.beta != 0.0f) x += e.beta * e.out[idx];
+                if (e.bias) x += e.col_scale ? bias * e.col_scale[n] : bias;
+                if (e.activation == 1) x = sigmoid_accurate(x);
+                if (e.out) e.out[idx] = x;
+                if (e.out_hi) {
+                  float hi, lo;
+                  split_tf32(x, hi, lo);
+                  e.out_hi[idx] = hi;
+                  if (e.out_lo) e.out_lo[idx] = lo;
+                }
+                if (e.sample) e.sample[idx] = word_to_uniform(pick_word(w, j)) < x ? 1.0f : 0.0f;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, ld;
+  uint32_t b0, b1;
+  int swz;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ k.d0;
+    h = h * 1000003u ^ k.d1;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 1 | (uint32_t)k.swz);
+    return h;
+  }
+};
+
+// 2-D fp32 map: inner (contiguous) extent d0, outer extent d1 with a stride of ld floats,
+// box b0 x b1, zero fill outside the tensor.  atom32 = false: 128-byte swizzle of 16-byte
+// chunks (K-major tiles); true: 128-byte swizzle of 32-byte chunks, the only shared-memory
+// layout tcgen05 accepts for MN-major 32-bit operands.  Encoded maps are cached.
+bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+              bool atom32) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, d0, d1, ld, b0, b1, atom32 ? 1 : 0};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {d0, d1};
+  const cuuint64_t strides[1] = {ld * sizeof(float)};
+  const cuuint32_t box[2] = {b0, b1};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0); }
+
+// Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
+// 16-byte units), descriptor version 1 for sm_100 (bits 46-47), layout type in bits 61-63.
+// K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart, 128-byte swizzle (type 2).
+// MN-major 32-bit tile: rows (one k each) of 128 bytes = 32 floats along M/N, 4-row groups
+// 512 bytes apart, 128-byte swizzle with 32-byte atoms (type 1).
+// The lower word carries the start address and the leading byte offset.
+constexpr uint32_t kDescHiK = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiMN = (512u >> 4) | (1u << 14) | (1u << 29);
+
+template <int BN>
+int launch_tc(TcParams& p) {
+  using Cfg = TcConfig<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+      return set_error("cudaFuncSetAttribute(max dynamic shared memory) failed");
+    attr_set = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  k_gemm_tc<BN><<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
+  return check_launch();
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmProblem& g) {
+  if (g.M <= 0 || g.N <= 0 || g.npass <= 0 || g.npass > kMaxPass) return false;
+  for (int q = 0; q < g.npass; q++) {
+    if (!tma_ok(g.pass[q].a) || !tma_ok(g.pass[q].b) || g.pass[q].k <= 0) return false;
+  }
+  if (g.epi.sample && (g.epi.col0 & 3)) return false;
+  return encode_fn() != nullptr;
+}
+
+int gemm_tc(const GemmProblem& g) {
+  if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
+  const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  TcParams p;
+  p.npass = g.npass;
+  p.M = g.M;
+  p.N = g.N;
+  p.epi = g.epi;
+  p.status = status_word();
+  for (int q = 0; q < g.npass; q++) {
+    const GemmPass& ps = g.pass[q];
+    TcPass& tp = p.pass[q];
+    tp.a_map = 2 * q;
+    tp.b_map = 2 * q + 1;
+    tp.k_iters = (ps.k + BK - 1) / BK;
+    // op(A) is M x k.  trans: stored k x M, k contiguous (K-major).  Otherwise M contiguous.
+    tp.a_mn = ps.a.trans ? 0 : 1;
+    // op(B) is k x N.  Not trans: stored k x N, k contiguous (K-major).  trans: N contiguous.
+    tp.b_mn = ps.b.trans ? 1 : 0;
+    bool ok;
+    if (tp.a_mn) ok = make_map(&p.maps[tp.a_map], ps.a.ptr, (uint64_t)g.M, (uint64_t)ps.k, (uint64_t)ps.a.ld, 32, BK, true);
+    else ok = make_map(&p.maps[tp.a_map], ps.a.ptr, (uint64_t)ps.k, (uint64_t)g.M, (uint64_t)ps.a.ld, BK, BM, false);
+    if (!ok) return set_error("cuTensorMapEncodeTiled failed for operand A");
+    if (tp.b_mn) ok = make_map(&p.maps[tp.b_map], ps.b.ptr, (uint64_t)g.N, (uint64_t)ps.k, (uint64_t)ps.b.ld, 32, BK, true);
+    else ok = make_map(&p.maps[tp.b_map], ps.b.ptr, (uint64_t)ps.k, (uint64_t)g.N, (uint64_t)ps.b.ld, BK, (uint32_t)BN, false);
+    if (!ok) return set_error("cuTensorMapEncodeTiled failed for operand B");
+    // instruction descriptor: D fp32 (bit 4), A and B TF32 (value 2 at bits 7 and 10), negate A
+    // (bit 13), A / B MN-major (bits 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
+    tp.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((ps.negate ? 1u : 0u) << 13) | ((uint32_t)tp.a_mn << 15) |
+               ((uint32_t)tp.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    tp.a_desc_hi = tp.a_mn ? kDescHiMN : kDescHiK;
+    tp.b_desc_hi = tp.b_mn ? kDescHiMN : kDescHiK;
+    // Leading byte offset (16-byte units): unused for K-major swizzled tiles (set to 1);
+    // for MN-major tiles it is the distance between 32-float column chunks = BK rows x 128 B.
+    tp.a_desc_lo = (tp.a_mn ? (uint32_t)(BK * 128 >> 4) : 1u) << 16;
+    tp.b_desc_lo = (tp.b_mn ? (uint32_t)(BK * 128 >> 4) : 1u) << 16;
+    // Advance per K=8 step: 32 bytes inside the swizzle row (K-major) or 8 rows = 1024 bytes (MN-major).
+    tp.a_adv = tp.a_mn ? (1024u >> 4) : (32u >> 4);
+    tp.b_adv = tp.b_mn ? (1024u >> 4) : (32u >> 4);
+  }
+  switch (BN) {
+    case 256: return launch_tc<256>(p);
+    case 128: return launch_tc<128>(p);
+    default: return launch_tc<64>(p);
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,398 @@
+// Reductions of the C ABI: sums and maxima along an axis, arg-max one-hot sampling
+// helpers, column softmax and the scalar reductions that return to the host
+// (cudamat/cudamat.cu:1148-1258, 1733-1759, 2104-2118, 2192-2240; the axis sums replace
+// the reference's GEMV with a ones vector, cudamat/cudamat.py:724-748,1546-1577).
+// Warp-shuffle trees inside a block; HBM-bound: 4 bytes read per input element.
+#include "common.cuh"
+
+using namespace b200;
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <class T>
+__device__ __forceinline__ T block_sum(T v, T* smem) {  // smem: 32 entries; result valid in every thread
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[wid] = v;
+  __syncthreads();
+  T r = (lane < nw) ? smem[lane] : T(0);
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* smem) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) smem[wid] = v;
+  __syncthreads();
+  float r = (lane < nw) ? smem[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+// First-maximum arg-max: (value, index) pairs, ties to the smaller index, which equals
+// the sequential `if (d[am] < d[r]) am = r` scan of eigenmat/eigenmat.cc:650-652.
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float v2, int i2) {
+  if (v2 > v || (v2 == v && i2 < i)) {
+    v = v2;
+    i = i2;
+  }
+}
+__device__ __forceinline__ void block_argmax(float& v, int& i, float* sv, int* si) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+    argmax_combine(v, i, v2, i2);
+  }
+  __syncthreads();
+  if (lane == 0) {
+    sv[wid] = v;
+    si[wid] = i;
+  }
+  __syncthreads();
+  v = (lane < nw) ? sv[lane] : -INFINITY;
+  i = (lane < nw) ? si[lane] : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+    argmax_combine(v, i, v2, i2);
+  }
+}
+
+// ---- sum down each column (contiguous): one block per column -----------------
+__global__ void __launch_bounds__(256) k_colsum(const float* __restrict__ m, float* __restrict__ t, int h, int w,
+                                                float mult, float beta) {
+  __shared__ float smem[32];
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = m + (long)c * h;
+    float s = 0;
+    if ((h & 3) == 0 && (((uintptr_t)col) & 15) == 0) {
+      const float4* col4 = reinterpret_cast<const float4*>(col);
+      for (int r = threadIdx.x; r < (h >> 2); r += blockDim.x) {
+        const float4 x = col4[r];
+        s += (x.x + x.y) + (x.z + x.w);
+      }
+    } else {
+      for (int r = threadIdx.x; r < h; r += blockDim.x) s += col[r];
+    }
+    s = block_sum(s, smem);
+    if (threadIdx.x == 0) t[c] = (beta == 0 ? 0.0f : beta * t[c]) + mult * s;
+  }
+}
+
+// ---- sum across columns for each row (strided) --------------------------------
+// Block = 32 rows x 8 column lanes; blockIdx.y splits the columns.  With one split the
+// block writes the result, otherwise a partial row into scratch[split][h].
+constexpr int kRowLanes = 8;
+__global__ void __launch_bounds__(32 * kRowLanes) k_rowsum(const float* __restrict__ m, float* __restrict__ out,
+                                                           int h, int w, int cols_per_split, float mult, float beta,
+                                                           bool final_pass) {
+  __shared__ float smem[kRowLanes][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int r = blockIdx.x * 32 + tx;
+  const int c0 = blockIdx.y * cols_per_split;
+  const int c1 = min(w, c0 + cols_per_split);
+  float s = 0;
+  if (r < h) {
+    int c = c0 + ty;
+    // four independent loads in flight per thread
+    for (; c + 3 * kRowLanes < c1; c += 4 * kRowLanes) {
+      const float a0 = m[(long)c * h + r], a1 = m[(long)(c + kRowLanes) * h + r];
+      const float a2 = m[(long)(c + 2 * kRowLanes) * h + r], a3 = m[(long)(c + 3 * kRowLanes) * h + r];
+      s += (a0 + a1) + (a2 + a3);
+    }
+    for (; c < c1; c += kRowLanes) s += m[(long)c * h + r];
+  }
+  smem[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && r < h) {
+    float tot = 0;
+#pragma unroll
+    for (int j = 0; j < kRowLanes; j++) tot += smem[j][tx];
+    if (final_pass)
+      out[r] = (beta == 0 ? 0.0f : beta * out[r]) + mult * tot;
+    else
+      out[(long)blockIdx.y * h + r] = tot;
+  }
+}
+__global__ void __launch_bounds__(256) k_rowsum_finish(const float* __restrict__ part, float* __restrict__ t, int h,
+                                                       int splits, float mult, float beta) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= h) return;
+  float tot = 0;
+  for (int s = 0; s < splits; s++) tot += part[(long)s * h + r];
+  t[r] = (beta == 0 ? 0.0f : beta * t[r]) + mult * tot;
+}
+
+// ---- column max / arg-max / one-hot -------------------------------------------
+__global__ void __launch_bounds__(256) k_colmax(const float* __restrict__ m, float* __restrict__ t, int h, int w) {
+  __shared__ float smem[32];
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = m + (long)c * h;
+    float v = -INFINITY;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) v = fmaxf(v, col[r]);
+    v = block_max(v, smem);
+    if (threadIdx.x == 0) t[c] = v;
+  }
+}
+__global__ void __launch_bounds__(256) k_rowmax(const float* __restrict__ m, float* __restrict__ t, int h, int w) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= h) return;
+  float v = m[r];
+  for (int c = 1; c < w; c++) v = fmaxf(v, m[(long)c * h + r]);
+  t[r] = v;
+}
+
+// mode 0: target = one-hot; 1: acc[argmax] += 1; 2: target[c] = argmax
+__global__ void __launch_bounds__(256) k_col_argmax(const float* m, float* t, int h, int w,
+                                                    int mode) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = m + (long)c * h;
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) argmax_combine(v, i, col[r], r);
+    block_argmax(v, i, sv, si);
+    if (i == 0x7fffffff) i = 0;  // all-NaN column: the sequential scan keeps index 0
+    if (mode == 0) {
+      float* tc = t + (long)c * h;
+      __syncthreads();  // every thread has read its part of the column (t may alias m)
+      for (int r = threadIdx.x; r < h; r += blockDim.x) tc[r] = (r == i) ? 1.0f : 0.0f;
+    } else if (threadIdx.x == 0) {
+      if (mode == 1)
+        t[(long)c * h + i] += 1.0f;
+      else
+        t[c] = (float)i;
+    }
+  }
+}
+
+// ---- column softmax -----------------------------------------------------------
+__global__ void __launch_bounds__(256) k_softmax(const float* m, float* t, int h, int w) {
+  __shared__ float smem[32];
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = m + (long)c * h;
+    float* tc = t + (long)c * h;
+    float mx = -INFINITY;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) mx = fmaxf(mx, col[r]);
+    mx = block_max(mx, smem);
+    float s = 0;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      const float e = expf(col[r] - mx);
+      tc[r] = e;
+      s += e;
+    }
+    s = block_sum(s, smem);
+    for (int r = threadIdx.x; r < h; r += blockDim.x) tc[r] = tc[r] / s;
+  }
+}
+
+// ---- scalar reductions --------------------------------------------------------
+// mode 0: sum a; 1: sum a*a; 2: sum a*b.  Stage 1 writes one double per block, stage 2
+// (one block) folds them.
+__global__ void __launch_bounds__(256) k_scalar_partial(const float* __restrict__ a, const float* __restrict__ b,
+                                                        long n, int mode, double* __restrict__ part) {
+  __shared__ double smem[32];
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  double s = 0;
+  for (long i = tid; i < n; i += nth) {
+    const float x = a[i];
+    s += mode == 0 ? (double)x : (mode == 1 ? (double)x * x : (double)x * b[i]);
+  }
+  s = block_sum(s, smem);
+  if (threadIdx.x == 0) part[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(256) k_scalar_final(const double* __restrict__ part, int nparts,
+                                                      double* __restrict__ out) {
+  __shared__ double smem[32];
+  double s = 0;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += part[i];
+  s = block_sum(s, smem);
+  if (threadIdx.x == 0) *out = s;
+}
+
+int scalar_reduce(cudamat* a, cudamat* b, int mode, double* result) {
+  if (!a->on_device || (b && !b->on_device)) return ERROR_NOT_ON_DEVICE;
+  const long n = numel(a);
+  int blocks = (int)((n + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
+  if (!part) return CUDA_ERROR;
+  k_scalar_partial<<<blocks, 256, 0, stream()>>>(a->data_device, b ? b->data_device : nullptr, n, mode, part + 1);
+  k_scalar_final<<<1, 256, 0, stream()>>>(part + 1, blocks, part);
+  int err = check_launch();
+  if (err) return err;
+  if (cudaMemcpyAsync(result, part, sizeof(double), cudaMemcpyDeviceToHost, stream()) != cudaSuccess)
+    return set_error("scalar readback failed");
+  if (cudaStreamSynchronize(stream()) != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
+
+}  // namespace
+
+namespace b200 {
+
+// target (h or w entries) = beta*target + mult * sum along `axis` of the stored matrix.
+int launch_axis_sum(const float* m, int h, int w, int axis, float* t, float mult, float beta) {
+  if ((long)h * w == 0) return 0;
+  if (axis == 0) {
+    int blocks = w < sm_count() * 8 ? w : sm_count() * 8;
+    k_colsum<<<blocks, 256, 0, stream()>>>(m, t, h, w, mult, beta);
+    return check_launch();
+  }
+  const int bx = (h + 31) / 32;
+  int splits = (4 * sm_count() + bx - 1) / bx;
+  const int max_splits = (w + 63) / 64;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  const int cps = (w + splits - 1) / splits;
+  splits = (w + cps - 1) / cps;
+  if (splits == 1) {
+    k_rowsum<<<dim3(bx, 1), 32 * kRowLanes, 0, stream()>>>(m, t, h, w, cps, mult, beta, true);
+    return check_launch();
+  }
+  float* part = (float*)workspace(0, (size_t)splits * h * sizeof(float));
+  if (!part) return CUDA_ERROR;
+  k_rowsum<<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(m, part, h, w, cps, 1.0f, 0.0f, false);
+  k_rowsum_finish<<<(h + 255) / 256, 256, 0, stream()>>>(part, t, h, splits, mult, beta);
+  return check_launch();
+}
+
+}  // namespace b200
+
+extern "C" {
+
+// eigenmat/eigenmat.cc:733-759 (cudamat builds the same from `dot` with a ones vector).
+int add_sum_by_axis(cudamat* mat, cudamat* target, int axis, float mult) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (axis != 0 && axis != 1) return ERROR_UNSUPPORTED;
+  if (mat->is_trans) axis = 1 - axis;
+  if (numel(target) != (axis == 0 ? mat->size[1] : mat->size[0])) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  return launch_axis_sum(mat->data_device, mat->size[0], mat->size[1], axis, target->data_device, mult, 1.0f);
+}
+int sum_by_axis(cudamat* mat, cudamat* target, int axis) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (axis != 0 && axis != 1) return ERROR_UNSUPPORTED;
+  if (mat->is_trans) axis = 1 - axis;
+  if (numel(target) != (axis == 0 ? mat->size[1] : mat->size[0])) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  return launch_axis_sum(mat->data_device, mat->size[0], mat->size[1], axis, target->data_device, 1.0f, 0.0f);
+}
+
+// cudamat/cudamat.cu:1148-1176.
+int max_by_axis(cudamat* mat, cudamat* target, int axis) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans) return ERROR_TRANSPOSED;
+  const int h = mat->size[0], w = mat->size[1];
+  if ((long)h * w == 0) return 0;
+  if (axis == 0) {
+    if (target->size[0] != 1 || target->size[1] != w) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    k_colmax<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w);
+  } else if (axis == 1) {
+    if (target->size[1] != 1 || target->size[0] != h) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    k_rowmax<<<(h + 255) / 256, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w);
+  } else {
+    return ERROR_UNSUPPORTED;
+  }
+  return check_launch();
+}
+
+// cudamat/cudamat.cu:1178-1201 with the meaning of eigenmat/eigenmat.cc:641-659.
+int choose_max_and_accumulate(cudamat* mat, cudamat* acc) {
+  if (!mat->on_device || !acc->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(mat, acc)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = mat->size[0], w = mat->size[1];
+  if ((long)h * w == 0) return 0;
+  k_col_argmax<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, acc->data_device, h, w, 1);
+  return check_launch();
+}
+
+// cudamat/cudamat.cu:1203-1230; full one-hot per column as eigenmat/eigenmat.cc:661-671
+// (the reference CUDA kernel clears only column 0, cudamat_kernels.cu:980).
+int choose_max_by_axis(cudamat* mat, cudamat* target, int axis) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans) return ERROR_TRANSPOSED;
+  if (axis != 0) return ERROR_UNSUPPORTED;
+  if (!same_shape(mat, target)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = mat->size[0], w = mat->size[1];
+  if ((long)h * w == 0) return 0;
+  k_col_argmax<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w, 0);
+  return check_launch();
+}
+
+// cudamat/cudamat.cu:1232-1258.
+int argmax_by_axis(cudamat* mat, cudamat* target, int axis) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans) return ERROR_TRANSPOSED;
+  if (axis != 0) return ERROR_UNSUPPORTED;
+  const int h = mat->size[0], w = mat->size[1];
+  if (target->size[0] != 1 || target->size[1] != w) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if ((long)h * w == 0) return 0;
+  k_col_argmax<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w, 2);
+  return check_launch();
+}
+
+// cudamat/cudamat.cu:2192-2240.
+int softmax(cudamat* mat, cudamat* target) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(mat, target)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = mat->size[0], w = mat->size[1];
+  if ((long)h * w == 0) return 0;
+  k_softmax<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w);
+  return check_launch();
+}
+int softmax_overwrite(cudamat* mat) { return softmax(mat, mat); }
+int apply_softmax(cudamat* mat, cudamat* target) { return softmax(mat, target); }
+
+// cudamat/cudamat.cu:2104-2118.  Blocks: the value returns to the host.
+float euclid_norm(cudamat* mat, int* err_code) {
+  double r = 0;
+  *err_code = scalar_reduce(mat, nullptr, 1, &r);
+  return (float)sqrt(r);
+}
+// cudamat/cudamat.cu:1733-1759.
+float vdot(cudamat* mat1, cudamat* mat2, int* err_code) {
+  if (mat1->is_trans != mat2->is_trans) {
+    *err_code = ERROR_TRANSPOSEDNESS;
+    return 0;
+  }
+  if (!same_shape(mat1, mat2)) {
+    *err_code = ERROR_INCOMPATIBLE_DIMENSIONS;
+    return 0;
+  }
+  double r = 0;
+  *err_code = scalar_reduce(mat1, mat2, 2, &r);
+  return (float)r;
+}
+// Sum of all elements (cudamat/cudamat.py:719-721 computes it as a vdot with ones).
+float sum_all(cudamat* mat, int* err_code) {
+  double r = 0;
+  *err_code = scalar_reduce(mat, nullptr, 0, &r);
+  return (float)r;
+}
+
+}  // extern "C"
