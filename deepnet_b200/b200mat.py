@@ -64,6 +64,13 @@ _lib.b200_host_free.argtypes = [ct.c_void_p]
 _lib.b200_get_stream.restype = ct.c_void_p
 _lib.b200_set_stream.argtypes = [ct.c_void_p]
 _lib.copy_from_host_ptr.argtypes = [ct.POINTER(cudamat), ct.c_void_p, ct.c_size_t]
+_lib.b200_prefetch.argtypes = [ct.POINTER(cudamat), ct.c_void_p, ct.c_size_t]
+_lib.b200_event_create.restype = ct.c_void_p
+_lib.b200_event_record.argtypes = [ct.c_void_p]
+_lib.b200_event_elapsed_ms.argtypes = [ct.c_void_p, ct.c_void_p]
+_lib.b200_event_elapsed_ms.restype = ct.c_float
+_lib.b200_event_destroy.argtypes = [ct.c_void_p]
+_lib.b200_event_destroy.restype = None
 _lib.init_from_array.restype = None
 _lib.set_transpose.restype = None
 _lib.cuda_sync_threads.restype = None
@@ -171,6 +178,9 @@ class CUDAMatrix(object):
 
     def reshape(self, shape):
         _check(_lib.reshape(self.p_mat, ct.c_uint(shape[0]), ct.c_uint(shape[1])))
+        if self.numpy_array is not None:
+            self.numpy_array = self.numpy_array.reshape(shape, order="F")
+            self.mat.data_host = self.numpy_array.ctypes.data_as(ct.POINTER(ct.c_float))
         return self
 
     def set_trans(self, is_trans):
@@ -184,7 +194,7 @@ class CUDAMatrix(object):
         _check(_lib.copy_to_device(self.p_mat))
 
     def copy_to_host(self):
-        if not self.mat.on_host or self.numpy_array is None:
+        if not self.mat.on_host or self.numpy_array is None or tuple(self.numpy_array.shape) != tuple(self.shape):
             self.numpy_array = np.empty(self.shape, dtype=np.float32, order="F")
             self.mat.data_host = self.numpy_array.ctypes.data_as(ct.POINTER(ct.c_float))
             self.mat.on_host = 1
@@ -205,6 +215,10 @@ class CUDAMatrix(object):
     def overwrite_from_pinned(self, ptr, nbytes):
         """Asynchronous host-to-device copy from a pinned buffer (see host_alloc)."""
         _check(_lib.copy_from_host_ptr(self.p_mat, ct.c_void_p(ptr), ct.c_size_t(nbytes)))
+
+    def prefetch_from_pinned(self, ptr, nbytes):
+        """Host-to-device copy on the copy stream; pair with prefetch_wait() / prefetch_fence()."""
+        _check(_lib.b200_prefetch(self.p_mat, ct.c_void_p(ptr), ct.c_size_t(nbytes)))
 
     def assign(self, val):
         if isinstance(val, CUDAMatrix):
@@ -438,9 +452,10 @@ class CUDAMatrix(object):
                                     ct.c_float(l1)))
         return self
 
-    def split_tf32(self, hi, lo):
-        _check(_lib.split_tf32(self.p_mat, hi.p_mat, lo.p_mat))
-        return hi, lo
+    def split_tf32(self, lo, hi=None):
+        """lo = self - tf32(self); hi (optional) = self with the low 13 mantissa bits cleared."""
+        _check(_lib.split_tf32(self.p_mat, hi.p_mat if hi is not None else None, lo.p_mat))
+        return lo
 
 
 class TransposedCUDAMatrix(CUDAMatrix):
@@ -608,6 +623,32 @@ def read_status():
     return _lib.b200_read_status()
 
 
+class Event(object):
+    """A CUDA event on the library stream: e.record(); ...; start.elapsed_ms(end)."""
+
+    def __init__(self):
+        _require_device()
+        self.ev = _lib.b200_event_create()
+        if not self.ev:
+            raise CUDAMatException("cudaEventCreate failed")
+
+    def record(self):
+        _check(_lib.b200_event_record(ct.c_void_p(self.ev)))
+        return self
+
+    def elapsed_ms(self, end):
+        ms = _lib.b200_event_elapsed_ms(ct.c_void_p(self.ev), ct.c_void_p(end.ev))
+        if ms < 0:
+            raise CUDAMatException("event timing failed: " + _lib.get_last_cuda_error().decode("utf-8", "replace"))
+        return ms
+
+    def __del__(self):
+        try:
+            _lib.b200_event_destroy(ct.c_void_p(self.ev))
+        except Exception:
+            pass
+
+
 def host_alloc(shape):
     """Returns (array, ptr): a pinned float32 Fortran-order host array; free with host_free(ptr)."""
     n = int(np.prod(shape))
@@ -617,6 +658,14 @@ def host_alloc(shape):
     buf = (ct.c_float * n).from_address(ptr)
     arr = np.frombuffer(buf, dtype=np.float32).reshape(shape, order="F")
     return arr, ptr
+
+
+def prefetch_wait():
+    _check(_lib.b200_prefetch_wait())
+
+
+def prefetch_fence():
+    _check(_lib.b200_prefetch_fence())
 
 
 def host_free(ptr):

@@ -153,6 +153,30 @@ int b200_set_stream(void* s) {
 }
 void* b200_get_stream() { return (void*)stream(); }
 
+// CUDA events on the library stream, for timing on the device.
+void* b200_event_create() {
+  cudaEvent_t ev = nullptr;
+  if (cudaEventCreate(&ev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return (void*)ev;
+}
+int b200_event_record(void* ev) {
+  if (cudaEventRecord((cudaEvent_t)ev, stream()) != cudaSuccess) return set_error("cudaEventRecord failed");
+  return 0;
+}
+// Milliseconds between two recorded events; blocks until `end` has happened.  < 0 on error.
+float b200_event_elapsed_ms(void* start, void* end) {
+  float ms = -1.0f;
+  if (cudaEventSynchronize((cudaEvent_t)end) != cudaSuccess) return -1.0f;
+  if (cudaEventElapsedTime(&ms, (cudaEvent_t)start, (cudaEvent_t)end) != cudaSuccess) return -1.0f;
+  return ms;
+}
+void b200_event_destroy(void* ev) {
+  if (ev) cudaEventDestroy((cudaEvent_t)ev);
+}
+
 // Reads and clears the device status word: non-zero means a kernel's bounded wait
 // gave up (the value encodes where).  Blocks until the stream is idle.
 int b200_read_status() {
@@ -223,6 +247,46 @@ int copy_from_host_ptr(cudamat* mat, const float* src, size_t bytes) {
   if (bytes > (size_t)numel(mat) * sizeof(float)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (cudaMemcpyAsync(mat->data_device, src, bytes, cudaMemcpyHostToDevice, stream()) != cudaSuccess)
     return set_error("copy_from_host_ptr failed");
+  return 0;
+}
+
+// Host-to-device copy on a second stream, so the next minibatch travels while the
+// current one is being processed.  b200_prefetch_wait makes the library stream wait for
+// every copy started so far; b200_prefetch_fence makes later copies wait for the work
+// already enqueued on the library stream (call it before overwriting a buffer in use).
+static cudaStream_t g_copy_stream = nullptr;
+static cudaEvent_t g_copy_done = nullptr, g_compute_done = nullptr;
+static int ensure_copy_stream() {
+  if (g_copy_stream) return 0;
+  if (cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&g_copy_done, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&g_compute_done, cudaEventDisableTiming) != cudaSuccess)
+    return set_error("copy stream creation failed");
+  return 0;
+}
+int b200_prefetch(cudamat* mat, const float* src, size_t bytes) {
+  if (!mat->on_device) return ERROR_NOT_ON_DEVICE;
+  if (bytes > (size_t)numel(mat) * sizeof(float)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  int err = ensure_copy_stream();
+  if (err) return err;
+  if (cudaMemcpyAsync(mat->data_device, src, bytes, cudaMemcpyHostToDevice, g_copy_stream) != cudaSuccess)
+    return set_error("b200_prefetch failed");
+  return 0;
+}
+int b200_prefetch_wait() {
+  int err = ensure_copy_stream();
+  if (err) return err;
+  if (cudaEventRecord(g_copy_done, g_copy_stream) != cudaSuccess ||
+      cudaStreamWaitEvent(stream(), g_copy_done, 0) != cudaSuccess)
+    return set_error("b200_prefetch_wait failed");
+  return 0;
+}
+int b200_prefetch_fence() {
+  int err = ensure_copy_stream();
+  if (err) return err;
+  if (cudaEventRecord(g_compute_done, stream()) != cudaSuccess ||
+      cudaStreamWaitEvent(g_copy_stream, g_compute_done, 0) != cudaSuccess)
+    return set_error("b200_prefetch_fence failed");
   return 0;
 }
 

@@ -40,6 +40,9 @@ struct GemmEpilogue {
 struct GemmProblem {
   int M, N;
   int npass;
+  // 1: operands are read as TF32 (low 13 mantissa bits ignored), the meaning of a pass on
+  // the tensor cores, which the CUDA-core kernel then reproduces; 0: full fp32 operands.
+  int tf32_operands;
   GemmPass pass[kMaxPass];
   GemmEpilogue epi;
 };
@@ -60,10 +63,10 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc,
   if (e.bias) v += e.col_scale ? e.bias[m] * e.col_scale[n] : e.bias[m];
   if (e.activation == 1) v = sigmoid_accurate(v);
   if (e.out) e.out[idx] = v;
-  if (e.out_hi) {
+  if (e.out_hi || e.out_lo) {
     float hi, lo;
     split_tf32(v, hi, lo);
-    e.out_hi[idx] = hi;
+    if (e.out_hi) e.out_hi[idx] = hi;
     if (e.out_lo) e.out_lo[idx] = lo;
   }
   if (e.sample) e.sample[idx] = u < v ? 1.0f : 0.0f;

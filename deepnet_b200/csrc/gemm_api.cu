@@ -29,6 +29,8 @@ int run(const GemmProblem& g) {
   return gemm_simt(g);
 }
 
+// hi may be null: the tensor core itself drops the low 13 mantissa bits of an fp32
+// operand, so the matrix x can stand in for its own high part and only lo is stored.
 __global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float* lo, long n, bool vec) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
@@ -37,12 +39,22 @@ __global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float*
       const float4 v = reinterpret_cast<const float4*>(x)[i];
       float4 h, l;
       split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-      reinterpret_cast<float4*>(hi)[i] = h;
+      if (hi) reinterpret_cast<float4*>(hi)[i] = h;
       reinterpret_cast<float4*>(lo)[i] = l;
     }
-    for (long i = (n4 << 2) + tid; i < n; i += nth) split_tf32(x[i], hi[i], lo[i]);
+    for (long i = (n4 << 2) + tid; i < n; i += nth) {
+      float h, l;
+      split_tf32(x[i], h, l);
+      if (hi) hi[i] = h;
+      lo[i] = l;
+    }
   } else {
-    for (long i = tid; i < n; i += nth) split_tf32(x[i], hi[i], lo[i]);
+    for (long i = tid; i < n; i += nth) {
+      float h, l;
+      split_tf32(x[i], h, l);
+      if (hi) hi[i] = h;
+      lo[i] = l;
+    }
   }
 }
 
@@ -91,7 +103,7 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       if (kSplit) {
         float4 H, L;
         split_tf32(W.x, H.x, L.x); split_tf32(W.y, H.y, L.y); split_tf32(W.z, H.z, L.z); split_tf32(W.w, H.w, L.w);
-        reinterpret_cast<float4*>(w_hi)[i] = H;
+        if (w_hi) reinterpret_cast<float4*>(w_hi)[i] = H;
         reinterpret_cast<float4*>(w_lo)[i] = L;
       }
     }
@@ -100,7 +112,12 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
       w[i] = W; delta[i] = D;
       if (kHasGrad) grad[i] = 0.0f;
-      if (kSplit) split_tf32(W, w_hi[i], w_lo[i]);
+      if (kSplit) {
+        float H, L;
+        split_tf32(W, H, L);
+        if (w_hi) w_hi[i] = H;
+        w_lo[i] = L;
+      }
     }
   } else {
     for (long i = tid; i < n; i += nth) {
@@ -108,7 +125,12 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
       w[i] = W; delta[i] = D;
       if (kHasGrad) grad[i] = 0.0f;
-      if (kSplit) split_tf32(W, w_hi[i], w_lo[i]);
+      if (kSplit) {
+        float H, L;
+        split_tf32(W, H, L);
+        if (w_hi) w_hi[i] = H;
+        w_lo[i] = L;
+      }
     }
   }
 }
@@ -150,17 +172,18 @@ int b200_set_dot_precision(int mode) {
   return 0;
 }
 
-// hi = x with the low 13 mantissa bits cleared, lo = x - hi.
+// hi = x with the low 13 mantissa bits cleared (optional, may be null), lo = x - hi.
 int split_tf32(cudamat* x, cudamat* hi, cudamat* lo) {
-  if (!x->on_device || !hi->on_device || !lo->on_device) return ERROR_NOT_ON_DEVICE;
-  if (!same_shape(x, hi) || !same_shape(x, lo)) return ERROR_INCOMPATIBLE_DIMENSIONS;
-  return launch_split(x->data_device, hi->data_device, lo->data_device, numel(x));
+  if (!x->on_device || (hi && !hi->on_device) || !lo->on_device) return ERROR_NOT_ON_DEVICE;
+  if ((hi && !same_shape(x, hi)) || !same_shape(x, lo)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  return launch_split(x->data_device, hi ? hi->data_device : nullptr, lo->data_device, numel(x));
 }
 
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   if (f->npass <= 0 || f->npass > kMaxPass) return ERROR_UNSUPPORTED;
   GemmProblem g;
   g.npass = f->npass;
+  g.tf32_operands = 1;
   g.M = lead(f->pass[0].a);
   g.N = nonlead(f->pass[0].b);
   for (int q = 0; q < f->npass; q++) {
@@ -192,7 +215,6 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   if (f->out_hi) e.out_hi = f->out_hi->data_device;
   if (f->out_lo) e.out_lo = f->out_lo->data_device;
   if (f->sample) e.sample = f->sample->data_device;
-  if (e.out_lo && !e.out_hi) return ERROR_UNSUPPORTED;
   if (e.beta != 0.0f && !e.out) return ERROR_UNSUPPORTED;
   if (f->bias) {
     if (!f->bias->on_device) return ERROR_NOT_ON_DEVICE;
@@ -223,6 +245,7 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
   GemmProblem g;
   g.M = m;
   g.N = n;
+  g.tf32_operands = 0;  // on CUDA cores `dot` multiplies full fp32 operands
   GemmEpilogue& e = g.epi;
   e.alpha = alpha;
   e.beta = beta;
@@ -249,18 +272,19 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
     return gemm_simt(g);
   }
   if (g_dot_mode == 1) return gemm_tc(g);
-  // fp32-grade: split both operands into scratch, then hi.hi + hi.lo + lo.hi
+  // fp32-grade: x = hi + lo, the tensor core reads hi out of x itself (it ignores the low
+  // 13 mantissa bits), lo goes to scratch; lo.hi + hi.lo + hi.hi, small terms first
   const long na = numel(mat1), nb = numel(mat2);
-  float* sa = (float*)workspace(2, (size_t)na * 2 * sizeof(float));
-  float* sb = (float*)workspace(3, (size_t)nb * 2 * sizeof(float));
+  float* sa = (float*)workspace(2, (size_t)na * sizeof(float));
+  float* sb = (float*)workspace(3, (size_t)nb * sizeof(float));
   if (!sa || !sb) return CUDA_ERROR;
-  int err = launch_split(mat1->data_device, sa, sa + na, na);
+  int err = launch_split(mat1->data_device, nullptr, sa, na);
   if (err) return err;
-  err = launch_split(mat2->data_device, sb, sb + nb, nb);
+  err = launch_split(mat2->data_device, nullptr, sb, nb);
   if (err) return err;
   g.npass = 3;
-  const float* ap[3] = {sa + na, sa, sa};  // small terms first
-  const float* bp[3] = {sb, sb + nb, sb};
+  const float* ap[3] = {sa, mat1->data_device, mat1->data_device};
+  const float* bp[3] = {mat2->data_device, sb, mat2->data_device};
   for (int q = 0; q < 3; q++) {
     g.pass[q].a = operand(mat1, ap[q]);
     g.pass[q].b = operand(mat2, bp[q]);
@@ -272,22 +296,23 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 
 // deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass over the parameter:
 //   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
-//   w -= eps * delta; grad = 0; and, when w_hi / w_lo are given, the TF32 split of the new w.
+//   w -= eps * delta; grad = 0; and, when w_lo (and optionally w_hi) is given, the TF32 split of the new w.
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
-// without grad and split, 36 with both.
+// without grad and split; +8 with grad, +4 with w_lo, +4 with w_hi.
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_hi, cudamat* w_lo,
                     float inv_batch, float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
   if (!same_shape(w, delta) || !same_shape(w, suff)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (grad && (!grad->on_device || !same_shape(w, grad))) return ERROR_INCOMPATIBLE_DIMENSIONS;
-  if ((w_hi == nullptr) != (w_lo == nullptr)) return ERROR_UNSUPPORTED;
-  if (w_hi && (!w_hi->on_device || !w_lo->on_device || !same_shape(w, w_hi) || !same_shape(w, w_lo)))
-    return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (w_hi && !w_lo) return ERROR_UNSUPPORTED;
+  if (w_hi && (!w_hi->on_device || !same_shape(w, w_hi))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (w_lo && (!w_lo->on_device || !same_shape(w, w_lo))) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const long n = numel(w);
   if (n == 0) return 0;
   uintptr_t bits = (uintptr_t)w->data_device | (uintptr_t)delta->data_device | (uintptr_t)suff->data_device;
   if (grad) bits |= (uintptr_t)grad->data_device;
-  if (w_hi) bits |= (uintptr_t)w_hi->data_device | (uintptr_t)w_lo->data_device;
+  if (w_hi) bits |= (uintptr_t)w_hi->data_device;
+  if (w_lo) bits |= (uintptr_t)w_lo->data_device;
   const bool vec = (bits & 15) == 0;
   long blocks = ((vec ? (n + 3) / 4 : n) + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
@@ -297,9 +322,9 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
 #define LAUNCH_UPDATE(G, S)                                                                                       \
   k_update<G, S><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, hp, \
                                                     lp, n, vec, -inv_batch, momentum, -eps, l2, l1)
-  if (grad && w_hi) LAUNCH_UPDATE(true, true);
+  if (grad && w_lo) LAUNCH_UPDATE(true, true);
   else if (grad) LAUNCH_UPDATE(true, false);
-  else if (w_hi) LAUNCH_UPDATE(false, true);
+  else if (w_lo) LAUNCH_UPDATE(false, true);
   else LAUNCH_UPDATE(false, false);
 #undef LAUNCH_UPDATE
   return check_launch();

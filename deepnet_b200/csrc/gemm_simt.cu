@@ -10,13 +10,16 @@ namespace {
 
 constexpr int TM = 64, TN = 64, TK = 16;
 
-__device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K) {
-  if (m >= M || k >= K) return 0.0f;
-  return a.trans ? a.ptr[(long)m * a.ld + k] : a.ptr[(long)k * a.ld + m];
+__device__ __forceinline__ float as_operand(float x, int tf32) {
+  return tf32 ? __uint_as_float(__float_as_uint(x) & 0xffffe000u) : x;
 }
-__device__ __forceinline__ float load_b(const GemmOperand& b, int k, int n, int K, int N) {
+__device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K, int tf32) {
+  if (m >= M || k >= K) return 0.0f;
+  return as_operand(a.trans ? a.ptr[(long)m * a.ld + k] : a.ptr[(long)k * a.ld + m], tf32);
+}
+__device__ __forceinline__ float load_b(const GemmOperand& b, int k, int n, int K, int N, int tf32) {
   if (n >= N || k >= K) return 0.0f;
-  return b.trans ? b.ptr[(long)k * b.ld + n] : b.ptr[(long)n * b.ld + k];
+  return as_operand(b.trans ? b.ptr[(long)k * b.ld + n] : b.ptr[(long)n * b.ld + k], tf32);
 }
 
 __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmProblem g) {
@@ -41,11 +44,11 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
         int m, k;
         if (ps.a.trans) { k = tid & 15; m = (tid >> 4) + 16 * i; }
         else { m = tid & 63; k = (tid >> 6) + 4 * i; }
-        As[k][m] = sgn * load_a(ps.a, m0 + m, k0 + k, g.M, ps.k);
+        As[k][m] = sgn * load_a(ps.a, m0 + m, k0 + k, g.M, ps.k, g.tf32_operands);
         int n, kb;
         if (ps.b.trans) { n = tid & 63; kb = (tid >> 6) + 4 * i; }
         else { kb = tid & 15; n = (tid >> 4) + 16 * i; }
-        Bs[kb][n] = load_b(ps.b, k0 + kb, n0 + n, ps.k, g.N);
+        Bs[kb][n] = load_b(ps.b, k0 + kb, n0 + n, ps.k, g.N, g.tf32_operands);
       }
       __syncthreads();
 #pragma unroll
@@ -64,6 +67,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
     }
   }
 
+  const GemmEpilogue e = g.epi;  // private copy: no reloads of the parameter block after each store
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int n = n0 + ty + 16 * j;
@@ -73,12 +77,12 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
       const int m = m0 + tx + 16 * i;
       if (m >= g.M) continue;
       float u = 0.0f;
-      if (g.epi.sample) {
-        const int gc = n + g.epi.col0;
-        const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), g.epi.key);
+      if (e.sample) {
+        const int gc = n + e.col0;
+        const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), e.key);
         u = word_to_uniform(pick_word(w, gc & 3));
       }
-      epilogue_store(g.epi, acc[i][j], m, n, u);
+      epilogue_store(e, acc[i][j], m, n, u);
     }
   }
 }

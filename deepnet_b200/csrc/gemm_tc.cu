@@ -10,14 +10,17 @@
 // "passes x K").  A pass may be negated (instruction-descriptor bit), which folds
 // positive-minus-negative statistics into one kernel.
 //
-// Kernel shape: persistent, one CTA per SM, 192 threads:
+// Kernel shape: persistent, one CTA per SM, 320 threads:
 //   warp 0     : TMA producer (one lane)       -> ring of kStages {A tile, B tile}
 //   warp 1     : TMEM allocation + MMA issuer (one lane), tcgen05.commit frees stages
-//   warps 2..5 : epilogue, one TMEM lane quarter each; two accumulators in TMEM let the
-//                epilogue of tile i overlap the main loop of tile i+1.
+//   warps 2..9 : epilogue; two warps share each TMEM lane quarter (half the columns each).
+//                They fold every finished 128-deep chunk of the product into fp32
+//                registers (two TMEM accumulators ping-pong with the MMA issuer) and run
+//                the fused epilogue from those registers at the end of the tile.
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, drains
 // and frees its tensor memory and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -30,7 +33,6 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 32;                       // 32 floats = one 128-byte swizzle row
-constexpr int kThreadsTc = 192;
 constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
 
 struct TcPass {
@@ -48,6 +50,7 @@ struct TcParams {
   TcPass pass[kMaxPass];
   int npass;
   int M, N, tiles_m, tiles_n;
+  int chunk_iters;  // k-iterations per TMEM accumulation chunk
   GemmEpilogue epi;
   int* status;
 };
@@ -146,6 +149,16 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gsize;
 }
 
+// The tensor core adds into its fp32 accumulator with truncation, not round-to-nearest:
+// a same-sign sum loses about 0.6 ulp per tcgen05.mma (-646 ulp measured at K = 8192,
+// 5e-5 relative).  To keep fp32-grade results the accumulation is split into chunks of
+// kChunkIters k-iterations (128 products): each chunk starts a fresh TMEM accumulator
+// (two of them ping-pong) and the epilogue warps add the finished chunk into fp32
+// registers with ordinary rounding while the next chunk is being multiplied.
+constexpr int kChunkItersDefault = 4;
+constexpr int kEpiWarps = 8;
+constexpr int kThreadsTc = 32 * (2 + kEpiWarps);
+
 template <int BN>
 struct TcConfig {
   static constexpr int kABytes = BM * BK * 4;
@@ -153,10 +166,19 @@ struct TcConfig {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kColsPerWarp = BN / 2;   // each lane quarter is shared by two epilogue warps
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+// Epilogue variants, chosen on the host.  The common cases are compiled without run-time
+// branches (they are instruction-bound otherwise):
+//   kEpiPlain   out = alpha * acc (+ beta * out)                      (`dot`, statistics)
+//   kEpiAct     out = act(alpha * acc + bias), out_lo = its TF32 remainder (act by kSigmoid)
+//   kEpiSample  kEpiAct plus sample = Bernoulli(out)
+//   kEpiGeneric every option tested at run time
+enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSigLo = 2, kEpiSigLoSample = 3, kEpiLinLo = 4 };
+
+template <int BN, int kEpi>
 __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant__ TcParams p) {
   using Cfg = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -181,7 +203,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -197,6 +219,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 
   int total_k_iters = 0;
   for (int q = 0; q < p.npass; q++) total_k_iters += p.pass[q].k_iters;
+  const int kChunkIters = p.chunk_iters;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -252,22 +275,26 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, chunk = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tcount++) {
-        const int acc = tcount & 1;
-        const uint32_t acc_ph = (tcount >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, &abort_flag)) {
-          if (!abort_flag) atomicCAS(p.status, 0, 2);
-          abort_flag = 1;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        uint32_t first = 1;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int in_tile = 0;
+        uint32_t fresh = 1;
         for (int q = 0; q < p.npass && ok; q++) {
           const TcPass& ps = p.pass[q];
           for (int kb = 0; kb < ps.k_iters; kb++, it++) {
+            const int acc = chunk & 1;
+            if (in_tile % kChunkIters == 0) {
+              // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
+              if (!mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag)) {
+                ok = false;
+                if (!abort_flag) atomicCAS(p.status, 0, 2);
+                abort_flag = 1;
+                break;
+              }
+              tc_fence_after();
+              fresh = 1;
+            }
             const int s = it % Cfg::kStages;
             const uint32_t ph = (it / Cfg::kStages) & 1u;
             if (!mbar_wait(full_bar(s), ph, &abort_flag)) {
@@ -277,6 +304,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               break;
             }
             tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
             const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
             const uint32_t b_addr = a_addr + Cfg::kABytes;
             const uint64_t a_desc = ((uint64_t)ps.a_desc_hi << 32) | (uint64_t)(ps.a_desc_lo | ((a_addr >> 4) & 0x3fffu));
@@ -284,62 +312,130 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 #pragma unroll
             for (int j = 0; j < BK / 8; j++) {
               mma_tf32(d_tmem, a_desc + (uint64_t)(j * ps.a_adv), b_desc + (uint64_t)(j * ps.b_adv), ps.idesc,
-                       first ? 0u : 1u);
-              first = 0;
+                       fresh ? 0u : 1u);
+              fresh = 0;
             }
             mma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+            in_tile++;
+            if (in_tile % kChunkIters == 0 || in_tile == total_k_iters) {
+              mma_commit(tfull_bar(acc));  // chunk complete: hand it to the epilogue warps
+              chunk++;
+            }
           }
         }
-        if (ok) mma_commit(tfull_bar(acc));
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const int wq = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t tcount = 0;
-    const GemmEpilogue& e = p.epi;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, tcount++) {
+    constexpr int COLS = Cfg::kColsPerWarp;
+    const int ew = warp - 2;
+    const int wq = warp & 3;          // TMEM lane quarter this warp may read
+    const int col_base = (ew >> 2) * COLS;
+    uint32_t chunk = 0;
+    // A private copy: read through the parameter block, every field would have to be
+    // reloaded after each store (the stores could alias it as far as the compiler knows).
+    const GemmEpilogue e = p.epi;
+    const int pM = p.M, pN = p.N;
+    const int nchunks = (total_k_iters + kChunkIters - 1) / kChunkIters;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const int acc = tcount & 1;
-      const uint32_t acc_ph = (tcount >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag)) {
-        if (!abort_flag) atomicCAS(p.status, 0, 4);
-        abort_flag = 1;
-        break;
-      }
-      tc_fence_after();
-      const int m = tm * BM + wq * 32 + lane;
-      const int n0 = tn * BN;
-      const bool m_ok = m < p.M;
-      float bias = 0.0f;
-      if (e.bias && m_ok) bias = e.bias[m];
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ch++) {
-        float v[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * BN + ch * 32);
-        tmem_ld32(taddr, v);
-        tmem_ld_wait();
-        const int nc = n0 + ch * 32;
-        if (m_ok && nc < p.N) {
+      float accum[COLS];
 #pragma unroll
-          for (int g4 = 0; g4 < 8; g4++) {
+      for (int j = 0; j < COLS; j++) accum[j] = 0.0f;
+      for (int c = 0; c < nchunks; c++, chunk++) {
+        const int acc = chunk & 1;
+        if (!mbar_wait(tfull_bar(acc), (chunk >> 1) & 1u, &abort_flag)) {
+          if (!abort_flag) atomicCAS(p.status, 0, 4);
+          abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * BN + col_base);
+#pragma unroll
+        for (int j = 0; j < COLS / 32; j++) {
+          float v[32];
+          tmem_ld32(taddr + 32 * j, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) accum[32 * j + i] += v[i];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      }
+      if (!ok) break;
+      const int m = tm * BM + wq * 32 + lane;
+      const int nc = tn * BN + col_base;
+      if (m < pM && nc < pN) {
+        if (kEpi == kEpiPlain) {
+          float* const out = e.out + (long)nc * e.ldo + m;
+          const float alpha = e.alpha, beta = e.beta;
+          const long ldo = e.ldo;
+          const int ncols = pN - nc < COLS ? pN - nc : COLS;
+          if (beta == 0.0f) {
+#pragma unroll
+            for (int j = 0; j < COLS; j++)
+              if (j < ncols) out[j * ldo] = alpha * accum[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < COLS; j++)
+              if (j < ncols) out[j * ldo] = alpha * accum[j] + beta * out[j * ldo];
+          }
+        } else if (kEpi == kEpiSigLo || kEpi == kEpiSigLoSample || kEpi == kEpiLinLo) {
+          // host guarantees: bias, out, out_lo set; beta = 0; no col_scale, no out_hi
+          const long off = (long)nc * e.ldo + m, ldo = e.ldo;
+          float* const out = e.out + off;
+          float* const out_lo = e.out_lo + off;
+          float* const smp = kEpi == kEpiSigLoSample ? e.sample + off : nullptr;
+          const float alpha = e.alpha, bias = e.bias[m];
+          const int ncols = pN - nc < COLS ? pN - nc : COLS;
+          const PhiloxKey key = e.key;
+          const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
+#pragma unroll
+          for (int g4 = 0; g4 < COLS / 4; g4++) {
+            if (4 * g4 < ncols) {
+              uint4 w = make_uint4(0, 0, 0, 0);
+              if (kEpi == kEpiSigLoSample) w = philox4x32_10((uint32_t)m, cblk0 + g4, key);
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                if (4 * g4 + j < ncols) {
+                  float x = alpha * accum[4 * g4 + j] + bias;
+                  if (kEpi != kEpiLinLo) x = sigmoid_accurate(x);
+                  float hi, lo;
+                  split_tf32(x, hi, lo);
+                  out[(4 * g4 + j) * ldo] = x;
+                  out_lo[(4 * g4 + j) * ldo] = lo;
+                  if (kEpi == kEpiSigLoSample)
+                    smp[(4 * g4 + j) * ldo] = word_to_uniform(pick_word(w, j)) < x ? 1.0f : 0.0f;
+                }
+              }
+            }
+          }
+        } else {
+          float bias = 0.0f;
+          if (e.bias) bias = e.bias[m];
+#pragma unroll
+          for (int g4 = 0; g4 < COLS / 4; g4++) {
             uint4 w = make_uint4(0, 0, 0, 0);
-            if (e.sample) w = philox4x32_10((uint32_t)m, (uint32_t)((nc + 4 * g4 + e.col0) >> 2), e.key);
+            if (e.sample && nc + 4 * g4 < pN)
+              w = philox4x32_10((uint32_t)m, (uint32_t)((nc + 4 * g4 + e.col0) >> 2), e.key);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
               const int n = nc + 4 * g4 + j;
-              if (n < p.N) {
+              if (n < pN) {
                 const long idx = (long)n * e.ldo + m;
-                float x = e.alpha * v[4 * g4 + j];
+                float x = e.alpha * accum[4 * g4 + j];
                 if (e.beta != 0.0f) x += e.beta * e.out[idx];
                 if (e.bias) x += e.col_scale ? bias * e.col_scale[n] : bias;
                 if (e.activation == 1) x = sigmoid_accurate(x);
                 if (e.out) e.out[idx] = x;
-                if (e.out_hi) {
+                if (e.out_hi || e.out_lo) {
                   float hi, lo;
                   split_tf32(x, hi, lo);
-                  e.out_hi[idx] = hi;
+                  if (e.out_hi) e.out_hi[idx] = hi;
                   if (e.out_lo) e.out_lo[idx] = lo;
                 }
                 if (e.sample) e.sample[idx] = word_to_uniform(pick_word(w, j)) < x ? 1.0f : 0.0f;
@@ -348,9 +444,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
   }
 
@@ -362,6 +455,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
 
 // ---- host side ------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -447,12 +541,13 @@ inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_
 constexpr uint32_t kDescHiK = (1024u >> 4) | (1u << 14) | (2u << 29);
 constexpr uint32_t kDescHiMN = (512u >> 4) | (1u << 14) | (1u << 29);
 
-template <int BN>
+template <int BN, int kEpi>
 int launch_tc(TcParams& p) {
   using Cfg = TcConfig<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(k_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(k_gemm_tc<BN, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+        cudaSuccess)
       return set_error("cudaFuncSetAttribute(max dynamic shared memory) failed");
     attr_set = true;
   }
@@ -460,7 +555,7 @@ int launch_tc(TcParams& p) {
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  k_gemm_tc<BN><<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
+  k_gemm_tc<BN, kEpi><<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
   return check_launch();
 }
 
@@ -484,6 +579,15 @@ int gemm_tc(const GemmProblem& g) {
   p.N = g.N;
   p.epi = g.epi;
   p.status = status_word();
+  {
+    static int chunk_iters = 0;
+    if (!chunk_iters) {
+      const char* e = getenv("B200_CHUNK_ITERS");
+      chunk_iters = e ? atoi(e) : kChunkItersDefault;
+      if (chunk_iters < 1) chunk_iters = kChunkItersDefault;
+    }
+    p.chunk_iters = chunk_iters;
+  }
   for (int q = 0; q < g.npass; q++) {
     const GemmPass& ps = g.pass[q];
     TcPass& tp = p.pass[q];
@@ -515,11 +619,26 @@ int gemm_tc(const GemmProblem& g) {
     tp.a_adv = tp.a_mn ? (1024u >> 4) : (32u >> 4);
     tp.b_adv = tp.b_mn ? (1024u >> 4) : (32u >> 4);
   }
-  switch (BN) {
-    case 256: return launch_tc<256>(p);
-    case 128: return launch_tc<128>(p);
-    default: return launch_tc<64>(p);
+  const GemmEpilogue& e = g.epi;
+  int epi = kEpiGeneric;
+  if (!e.bias && e.activation == 0 && !e.out_hi && !e.out_lo && !e.sample && e.out) {
+    epi = kEpiPlain;
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out && e.out_lo && !e.out_hi) {
+    if (e.activation == 1) epi = e.sample ? kEpiSigLoSample : kEpiSigLo;
+    else if (!e.sample) epi = kEpiLinLo;
   }
+#define B200_TC_CASE(BNV)                                            \
+  switch (epi) {                                                     \
+    case kEpiPlain: return launch_tc<BNV, kEpiPlain>(p);             \
+    case kEpiSigLo: return launch_tc<BNV, kEpiSigLo>(p);             \
+    case kEpiSigLoSample: return launch_tc<BNV, kEpiSigLoSample>(p); \
+    case kEpiLinLo: return launch_tc<BNV, kEpiLinLo>(p);             \
+    default: return launch_tc<BNV, kEpiGeneric>(p);                  \
+  }
+  if (BN == 256) { B200_TC_CASE(256) }
+  if (BN == 128) { B200_TC_CASE(128) }
+  B200_TC_CASE(64)
+#undef B200_TC_CASE
 }
 
 }  // namespace b200

@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(256) k_softmax(const float* m, float* t, int h
 }
 
 // ---- scalar reductions --------------------------------------------------------
-// mode 0: sum a; 1: sum a*a; 2: sum a*b.  Stage 1 writes one double per block, stage 2
-// (one block) folds them.
+// mode 0: sum a; 1: sum a*a; 2: sum a*b; 3: sum (a-b)^2.  Stage 1 writes one double per
+// block, stage 2 (one block) folds them.
 __global__ void __launch_bounds__(256) k_scalar_partial(const float* __restrict__ a, const float* __restrict__ b,
                                                         long n, int mode, double* __restrict__ part) {
   __shared__ double smem[32];
@@ -218,18 +218,26 @@ __global__ void __launch_bounds__(256) k_scalar_partial(const float* __restrict_
   double s = 0;
   for (long i = tid; i < n; i += nth) {
     const float x = a[i];
-    s += mode == 0 ? (double)x : (mode == 1 ? (double)x * x : (double)x * b[i]);
+    if (mode == 3) {
+      const float d = x - b[i];
+      s += (double)d * d;
+    } else {
+      s += mode == 0 ? (double)x : (mode == 1 ? (double)x * x : (double)x * b[i]);
+    }
   }
   s = block_sum(s, smem);
   if (threadIdx.x == 0) part[blockIdx.x] = s;
 }
 __global__ void __launch_bounds__(256) k_scalar_final(const double* __restrict__ part, int nparts,
-                                                      double* __restrict__ out) {
+                                                      double* __restrict__ out, float* acc) {
   __shared__ double smem[32];
   double s = 0;
   for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += part[i];
   s = block_sum(s, smem);
-  if (threadIdx.x == 0) *out = s;
+  if (threadIdx.x == 0) {
+    if (out) *out = s;
+    if (acc) *acc += (float)s;
+  }
 }
 
 int scalar_reduce(cudamat* a, cudamat* b, int mode, double* result) {
@@ -242,7 +250,7 @@ int scalar_reduce(cudamat* a, cudamat* b, int mode, double* result) {
   double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
   if (!part) return CUDA_ERROR;
   k_scalar_partial<<<blocks, 256, 0, stream()>>>(a->data_device, b ? b->data_device : nullptr, n, mode, part + 1);
-  k_scalar_final<<<1, 256, 0, stream()>>>(part + 1, blocks, part);
+  k_scalar_final<<<1, 256, 0, stream()>>>(part + 1, blocks, part, nullptr);
   int err = check_launch();
   if (err) return err;
   if (cudaMemcpyAsync(result, part, sizeof(double), cudaMemcpyDeviceToHost, stream()) != cudaSuccess)
@@ -388,6 +396,24 @@ float vdot(cudamat* mat1, cudamat* mat2, int* err_code) {
   *err_code = scalar_reduce(mat1, mat2, 2, &r);
   return (float)r;
 }
+// acc[0] += sum((a - b)^2) without a host round trip: the squared reconstruction error of
+// deepnet/logistic_layer.py:48-52 (subtract + euclid_norm()**2) kept on the device.
+int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc) {
+  if (!a->on_device || !b->on_device || !acc->on_device) return ERROR_NOT_ON_DEVICE;
+  if (!same_shape(a, b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (numel(acc) < 1) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const long n = numel(a);
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
+  if (!part) return CUDA_ERROR;
+  k_scalar_partial<<<blocks, 256, 0, stream()>>>(a->data_device, b->data_device, n, 3, part + 1);
+  k_scalar_final<<<1, 256, 0, stream()>>>(part + 1, blocks, nullptr, acc->data_device);
+  return check_launch();
+}
+
 // Sum of all elements (cudamat/cudamat.py:719-721 computes it as a vdot with ones).
 float sum_all(cudamat* mat, int* err_code) {
   double r = 0;

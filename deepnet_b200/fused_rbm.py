@@ -1,0 +1,140 @@
+"""The CD-k step of an RBM on the fused entry points of b200mat.
+
+Same arithmetic and the same random stream as `dbm.DBM.TrainOneBatch` (one sampling
+call for the positive hidden sample, one per Gibbs step), but every group of
+reference calls is one kernel:
+
+  dot + add_col_vec + sigmoid + sample_bernoulli   -> fused_gemm (bias, activation, Bernoulli in the
+      (deepnet/dbm.py:88-105, logistic_layer.py:11-15)  epilogue; TF32 hi/lo split of the result written too)
+  dot(v, h.T) and add_dot(..., mult=-1)            -> one fused_gemm with negated passes
+      (deepnet/edge.py:236,242)
+  add_mult / mult / add_mult / assign(0)           -> momentum_update (one pass over W)
+      (deepnet/dbm.py:242,254, parameter.py:89-106)
+  subtract + euclid_norm()**2                      -> add_sq_diff, accumulated on the device
+      (deepnet/logistic_layer.py:48-52)
+
+fp32-grade products: the tensor core reads an fp32 operand as TF32 (low 13 mantissa
+bits ignored), so x serves as its own high part and only lo = x - tf32(x) is kept
+beside it; x.y ~= lo_x.y + x.lo_y + x.y.  Binary matrices (data, Bernoulli samples)
+have lo = 0 and need one pass fewer.
+
+With more than one rank the sufficient statistics of the ranks' minibatch shards are
+summed by one NCCL all-reduce of a packed buffer before the update.
+"""
+import numpy as np
+
+from .dbm import LINEAR, LOGISTIC, Parameter
+
+
+class FusedRBM(object):
+    def __init__(self, cm, V, H, batchsize, weight, hyperparams, edge_hyperparams=None, visible=LOGISTIC,
+                 binary_data=True, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0):
+        self.cm = cm
+        self.V, self.H, self.B = V, H, batchsize
+        self.visible = visible
+        self.binary_data = binary_data
+        self.hyp = hyperparams
+        self.ehyp = edge_hyperparams or hyperparams
+        self.world_size = world_size
+        cm.CUDAMatrix.init_random(seed)
+        cm.set_rng_column_offset(rank * batchsize)
+        z = lambda r, c: cm.empty((r, c))
+        w = np.asarray(weight, np.float32)
+        assert w.shape == (V, H)
+        self.W = cm.CUDAMatrix(w)
+        self.W_lo = z(V, H)
+        self.W.split_tf32(self.W_lo)
+        self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
+        self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
+        self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
+        # packed statistics [W | b_v | b_h]: one buffer, one all-reduce
+        self.pack = z(V * H + V + H, 1)
+        self.suff_W = self.pack.slice(0, V * H).reshape((V, H))
+        self.suff_bv = self.pack.slice(V * H, V * H + V)
+        self.suff_bh = self.pack.slice(V * H + V, V * H + V + H)
+        B = batchsize
+        self.data_lo = None if binary_data else z(V, B)
+        self.h_pos, self.h_pos_lo, self.h_samp = z(H, B), z(H, B), z(H, B)
+        self.v_neg, self.v_neg_lo = z(V, B), z(V, B)
+        self.h_neg, self.h_neg_lo = z(H, B), z(H, B)
+        self.loss_acc = z(1, 1)
+        self._sched = Parameter(cm, self.hyp)
+        self._esched = Parameter(cm, self.ehyp)
+        self.kernel_launches = 0
+        self.timeline = None   # set to a list to record (name, flops, bytes, start, end) per launch
+
+    def _act(self, layer_activation):
+        return 1 if layer_activation == LOGISTIC else 0
+
+    def _op(self, name, flops, nbytes, fn, *args, **kw):
+        """Runs one kernel-launching call; with a timeline attached, brackets it with CUDA events."""
+        self.kernel_launches += 1
+        if self.timeline is None:
+            return fn(*args, **kw)
+        e0 = self.cm.Event().record()
+        r = fn(*args, **kw)
+        e1 = self.cm.Event().record()
+        self.timeline.append((name, flops, nbytes, e0, e1))
+        return r
+
+    def TrainOneBatch(self, step, data):
+        """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host."""
+        cm, k = self.cm, self.hyp.gibbs_steps
+        V, H, B = self.V, self.H, self.B
+        W, Wl = self.W, self.W_lo
+        v0 = data
+        self.kernel_launches = 0
+        gf = 2.0 * V * H * B                      # algorithmic flops of one product
+        vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
+        lib = cm._lib
+        # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
+        if self.binary_data:
+            up0 = [(Wl.T, v0), (W.T, v0)]
+        else:
+            self._op("split", 0, 2 * vb, v0.split_tf32, self.data_lo)
+            up0 = [(Wl.T, v0), (W.T, self.data_lo), (W.T, v0)]
+        self._op("gemm_up", gf, 3 * hb, cm.fused_gemm, up0, out=self.h_pos, out_lo=self.h_pos_lo, sample=self.h_samp,
+                 bias=self.bh, activation=1)
+        # negative phase: k Gibbs steps, visible mean fed upward (sample_input off)
+        for i in range(k):
+            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, [(Wl, self.h_samp), (W, self.h_samp)], out=self.v_neg,
+                     out_lo=self.v_neg_lo, bias=self.bv, activation=self._act(self.visible))
+            if i == 0:
+                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
+                                                                                self.loss_acc.p_mat)))
+                self.kernel_launches += 1          # add_sq_diff is two launches
+            self._op("gemm_up", gf, 3 * hb, cm.fused_gemm,
+                     [(Wl.T, self.v_neg), (W.T, self.v_neg_lo), (W.T, self.v_neg)], out=self.h_neg,
+                     out_lo=self.h_neg_lo, sample=self.h_samp, bias=self.bh, activation=1)
+        # statistics: pos - neg in one product; bias statistics by row sums
+        if self.binary_data:
+            pos = [(v0, self.h_pos_lo.T), (v0, self.h_pos.T)]
+        else:
+            pos = [(self.data_lo, self.h_pos.T), (v0, self.h_pos_lo.T), (v0, self.h_pos.T)]
+        neg = [(self.v_neg_lo, self.h_neg.T, 1), (self.v_neg, self.h_neg_lo.T, 1), (self.v_neg, self.h_neg.T, 1)]
+        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
+        self._op("row_sum", 0, vb, v0.sum, axis=1, target=self.suff_bv)
+        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_neg, axis=1, mult=-1.0)
+        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
+        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
+        self.kernel_launches += 4                  # each row sum is a partial + a finish launch
+        if self.world_size > 1:
+            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
+        inv_b = 1.0 / (self.B * self.world_size)
+        # updates (biases are not regularised, deepnet/dbm.py:249)
+        mom, eps = self._sched.GetMomentumAndEpsilon(step)
+        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
+        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
+        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
+        eh = self.ehyp
+        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
+        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
+        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1, w_lo=Wl)
+
+    def read_loss(self, reset=True):
+        """Sum of squared reconstruction errors accumulated since the last reset (blocks)."""
+        v = float(np.array(self.loss_acc.asarray())[0, 0])
+        if reset:
+            self.loss_acc.assign(0)
+        return v

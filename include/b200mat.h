@@ -1,0 +1,226 @@
+/*
+ * b200mat.h -- C ABI of libb200mat.so, an sm_100a replacement for the cudamat shared
+ * library on the contrastive-divergence path of deepnet.
+ *
+ * Every entry point takes plain pointers and scalars (no C++ or framework types) and,
+ * unless noted, returns 0 or one of the negative codes below.  Each declaration cites
+ * the reference interface it replaces (paths relative to the reference project);
+ * additions that have no counterpart there say so.  Matrices are float32,
+ * column-major, size[0] rows by size[1] columns; operations are enqueued on one
+ * library stream and the host blocks only where a value returns to it.
+ */
+#ifndef B200MAT_H_
+#define B200MAT_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudamat/cudamat.cuh:1-9 */
+#define ERROR_INCOMPATIBLE_DIMENSIONS -1
+#define CUBLAS_ERROR -2
+#define CUDA_ERROR -3
+#define VIEW_ERROR -4
+#define ERROR_TRANSPOSED -5
+#define ERROR_GENERIC -6
+#define ERROR_TRANSPOSEDNESS -7
+#define ERROR_NOT_ON_DEVICE -8
+#define ERROR_UNSUPPORTED -9
+/* additions */
+#define ERROR_NCCL -10
+#define ERROR_DEVICE_TIMEOUT -11
+
+/* cudamat/cudamat.cuh:21-29 (same layout) */
+typedef struct cudamat {
+  float* data_host;
+  float* data_device;
+  int on_device;
+  int on_host;
+  int size[2];
+  int is_trans;
+  int owns_data;
+} cudamat;
+
+/* cudamat/cudamat.cuh:31-34 held two device pointers; the same 16 bytes now hold the
+ * Philox key and the count of sampling calls issued. */
+typedef struct rnd_struct {
+  unsigned long long seed;
+  unsigned long long calls;
+} rnd_struct;
+
+/* ---- library, device, memory: cudamat/cudamat.cu:25-435 ---------------------------- */
+const char* get_last_cuda_error(void);                          /* cudamat.cu:25 */
+int cublas_init(void);                                          /* cudamat.cu:31 */
+int cublas_shutdown(void);                                      /* cudamat.cu:39 */
+int cuda_set_device(int deviceId);                              /* cudamat.cu:46 */
+int init_random(rnd_struct* rnd_state, int seed, char* cudamatpath); /* cudamat.cu:55 */
+int get_leading_dimension(cudamat* mat);                        /* cudamat.cu:87 */
+int get_nonleading_dimension(cudamat* mat);                     /* cudamat.cu:91 */
+void set_transpose(cudamat* mat, int is_trans);                 /* cudamat.cu:95 */
+void cuda_sync_threads(void);                                   /* cudamat.cu:103 */
+int allocate_device_memory(cudamat* mat);                       /* cudamat.cu:109 */
+int copy_to_host(cudamat* mat);                                 /* cudamat.cu:153 */
+int copy_to_device(cudamat* mat);                               /* cudamat.cu:167 */
+int copy_on_device(cudamat* mat1, cudamat* mat2);               /* cudamat.cu:217 */
+int free_device_memory(cudamat* mat);                           /* cudamat.cu:298 */
+int set_shape(cudamat* mat, unsigned int m, unsigned int n);    /* cudamat.cu:312 */
+int reshape(cudamat* mat, unsigned int m, unsigned int n);      /* cudamat.cu:321 */
+int get_slice(cudamat* source, cudamat* target, unsigned int first_col, unsigned int last_col);        /* cudamat.cu:331 */
+int get_vector_slice(cudamat* source, cudamat* target, unsigned int first_ind, unsigned int last_ind); /* cudamat.cu:355 */
+void init_from_array(cudamat* mat, float* data, int m, int n);  /* cudamat.cu:397 */
+void set_on_device(cudamat* mat);                               /* cudamat.cu:421 */
+int init_empty(cudamat* mat, int m, int n);                     /* cudamat.cu:425 (zero-filled, as eigenmat/eigenmat.py:1339) */
+
+/* ---- sampling: cudamat/cudamat.cu:437-590, eigenmat/eigenmat.cc:177-256 ------------- */
+int fill_with_rand(rnd_struct* rnd_state, cudamat* mat);                           /* cudamat.cu:437 */
+int fill_with_randn(rnd_struct* rnd_state, cudamat* mat);                          /* cudamat.cu:453 */
+int sample_bernoulli(rnd_struct* rnd_state, cudamat* mat, cudamat* target);        /* cudamat.cu:469 */
+int sample_bernoulli_tanh(rnd_struct* rnd_state, cudamat* mat, cudamat* target);   /* cudamat.cu:486 */
+int sample_gaussian(rnd_struct* rnd_state, cudamat* mat, cudamat* target, float mult); /* cudamat.cu:520 */
+int perturb_energy(rnd_struct* rnd_state, cudamat* mat, cudamat* target);          /* cudamat.cu:538 */
+int perturb_prob(rnd_struct* rnd_state, cudamat* mat, cudamat* target);            /* cudamat.cu:556 */
+int dropout(rnd_struct* rnd_state, cudamat* mat, float dropprob, float val);       /* cudamat.cu:574 */
+
+/* ---- broadcasts: cudamat/cudamat.cu:592-876 ------------------------------------------ */
+int add_col_vec(cudamat* mat, cudamat* vec, cudamat* target);                 /* cudamat.cu:592 */
+int add_col_mult(cudamat* mat, cudamat* vec, cudamat* target, float mult);    /* cudamat.cu:617 */
+int add_row_mult(cudamat* mat, cudamat* vec, cudamat* target, float mult);    /* cudamat.cu:735 */
+int add_row_vec(cudamat* mat, cudamat* vec, cudamat* target);                 /* cudamat.cu:759 */
+int mult_by_col_vec(cudamat* mat, cudamat* vec, cudamat* target);             /* cudamat.cu:783 */
+int mult_by_row_vec(cudamat* mat, cudamat* vec, cudamat* target);             /* cudamat.cu:807 */
+int div_by_col_vec(cudamat* mat, cudamat* vec, cudamat* target);              /* cudamat.cu:831 */
+int div_by_row_vec(cudamat* mat, cudamat* vec, cudamat* target);              /* cudamat.cu:855 */
+
+/* ---- comparisons and clamps: cudamat/cudamat.cu:878-1146 ----------------------------- */
+int less_than_eq(cudamat* mat1, cudamat* mat2, cudamat* target);              /* cudamat.cu:878 */
+int less_than(cudamat* mat1, cudamat* mat2, cudamat* target);                 /* cudamat.cu:901 */
+int less_than_eq_scalar(cudamat* mat, float val, cudamat* target);            /* cudamat.cu:923 */
+int less_than_scalar(cudamat* mat, float val, cudamat* target);               /* cudamat.cu:946 */
+int greater_than_eq(cudamat* mat1, cudamat* mat2, cudamat* target);           /* cudamat.cu:968 */
+int greater_than(cudamat* mat1, cudamat* mat2, cudamat* target);              /* cudamat.cu:991 */
+int upper_bound(cudamat* mat1, cudamat* mat2, cudamat* target);               /* cudamat.cu:1014 */
+int lower_bound(cudamat* mat1, cudamat* mat2, cudamat* target);               /* cudamat.cu:1038 */
+int greater_than_eq_scalar(cudamat* mat, float val, cudamat* target);         /* cudamat.cu:1060 */
+int greater_than_scalar(cudamat* mat, float val, cudamat* target);            /* cudamat.cu:1082 */
+int upper_bound_scalar(cudamat* mat, float val, cudamat* target);             /* cudamat.cu:1103 */
+int lower_bound_scalar(cudamat* mat, float val, cudamat* target);             /* cudamat.cu:1126 */
+
+/* ---- reductions: cudamat/cudamat.cu:1148-1258, 1733, 2104, 2192; eigenmat.cc:733-759 -- */
+int max_by_axis(cudamat* mat, cudamat* target, int axis);                     /* cudamat.cu:1148 */
+int choose_max_and_accumulate(cudamat* mat, cudamat* acc);                    /* cudamat.cu:1178 */
+int choose_max_by_axis(cudamat* mat, cudamat* target, int axis);              /* cudamat.cu:1203, meaning of eigenmat.cc:661 */
+int argmax_by_axis(cudamat* mat, cudamat* target, int axis);                  /* cudamat.cu:1232 */
+int sum_by_axis(cudamat* mat, cudamat* target, int axis);                     /* eigenmat/eigenmat.cc:746; cudamat/cudamat.py:1546 */
+int add_sum_by_axis(cudamat* mat, cudamat* target, int axis, float mult);     /* eigenmat/eigenmat.cc:733; cudamat/cudamat.py:724 */
+float vdot(cudamat* mat1, cudamat* mat2, int* err_code);                      /* cudamat.cu:1733 */
+float euclid_norm(cudamat* mat, int* err_code);                               /* cudamat.cu:2104 */
+float sum_all(cudamat* mat, int* err_code);                                   /* cudamat/cudamat.py:719-721 (vdot with ones) */
+int softmax(cudamat* mat, cudamat* target);                                   /* cudamat.cu:2192 */
+int softmax_overwrite(cudamat* mat);                                          /* cudamat.cu:2220 */
+int apply_softmax(cudamat* mat, cudamat* target);                             /* eigenmat/eigenmat.cc:808 */
+
+/* ---- elementwise: cudamat/cudamat.cu:1318-1670, 1763-2102 ---------------------------- */
+int sign(cudamat* mat, cudamat* target);                                      /* cudamat.cu:1318 */
+int apply_sigmoid(cudamat* mat, cudamat* target);                             /* cudamat.cu:1376 */
+int apply_tanh(cudamat* mat, cudamat* target);                                /* cudamat.cu:1395 */
+int apply_abs(cudamat* mat, cudamat* target);                                 /* cudamat.cu:1414 */
+int apply_log_1_plus_exp(cudamat* mat, cudamat* target);                      /* cudamat.cu:1433 */
+int apply_log(cudamat* mat, cudamat* target, float tiny);                     /* cudamat.cu:1452 */
+int apply_exp(cudamat* mat, cudamat* target);                                 /* cudamat.cu:1471 */
+int apply_sqrt(cudamat* mat, cudamat* target);                                /* cudamat.cu:1528 */
+int apply_pow(cudamat* mat, float pow, cudamat* target);                      /* cudamat.cu:1547 */
+int compute_cross_entropy_bernoulli(cudamat* mat, cudamat* p, cudamat* target, float tiny); /* cudamat.cu:1609 */
+int correct_preds(cudamat* mat, cudamat* p, cudamat* target, float cutoff);   /* cudamat.cu:1630 */
+int reciprocal(cudamat* mat, cudamat* target);                                /* cudamat.cu:1652 */
+int add_mult(cudamat* mat1, cudamat* mat2, float alpha);                      /* cudamat.cu:1763 */
+int add_mult_sign(cudamat* mat1, cudamat* mat2, float mult);                  /* cudamat.cu:1782 */
+int add_elementwise(cudamat* mat1, cudamat* mat2, cudamat* target);           /* cudamat.cu:1803 */
+int subtract_elementwise(cudamat* mat1, cudamat* mat2, cudamat* target);      /* cudamat.cu:1826 */
+int divide_elementwise(cudamat* mat1, cudamat* mat2, cudamat* target);        /* cudamat.cu:1849 */
+int mult_elementwise(cudamat* mat1, cudamat* mat2, cudamat* target);          /* cudamat.cu:1873 */
+int apply_logistic_deriv(cudamat* mat1, cudamat* mat2, cudamat* target);      /* cudamat.cu:1940 */
+int assign_scalar(cudamat* mat, float alpha);                                 /* cudamat.cu:2031 */
+int mult_by_scalar(cudamat* mat, float alpha, cudamat* target);               /* cudamat.cu:2047 */
+int divide_by_scalar(cudamat* mat, float alpha, cudamat* target);             /* cudamat.cu:2066 */
+int add_scalar(cudamat* mat, float alpha, cudamat* target);                   /* cudamat.cu:2085 */
+
+/* ---- matrix product: cudamat/cudamat.cu:1671-1696 (cublasSgemm) ---------------------- */
+/* target = beta * target + alpha * op(mat1) . op(mat2); tcgen05 split-TF32 when the
+ * operands are TMA-addressable (leading dimension a multiple of 4, 16-byte aligned). */
+int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha);
+
+/* ================= additions: no counterpart in the reference ======================== */
+
+/* One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans). */
+typedef struct b200_pass {
+  cudamat* a;
+  cudamat* b;
+  int negate;
+} b200_pass;
+
+/* out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale).
+ * Replaces dot / add_dot / mult / add_col_vec (or add_dot(b, NN)) / apply_sigmoid /
+ * sample_bernoulli of deepnet/dbm.py:88-105 and logistic_layer.py:11-15, and the
+ * dot + add_dot(mult=-1) pair of deepnet/edge.py:236,242, by one kernel. */
+typedef struct b200_fused_gemm {
+  int npass;             /* 1..8 */
+  b200_pass pass[8];
+  float alpha, beta;
+  cudamat* bias;         /* M x 1 or NULL */
+  cudamat* col_scale;    /* 1 x N or NULL: bias of column n is bias[m] * col_scale[n] */
+  int activation;        /* 0 identity, 1 logistic */
+  cudamat* out;          /* M x N or NULL */
+  cudamat* out_hi;       /* result with the low 13 mantissa bits cleared, or NULL */
+  cudamat* out_lo;       /* result - out_hi, or NULL */
+  cudamat* sample;       /* Bernoulli(result): consumes one sampling call, or NULL */
+} b200_fused_gemm;
+int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f);
+
+/* lo = x - tf32(x); hi (may be NULL) = tf32(x). */
+int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
+
+/* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass over the parameter:
+ * grad += -inv_batch * suff; delta = momentum*delta + l2*w + l1*sign(w) + grad;
+ * w -= eps*delta; grad = 0.  grad, w_hi, w_lo may be NULL. */
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_hi, cudamat* w_lo,
+                    float inv_batch, float momentum, float eps, float l2, float l1);
+
+/* acc[0] += sum((a - b)^2), kept on the device (subtract + euclid_norm()**2 of
+ * deepnet/logistic_layer.py:48-52 without the host round trip). */
+int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc);
+
+/* Library control. */
+int b200_device_count(void);
+int b200_set_stream(void* cuda_stream);   /* NULL restores the library's own stream */
+void* b200_get_stream(void);
+void* b200_event_create(void);            /* CUDA events recorded on the library stream */
+int b200_event_record(void* ev);
+float b200_event_elapsed_ms(void* start, void* end);  /* blocks until `end`; < 0 on error */
+void b200_event_destroy(void* ev);
+int b200_read_status(void);               /* non-zero: a kernel's bounded wait gave up (blocks, clears) */
+int b200_set_gemm_path(int path);         /* 0 auto, 1 tensor cores only, 2 CUDA cores only */
+int b200_set_dot_precision(int mode);     /* 0 fp32-grade split TF32 (default), 1 one TF32 pass */
+int set_rng_column_offset(int col0);      /* first global minibatch column of this process */
+void* b200_host_alloc(size_t bytes);      /* pinned host memory */
+void b200_host_free(void* p);
+int copy_from_host_ptr(cudamat* mat, const float* src, size_t bytes);  /* async H2D into mat */
+int b200_prefetch(cudamat* mat, const float* src, size_t bytes);       /* H2D on a second (copy) stream */
+int b200_prefetch_wait(void);             /* library stream waits for the copies started so far */
+int b200_prefetch_fence(void);            /* later copies wait for work already enqueued */
+
+/* Data parallelism over NCCL: one process per GPU. */
+int dp_unique_id(char* out128);
+int dp_init(const char* id128, int nranks, int rank);
+int dp_world_size(void);
+int dp_rank(void);
+int dp_allreduce(cudamat* mat);           /* in-place sum over ranks, on the library stream */
+int dp_check(void);
+int dp_destroy(void);
+int dp_abort(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MAT_H_ */

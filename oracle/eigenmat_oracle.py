@@ -17,6 +17,9 @@ import ctypes as ct
 import os
 import subprocess
 
+# libgomp's idle threads would otherwise spin and starve the BLAS threads between loops
+os.environ.setdefault("OMP_WAIT_POLICY", "passive")
+
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -346,11 +349,19 @@ def _dot_into(m1, m2, target, beta, alpha):
     if a.shape[0] * a.shape[1] * b.shape[1] <= _C_DOT_LIMIT:
         _check(_lib.dot(m1.p_mat, m2.p_mat, target.p_mat, ct.c_float(beta), ct.c_float(alpha)))
         return
-    prod = np.float32(alpha) * (a @ b)
+    # target is Fortran-ordered: form (a b)' = b' a' straight into its C-ordered transpose view
+    tt = target.numpy_array.T
     if beta == 0:
-        target.numpy_array[...] = prod
+        np.matmul(b.T, a.T, out=tt)
+        if alpha != 1:
+            tt *= np.float32(alpha)
     else:
-        target.numpy_array[...] = np.float32(beta) * target.numpy_array + prod
+        prod = np.matmul(b.T, a.T)
+        if alpha != 1:
+            prod *= np.float32(alpha)
+        if beta != 1:
+            tt *= np.float32(beta)
+        tt += prod
 
 
 def dot(m1, m2, mult=1.0, target=None):

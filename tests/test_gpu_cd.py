@@ -1,0 +1,155 @@
+"""GPU parity of the whole contrastive-divergence step: the per-call driver and the
+fused engine on b200mat against the oracle-generated golden traces and against the
+oracle run side by side; then size-independent properties at the full 8192 x 8192,
+batch 4096 configuration.
+
+Bounds: mean-field activations and gradients within 1e-5 relative (to the largest
+magnitude), reconstruction-error curves within 2 %."""
+import os
+
+import numpy as np
+import pytest
+
+from deepnet_b200 import configs, dbm
+from deepnet_b200.fused_rbm import FusedRBM
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = 1e-5
+
+
+def get(m):
+    return np.array(m.asarray(), copy=True)
+
+
+def relerr(got, want):
+    return np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+
+
+def run_driver(backend, cfg, cases, steps):
+    B = cfg["batchsize"]
+    m = dbm.DBM(backend, cfg["layers"], cfg["edges"], cfg["hyperparams"], B, cfg["optimizer"], seed=cfg["seed"])
+    data = backend.CUDAMatrix(cfg["data"])
+    losses = []
+    for step in range(steps):
+        s = (step % (cases // B)) * B
+        m.SetBatch([data.slice(s, s + B)])
+        losses.append(m.TrainOneBatch(step)[0])
+    return m, losses
+
+
+@pytest.mark.parametrize("name,config,scale,cases,steps", [
+    ("cd1_c0.npz", 0, 0.25, 300, 3), ("cd1_c1.npz", 1, 0.0625, 768, 3), ("pcd_c3.npz", 3, 0.1, 200, 2)])
+def test_per_call_driver_matches_golden_trace(cm, name, config, scale, cases, steps):
+    g = np.load(os.path.join(GOLDEN, name))
+    cfg = configs.build(config, cases=cases, dims_scale=scale)
+    m, losses = run_driver(cm, cfg, cases, steps)
+    np.testing.assert_allclose(losses, g["losses"], rtol=1e-5)
+    for i, e in enumerate(m.edge):
+        assert relerr(get(e.params["weight"]), g["W%d" % i]) < TOL
+        assert relerr(get(e.gradient_history), g["dW%d" % i]) < 2 * TOL
+    for l in m.layer:
+        assert relerr(get(l.state), g["state_" + l.name]) < TOL, l.name
+        assert np.abs(get(l.params["bias"]) - g["b_" + l.name]).max() < 1e-6
+    assert cm.read_status() == 0
+
+
+def test_replicated_softmax_step_matches_oracle(cm, oracle):
+    # config 2 at 1/50 size: multinomial sampling of the visible layer (sample_input on)
+    cfg = configs.build(2, cases=200, dims_scale=0.02)
+    mg, lg = run_driver(cm, cfg, 200, 2)
+    mo, lo = run_driver(oracle, cfg, 200, 2)
+    np.testing.assert_allclose(lg, lo, rtol=1e-4)
+    vg, vo = mg.GetLayerByName("v"), mo.GetLayerByName("v")
+    np.testing.assert_array_equal(get(vg.sample), get(vo.sample))        # word counts: integers
+    assert get(vg.sample).sum(axis=0) == pytest.approx(get(vg.NN).ravel(), abs=1e-3)
+    assert relerr(get(mg.edge[0].params["weight"]), get(mo.edge[0].params["weight"])) < TOL
+
+
+@pytest.mark.parametrize("config,scale,cases", [(0, 0.25, 300), (1, 0.0625, 768), (0, 1.0, 200)])
+def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases):
+    cfg = configs.build(config, cases=cases, dims_scale=scale)
+    B, steps = cfg["batchsize"], 3
+    mo, lo = run_driver(oracle, cfg, cases, steps)
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), visible=cfg["layers"][0]["activation"],
+                   binary_data=(config != 1), seed=cfg["seed"])
+    data = cm.CUDAMatrix(cfg["data"])
+    lg = []
+    for step in range(steps):
+        s = (step % (cases // B)) * B
+        eng.TrainOneBatch(step, data.slice(s, s + B))
+        lg.append(eng.read_loss())
+    np.testing.assert_allclose(lg, lo, rtol=1e-5)
+    assert relerr(get(eng.W), get(mo.edge[0].params["weight"])) < TOL
+    assert relerr(get(eng.dW), get(mo.edge[0].gradient_history)) < 2 * TOL
+    assert relerr(get(eng.h_neg), get(mo.GetLayerByName("h").state)) < TOL       # mean-field activations
+    assert relerr(get(eng.v_neg), get(mo.GetLayerByName("v").state)) < TOL
+    np.testing.assert_array_equal(get(eng.h_samp), get(mo.GetLayerByName("h").sample))  # Bernoulli bits
+    assert np.abs(get(eng.bh) - get(mo.GetLayerByName("h").params["bias"])).max() < 1e-6
+    np.testing.assert_array_equal(get(eng.W) , get(eng.W_lo) + (get(eng.W).view(np.uint32) & np.uint32(0xffffe000)).view(np.float32))
+    assert cm.read_status() == 0
+
+
+def test_reconstruction_error_curve_within_two_percent(cm, oracle):
+    cases, steps = 1000, 60
+    cfg = configs.build(0, cases=cases, dims_scale=0.25)
+    B = cfg["batchsize"]
+    _, lo = run_driver(oracle, cfg, cases, steps)
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+    data = cm.CUDAMatrix(cfg["data"])
+    lg = []
+    for step in range(steps):
+        s = (step % (cases // B)) * B
+        eng.TrainOneBatch(step, data.slice(s, s + B))
+        lg.append(eng.read_loss())
+    lo, lg = np.array(lo), np.array(lg)
+    assert np.abs(lg - lo).max() / lo.max() < 0.02
+    assert np.abs(lg / lo - 1).max() < 0.02
+    assert lg[-1] < 0.6 * lg[0]
+
+
+def test_full_size_properties(cm):
+    """Config 4 shapes (V = H = 8192, batch 4096): checks that do not need a CPU run of the step."""
+    V = H = 8192
+    B = 4096
+    rng = np.random.default_rng(44)
+    W = (rng.standard_normal((V, H)) * 0.01).astype(np.float32)
+    p = rng.beta(0.3, 2.0, size=(V, 1)).astype(np.float32)
+    x = (rng.random((V, B), dtype=np.float32) < p).astype(np.float32)
+    hyp = dbm.Hyperparams(base_epsilon=0.05, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=1)
+    eng = FusedRBM(cm, V, H, B, W, hyp, seed=3004)
+    data = cm.CUDAMatrix(x)
+    eng.TrainOneBatch(0, data)
+    h_pos, h_samp, v_neg = get(eng.h_pos), get(eng.h_samp), get(eng.v_neg)
+    # (1) sampled entries of the positive hidden activations against float64 dot products
+    idx = rng.integers(0, H, 200), rng.integers(0, B, 200)
+    pre = np.einsum("ki,ki->i", W[:, idx[0]].astype(np.float64), x[:, idx[1]].astype(np.float64))
+    want = 1 / (1 + np.exp(-pre))
+    assert np.abs(h_pos[idx] - want).max() < TOL
+    # (2) Bernoulli draws are 0/1 and their mean tracks the mean probability (checksum of the draw)
+    assert set(np.unique(h_samp)) <= {0.0, 1.0}
+    # h_samp holds the draw of the negative-phase hidden state after the Gibbs step
+    h_neg = get(eng.h_neg)
+    assert abs(h_samp.mean() - h_neg.mean()) < 5 * 0.5 / np.sqrt(h_samp.size)
+    # (3) statistics: row sums and the packed gradient against float64 on sampled entries
+    sb = get(eng.suff_bh).ravel()
+    np.testing.assert_allclose(sb, h_pos.astype(np.float64).sum(axis=1) - h_neg.astype(np.float64).sum(axis=1),
+                               rtol=1e-5, atol=2e-3)
+    ii, jj = rng.integers(0, V, 64), rng.integers(0, H, 64)
+    want_s = (x[ii].astype(np.float64) * h_pos[jj]).sum(axis=1) - (v_neg[ii].astype(np.float64) * h_neg[jj]).sum(axis=1)
+    got_s = get(eng.suff_W)[ii, jj]
+    assert np.abs(got_s - want_s).max() < TOL * max(np.abs(want_s).max(), 1.0) * 10
+    # (4) the update applied what the statistics say: W1 = W0 - eps * (-(suff)/B) with zero history
+    W1 = get(eng.W)
+    want_w = W[ii, jj] - np.float32(0.05) * (-(got_s) / B)
+    assert np.abs(W1[ii, jj] - want_w).max() < 1e-6
+    # (5) a zero learning rate leaves the parameters untouched (idempotence of the update path)
+    eng.hyp.base_epsilon = 0.0
+    eng.ehyp.base_epsilon = 0.0
+    eng.TrainOneBatch(1, data)
+    np.testing.assert_array_equal(get(eng.W), W1)
+    assert cm.read_status() == 0

@@ -1,0 +1,176 @@
+"""GPU parity of the matrix product: the tcgen05 split-TF32 kernel and the CUDA-core
+kernel against float64 numpy and the oracle, all four transpose layouts, ragged edges,
+and the fused epilogue (bias, logistic, Bernoulli draw, TF32 split, negated passes).
+
+Tolerance: 1e-5 of the largest magnitude of the exact result (the bound the path must
+meet on activations and gradients); the single-pass TF32 mode is checked at 2e-3."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+def get(m):
+    return np.array(m.asarray(), copy=True)
+
+
+def relerr(got, want):
+    return np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+
+
+@pytest.fixture(autouse=True)
+def _auto_path(cm):
+    yield
+    cm.set_gemm_path(0)
+    cm.set_dot_precision(0)
+
+
+def make(cm, x, trans):
+    """A handle whose op() equals x: stored transposed when trans."""
+    if trans:
+        return cm.CUDAMatrix(np.ascontiguousarray(x.T)).T
+    return cm.CUDAMatrix(x)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 32), (500, 1000, 600), (128, 256, 64), (4, 4, 4), (132, 68, 36),
+                                   (784, 100, 500), (1024, 256, 4096)])
+def test_dot_all_layouts(cm, path, ta, tb, m, n, k):
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    cm.set_gemm_path(path)
+    out = cm.empty((m, n))
+    cm.dot(make(cm, A, ta), make(cm, B, tb), target=out)
+    want = A.astype(np.float64) @ B.astype(np.float64)
+    assert relerr(get(out), want) < TOL
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(7, 5, 3), (127, 33, 65), (1, 1, 1), (1, 257, 19)])
+def test_dot_untileable_shapes_use_cuda_cores(cm, m, n, k):
+    # leading dimensions that TMA cannot address: auto falls back, tensor-core-only refuses
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    out = cm.dot(cm.CUDAMatrix(A), cm.CUDAMatrix(B))
+    assert relerr(get(out), A.astype(np.float64) @ B) < TOL
+    if m % 4 or k % 4:
+        cm.set_gemm_path(1)
+        with pytest.raises(cm.CUDAMatException):
+            cm.dot(cm.CUDAMatrix(A), cm.CUDAMatrix(B))
+
+
+def test_add_dot_subtract_dot_and_scaling(cm):
+    # cudamat/test_cudamat.py:829-880
+    rng = np.random.default_rng(6)
+    A = rng.standard_normal((128, 64)).astype(np.float32)
+    B = rng.standard_normal((64, 256)).astype(np.float32)
+    C = rng.standard_normal((128, 256)).astype(np.float32)
+    for path in (1, 2):
+        cm.set_gemm_path(path)
+        c = cm.CUDAMatrix(C)
+        c.add_dot(cm.CUDAMatrix(A), cm.CUDAMatrix(B), mult=0.5)
+        want = C + 0.5 * (A.astype(np.float64) @ B)
+        assert relerr(get(c), want) < TOL
+        c.subtract_dot(cm.CUDAMatrix(A), cm.CUDAMatrix(B))
+        assert relerr(get(c), want - A.astype(np.float64) @ B) < TOL
+
+
+def test_single_pass_tf32_mode_truncates_operands(cm):
+    rng = np.random.default_rng(7)
+    A = rng.standard_normal((256, 512)).astype(np.float32)
+    B = rng.standard_normal((512, 128)).astype(np.float32)
+    cm.set_gemm_path(1)
+    cm.set_dot_precision(1)
+    out = get(cm.dot(cm.CUDAMatrix(A), cm.CUDAMatrix(B)))
+    tr = lambda x: (x.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32).astype(np.float64)
+    assert relerr(out, tr(A) @ tr(B)) < TOL          # the tensor core drops the low 13 mantissa bits
+    assert relerr(out, A.astype(np.float64) @ B) < 2e-3
+
+
+def test_split_tf32_is_exact(cm):
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((100, 33)) * 10.0 ** rng.integers(-3, 4, (100, 33))).astype(np.float32)
+    g = cm.CUDAMatrix(x)
+    hi, lo = cm.empty(x.shape), cm.empty(x.shape)
+    g.split_tf32(lo, hi=hi)
+    h, l = get(hi), get(lo)
+    np.testing.assert_array_equal(h, (x.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32))
+    np.testing.assert_array_equal(h + l, x)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(500, 100, 784), (128, 256, 64), (260, 36, 40)])
+def test_fused_epilogue_bias_logistic_sample_split(cm, oracle, path, m, n, k):
+    rng = np.random.default_rng(9)
+    W = (rng.standard_normal((k, m)) * 0.1).astype(np.float32)
+    X = (rng.random((k, n)) < 0.3).astype(np.float32)
+    b = rng.standard_normal((m, 1)).astype(np.float32)
+    cm.set_gemm_path(path)
+    seed = 99
+    cm.CUDAMatrix.init_random(seed)
+    oracle.EigenMatrix.init_random(seed)
+    w, x, bias = cm.CUDAMatrix(W), cm.CUDAMatrix(X), cm.CUDAMatrix(b)
+    w_lo = cm.empty(W.shape)
+    w.split_tf32(w_lo)
+    out, out_hi, out_lo, smp = (cm.empty((m, n)) for _ in range(4))
+    cm.fused_gemm([(w_lo.T, x), (w.T, x)], out=out, out_hi=out_hi, out_lo=out_lo, sample=smp, bias=bias,
+                  activation=1, alpha=1.0)
+    pre = W.astype(np.float64).T @ X + b
+    want = 1 / (1 + np.exp(-pre))
+    got = get(out)
+    assert relerr(got, want) < TOL
+    np.testing.assert_array_equal(get(out_hi) + get(out_lo), got)
+    np.testing.assert_array_equal(get(out_hi), (got.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32))
+    # the draw thresholds the probabilities the kernel itself produced against the shared
+    # uniforms of call 0: bit-exact with the oracle fed the same probabilities
+    want_s = get(oracle.EigenMatrix(got).sample_bernoulli(target=oracle.empty((m, n))))
+    np.testing.assert_array_equal(get(smp), want_s)
+    assert cm.CUDAMatrix.rnd_state.calls == 1
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_fused_negated_passes_with_unequal_depths_and_col_scale(cm, path):
+    rng = np.random.default_rng(10)
+    m, n = 132, 72
+    A1 = rng.standard_normal((m, 48)).astype(np.float32)
+    B1 = rng.standard_normal((48, n)).astype(np.float32)
+    A2 = rng.standard_normal((m, 100)).astype(np.float32)
+    B2 = rng.standard_normal((100, n)).astype(np.float32)
+    b = rng.standard_normal((m, 1)).astype(np.float32)
+    cs = rng.random((1, n)).astype(np.float32) * 50
+    old = rng.standard_normal((m, n)).astype(np.float32)
+    cm.set_gemm_path(path)
+    cm.set_dot_precision(1)
+    out = cm.CUDAMatrix(old)
+    cm.fused_gemm([(cm.CUDAMatrix(A1), cm.CUDAMatrix(B1)), (cm.CUDAMatrix(A2), cm.CUDAMatrix(B2), 1)], out=out,
+                  bias=cm.CUDAMatrix(b), col_scale=cm.CUDAMatrix(cs), alpha=0.5, beta=2.0)
+    # a pass multiplies its operands as TF32 on either path
+    tr = lambda x: (x.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32).astype(np.float64)
+    want = 0.5 * (tr(A1) @ tr(B1) - tr(A2) @ tr(B2)) + 2.0 * old + b * cs
+    assert relerr(get(out), want) < TOL
+
+
+@pytest.mark.parametrize("shape", [(33, 17), (784, 500), (8192, 1), (1, 4)])
+@pytest.mark.parametrize("with_grad", [True, False])
+def test_momentum_update_is_bit_exact(cm, oracle, shape, with_grad):
+    rng = np.random.default_rng(11)
+    w0, d0, s0 = (rng.standard_normal(shape).astype(np.float32) for _ in range(3))
+    g0 = rng.standard_normal(shape).astype(np.float32) if with_grad else np.zeros(shape, np.float32)
+    args = (1.0 / 100, 0.7, 0.1)
+    wo, do, go = oracle.EigenMatrix(w0), oracle.EigenMatrix(d0), oracle.EigenMatrix(g0)
+    wo.momentum_update(do, go, oracle.EigenMatrix(s0), *args, l2=2e-4, l1=1e-3)
+    wg, dg = cm.CUDAMatrix(w0), cm.CUDAMatrix(d0)
+    gg = cm.CUDAMatrix(g0) if with_grad else None
+    hi, lo = cm.empty(shape), cm.empty(shape)
+    wg.momentum_update(dg, gg, cm.CUDAMatrix(s0), *args, l2=2e-4, l1=1e-3, w_hi=hi, w_lo=lo)
+    np.testing.assert_array_equal(get(wg), get(wo))
+    np.testing.assert_array_equal(get(dg), get(do))
+    if with_grad:
+        assert not get(gg).any()
+    np.testing.assert_array_equal(get(hi) + get(lo), get(wg))
