@@ -199,20 +199,29 @@ def run_ours(args):
     peaks = measured_peaks()
     gemm_ms = sum(v[1] for n, v in agg.items() if n.startswith("gemm"))
     gemm_flops = sum(v[2] for n, v in agg.items() if n.startswith("gemm"))
-    gemm_launches = sum(v[0] for n, v in agg.items() if n.startswith("gemm"))
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     passes = {"gemm_up": 3, "gemm_down": 2, "gemm_stats": 2.5}   # TF32 passes per algorithmic product
     hw_flops = sum(v[2] * passes.get(n, 1) for n, v in agg.items() if n.startswith("gemm"))
-    kernels = {n: dict(launches=v[0], ms_per_launch=v[1] / v[0],
-                       tflops=(v[2] / (v[1] * 1e-3) / 1e12) if v[2] else None,
-                       gbs=(v[3] / (v[1] * 1e-3) / 1e9) if v[3] else None) for n, v in agg.items()}
+    kernels = {n: dict(launches=v[0], ms_per_launch=round(v[1] / v[0], 5),
+                       tflops=round(v[2] / (v[1] * 1e-3) / 1e12, 2) if v[2] else None,
+                       gbs=round(v[3] / (v[1] * 1e-3) / 1e9, 1) if v[3] else None) for n, v in agg.items()}
+    # dominant kernel: the up half-step product (k_gemm_tc, sigmoid + Bernoulli epilogue),
+    # the largest share of the step.  achieved = algorithmic flops of one launch (2 V H B)
+    # / its mean CUDA-event duration inside the timed region.
+    up = agg["gemm_up"]
+    achieved = up[2] / (up[1] * 1e-3) / 1e12
     roofline = dict(bound="tensor", achieved=round(achieved, 2), peak=peaks["tensor"], unit="TFLOP/s",
-                    frac=round(achieved / peaks["tensor"], 4), traffic=None,
-                    kernel="k_gemm_tc (tcgen05 kind::tf32, split-TF32 passes)",
-                    peak_source="%s bf16 sustained; TF32 runs at half the bf16 rate" % peaks["source"],
-                    tf32_pass_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2) if gemm_ms > 0 else None,
-                    launches=gemm_launches, ms_per_launch=round(gemm_ms / max(gemm_launches, 1), 4),
-                    share_of_step=round(gemm_ms / ms, 4) if world == 1 else None)
+                    frac=round(achieved / peaks["tensor"], 4),
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
+                    # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
+                    traffic=4.13e9 if config == 4 else None,
+                    kernel="k_gemm_tc<256, sigmoid+split+Bernoulli> (tcgen05 kind::tf32, 3 split-TF32 passes)",
+                    peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
+                                "and 3 passes make one fp32-grade product" % peaks["source"],
+                    launches=up[0], ms_per_launch=round(up[1] / up[0], 4),
+                    share_of_step=round(up[1] / ms, 4) if world == 1 else None,
+                    all_gemm_algorithmic_tflops=round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 2),
+                    all_gemm_tf32_issued_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2),
+                    all_gemm_share_of_step=round(gemm_ms / ms, 4) if world == 1 else None)
 
     # ---- end to end: host batches in, loss out, every step --------------------------------
     host = []
