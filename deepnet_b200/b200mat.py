@@ -325,6 +325,14 @@ class CUDAMatrix(object):
         _check(_lib.add_sum_by_axis(mat.p_mat, self.p_mat, ct.c_int(axis), ct.c_float(mult)))
         return self
 
+    def add_sums_noalloc(self, mat, axis, mult=1.0):
+        """add_sums for hosts that may not allocate device memory (their own pool owns the GPU, or
+        they cannot afford an allocation's device-wide synchronisation): same result, but the
+        partial sums go to a fixed 128 KiB array inside the library.  Raises for matrices whose
+        partial sums do not fit; calls must not overlap on the GPU."""
+        _check(_lib.add_sum_by_axis_noalloc(mat.p_mat, self.p_mat, ct.c_int(axis), ct.c_float(mult)))
+        return self
+
     def max(self, axis, target=None):
         m, n = self.shape
         if target is None:

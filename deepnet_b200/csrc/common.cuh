@@ -40,6 +40,7 @@ struct rnd_struct {
 namespace b200 {
 
 cudaStream_t stream();                 // the stream every operation of the library runs on
+cudaStream_t stream_if_initialised();  // the same, or the default stream when the library was never initialised
 int sm_count();                        // SMs of the current device
 int check_launch();                    // cudaGetLastError -> 0 or CUDA_ERROR (message kept)
 int set_error(const char* msg);        // records msg, returns CUDA_ERROR

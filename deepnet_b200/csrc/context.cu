@@ -40,6 +40,7 @@ cudaStream_t stream() {
   ensure_init();
   return g_stream;
 }
+cudaStream_t stream_if_initialised() { return g_stream; }
 int sm_count() {
   ensure_init();
   return g_sm_count > 0 ? g_sm_count : 148;

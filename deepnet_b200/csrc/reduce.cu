@@ -422,3 +422,84 @@ float sum_all(cudamat* mat, int* err_code) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Row sums without any allocation.
+//
+// Some hosts of this library must never reach cudaMalloc: a process that has handed the
+// whole device to its own memory pool (a later cudaMalloc fails or eats into the pool's
+// headroom), or a control loop that cannot tolerate the device-wide synchronisation an
+// allocation may imply.  add_sum_by_axis above takes its scratch (the per-split partial row
+// sums) from the library's grow-only workspace, which allocates on first use and whenever a
+// larger matrix arrives.  The variant below keeps that scratch in a fixed array that is part
+// of the loaded module instead: kNoAllocScratchFloats floats (128 KiB), resident on every GPU
+// that loads the library until the process exits.
+//
+// Rules for callers:
+//  * The first call on a device looks the array's device address up (once per device, with
+//    that device current).  Make that first call during start-up, before any stream capture.
+//  * The partial sums need splits x rows floats (splits is chosen from the SM count, at
+//    most ceil(4 * SMs / ceil(rows / 32))).  A matrix that needs more than the array holds is
+//    refused with ERROR_UNSUPPORTED and a message; nothing is launched.
+//  * All calls share the one array and it keeps whatever the last call left in it.  Nothing
+//    in it has to start at zero: every slot a call reads is written earlier in that same
+//    call.  Two calls that overlap on the GPU (different streams or processes sharing the
+//    module) race on it; issue them in order on one stream.
+//  * Launches go to the library stream if the library was initialised, else to the default
+//    stream; the call itself never creates streams or memory.
+constexpr int kNoAllocScratchFloats = 32768;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address per device ordinal
+static int g_noalloc_sms[kMaxDevices] = {0};
+
+extern "C" int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult) {
+  if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (axis != 0 && axis != 1) return ERROR_UNSUPPORTED;
+  if (mat->is_trans) axis = 1 - axis;
+  const int h = mat->size[0], w = mat->size[1];
+  if (numel(target) != (axis == 0 ? w : h)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if ((long)h * w == 0) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return set_error("cudaGetDevice failed");
+  if (!g_noalloc_ptr[dev]) {
+    // In host code the array's name is only a handle; the kernels need its device address.
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
+      cudaGetLastError();
+      return set_error("cudaGetSymbolAddress(g_noalloc_scratch) failed");
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return set_error("cudaDeviceGetAttribute(multiprocessor count) failed");
+    g_noalloc_sms[dev] = sms;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  cudaStream_t st = stream_if_initialised();
+  const int sms = g_noalloc_sms[dev];
+  if (axis == 0) {  // sums down the columns need no scratch
+    const int blocks = w < sms * 8 ? w : sms * 8;
+    k_colsum<<<blocks, 256, 0, st>>>(mat->data_device, target->data_device, h, w, mult, 1.0f);
+    return check_launch();
+  }
+  const int bx = (h + 31) / 32;
+  int splits = (4 * sms + bx - 1) / bx;
+  const int max_splits = (w + 63) / 64;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  const int cps = (w + splits - 1) / splits;
+  splits = (w + cps - 1) / cps;
+  if (splits == 1) {
+    k_rowsum<<<dim3(bx, 1), 32 * kRowLanes, 0, st>>>(mat->data_device, target->data_device, h, w, cps, mult, 1.0f, true);
+    return check_launch();
+  }
+  if ((long)splits * h > kNoAllocScratchFloats) {
+    set_error("add_sum_by_axis_noalloc: the partial sums of this matrix (splits x rows floats) exceed the "
+              "32768-float static scratch; use add_sum_by_axis");
+    return ERROR_UNSUPPORTED;
+  }
+  float* part = g_noalloc_ptr[dev];
+  k_rowsum<<<dim3(bx, splits), 32 * kRowLanes, 0, st>>>(mat->data_device, part, h, w, cps, 1.0f, 0.0f, false);
+  k_rowsum_finish<<<(h + 255) / 256, 256, 0, st>>>(part, target->data_device, h, splits, mult, 1.0f);
+  return check_launch();
+}

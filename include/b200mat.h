@@ -187,6 +187,16 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_hi, cudamat* w_lo,
                     float inv_batch, float momentum, float eps, float l2, float l1);
 
+/* Has no counterpart in the reference.  add_sum_by_axis for callers that must never reach
+ * cudaMalloc (a host that gave the whole device to its own memory pool, or a loop that cannot
+ * afford the device-wide synchronisation an allocation may bring): the partial sums live in a
+ * fixed 128 KiB array inside the module (32768 floats, held on every GPU that loads the
+ * library until exit) instead of the library's allocate-on-demand workspace.  A matrix whose
+ * partial sums (splits x rows floats) do not fit is refused with ERROR_UNSUPPORTED.  The first
+ * call on a device looks the array's address up: make it before any stream capture.  Calls
+ * share the array, so calls that overlap on the GPU race; issue them in order on one stream. */
+int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult);
+
 /* acc[0] += sum((a - b)^2), kept on the device (subtract + euclid_norm()**2 of
  * deepnet/logistic_layer.py:48-52 without the host round trip). */
 int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc);
