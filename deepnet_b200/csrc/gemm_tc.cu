@@ -32,25 +32,43 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;                       // 32 floats = one 128-byte swizzle row
 constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
+constexpr int kMaxStages = 8;
+constexpr int kStageBudget = 225 * 1024;      // shared memory available to the operand ring
 
-struct TcPass {
-  int a_map, b_map;      // indices into TcParams::maps
-  int k_iters;           // ceil(k / BK)
-  uint32_t idesc;        // tcgen05 instruction descriptor of this pass
-  uint32_t a_desc_hi, b_desc_hi;  // upper 32 bits of the shared-memory descriptors
-  uint32_t a_desc_lo, b_desc_lo;  // leading byte offset field (bits 16-29 of the low word)
-  uint32_t a_adv, b_adv;          // descriptor advance per K=8 step, in 16-byte units
-  int a_mn, b_mn;        // 1: operand is MN-major (loaded as 32x32 boxes)
+// One operand tile of a k-block: where it comes from and how tcgen05 must read it.
+struct TcOperand {
+  int map;                 // index into TcParams::maps
+  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as 32-wide boxes)
+  uint32_t desc_hi;        // upper 32 bits of the shared-memory matrix descriptor
+  uint32_t desc_lo;        // leading-byte-offset field (bits 16-29 of the low word)
+  uint32_t adv;            // descriptor advance per K = 8 step, in 16-byte units
+  uint32_t smem_off;       // byte offset of the tile inside a stage
+};
+struct TcMma {
+  int a, b;                // operand slots of the group
+  uint32_t idesc;          // tcgen05 instruction descriptor (carries the negate bit)
+};
+// A group = the passes that walk the same K range together.  Each k-block stages every
+// distinct operand tile once (at most two A and two B tiles: x and its TF32 remainder)
+// and issues all the group's products from that one stage.
+struct TcGroup {
+  int k_iters;             // ceil(k / bk)
+  int nA, nB, nmma;
+  uint32_t stage_tx;       // bytes TMA delivers per k-block
+  TcOperand A[2], B[2];
+  TcMma mma[4];
 };
 
 struct TcParams {
   CUtensorMap maps[2 * kMaxPass];
-  TcPass pass[kMaxPass];
-  int npass;
+  TcGroup group[kMaxPass];
+  int ngroups;
   int M, N, tiles_m, tiles_n;
-  int chunk_iters;  // k-iterations per TMEM accumulation chunk
+  int bk;                  // floats of K per k-block: 32 or 16
+  int num_stages;          // ring depth
+  uint32_t stage_bytes;    // ring pitch
+  int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
   GemmEpilogue epi;
   int* status;
 };
@@ -155,19 +173,14 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // kChunkIters k-iterations (128 products): each chunk starts a fresh TMEM accumulator
 // (two of them ping-pong) and the epilogue warps add the finished chunk into fp32
 // registers with ordinary rounding while the next chunk is being multiplied.
-constexpr int kChunkItersDefault = 4;
 constexpr int kEpiWarps = 8;
 constexpr int kThreadsTc = 32 * (2 + kEpiWarps);
 
 template <int BN>
 struct TcConfig {
-  static constexpr int kABytes = BM * BK * 4;
-  static constexpr int kBBytes = BN * BK * 4;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kColsPerWarp = BN / 2;   // each lane quarter is shared by two epilogue warps
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStageBudget + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // Epilogue variants, chosen on the host.  The common cases are compiled without run-time
@@ -183,12 +196,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   using Cfg = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
-  // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  const uint32_t bar_base = smem_base + kStageBudget;
+  // barrier layout (8 bytes each): full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + 2 + a); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  const int num_stages = p.num_stages;
+  const uint32_t stage_bytes = p.stage_bytes;
+  const int bk = p.bk;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -197,7 +213,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < Cfg::kStages; s++) {
+    for (int s = 0; s < kMaxStages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -218,53 +234,64 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   const uint32_t tmem_base = tmem_base_slot;
 
   int total_k_iters = 0;
-  for (int q = 0; q < p.npass; q++) total_k_iters += p.pass[q].k_iters;
+  for (int q = 0; q < p.ngroups; q++) total_k_iters += p.group[q].k_iters;
   const int kChunkIters = p.chunk_iters;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int q = 0; q < p.npass && ok; q++) {
-          const TcPass& ps = p.pass[q];
-          const CUtensorMap* amap = &p.maps[ps.a_map];
-          const CUtensorMap* bmap = &p.maps[ps.b_map];
-          for (int kb = 0; kb < ps.k_iters; kb++, it++) {
-            const int s = it % Cfg::kStages;
-            const uint32_t ph = (it / Cfg::kStages) & 1u;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) {
+        for (int q = 0; q < p.ngroups && ok; q++) {
+          const TcGroup& gr = p.group[q];
+          for (int kb = 0; kb < gr.k_iters; kb++, it++) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 1);
               abort_flag = 1;
               break;
             }
-            const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
-            const uint32_t b_dst = a_dst + Cfg::kABytes;
-            mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
-            const int k0 = kb * BK;
-            if (ps.a_mn) {
+            const uint32_t base = smem_base + stage * stage_bytes;
+            mbar_expect_tx(full_bar(stage), gr.stage_tx);
+            const int k0 = kb * bk;
+            for (int i = 0; i < gr.nA; i++) {
+              const TcOperand& op = gr.A[i];
+              const uint32_t dst = base + op.smem_off;
+              if (op.mn) {
 #pragma unroll
-              for (int j = 0; j < BM / 32; j++) tma_load_2d(a_dst + j * 4096, amap, m0 + 32 * j, k0, full_bar(s));
-            } else {
-              tma_load_2d(a_dst, amap, k0, m0, full_bar(s));
+                for (int j = 0; j < BM / 32; j++)
+                  tma_load_2d(dst + j * bk * 128, &p.maps[op.map], m0 + 32 * j, k0, full_bar(stage));
+              } else {
+                tma_load_2d(dst, &p.maps[op.map], k0, m0, full_bar(stage));
+              }
             }
-            if (ps.b_mn) {
+            for (int i = 0; i < gr.nB; i++) {
+              const TcOperand& op = gr.B[i];
+              const uint32_t dst = base + op.smem_off;
+              if (op.mn) {
 #pragma unroll
-              for (int j = 0; j < BN / 32; j++) tma_load_2d(b_dst + j * 4096, bmap, n0 + 32 * j, k0, full_bar(s));
-            } else {
-              tma_load_2d(b_dst, bmap, k0, n0, full_bar(s));
+                for (int j = 0; j < BN / 32; j++)
+                  tma_load_2d(dst + j * bk * 128, &p.maps[op.map], n0 + 32 * j, k0, full_bar(stage));
+              } else {
+                tma_load_2d(dst, &p.maps[op.map], k0, n0, full_bar(stage));
+              }
+            }
+            if (++stage == num_stages) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
         }
       }
       if (!ok) {
         // let copies already issued land before the CTA leaves
-        for (int s = 0; s < Cfg::kStages; s++) {
+        for (int s = 0; s < num_stages; s++) {
           for (uint32_t i = 0; i < 4096; i++) {
             if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
             __nanosleep(100);
@@ -275,14 +302,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t it = 0, chunk = 0;
+      uint32_t chunk = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
+      const int ksteps = bk / 8;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int in_tile = 0;
         uint32_t fresh = 1;
-        for (int q = 0; q < p.npass && ok; q++) {
-          const TcPass& ps = p.pass[q];
-          for (int kb = 0; kb < ps.k_iters; kb++, it++) {
+        for (int q = 0; q < p.ngroups && ok; q++) {
+          const TcGroup& gr = p.group[q];
+          for (int kb = 0; kb < gr.k_iters; kb++) {
             const int acc = chunk & 1;
             if (in_tile % kChunkIters == 0) {
               // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
@@ -295,9 +325,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               tc_fence_after();
               fresh = 1;
             }
-            const int s = it % Cfg::kStages;
-            const uint32_t ph = (it / Cfg::kStages) & 1u;
-            if (!mbar_wait(full_bar(s), ph, &abort_flag)) {
+            if (!mbar_wait(full_bar(stage), phase, &abort_flag)) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 3);
               abort_flag = 1;
@@ -305,17 +333,26 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
-            const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
-            const uint32_t b_addr = a_addr + Cfg::kABytes;
-            const uint64_t a_desc = ((uint64_t)ps.a_desc_hi << 32) | (uint64_t)(ps.a_desc_lo | ((a_addr >> 4) & 0x3fffu));
-            const uint64_t b_desc = ((uint64_t)ps.b_desc_hi << 32) | (uint64_t)(ps.b_desc_lo | ((b_addr >> 4) & 0x3fffu));
-#pragma unroll
-            for (int j = 0; j < BK / 8; j++) {
-              mma_tf32(d_tmem, a_desc + (uint64_t)(j * ps.a_adv), b_desc + (uint64_t)(j * ps.b_adv), ps.idesc,
-                       fresh ? 0u : 1u);
-              fresh = 0;
+            const uint32_t base = smem_base + stage * stage_bytes;
+            for (int i = 0; i < gr.nmma; i++) {
+              const TcMma& mm = gr.mma[i];
+              const TcOperand& oa = gr.A[mm.a];
+              const TcOperand& ob = gr.B[mm.b];
+              const uint64_t a_desc =
+                  ((uint64_t)oa.desc_hi << 32) | (uint64_t)(oa.desc_lo | (((base + oa.smem_off) >> 4) & 0x3fffu));
+              const uint64_t b_desc =
+                  ((uint64_t)ob.desc_hi << 32) | (uint64_t)(ob.desc_lo | (((base + ob.smem_off) >> 4) & 0x3fffu));
+              for (int j = 0; j < ksteps; j++) {
+                mma_tf32(d_tmem, a_desc + (uint64_t)(j * oa.adv), b_desc + (uint64_t)(j * ob.adv), mm.idesc,
+                         fresh ? 0u : 1u);
+                fresh = 0;
+              }
             }
-            mma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+            mma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+            if (++stage == num_stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
             in_tile++;
             if (in_tile % kChunkIters == 0 || in_tile == total_k_iters) {
               mma_commit(tfull_bar(acc));  // chunk complete: hand it to the epilogue warps
@@ -481,7 +518,7 @@ struct MapKey {
   const void* ptr;
   uint64_t d0, d1, ld;
   uint32_t b0, b1;
-  int swz;
+  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
   }
@@ -492,20 +529,21 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.d0;
     h = h * 1000003u ^ k.d1;
     h = h * 1000003u ^ k.ld;
-    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 1 | (uint32_t)k.swz);
+    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 2 | (uint32_t)k.swz);
     return h;
   }
 };
 
 // 2-D fp32 map: inner (contiguous) extent d0, outer extent d1 with a stride of ld floats,
-// box b0 x b1, zero fill outside the tensor.  atom32 = false: 128-byte swizzle of 16-byte
-// chunks (K-major tiles); true: 128-byte swizzle of 32-byte chunks, the only shared-memory
-// layout tcgen05 accepts for MN-major 32-bit operands.  Encoded maps are cached.
+// box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of 16-byte chunks
+// (K-major tiles, 32 floats of K per row); 2: 64-byte swizzle (K-major, 16 floats per row);
+// 1: 128-byte swizzle of 32-byte chunks, the only shared-memory layout tcgen05 accepts for
+// MN-major 32-bit operands.  Encoded maps are cached.
 bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
-              bool atom32) {
+              int swz) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  const MapKey key{ptr, d0, d1, ld, b0, b1, atom32 ? 1 : 0};
+  const MapKey key{ptr, d0, d1, ld, b0, b1, swz};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -520,7 +558,9 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swz == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                 : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
@@ -534,12 +574,41 @@ inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_
 
 // Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
 // 16-byte units), descriptor version 1 for sm_100 (bits 46-47), layout type in bits 61-63.
-// K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart, 128-byte swizzle (type 2).
-// MN-major 32-bit tile: rows (one k each) of 128 bytes = 32 floats along M/N, 4-row groups
-// 512 bytes apart, 128-byte swizzle with 32-byte atoms (type 1).
+//  K-major, 32 floats of K per row: rows of 128 B, 8-row groups 1024 B apart, 128B swizzle (type 2).
+//  K-major, 16 floats of K per row: rows of 64 B, 8-row groups 512 B apart, 64B swizzle (type 4).
+//  MN-major 32-bit: rows (one k each) of 128 B = 32 floats along M/N, 4-row groups 512 B apart,
+//                   128B swizzle with 32-byte atoms (type 1).
 // The lower word carries the start address and the leading byte offset.
-constexpr uint32_t kDescHiK = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiK32 = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiK16 = (512u >> 4) | (1u << 14) | (4u << 29);
 constexpr uint32_t kDescHiMN = (512u >> 4) | (1u << 14) | (1u << 29);
+
+// Fills the tcgen05 view of one operand; `rows` = extent of the tile along M or N.
+bool fill_operand(TcOperand& op, CUtensorMap* map_slot, int map_index, const GemmOperand& src, bool is_a, int mn_extent,
+                  int k, int rows, int bk) {
+  // op(A) is M x k: trans -> stored k x M, k contiguous (K-major); else M contiguous.
+  // op(B) is k x N: not trans -> stored k x N, k contiguous (K-major); trans -> N contiguous.
+  op.mn = is_a ? (src.trans ? 0 : 1) : (src.trans ? 1 : 0);
+  op.map = map_index;
+  bool ok;
+  if (op.mn) {
+    ok = make_map(map_slot, src.ptr, (uint64_t)mn_extent, (uint64_t)k, (uint64_t)src.ld, 32, (uint32_t)bk, 1);
+    op.desc_hi = kDescHiMN;
+    op.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;  // distance between 32-float chunks = bk rows x 128 B
+    op.adv = 1024u >> 4;                             // K = 8 step: 8 rows of 128 B
+  } else {
+    ok = make_map(map_slot, src.ptr, (uint64_t)k, (uint64_t)mn_extent, (uint64_t)src.ld, (uint32_t)bk, (uint32_t)rows,
+                  bk == 32 ? 0 : 2);
+    op.desc_hi = bk == 32 ? kDescHiK32 : kDescHiK16;
+    op.desc_lo = 1u << 16;                           // leading byte offset is unused for swizzled K-major tiles
+    op.adv = 32u >> 4;                               // K = 8 step: 32 bytes inside the swizzled row
+  }
+  return ok;
+}
+
+inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
+  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
+}
 
 template <int BN, int kEpi>
 int launch_tc(TcParams& p) {
@@ -574,50 +643,107 @@ int gemm_tc(const GemmProblem& g) {
   if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
   TcParams p;
-  p.npass = g.npass;
   p.M = g.M;
   p.N = g.N;
   p.epi = g.epi;
   p.status = status_word();
-  {
-    static int chunk_iters = 0;
-    if (!chunk_iters) {
-      const char* e = getenv("B200_CHUNK_ITERS");
-      chunk_iters = e ? atoi(e) : kChunkItersDefault;
-      if (chunk_iters < 1) chunk_iters = kChunkItersDefault;
-    }
-    p.chunk_iters = chunk_iters;
-  }
+
+  // ---- group consecutive passes that share K and need at most two distinct A and B operands
+  struct HostGroup {
+    int k, nA, nB, nmma;
+    GemmOperand A[2], B[2];
+    int ma[4], mb[4], neg[4];
+  } hg[kMaxPass];
+  int ngroups = 0;
   for (int q = 0; q < g.npass; q++) {
     const GemmPass& ps = g.pass[q];
-    TcPass& tp = p.pass[q];
-    tp.a_map = 2 * q;
-    tp.b_map = 2 * q + 1;
-    tp.k_iters = (ps.k + BK - 1) / BK;
-    // op(A) is M x k.  trans: stored k x M, k contiguous (K-major).  Otherwise M contiguous.
-    tp.a_mn = ps.a.trans ? 0 : 1;
-    // op(B) is k x N.  Not trans: stored k x N, k contiguous (K-major).  trans: N contiguous.
-    tp.b_mn = ps.b.trans ? 1 : 0;
-    bool ok;
-    if (tp.a_mn) ok = make_map(&p.maps[tp.a_map], ps.a.ptr, (uint64_t)g.M, (uint64_t)ps.k, (uint64_t)ps.a.ld, 32, BK, true);
-    else ok = make_map(&p.maps[tp.a_map], ps.a.ptr, (uint64_t)ps.k, (uint64_t)g.M, (uint64_t)ps.a.ld, BK, BM, false);
-    if (!ok) return set_error("cuTensorMapEncodeTiled failed for operand A");
-    if (tp.b_mn) ok = make_map(&p.maps[tp.b_map], ps.b.ptr, (uint64_t)g.N, (uint64_t)ps.k, (uint64_t)ps.b.ld, 32, BK, true);
-    else ok = make_map(&p.maps[tp.b_map], ps.b.ptr, (uint64_t)ps.k, (uint64_t)g.N, (uint64_t)ps.b.ld, BK, (uint32_t)BN, false);
-    if (!ok) return set_error("cuTensorMapEncodeTiled failed for operand B");
-    // instruction descriptor: D fp32 (bit 4), A and B TF32 (value 2 at bits 7 and 10), negate A
-    // (bit 13), A / B MN-major (bits 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
-    tp.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((ps.negate ? 1u : 0u) << 13) | ((uint32_t)tp.a_mn << 15) |
-               ((uint32_t)tp.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    tp.a_desc_hi = tp.a_mn ? kDescHiMN : kDescHiK;
-    tp.b_desc_hi = tp.b_mn ? kDescHiMN : kDescHiK;
-    // Leading byte offset (16-byte units): unused for K-major swizzled tiles (set to 1);
-    // for MN-major tiles it is the distance between 32-float column chunks = BK rows x 128 B.
-    tp.a_desc_lo = (tp.a_mn ? (uint32_t)(BK * 128 >> 4) : 1u) << 16;
-    tp.b_desc_lo = (tp.b_mn ? (uint32_t)(BK * 128 >> 4) : 1u) << 16;
-    // Advance per K=8 step: 32 bytes inside the swizzle row (K-major) or 8 rows = 1024 bytes (MN-major).
-    tp.a_adv = tp.a_mn ? (1024u >> 4) : (32u >> 4);
-    tp.b_adv = tp.b_mn ? (1024u >> 4) : (32u >> 4);
+    bool placed = false;
+    if (ngroups > 0) {
+      HostGroup& h = hg[ngroups - 1];
+      if (h.k == ps.k && h.nmma < 4) {
+        int ia = -1, ib = -1;
+        for (int i = 0; i < h.nA; i++) if (same_operand(h.A[i], ps.a)) ia = i;
+        for (int i = 0; i < h.nB; i++) if (same_operand(h.B[i], ps.b)) ib = i;
+        const int needA = ia < 0 ? 1 : 0, needB = ib < 0 ? 1 : 0;
+        if (h.nA + needA <= 2 && h.nB + needB <= 2) {
+          if (ia < 0) { ia = h.nA; h.A[h.nA++] = ps.a; }
+          if (ib < 0) { ib = h.nB; h.B[h.nB++] = ps.b; }
+          h.ma[h.nmma] = ia; h.mb[h.nmma] = ib; h.neg[h.nmma] = ps.negate;
+          h.nmma++;
+          placed = true;
+        }
+      }
+    }
+    if (!placed) {
+      HostGroup& h = hg[ngroups++];
+      h.k = ps.k;
+      h.nA = h.nB = h.nmma = 1;
+      h.A[0] = ps.a;
+      h.B[0] = ps.b;
+      h.ma[0] = h.mb[0] = 0;
+      h.neg[0] = ps.negate;
+    }
+  }
+  // ---- ring geometry: 32 floats of K per k-block (one 128-byte swizzle row); 16-float blocks
+  // double the stage count but measured slower (64-byte rows, twice the MMA and TMA issues)
+  auto stage_bytes_for = [&](int bk) {
+    uint32_t mx = 0;
+    for (int q = 0; q < ngroups; q++) {
+      const uint32_t b = (uint32_t)(hg[q].nA * BM + hg[q].nB * BN) * bk * 4;
+      if (b > mx) mx = b;
+    }
+    return mx;
+  };
+  static int forced_bk = -1, chunk_k = 0;
+  if (forced_bk < 0) {
+    const char* e = getenv("B200_GEMM_BK");
+    forced_bk = e ? atoi(e) : 0;
+    const char* c = getenv("B200_CHUNK_K");
+    chunk_k = c ? atoi(c) : 128;
+    if (chunk_k < 16) chunk_k = 128;
+  }
+  int bk = 32;
+  if (forced_bk == 16 || forced_bk == 32) bk = forced_bk;
+  p.bk = bk;
+  p.stage_bytes = stage_bytes_for(bk);
+  p.num_stages = (int)(kStageBudget / p.stage_bytes);
+  if (p.num_stages > kMaxStages) p.num_stages = kMaxStages;
+  if (p.num_stages < 1) return ERROR_UNSUPPORTED;
+  p.chunk_iters = chunk_k / bk < 1 ? 1 : chunk_k / bk;   // fold into fp32 registers every 128 products
+  p.ngroups = ngroups;
+  int nmaps = 0;
+  for (int q = 0; q < ngroups; q++) {
+    const HostGroup& h = hg[q];
+    TcGroup& tg = p.group[q];
+    tg.k_iters = (h.k + bk - 1) / bk;
+    tg.nA = h.nA;
+    tg.nB = h.nB;
+    tg.nmma = h.nmma;
+    uint32_t off = 0;
+    for (int i = 0; i < h.nA; i++) {
+      if (!fill_operand(tg.A[i], &p.maps[nmaps], nmaps, h.A[i], true, g.M, h.k, BM, bk))
+        return set_error("cuTensorMapEncodeTiled failed for operand A");
+      nmaps++;
+      tg.A[i].smem_off = off;
+      off += (uint32_t)BM * bk * 4;
+    }
+    for (int i = 0; i < h.nB; i++) {
+      if (!fill_operand(tg.B[i], &p.maps[nmaps], nmaps, h.B[i], false, g.N, h.k, BN, bk))
+        return set_error("cuTensorMapEncodeTiled failed for operand B");
+      nmaps++;
+      tg.B[i].smem_off = off;
+      off += (uint32_t)BN * bk * 4;
+    }
+    tg.stage_tx = off;
+    for (int i = 0; i < h.nmma; i++) {
+      tg.mma[i].a = h.ma[i];
+      tg.mma[i].b = h.mb[i];
+      // instruction descriptor: D fp32 (bit 4), A and B TF32 (value 2 at bits 7 and 10), negate A
+      // (bit 13), A / B MN-major (bits 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
+      tg.mma[i].idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((h.neg[i] ? 1u : 0u) << 13) |
+                        ((uint32_t)tg.A[h.ma[i]].mn << 15) | ((uint32_t)tg.B[h.mb[i]].mn << 16) |
+                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    }
   }
   const GemmEpilogue& e = g.epi;
   int epi = kEpiGeneric;
