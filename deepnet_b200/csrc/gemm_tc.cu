@@ -109,8 +109,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
+      "l"(map), "r"(x), "r"(y), "r"(bar));
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -131,12 +130,66 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- two-CTA (cta_group::2) forms: the pair of CTAs of a cluster works on one 256-row tile.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-window addresses carry the CTA's rank within the pair in bit 24; clearing it names the
+// same location in the pair's leader (rank 0).
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+// Loads into THIS CTA's shared memory, completes the transaction on the LEADER's mbarrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar & kPeerBitMask));
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// One instruction multiplies a 256-row A (128 rows from each CTA's shared memory) by B (half of
+// its N rows from each CTA) into both CTAs' tensor memory.
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
+}
+// Arrives (once all earlier MMAs of this thread are done) on the barrier at this offset in
+// every CTA named by the mask.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(cta_mask)
+               : "memory");
+}
+// Arrive on the barrier at this offset in the pair's leader.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar)
+      : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -191,7 +244,9 @@ struct TcConfig {
 //   kEpiGeneric every option tested at run time
 enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSigLo = 2, kEpiSigLoSample = 3, kEpiLinLo = 4 };
 
-template <int BN, int kEpi>
+// kTwo: two CTAs of a cluster share one 256 x BN tile (cta_group::2): each stages its own 128
+// rows of A and half of B's rows, the leader issues the MMAs for both.
+template <int BN, int kEpi, bool kTwo>
 __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant__ TcParams p) {
   using Cfg = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -210,6 +265,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t rank = kTwo ? cluster_ctarank() : 0u;        // 0 = leader of the pair
+  const int first_tile = kTwo ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = kTwo ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TILE_M = kTwo ? 2 * BM : BM;                  // rows of the tile a CTA (pair) owns
+  constexpr int BN_LOCAL = kTwo ? BN / 2 : BN;                // B rows staged by this CTA
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -219,17 +279,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), kEpiWarps);
+      mbar_init(tempty_bar(a), kTwo ? 2 * kEpiWarps : kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
-    tmem_relinquish();
+    if (kTwo) {
+      tmem_alloc2(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
+      tmem_relinquish2();
+    } else {
+      tmem_alloc(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kTwo) cluster_sync();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
@@ -239,48 +305,50 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
+    // The whole warp runs the loop; lane l issues (at most) one box per k-block: operand l / 8
+    // (A0, A1, B0, B1), box l % 8 of it.  The refill of a freed stage is on the critical path of
+    // a ring this shallow, so every constant sits in registers and a lane issues one copy only.
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int opi = lane >> 3, box = lane & 7;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * TILE_M + (int)rank * BM, n0 = tn * BN + (int)rank * BN_LOCAL;
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
-          for (int kb = 0; kb < gr.k_iters; kb++, it++) {
+          const int k_iters = gr.k_iters;
+          const uint32_t tx = kTwo ? 2 * gr.stage_tx : gr.stage_tx;
+          // this lane's copy, if any
+          const bool is_a = opi < 2;
+          const int slot = is_a ? opi : opi - 2;
+          bool active = slot < (is_a ? gr.nA : gr.nB);
+          TcOperand op = gr.A[0];
+          if (active) op = is_a ? gr.A[slot] : gr.B[slot];
+          const int nboxes = op.mn ? (is_a ? BM / 32 : BN_LOCAL / 32) : 1;
+          active = active && box < nboxes;
+          const CUtensorMap* map = &p.maps[op.map];
+          const int row0 = (is_a ? m0 : n0) + (op.mn ? 32 * box : 0);
+          const uint32_t dst_off = op.smem_off + (op.mn ? (uint32_t)(box * bk * 128) : 0u);
+          const int mn = op.mn;
+          for (int kb = 0; kb < k_iters; kb++) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 1);
               abort_flag = 1;
               break;
             }
-            const uint32_t base = smem_base + stage * stage_bytes;
-            mbar_expect_tx(full_bar(stage), gr.stage_tx);
-            const int k0 = kb * bk;
-            for (int i = 0; i < gr.nA; i++) {
-              const TcOperand& op = gr.A[i];
-              const uint32_t dst = base + op.smem_off;
-              if (op.mn) {
-#pragma unroll
-                for (int j = 0; j < BM / 32; j++)
-                  tma_load_2d(dst + j * bk * 128, &p.maps[op.map], m0 + 32 * j, k0, full_bar(stage));
-              } else {
-                tma_load_2d(dst, &p.maps[op.map], k0, m0, full_bar(stage));
-              }
-            }
-            for (int i = 0; i < gr.nB; i++) {
-              const TcOperand& op = gr.B[i];
-              const uint32_t dst = base + op.smem_off;
-              if (op.mn) {
-#pragma unroll
-                for (int j = 0; j < BN / 32; j++)
-                  tma_load_2d(dst + j * bk * 128, &p.maps[op.map], n0 + 32 * j, k0, full_bar(stage));
-              } else {
-                tma_load_2d(dst, &p.maps[op.map], k0, n0, full_bar(stage));
-              }
+            const uint32_t bar = full_bar(stage);
+            // the leader's barrier collects the bytes of both CTAs of a pair
+            if (lane == 0 && rank == 0) mbar_expect_tx(bar, tx);
+            if (active) {
+              const uint32_t dst = smem_base + stage * stage_bytes + dst_off;
+              const int k0 = kb * bk;
+              const int x = mn ? row0 : k0, y = mn ? k0 : row0;
+              if (kTwo) tma_load_2d_pair(dst, map, x, y, bar);
+              else tma_load_2d(dst, map, x, y, bar);
             }
             if (++stage == num_stages) {
               stage = 0;
@@ -289,7 +357,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         // let copies already issued land before the CTA leaves
         for (int s = 0; s < num_stages; s++) {
           for (uint32_t i = 0; i < 4096; i++) {
@@ -300,21 +368,40 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (the pair's leader only)
+    if (lane == 0 && rank == 0) {
       uint32_t chunk = 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       const int ksteps = bk / 8;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int in_tile = 0;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        int in_tile = 0, in_chunk = 0;
         uint32_t fresh = 1;
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
-          for (int kb = 0; kb < gr.k_iters; kb++) {
+          // The issuing thread must launch an MMA every ~70 ns to keep the tensor pipe busy: all
+          // per-product constants live in registers, the k-loop only adds the stage address.
+          const int nm = gr.nmma, k_iters = gr.k_iters;
+          uint32_t a_lo[4], b_lo[4], a_hi[4], b_hi[4], a_adv[4], b_adv[4], idesc[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            a_lo[i] = b_lo[i] = a_hi[i] = b_hi[i] = a_adv[i] = b_adv[i] = idesc[i] = 0;
+            if (i < nm) {
+              const TcOperand oa = gr.A[gr.mma[i].a];
+              const TcOperand ob = gr.B[gr.mma[i].b];
+              a_lo[i] = oa.desc_lo + (oa.smem_off >> 4);
+              b_lo[i] = ob.desc_lo + (ob.smem_off >> 4);
+              a_hi[i] = oa.desc_hi;
+              b_hi[i] = ob.desc_hi;
+              a_adv[i] = oa.adv;
+              b_adv[i] = ob.adv;
+              idesc[i] = gr.mma[i].idesc;
+            }
+          }
+          for (int kb = 0; kb < k_iters; kb++) {
             const int acc = chunk & 1;
-            if (in_tile % kChunkIters == 0) {
+            if (in_chunk == 0) {
               // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
               if (!mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag)) {
                 ok = false;
@@ -333,30 +420,37 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
-            const uint32_t base = smem_base + stage * stage_bytes;
-            for (int i = 0; i < gr.nmma; i++) {
-              const TcMma& mm = gr.mma[i];
-              const TcOperand& oa = gr.A[mm.a];
-              const TcOperand& ob = gr.B[mm.b];
-              const uint64_t a_desc =
-                  ((uint64_t)oa.desc_hi << 32) | (uint64_t)(oa.desc_lo | (((base + oa.smem_off) >> 4) & 0x3fffu));
-              const uint64_t b_desc =
-                  ((uint64_t)ob.desc_hi << 32) | (uint64_t)(ob.desc_lo | (((base + ob.smem_off) >> 4) & 0x3fffu));
-              for (int j = 0; j < ksteps; j++) {
-                mma_tf32(d_tmem, a_desc + (uint64_t)(j * oa.adv), b_desc + (uint64_t)(j * ob.adv), mm.idesc,
-                         fresh ? 0u : 1u);
-                fresh = 0;
+            const uint32_t sb = (smem_base + stage * stage_bytes) >> 4;   // stage address, 16-byte units
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              if (i < nm) {
+                const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  if (j < ksteps) {
+                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                    if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    fresh = 0;
+                  }
+                }
               }
             }
-            mma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+            // the stage is free (in both CTAs of a pair) once these MMAs have read it
+            if (kTwo) mma_commit_pair(empty_bar(stage), 3);
+            else mma_commit(empty_bar(stage));
             if (++stage == num_stages) {
               stage = 0;
               phase ^= 1u;
             }
             in_tile++;
-            if (in_tile % kChunkIters == 0 || in_tile == total_k_iters) {
-              mma_commit(tfull_bar(acc));  // chunk complete: hand it to the epilogue warps
+            if (++in_chunk == kChunkIters || in_tile == total_k_iters) {
+              // chunk complete: hand it to the epilogue warps (of both CTAs)
+              if (kTwo) mma_commit_pair(tfull_bar(acc), 3);
+              else mma_commit(tfull_bar(acc));
               chunk++;
+              in_chunk = 0;
             }
           }
         }
@@ -375,7 +469,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     const int pM = p.M, pN = p.N;
     const int nchunks = (total_k_iters + kChunkIters - 1) / kChunkIters;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       float accum[COLS];
@@ -401,10 +495,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (lane == 0) {
+          if (kTwo) mbar_arrive_leader(tempty_bar(acc));   // the leader's issuer waits for both CTAs
+          else mbar_arrive(tempty_bar(acc));
+        }
       }
       if (!ok) break;
-      const int m = tm * BM + wq * 32 + lane;
+      const int m = tm * TILE_M + (int)rank * BM + wq * 32 + lane;
       const int nc = tn * BN + col_base;
       if (m < pM && nc < pN) {
         if (kEpi == kEpiPlain) {
@@ -487,9 +584,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (kTwo) cluster_sync();   // neither CTA leaves (or frees tensor memory) while its peer may still use it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (kTwo) tmem_dealloc2(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -610,21 +709,60 @@ inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
   return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
 }
 
-template <int BN, int kEpi>
+template <int BN, int kEpi, bool kTwo>
 int launch_tc(TcParams& p) {
   using Cfg = TcConfig<BN>;
   static bool attr_set = false;
+  static int max_pairs = 0;
+  auto kernel = k_gemm_tc<BN, kEpi, kTwo>;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(k_gemm_tc<BN, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
       return set_error("cudaFuncSetAttribute(max dynamic shared memory) failed");
+    if (kTwo) {
+      // how many CTA pairs the device can keep resident at once (a pair needs two SMs of one TPC)
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * (sm_count() / 2));
+      q.blockDim = dim3(kThreadsTc);
+      q.dynamicSmemBytes = Cfg::kSmemBytes;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      q.attrs = at;
+      q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        return set_error("cudaOccupancyMaxActiveClusters failed for the paired-CTA product");
+      }
+      max_pairs = n;
+    }
     attr_set = true;
   }
-  p.tiles_m = (p.M + BM - 1) / BM;
+  constexpr int TILE_M = kTwo ? 2 * BM : BM;
+  p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  k_gemm_tc<BN, kEpi><<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
+  if (!kTwo) {
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kernel<<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
+    return check_launch();
+  }
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreadsTc);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream();
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 
@@ -642,6 +780,14 @@ bool gemm_tc_supported(const GemmProblem& g) {
 int gemm_tc(const GemmProblem& g) {
   if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  static int pair_mode = -1;   // B200_GEMM_2CTA=0 keeps one CTA per tile
+  if (pair_mode < 0) {
+    const char* e = getenv("B200_GEMM_2CTA");
+    pair_mode = e ? atoi(e) : 1;
+  }
+  // pairs of CTAs (cta_group::2) on 256-row tiles when the product has at least two row tiles
+  const bool two = pair_mode != 0 && BN == 256 && g.M > BM;
+  const int BN_LOCAL = two ? BN / 2 : BN;      // rows of B staged per CTA
   TcParams p;
   p.M = g.M;
   p.N = g.N;
@@ -689,7 +835,7 @@ int gemm_tc(const GemmProblem& g) {
   auto stage_bytes_for = [&](int bk) {
     uint32_t mx = 0;
     for (int q = 0; q < ngroups; q++) {
-      const uint32_t b = (uint32_t)(hg[q].nA * BM + hg[q].nB * BN) * bk * 4;
+      const uint32_t b = (uint32_t)(hg[q].nA * BM + hg[q].nB * BN_LOCAL) * bk * 4;
       if (b > mx) mx = b;
     }
     return mx;
@@ -728,11 +874,11 @@ int gemm_tc(const GemmProblem& g) {
       off += (uint32_t)BM * bk * 4;
     }
     for (int i = 0; i < h.nB; i++) {
-      if (!fill_operand(tg.B[i], &p.maps[nmaps], nmaps, h.B[i], false, g.N, h.k, BN, bk))
+      if (!fill_operand(tg.B[i], &p.maps[nmaps], nmaps, h.B[i], false, g.N, h.k, BN_LOCAL, bk))
         return set_error("cuTensorMapEncodeTiled failed for operand B");
       nmaps++;
       tg.B[i].smem_off = off;
-      off += (uint32_t)BN * bk * 4;
+      off += (uint32_t)BN_LOCAL * bk * 4;
     }
     tg.stage_tx = off;
     for (int i = 0; i < h.nmma; i++) {
@@ -742,7 +888,7 @@ int gemm_tc(const GemmProblem& g) {
       // (bit 13), A / B MN-major (bits 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
       tg.mma[i].idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((h.neg[i] ? 1u : 0u) << 13) |
                         ((uint32_t)tg.A[h.ma[i]].mn << 15) | ((uint32_t)tg.B[h.mb[i]].mn << 16) |
-                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((two ? 2 * BM : BM) >> 4) << 24);
     }
   }
   const GemmEpilogue& e = g.epi;
@@ -753,17 +899,18 @@ int gemm_tc(const GemmProblem& g) {
     if (e.activation == 1) epi = e.sample ? kEpiSigLoSample : kEpiSigLo;
     else if (!e.sample) epi = kEpiLinLo;
   }
-#define B200_TC_CASE(BNV)                                            \
-  switch (epi) {                                                     \
-    case kEpiPlain: return launch_tc<BNV, kEpiPlain>(p);             \
-    case kEpiSigLo: return launch_tc<BNV, kEpiSigLo>(p);             \
-    case kEpiSigLoSample: return launch_tc<BNV, kEpiSigLoSample>(p); \
-    case kEpiLinLo: return launch_tc<BNV, kEpiLinLo>(p);             \
-    default: return launch_tc<BNV, kEpiGeneric>(p);                  \
+#define B200_TC_CASE(BNV, TWO)                                            \
+  switch (epi) {                                                          \
+    case kEpiPlain: return launch_tc<BNV, kEpiPlain, TWO>(p);             \
+    case kEpiSigLo: return launch_tc<BNV, kEpiSigLo, TWO>(p);             \
+    case kEpiSigLoSample: return launch_tc<BNV, kEpiSigLoSample, TWO>(p); \
+    case kEpiLinLo: return launch_tc<BNV, kEpiLinLo, TWO>(p);             \
+    default: return launch_tc<BNV, kEpiGeneric, TWO>(p);                  \
   }
-  if (BN == 256) { B200_TC_CASE(256) }
-  if (BN == 128) { B200_TC_CASE(128) }
-  B200_TC_CASE(64)
+  if (BN == 256 && two) { B200_TC_CASE(256, true) }
+  if (BN == 256) { B200_TC_CASE(256, false) }
+  if (BN == 128) { B200_TC_CASE(128, false) }
+  B200_TC_CASE(64, false)
 #undef B200_TC_CASE
 }
 
