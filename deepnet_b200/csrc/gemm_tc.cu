@@ -845,8 +845,7 @@ int gemm_tc(const GemmProblem& g) {
     const char* e = getenv("B200_GEMM_BK");
     forced_bk = e ? atoi(e) : 0;
     const char* c = getenv("B200_CHUNK_K");
-    chunk_k = c ? atoi(c) : 128;
-    if (chunk_k < 16) chunk_k = 128;
+    chunk_k = c ? atoi(c) : 0;
   }
   int bk = 32;
   if (forced_bk == 16 || forced_bk == 32) bk = forced_bk;
@@ -855,7 +854,12 @@ int gemm_tc(const GemmProblem& g) {
   p.num_stages = (int)(kStageBudget / p.stage_bytes);
   if (p.num_stages > kMaxStages) p.num_stages = kMaxStages;
   if (p.num_stages < 1) return ERROR_UNSUPPORTED;
-  p.chunk_iters = chunk_k / bk < 1 ? 1 : chunk_k / bk;   // fold into fp32 registers every 128 products
+  // Products folded in tensor memory before they join the fp32 registers.  128 keeps linear
+  // outputs (statistics, `dot`) within 2e-6 of the largest entry at K = 4096..8192; behind a
+  // logistic epilogue the slope <= 1/4 and the small pre-activations leave room for 512
+  // (measured 2e-7 absolute on the probabilities), which costs 8 % less time.
+  const int ck = chunk_k >= 16 ? chunk_k : (g.epi.activation == 1 ? 512 : 128);
+  p.chunk_iters = ck / bk < 1 ? 1 : ck / bk;
   p.ngroups = ngroups;
   int nmaps = 0;
   for (int q = 0; q < ngroups; q++) {

@@ -135,6 +135,56 @@ __global__ void __launch_bounds__(32 * kRowLanes) k_rowsum(const float* __restri
       out[(long)blockIdx.y * h + r] = tot;
   }
 }
+// Same sums with 128-bit loads: a thread owns 4 consecutive rows, a block 128 rows x 8 column
+// lanes, and enough column splits are launched to keep every SM several blocks deep.
+__global__ void __launch_bounds__(32 * kRowLanes) k_rowsum4(const float* __restrict__ m, float* __restrict__ out,
+                                                            int h, int w, int cols_per_split, float mult, float beta,
+                                                            bool final_pass) {
+  __shared__ float4 smem[kRowLanes][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int r = (blockIdx.x * 32 + tx) * 4;
+  const int c0 = blockIdx.y * cols_per_split;
+  const int c1 = min(w, c0 + cols_per_split);
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (r < h) {
+    const float* base = m + r;
+    int c = c0 + ty;
+    for (; c + 3 * kRowLanes < c1; c += 4 * kRowLanes) {
+      const float4 a0 = *reinterpret_cast<const float4*>(base + (long)c * h);
+      const float4 a1 = *reinterpret_cast<const float4*>(base + (long)(c + kRowLanes) * h);
+      const float4 a2 = *reinterpret_cast<const float4*>(base + (long)(c + 2 * kRowLanes) * h);
+      const float4 a3 = *reinterpret_cast<const float4*>(base + (long)(c + 3 * kRowLanes) * h);
+      s.x += (a0.x + a1.x) + (a2.x + a3.x);
+      s.y += (a0.y + a1.y) + (a2.y + a3.y);
+      s.z += (a0.z + a1.z) + (a2.z + a3.z);
+      s.w += (a0.w + a1.w) + (a2.w + a3.w);
+    }
+    for (; c < c1; c += kRowLanes) {
+      const float4 a = *reinterpret_cast<const float4*>(base + (long)c * h);
+      s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w;
+    }
+  }
+  smem[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && r < h) {
+    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < kRowLanes; j++) {
+      const float4 v = smem[j][tx];
+      tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+    }
+    if (final_pass) {
+      float4 o = *reinterpret_cast<float4*>(out + r);
+      o.x = (beta == 0 ? 0.0f : beta * o.x) + mult * tot.x;
+      o.y = (beta == 0 ? 0.0f : beta * o.y) + mult * tot.y;
+      o.z = (beta == 0 ? 0.0f : beta * o.z) + mult * tot.z;
+      o.w = (beta == 0 ? 0.0f : beta * o.w) + mult * tot.w;
+      *reinterpret_cast<float4*>(out + r) = o;
+    } else {
+      *reinterpret_cast<float4*>(out + (long)blockIdx.y * h + r) = tot;
+    }
+  }
+}
 __global__ void __launch_bounds__(256) k_rowsum_finish(const float* __restrict__ part, float* __restrict__ t, int h,
                                                        int splits, float mult, float beta) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -216,7 +266,40 @@ __global__ void __launch_bounds__(256) k_scalar_partial(const float* __restrict_
   __shared__ double smem[32];
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   double s = 0;
-  for (long i = tid; i < n; i += nth) {
+  long start = 0;
+  if (((((uintptr_t)a) | (b ? (uintptr_t)b : 0)) & 15) == 0) {
+    // 128-bit loads, four elements folded in fp32 before joining the fp64 running sum
+    const long n4 = n >> 2;
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    long i = tid;
+    if (mode == 3) {
+      // squared difference: two independent 128-bit load pairs in flight per thread
+      for (; i + nth < n4; i += 2 * nth) {
+        const float4 x0 = a4[i], y0 = b4[i], x1 = a4[i + nth], y1 = b4[i + nth];
+        const float e0 = x0.x - y0.x, e1 = x0.y - y0.y, e2 = x0.z - y0.z, e3 = x0.w - y0.w;
+        const float f0 = x1.x - y1.x, f1 = x1.y - y1.y, f2 = x1.z - y1.z, f3 = x1.w - y1.w;
+        s += (double)((e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3)) + (double)((f0 * f0 + f1 * f1) + (f2 * f2 + f3 * f3));
+      }
+    }
+    for (; i < n4; i += nth) {
+      const float4 x = a4[i];
+      float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (mode >= 2) y = b4[i];
+      if (mode == 3) {
+        const float d0 = x.x - y.x, d1 = x.y - y.y, d2 = x.z - y.z, d3 = x.w - y.w;
+        s += (double)(d0 * d0 + d1 * d1) + (double)(d2 * d2 + d3 * d3);
+      } else if (mode == 0) {
+        s += (double)(x.x + x.y) + (double)(x.z + x.w);
+      } else if (mode == 1) {
+        s += (double)(x.x * x.x + x.y * x.y) + (double)(x.z * x.z + x.w * x.w);
+      } else {
+        s += (double)(x.x * y.x + x.y * y.y) + (double)(x.z * y.z + x.w * y.w);
+      }
+    }
+    start = n4 << 2;
+  }
+  for (long i = start + tid; i < n; i += nth) {
     const float x = a[i];
     if (mode == 3) {
       const float d = x - b[i];
@@ -271,21 +354,29 @@ int launch_axis_sum(const float* m, int h, int w, int axis, float* t, float mult
     k_colsum<<<blocks, 256, 0, stream()>>>(m, t, h, w, mult, beta);
     return check_launch();
   }
-  const int bx = (h + 31) / 32;
-  int splits = (4 * sm_count() + bx - 1) / bx;
-  const int max_splits = (w + 63) / 64;
+  const bool vec4 = (h % 4 == 0) && (((uintptr_t)m | (uintptr_t)t) & 15) == 0;
+  const int rows_per_block = vec4 ? 128 : 32;
+  const int bx = (h + rows_per_block - 1) / rows_per_block;
+  // enough blocks for about two full waves of 8 resident blocks per SM
+  int splits = (16 * sm_count() + bx - 1) / bx;
+  const int max_splits = (w + 31) / 32;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
   const int cps = (w + splits - 1) / splits;
   splits = (w + cps - 1) / cps;
-  if (splits == 1) {
-    k_rowsum<<<dim3(bx, 1), 32 * kRowLanes, 0, stream()>>>(m, t, h, w, cps, mult, beta, true);
-    return check_launch();
+  float* dst = t;
+  if (splits > 1) {
+    dst = (float*)workspace(0, (size_t)splits * h * sizeof(float));
+    if (!dst) return CUDA_ERROR;
   }
-  float* part = (float*)workspace(0, (size_t)splits * h * sizeof(float));
-  if (!part) return CUDA_ERROR;
-  k_rowsum<<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(m, part, h, w, cps, 1.0f, 0.0f, false);
-  k_rowsum_finish<<<(h + 255) / 256, 256, 0, stream()>>>(part, t, h, splits, mult, beta);
+  const bool final_pass = splits == 1;
+  if (vec4)
+    k_rowsum4<<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(m, dst, h, w, cps, final_pass ? mult : 1.0f,
+                                                                final_pass ? beta : 0.0f, final_pass);
+  else
+    k_rowsum<<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(m, dst, h, w, cps, final_pass ? mult : 1.0f,
+                                                               final_pass ? beta : 0.0f, final_pass);
+  if (!final_pass) k_rowsum_finish<<<(h + 255) / 256, 256, 0, stream()>>>(dst, t, h, splits, mult, beta);
   return check_launch();
 }
 
