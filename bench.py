@@ -213,7 +213,7 @@ def run_ours(args):
                     frac=round(achieved / peaks["tensor"], 4),
                     # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
                     # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
-                    traffic=4.13e9 if config == 4 else None,
+                    traffic=3.17e9 if config == 4 else None,
                     kernel="k_gemm_tc<256, sigmoid+split+Bernoulli> (tcgen05 kind::tf32, 3 split-TF32 passes)",
                     peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
                                 "and 3 passes make one fp32-grade product" % peaks["source"],
