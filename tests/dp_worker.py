@@ -1,0 +1,51 @@
+"""One rank of the two-GPU data-parallel test: trains its shard of the global minibatch
+with the fused engine and writes its final weights and hidden draw.  Launched by
+tests/test_gpu_dp.py as a child process (one per GPU); not collected by pytest."""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, tmp = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    from deepnet_b200 import b200mat as cm
+    from deepnet_b200 import configs
+    from deepnet_b200.fused_rbm import FusedRBM
+    cm.cuda_set_device(rank)
+    cm.cublas_init()
+    idfile = os.path.join(tmp, "nccl_id")
+    if rank == 0:
+        with open(idfile + ".tmp", "wb") as f:
+            f.write(cm.dp_unique_id())
+        os.rename(idfile + ".tmp", idfile)
+    deadline = time.time() + 60
+    while not os.path.exists(idfile):
+        if time.time() > deadline:
+            raise SystemExit("rank %d: no NCCL id after 60 s" % rank)
+        time.sleep(0.05)
+    with open(idfile, "rb") as f:
+        uid = f.read()
+    cm.dp_init(uid, world, rank)
+    cfg = configs.build(0, cases=400, dims_scale=0.5)
+    gb = cfg["batchsize"]                       # global minibatch, split evenly over the ranks
+    b = gb // world
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, b, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"], world_size=world, rank=rank)
+    data = cm.CUDAMatrix(cfg["data"])
+    for step in range(3):
+        s = step * gb + rank * b
+        eng.TrainOneBatch(step, data.slice(s, s + b))
+    cm.dp_check()
+    np.savez(os.path.join(tmp, "rank%d.npz" % rank), W=np.array(eng.W.asarray()), hs=np.array(eng.h_samp.asarray()),
+             loss=eng.read_loss(), status=cm.read_status())
+    cm.dp_destroy()          # leaves only after its last collective has completed
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,45 @@
+"""Two-GPU data parallelism on the real path: two child processes (one per GPU) train the two
+halves of every global minibatch with the fused engine and one NCCL all-reduce of the packed
+statistics per update; the result must equal one GPU training the whole minibatch: identical
+Bernoulli bits (the random stream is indexed by global column), weights within 1e-5, and
+bit-identical replicas.  Skipped when fewer than two GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_two_gpu_shards_match_one_gpu(cm, tmp_path):
+    if cm._lib.b200_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path)], env=env)
+             for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=300) == 0
+    r0, r1 = (np.load(os.path.join(tmp_path, "rank%d.npz" % r)) for r in range(2))
+    assert int(r0["status"]) == 0 and int(r1["status"]) == 0
+    assert np.array_equal(r0["W"], r1["W"])                 # replicas stay bit-identical
+
+    from deepnet_b200 import configs
+    from deepnet_b200.fused_rbm import FusedRBM
+    cfg = configs.build(0, cases=400, dims_scale=0.5)
+    gb = cfg["batchsize"]
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, gb, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+    data = cm.CUDAMatrix(cfg["data"])
+    for step in range(3):
+        eng.TrainOneBatch(step, data.slice(step * gb, (step + 1) * gb))
+    W1 = np.array(eng.W.asarray())
+    hs = np.array(eng.h_samp.asarray())
+    cm.set_rng_column_offset(0)
+    assert np.abs(r0["W"] - W1).max() / np.abs(W1).max() < 1e-5
+    assert np.array_equal(np.concatenate([r0["hs"], r1["hs"]], axis=1), hs)
+    total = eng.read_loss()
+    assert abs(float(r0["loss"]) + float(r1["loss"]) - total) < 1e-5 * total
