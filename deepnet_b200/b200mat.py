@@ -450,6 +450,28 @@ class CUDAMatrix(object):
     def subtract_dot(self, m1, m2):
         return self.add_dot(m1, m2, -1.0)
 
+    def softmax_scaled(self, scale, target=None):
+        """target[:, j] = scale[j] * softmax(self[:, j]) (deepnet/replicated_softmax_layer.py:12-21 fused)."""
+        target = target or self
+        _check(_lib.softmax_scaled(self.p_mat, scale.p_mat, target.p_mat))
+        return target
+
+    def sample_multinomial(self, nn, target, max_draws=1000):
+        """target[:, i] = counts of int(nn[i]) draws from self[:, i] (replicated_softmax_layer.py:43-60 fused)."""
+        _check(_lib.sample_multinomial(CUDAMatrix.rnd_state_p, self.p_mat, nn.p_mat, target.p_mat, ct.c_int(max_draws)))
+        return target
+
+    def select_columns(self, indices, target):
+        """cudamat/cudamat.py:1478-1493: target[:, c] = self[:, indices[c]] (indices: float32 row vector)."""
+        _check(_lib.selectRows(self.p_mat, target.p_mat, indices.p_mat))
+        return target
+
+    def swap_columns(self, indices1, indices2, target):
+        """cudamat/cudamat.py:1496-1512: columns indices1 of self and indices2 of target change places."""
+        assert indices1.shape == indices2.shape
+        _check(_lib.swapColumns(self.p_mat, target.p_mat, indices1.p_mat, indices2.p_mat))
+        return target
+
     # -- fused entry points (no counterpart in the reference API) -------------
     def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_hi=None, w_lo=None):
         """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter."""

@@ -1,0 +1,167 @@
+// Replicated-softmax visible layer on the device, two fused operations:
+//   softmax_scaled      state = NN (x) softmax_col(pre): the six calls of
+//                       deepnet/replicated_softmax_layer.py:12-21 (max, add_row_mult(-1), exp,
+//                       sum, divide, mult_by_row) in one pass-structured kernel;
+//   sample_multinomial  the per-document loop of replicated_softmax_layer.py:43-60
+//                       (assign 0, add_col_vec, perturb_prob, choose_max, sum) as one kernel:
+//                       NN[i] draws per document by the exponential race
+//                       argmax_w p_w / (-log u_wd), counted per word.
+// Random numbers: document i uses sampling call (calls + i); draw d of word w takes the
+// uniform of element (w, d) of that call - exactly what the call-by-call path draws when it
+// perturbs its (words x draws) scratch matrix, so both paths give the same counts.
+#include "common.cuh"
+
+using namespace b200;
+
+namespace {
+
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(256) k_softmax_scaled(const float* m, const float* __restrict__ scale, float* t,
+                                                        int h, int w) {
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = m + (long)c * h;
+    float* tc = t + (long)c * h;
+    float mx = -INFINITY;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) mx = fmaxf(mx, col[r]);
+    mx = warp_max_f(mx);
+    __syncthreads();
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    mx = warp_max_f(lane < nw ? red[lane] : -INFINITY);
+    float s = 0;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      const float e = expf(col[r] - mx);
+      tc[r] = e;
+      s += e;
+    }
+    s = warp_sum_f(s);
+    __syncthreads();
+    if (lane == 0) red[wid] = s;
+    __syncthreads();
+    s = warp_sum_f(lane < nw ? red[lane] : 0.0f);
+    const float f = scale[c] / s;   // NN / sum, then one multiply per element (mult_by_row)
+    for (int r = threadIdx.x; r < h; r += blockDim.x) tc[r] = tc[r] * f;
+  }
+}
+
+// grid = (draw groups, documents); a block races 4 draws (the 4 words of one Philox block) of
+// one document over all words.
+__global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restrict__ probs,
+                                                            const float* __restrict__ nn, float* counts, int h, int w,
+                                                            int max_draws, int col0, unsigned long long seed,
+                                                            unsigned long long call0) {
+  __shared__ float sv[4][8];
+  __shared__ int si[4][8];
+  const int doc = blockIdx.y;
+  int ndraws = (int)nn[doc];
+  if (ndraws > max_draws) ndraws = max_draws;
+  const float* p = probs + (long)doc * h;
+  const PhiloxKey key = make_philox_key(seed, call0 + (unsigned long long)doc);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  // global draw columns of this document's scratch matrix: col0 + d, d = 0 .. ndraws-1
+  const int first_blk = col0 >> 2, last_blk = (col0 + ndraws - 1) >> 2;
+  for (int blk = first_blk + blockIdx.x; ndraws > 0 && blk <= last_blk; blk += gridDim.x) {
+    float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int bi[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      const uint4 wd = philox4x32_10((uint32_t)r, (uint32_t)blk, key);
+      const float pr = p[r];
+      const float u[4] = {word_to_uniform(wd.x), word_to_uniform(wd.y), word_to_uniform(wd.z), word_to_uniform(wd.w)};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float v = -pr / logf(u[j]);        // perturb_prob: cudamat_kernels.cu:227-238
+        if (v > bv[j] || (v == bv[j] && r < bi[j])) {
+          bv[j] = v;
+          bi[j] = r;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, bv[j], o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi[j], o);
+        if (v2 > bv[j] || (v2 == bv[j] && i2 < bi[j])) {
+          bv[j] = v2;
+          bi[j] = i2;
+        }
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        sv[j][wid] = bv[j];
+        si[j][wid] = bi[j];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 4) {
+      const int j = threadIdx.x;
+      const int d = (blk << 2) + j - col0;       // draw index of this word of the block
+      if (d >= 0 && d < ndraws) {
+        float v = sv[j][0];
+        int i = si[j][0];
+        for (int k = 1; k < (int)(blockDim.x >> 5); k++) {
+          if (sv[j][k] > v || (sv[j][k] == v && si[j][k] < i)) {
+            v = sv[j][k];
+            i = si[j][k];
+          }
+        }
+        if (i == 0x7fffffff) i = 0;              // all-NaN column: the sequential scan keeps word 0
+        atomicAdd(&counts[(long)doc * h + i], 1.0f);   // choose_max one-hot summed over the draws
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// target[:, j] = scale[j] * softmax(mat[:, j]); scale is 1 x cols (the document lengths NN).
+int softmax_scaled(cudamat* mat, cudamat* scale, cudamat* target) {
+  if (!mat->on_device || !scale->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (mat->is_trans || target->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(mat, target) || numel(scale) != mat->size[1]) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = mat->size[0], w = mat->size[1];
+  if ((long)h * w == 0) return 0;
+  k_softmax_scaled<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, scale->data_device,
+                                                                                 target->data_device, h, w);
+  return check_launch();
+}
+
+// target[:, i] = word counts of int(nn[i]) draws (at most max_draws) from the distribution
+// proportional to probs[:, i].  Consumes one sampling call per document.
+int sample_multinomial(rnd_struct* rnd_state, cudamat* probs, cudamat* nn, cudamat* target, int max_draws) {
+  if (!probs->on_device || !nn->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (probs->is_trans || target->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(probs, target) || numel(nn) != probs->size[1]) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (max_draws < 1) return ERROR_UNSUPPORTED;
+  const int h = probs->size[0], w = probs->size[1];
+  if ((long)h * w == 0) return 0;
+  if (cudaMemsetAsync(target->data_device, 0, (size_t)h * w * sizeof(float), stream()) != cudaSuccess)
+    return set_error("cudaMemsetAsync failed");
+  const unsigned long long call0 = rnd_state->calls;
+  rnd_state->calls += (unsigned long long)w;
+  int groups = (max_draws + 3) / 4 + 1;
+  if (groups > 64) groups = 64;
+  k_sample_multinomial<<<dim3(groups, w), 256, 0, stream()>>>(probs->data_device, nn->data_device, target->data_device,
+                                                              h, w, max_draws, rng_col0(), rnd_state->seed, call0);
+  return check_launch();
+}
+
+}  // extern "C"

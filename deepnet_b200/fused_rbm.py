@@ -23,7 +23,7 @@ summed by one NCCL all-reduce of a packed buffer before the update.
 """
 import numpy as np
 
-from .dbm import LINEAR, LOGISTIC, Parameter
+from .dbm import LINEAR, LOGISTIC, REPLICATED_SOFTMAX, Parameter
 
 
 class FusedRBM(object):
@@ -58,6 +58,14 @@ class FusedRBM(object):
         self.v_neg, self.v_neg_lo = z(V, B), z(V, B)
         self.h_neg, self.h_neg_lo = z(H, B), z(H, B)
         self.loss_acc = z(1, 1)
+        if visible == REPLICATED_SOFTMAX:
+            # document lengths, length-normalised visible states (the statistics use state / NN,
+            # deepnet/edge.py:225-228) and the multinomial sample fed upward
+            self.NN = z(1, B)
+            self.v0n, self.v0n_lo = z(V, B), z(V, B)
+            self.v_negn, self.v_negn_lo = z(V, B), z(V, B)
+            self.v_samp = z(V, B)
+            self.tiny = 1e-10
         self._sched = Parameter(cm, self.hyp)
         self._esched = Parameter(cm, self.ehyp)
         self.kernel_launches = 0
@@ -79,6 +87,8 @@ class FusedRBM(object):
 
     def TrainOneBatch(self, step, data):
         """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host."""
+        if self.visible == REPLICATED_SOFTMAX:
+            return self._train_replicated_softmax(step, data)
         cm, k = self.cm, self.hyp.gibbs_steps
         V, H, B = self.V, self.H, self.B
         W, Wl = self.W, self.W_lo
@@ -122,6 +132,61 @@ class FusedRBM(object):
             self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
         inv_b = 1.0 / (self.B * self.world_size)
         # updates (biases are not regularised, deepnet/dbm.py:249)
+        mom, eps = self._sched.GetMomentumAndEpsilon(step)
+        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
+        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
+        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
+        eh = self.ehyp
+        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
+        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
+        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1, w_lo=Wl)
+
+    def _train_replicated_softmax(self, step, data):
+        """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:
+        the call sequence of deepnet/dbm.py:118-238 with replicated_softmax_layer.py:12-60,90-154
+        and edge.py:222-246, on fused kernels.  Same random stream as the call-by-call driver:
+        one call for the positive hidden draw, then per Gibbs step one call per document for the
+        multinomial draw and one for the hidden draw."""
+        cm, k = self.cm, self.hyp.gibbs_steps
+        V, H, B = self.V, self.H, self.B
+        W, Wl = self.W, self.W_lo
+        gf = 2.0 * V * H * B
+        vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
+        lib = cm._lib
+        self.kernel_launches = 0
+        v0 = data                                              # integer counts: exact in TF32
+        # GetData: NN = column sums + tiny; v0n = data / NN for the statistics
+        self._op("col_sum", 0, vb, v0.sum, axis=0, target=self.NN)
+        self._op("add_scalar", 0, 8.0 * B, self.NN.add, self.tiny)
+        self._op("div_by_row", 0, 2 * vb, v0.div_by_row, self.NN, target=self.v0n)
+        self._op("split", 0, 2 * vb, self.v0n.split_tf32, self.v0n_lo)
+        # positive phase: hidden bias is scaled by the document length (deepnet/dbm.py:101-104)
+        self._op("gemm_up", gf, 3 * hb, cm.fused_gemm, [(Wl.T, v0), (W.T, v0)], out=self.h_pos, out_lo=self.h_pos_lo,
+                 sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
+        for i in range(k):
+            # visible: NN * softmax(W h + b_v)
+            self._op("gemm_down", gf, vb, cm.fused_gemm, [(Wl, self.h_samp), (W, self.h_samp)], out=self.v_neg_lo,
+                     bias=self.bv, activation=0)
+            self._op("softmax", 0, 2 * vb, self.v_neg_lo.softmax_scaled, self.NN, target=self.v_neg)
+            self._op("div_by_row", 0, 2 * vb, self.v_neg.div_by_row, self.NN, target=self.v_negn)
+            if i == 0:   # squared error between state / NN and the counts (replicated_softmax_layer.py:128-135)
+                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat,
+                                                                                self.loss_acc.p_mat)))
+            self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
+            self._op("gemm_up", gf, 3 * hb, cm.fused_gemm, [(Wl.T, self.v_samp), (W.T, self.v_samp)], out=self.h_neg,
+                     out_lo=self.h_neg_lo, sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
+        self._op("split", 0, 2 * vb, self.v_negn.split_tf32, self.v_negn_lo)
+        pos = [(self.v0n_lo, self.h_pos.T), (self.v0n, self.h_pos_lo.T), (self.v0n, self.h_pos.T)]
+        neg = [(self.v_negn_lo, self.h_neg.T, 1), (self.v_negn, self.h_neg_lo.T, 1), (self.v_negn, self.h_neg.T, 1)]
+        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
+        self._op("row_sum", 0, vb, self.v0n.sum, axis=1, target=self.suff_bv)
+        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_negn, axis=1, mult=-1.0)
+        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
+        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
+        if self.world_size > 1:
+            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
+        inv_b = 1.0 / (self.B * self.world_size)
         mom, eps = self._sched.GetMomentumAndEpsilon(step)
         self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
         self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)

@@ -146,6 +146,10 @@ int mult_by_scalar(cudamat* mat, float alpha, cudamat* target);               /*
 int divide_by_scalar(cudamat* mat, float alpha, cudamat* target);             /* cudamat.cu:2066 */
 int add_scalar(cudamat* mat, float alpha, cudamat* target);                   /* cudamat.cu:2085 */
 
+/* ---- index operations: cudamat/cudamat.cu:2120-2150 ----------------------------------- */
+int selectRows(cudamat* source, cudamat* target, cudamat* indices);                         /* cudamat.cu:2120 (select_columns) */
+int swapColumns(cudamat* source, cudamat* target, cudamat* indices1, cudamat* indices2);   /* cudamat.cu:2138 */
+
 /* ---- matrix product: cudamat/cudamat.cu:1671-1696 (cublasSgemm) ---------------------- */
 /* target = beta * target + alpha * op(mat1) . op(mat2); tcgen05 split-TF32 when the
  * operands are TMA-addressable (leading dimension a multiple of 4, 16-byte aligned). */
@@ -196,6 +200,15 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
  * call on a device looks the array's address up: make it before any stream capture.  Calls
  * share the array, so calls that overlap on the GPU race; issue them in order on one stream. */
 int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult);
+
+/* target[:, j] = scale[j] * softmax(mat[:, j]): the six calls of
+ * deepnet/replicated_softmax_layer.py:12-21 (max, add_row_mult, exp, sum, divide, mult_by_row). */
+int softmax_scaled(cudamat* mat, cudamat* scale, cudamat* target);
+
+/* target[:, i] = word counts of int(nn[i]) (at most max_draws) exponential-race draws from the
+ * distribution proportional to probs[:, i]: the per-document loop of
+ * deepnet/replicated_softmax_layer.py:43-60 as one kernel.  One sampling call per document. */
+int sample_multinomial(rnd_struct* rnd_state, cudamat* probs, cudamat* nn, cudamat* target, int max_draws);
 
 /* acc[0] += sum((a - b)^2), kept on the device (subtract + euclid_norm()**2 of
  * deepnet/logistic_layer.py:48-52 without the host round trip). */

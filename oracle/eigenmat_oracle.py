@@ -314,6 +314,14 @@ class EigenMatrix(object):
     def subtract_dot(self, m1, m2):
         return self.add_dot(m1, m2, -1.0)
 
+    def select_columns(self, indices, target):
+        _check(_lib.selectCols(self.p_mat, target.p_mat, indices.p_mat))
+        return target
+
+    def swap_columns(self, indices1, indices2, target):
+        _check(_lib.swapCols(self.p_mat, target.p_mat, indices1.p_mat, indices2.p_mat))
+        return target
+
     def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0):
         """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass (self is the parameter)."""
         _check(_lib.momentum_update(self.p_mat, delta.p_mat, grad.p_mat, suff.p_mat, ct.c_float(inv_batch),

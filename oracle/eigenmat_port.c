@@ -424,6 +424,34 @@ int dot(const eigenmat* mat1, const eigenmat* mat2, eigenmat* target, float beta
   return 0;
 }
 
+/* ------------------------------------------------------------------ index ops */
+
+/* eigenmat/eigenmat.cc:1321-1335 (selectCols): target[:, i] = source[:, indices[i]]. */
+int selectCols(const eigenmat* source, eigenmat* target, const eigenmat* indices) {
+  const int n = indices->size[0] * indices->size[1], h = source->size[0];
+  if (target->size[0] != h || target->size[1] != n) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  for (int i = 0; i < n; i++) {
+    int s = (int)indices->data[i];
+    if (s < 0) s += source->size[1];   /* cudamat/cudamat_kernels.cu:728-731 */
+    for (int j = 0; j < h; j++) target->data[(long)i * h + j] = source->data[(long)s * h + j];
+  }
+  return 0;
+}
+
+/* eigenmat/eigenmat.cc:1351-1367 (swapCols): column indices1[i] of source <-> column indices2[i] of target. */
+int swapCols(eigenmat* source, eigenmat* target, const eigenmat* indices1, const eigenmat* indices2) {
+  const int n = indices1->size[0] * indices1->size[1], h = source->size[0];
+  for (int i = 0; i < n; i++) {
+    const long so = (long)(int)indices1->data[i] * h, to = (long)(int)indices2->data[i] * h;
+    for (int j = 0; j < h; j++) {
+      const float temp = target->data[to + j];
+      target->data[to + j] = source->data[so + j];
+      source->data[so + j] = temp;
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------------ parameter update */
 
 /* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass, in the order the

@@ -92,6 +92,64 @@ def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases):
     assert cm.read_status() == 0
 
 
+def test_fused_softmax_ops_match_the_call_sequence(cm, oracle):
+    rng = np.random.default_rng(21)
+    V, B = 400, 12
+    pre = rng.standard_normal((V, B)).astype(np.float32) * 2
+    lens = rng.integers(1, 60, (1, B)).astype(np.float32)
+    lens[0, 3] = 1030                                   # more draws than the 1000-draw cap
+    # activation: NN * softmax, against replicated_softmax_layer.py:12-21 issued call by call on the oracle
+    st, tmp, nn = oracle.CUDAMatrix(pre), oracle.empty((1, B)), oracle.CUDAMatrix(lens)
+    st.max(axis=0, target=tmp)
+    st.add_row_mult(tmp, -1)
+    oracle.exp(st)
+    st.sum(axis=0, target=tmp)
+    nn.divide(tmp, target=tmp)
+    st.mult_by_row(tmp)
+    g = cm.CUDAMatrix(pre).softmax_scaled(cm.CUDAMatrix(lens), target=cm.empty((V, B)))
+    assert relerr(get(g), get(st)) < TOL
+    # sampling: fused kernel vs the per-document loop of the call-by-call layer, same stream
+    from deepnet_b200 import dbm
+    counts = {}
+    for backend in (cm, oracle):
+        lay = dbm.ReplicatedSoftmaxLayer(backend, "v", V, dbm.Hyperparams(sample_input=True), is_input=True)
+        lay.AllocateMemory(B)
+        lay.state.assign(backend.CUDAMatrix(get(st)))
+        lay.NN.assign(backend.CUDAMatrix(lens))
+        backend.CUDAMatrix.init_random(5)
+        lay.Sample()
+        counts[backend] = get(lay.sample)
+    cm.CUDAMatrix.init_random(5)
+    fused = get(cm.CUDAMatrix(get(st)).sample_multinomial(cm.CUDAMatrix(lens), cm.empty((V, B))))
+    np.testing.assert_array_equal(fused, counts[cm])          # same GPU arithmetic: identical counts
+    assert np.abs(fused - counts[oracle]).sum() <= 4           # libm vs GPU logf may move a rare near-tie
+    np.testing.assert_array_equal(fused.sum(axis=0), np.minimum(lens.ravel(), 1000))
+    assert cm.CUDAMatrix.rnd_state.calls == B
+
+
+def test_fused_engine_replicated_softmax_matches_oracle(cm, oracle):
+    # config 2 at 1/50 size through the fused engine against the call-by-call driver on the oracle
+    cases = 200
+    cfg = configs.build(2, cases=cases, dims_scale=0.02)
+    B, steps = cfg["batchsize"], 2
+    mo, lo = run_driver(oracle, cfg, cases, steps)
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"], visible=dbm.REPLICATED_SOFTMAX,
+                   seed=cfg["seed"])
+    data = cm.CUDAMatrix(cfg["data"])
+    lg = []
+    for step in range(steps):
+        eng.TrainOneBatch(step, data.slice(step * B, (step + 1) * B))
+        lg.append(eng.read_loss())
+    np.testing.assert_allclose(lg, lo, rtol=1e-4)
+    np.testing.assert_array_equal(get(eng.v_samp), get(mo.GetLayerByName("v").sample))
+    np.testing.assert_array_equal(get(eng.h_samp), get(mo.GetLayerByName("h").sample))
+    assert relerr(get(eng.W), get(mo.edge[0].params["weight"])) < TOL
+    assert relerr(get(eng.dW), get(mo.edge[0].gradient_history)) < 2 * TOL
+    assert relerr(get(eng.v_neg), get(mo.GetLayerByName("v").state)) < TOL
+    assert cm.read_status() == 0
+
+
 def test_reconstruction_error_curve_within_two_percent(cm, oracle):
     cases, steps = 1000, 60
     cfg = configs.build(0, cases=cases, dims_scale=0.25)
