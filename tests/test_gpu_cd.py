@@ -150,6 +150,34 @@ def test_fused_engine_replicated_softmax_matches_oracle(cm, oracle):
     assert cm.read_status() == 0
 
 
+def test_fused_dbm_matches_oracle(cm, oracle):
+    # config 3 (784-500-1000 DBM, 10 mean-field + 5 Gibbs sweeps, PCD) at 1/10 and at full size
+    from deepnet_b200.fused_dbm import FusedDBM
+    for scale, cases, steps in ((0.1, 300, 3), (1.0, 200, 2)):
+        cfg = configs.build(3, cases=cases, dims_scale=scale)
+        B = cfg["batchsize"]
+        mo, lo = run_driver(oracle, cfg, cases, steps)
+        sizes = [l["numdims"] for l in cfg["layers"]]
+        eng = FusedDBM(cm, sizes, B, [e["weight"] for e in cfg["edges"]], cfg["hyperparams"], seed=cfg["seed"])
+        data = cm.CUDAMatrix(cfg["data"])
+        lg = []
+        for step in range(steps):
+            s = (step % (cases // B)) * B
+            eng.TrainOneBatch(step, data.slice(s, s + B))
+            lg.append(eng.read_loss())
+        np.testing.assert_allclose(lg, lo, rtol=1e-5)
+        for i, e in enumerate(mo.edge):
+            assert relerr(get(eng.W[i]), get(e.params["weight"])) < TOL
+            assert relerr(get(eng.dW[i]), get(e.gradient_history)) < 2 * TOL
+        for j, l in enumerate(mo.layer):
+            assert relerr(get(eng.neg[j]), get(l.neg_state)) < TOL, l.name          # persistent particles
+            assert relerr(get(eng.pos[j]), get(l.pos_state)) < TOL, l.name          # mean-field activations
+            if j > 0:
+                np.testing.assert_array_equal(get(eng.neg_sample[j]), get(l.neg_sample))
+            assert np.abs(get(eng.b[j]) - get(l.params["bias"])).max() < 1e-6
+    assert cm.read_status() == 0
+
+
 def test_reconstruction_error_curve_within_two_percent(cm, oracle):
     cases, steps = 1000, 60
     cfg = configs.build(0, cases=cases, dims_scale=0.25)
