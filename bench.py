@@ -92,6 +92,14 @@ class ClockSampler(object):
 
 def make_engine(cm, cfg, world, rank):
     from deepnet_b200.fused_rbm import FusedRBM
+    if len(cfg["layers"]) > 2:
+        from deepnet_b200.fused_dbm import FusedDBM
+        if world > 1:
+            raise SystemExit("the DBM configuration is benchmarked on one GPU")
+        eng = FusedDBM(cm, [l["numdims"] for l in cfg["layers"]], cfg["batchsize"], [e["weight"] for e in cfg["edges"]],
+                       cfg["hyperparams"], seed=cfg["seed"])
+        eng.timeline = None
+        return eng
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     return FusedRBM(cm, V, H, cfg["batchsize"], cfg["edges"][0]["weight"], cfg["hyperparams"],
                     edge_hyperparams=cfg["edges"][0].get("hyperparams"), visible=cfg["layers"][0]["activation"],
@@ -109,7 +117,7 @@ def workload(config, cases):
         cfg["data"] = data
     else:
         cfg = configs.build(config, cases=cases)
-    cfg["binary"] = config in (0, 3, 4)
+    cfg["binary"] = config in (0, 2, 3, 4)   # inputs exact in TF32 (0/1 or small integer counts)
     return cfg
 
 
@@ -157,6 +165,9 @@ def run_ours(args):
             cfg["data"], _ = synthetic.binary_data(8192, pool * B, 1004 + 7919 * rank)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     k = cfg["hyperparams"].gibbs_steps
+    if config in (2, 3):
+        pool = 2
+        cfg["data"] = cfg["data"][:, :pool * B]
     eng = make_engine(cm, cfg, world, rank)
 
     # ---- device-resident inputs --------------------------------------------------------
@@ -207,21 +218,29 @@ def run_ours(args):
     # dominant kernel: the up half-step product (k_gemm_tc, sigmoid + Bernoulli epilogue),
     # the largest share of the step.  achieved = algorithmic flops of one launch (2 V H B)
     # / its mean CUDA-event duration inside the timed region.
-    up = agg["gemm_up"]
-    achieved = up[2] / (up[1] * 1e-3) / 1e12
-    roofline = dict(bound="tensor", achieved=round(achieved, 2), peak=peaks["tensor"], unit="TFLOP/s",
-                    frac=round(achieved / peaks["tensor"], 4),
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
-                    # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
-                    traffic=3.17e9 if config == 4 else None,
-                    kernel="k_gemm_tc<256, sigmoid+split+Bernoulli> (tcgen05 kind::tf32, 3 split-TF32 passes)",
-                    peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
-                                "and 3 passes make one fp32-grade product" % peaks["source"],
-                    launches=up[0], ms_per_launch=round(up[1] / up[0], 4),
-                    share_of_step=round(up[1] / ms, 4) if world == 1 else None,
-                    all_gemm_algorithmic_tflops=round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 2),
-                    all_gemm_tf32_issued_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2),
-                    all_gemm_share_of_step=round(gemm_ms / ms, 4) if world == 1 else None)
+    up = agg.get("gemm_up")
+    if up is None:
+        # no per-launch events for this engine: algorithmic flops of the whole update / its time
+        achieved = configs.flops_per_example(config) * B / (ms / args.steps * 1e-3) / 1e12
+        roofline = dict(bound="tensor", achieved=round(achieved, 3), peak=peaks["tensor"], unit="TFLOP/s",
+                        frac=round(achieved / peaks["tensor"], 5), traffic=None,
+                        kernel="k_gemm_tc (whole update; launch-latency-bound at this size)",
+                        peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json)" % peaks["source"])
+    else:
+      achieved = up[2] / (up[1] * 1e-3) / 1e12
+      roofline = dict(bound="tensor", achieved=round(achieved, 2), peak=peaks["tensor"], unit="TFLOP/s",
+                      frac=round(achieved / peaks["tensor"], 4),
+                      # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
+                      # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
+                      traffic=3.17e9 if config == 4 else None,
+                      kernel="k_gemm_tc<256, sigmoid+split+Bernoulli> (tcgen05 kind::tf32, 3 split-TF32 passes)",
+                      peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
+                                  "and 3 passes make one fp32-grade product" % peaks["source"],
+                      launches=up[0], ms_per_launch=round(up[1] / up[0], 4),
+                      share_of_step=round(up[1] / ms, 4) if world == 1 else None,
+                      all_gemm_algorithmic_tflops=round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 2),
+                      all_gemm_tf32_issued_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2),
+                      all_gemm_share_of_step=round(gemm_ms / ms, 4) if world == 1 else None)
 
     # ---- end to end: host batches in, loss out, every step --------------------------------
     host = []
@@ -330,11 +349,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=4, help="benchmark configuration 0, 1 or 4 (RBMs on the fused engine)")
+    ap.add_argument("--config", type=int, default=4, help="benchmark configuration 0..4 (default 4, the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.config not in (0, 1, 4):
-        raise SystemExit("bench.py runs the RBM configurations 0, 1 and 4")
+    if args.config not in (0, 1, 2, 3, 4):
+        raise SystemExit("--config must be 0..4")
     if args.impl == "reference":
         out = run_reference(args)
         if out is not None:
