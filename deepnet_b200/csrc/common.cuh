@@ -99,7 +99,9 @@ __device__ __forceinline__ uint32_t pick_word(const uint4& w, int i) {
 
 // 1 / (1 + exp(-x)) with the accurate expf (the reference's fast __expf of
 // cudamat_kernels.cu:404 would miss the 1e-5 relative bound against libm).
-__device__ __forceinline__ float sigmoid_accurate(float x) { return 1.0f / (1.0f + expf(-x)); }
+// The reciprocal is the correctly rounded one, which for a numerator of exactly 1 equals the
+// IEEE quotient 1.0f / (1.0f + expf(-x)) bit for bit, without the division's slow path.
+__device__ __forceinline__ float sigmoid_accurate(float x) { return __frcp_rn(1.0f + expf(-x)); }
 
 // Split x = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits zero)
 // and lo = x - hi (exact in fp32).  The tensor core reads only the TF32 bits of lo.

@@ -71,7 +71,16 @@ struct TcParams {
   int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
   GemmEpilogue epi;
   int* status;
+#ifdef B200_GEMM_TIMING
+  unsigned long long* dbg;   // per CTA: issuer total, wait-full, wait-tmem-empty; producer wait-empty; epilogue wait
+#endif
 };
+#ifdef B200_GEMM_TIMING
+#define TIMED_WAIT(acc_var, call) \
+  [&]() { const long long t0 = clock64(); const bool r = (call); acc_var += clock64() - t0; return r; }()
+#else
+#define TIMED_WAIT(acc_var, call) (call)
+#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -209,8 +218,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // Tile order: groups of 16 row tiles sweep the column tiles, so that one wave of
 // CTAs shares a compact set of A and B panels in L2.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int GM = 16;
+template <int GM>
+__device__ __forceinline__ void tile_coords_g(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = GM * tiles_n;
   const int g = t / per_group;
   const int first = g * GM;
@@ -219,6 +228,9 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tm = first + r % gsize;
   tn = r / gsize;
 }
+// One wave of CTAs should cover about as many A rows as B rows: 16 row tiles of 128 (one CTA per
+// tile) or 8 row tiles of 256 (paired CTAs) against about 9 column tiles of 256.
+#define tile_coords(t, tiles_m, tiles_n, tm, tn) tile_coords_g<(kTwo ? 8 : 16)>(t, tiles_m, tiles_n, tm, tn)
 
 // The tensor core adds into its fp32 accumulator with truncation, not round-to-nearest:
 // a same-sign sum loses about 0.6 ulp per tcgen05.mma (-646 ulp measured at K = 8192,
@@ -313,6 +325,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       const int opi = lane >> 3, box = lane & 7;
+      long long t_empty = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -334,7 +347,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           const uint32_t dst_off = op.smem_off + (op.mn ? (uint32_t)(box * bk * 128) : 0u);
           const int mn = op.mn;
           for (int kb = 0; kb < k_iters; kb++) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) {
+            if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag))) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 1);
               abort_flag = 1;
@@ -357,6 +370,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
+#ifdef B200_GEMM_TIMING
+      if (p.dbg && lane == 0) p.dbg[blockIdx.x * 8 + 3] = (unsigned long long)t_empty;
+#else
+      (void)t_empty;
+#endif
       if (!ok && lane == 0) {
         // let copies already issued land before the CTA leaves
         for (int s = 0; s < num_stages; s++) {
@@ -375,6 +393,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       const int ksteps = bk / 8;
+      long long t_full = 0, t_tempty = 0;
+      const long long t_start = clock64();
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int in_tile = 0, in_chunk = 0;
         uint32_t fresh = 1;
@@ -403,7 +423,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             const int acc = chunk & 1;
             if (in_chunk == 0) {
               // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
-              if (!mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag)) {
+              if (!TIMED_WAIT(t_tempty, mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag))) {
                 ok = false;
                 if (!abort_flag) atomicCAS(p.status, 0, 2);
                 abort_flag = 1;
@@ -412,13 +432,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               tc_fence_after();
               fresh = 1;
             }
-            if (!mbar_wait(full_bar(stage), phase, &abort_flag)) {
+            if (!TIMED_WAIT(t_full, mbar_wait(full_bar(stage), phase, &abort_flag))) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 3);
               abort_flag = 1;
               break;
             }
-            tc_fence_after();
+            // No tcgen05 fence here: the stage was filled by TMA (async proxy, ordered by the
+            // mbarrier); a fence per k-block would make the issuer wait for the MMAs in flight.
             const uint32_t d_tmem = tmem_base + acc * BN;
             const uint32_t sb = (smem_base + stage * stage_bytes) >> 4;   // stage address, 16-byte units
 #pragma unroll
@@ -455,6 +476,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
+#ifdef B200_GEMM_TIMING
+      if (p.dbg) {
+        p.dbg[blockIdx.x * 8 + 0] = (unsigned long long)(clock64() - t_start);
+        p.dbg[blockIdx.x * 8 + 1] = (unsigned long long)t_full;
+        p.dbg[blockIdx.x * 8 + 2] = (unsigned long long)t_tempty;
+      }
+#else
+      (void)t_full; (void)t_tempty; (void)t_start;
+#endif
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
@@ -469,6 +499,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     const int pM = p.M, pN = p.N;
     const int nchunks = (total_k_iters + kChunkIters - 1) / kChunkIters;
     bool ok = true;
+    long long t_tfull = 0, t_epi = 0;
     for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -477,7 +508,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       for (int j = 0; j < COLS; j++) accum[j] = 0.0f;
       for (int c = 0; c < nchunks; c++, chunk++) {
         const int acc = chunk & 1;
-        if (!mbar_wait(tfull_bar(acc), (chunk >> 1) & 1u, &abort_flag)) {
+        if (!TIMED_WAIT(t_tfull, mbar_wait(tfull_bar(acc), (chunk >> 1) & 1u, &abort_flag))) {
           if (!abort_flag) atomicCAS(p.status, 0, 4);
           abort_flag = 1;
           ok = false;
@@ -501,6 +532,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         }
       }
       if (!ok) break;
+#ifdef B200_GEMM_TIMING
+      const long long t_e0 = clock64();
+#endif
       const int m = tm * TILE_M + (int)rank * BM + wq * 32 + lane;
       const int nc = tn * BN + col_base;
       if (m < pM && nc < pN) {
@@ -578,7 +612,18 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
+#ifdef B200_GEMM_TIMING
+      t_epi += clock64() - t_e0;
+#endif
     }
+#ifdef B200_GEMM_TIMING
+    if (p.dbg && threadIdx.x == 64) {
+      p.dbg[blockIdx.x * 8 + 4] = (unsigned long long)t_tfull;
+      p.dbg[blockIdx.x * 8 + 5] = (unsigned long long)t_epi;
+    }
+#else
+    (void)t_tfull; (void)t_epi;
+#endif
   }
 
   // ---------------------------------------------------------------- teardown
@@ -793,6 +838,9 @@ int gemm_tc(const GemmProblem& g) {
   p.N = g.N;
   p.epi = g.epi;
   p.status = status_word();
+#ifdef B200_GEMM_TIMING
+  p.dbg = (unsigned long long*)workspace(7, 8 * 512 * sizeof(unsigned long long));
+#endif
 
   // ---- group consecutive passes that share K and need at most two distinct A and B operands
   struct HostGroup {
@@ -919,3 +967,12 @@ int gemm_tc(const GemmProblem& g) {
 }
 
 }  // namespace b200
+
+#ifdef B200_GEMM_TIMING
+// Debug build only: copies the per-CTA cycle counters of the last launch (8 words per CTA).
+extern "C" int b200_gemm_timing(unsigned long long* out, int nctas) {
+  cudaStreamSynchronize(b200::stream());
+  void* ws = b200::workspace(7, 8 * 512 * sizeof(unsigned long long));
+  return cudaMemcpy(out, ws, (size_t)nctas * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
+}
+#endif

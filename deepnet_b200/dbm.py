@@ -500,6 +500,28 @@ class DBM(object):
         if edge.num_grads_received == edge.num_shares:
             edge.Update("weight", step)
 
+    def Inference(self, data, layernames, batchsize=None, input_recon=False):
+        """Representations of `data` (dims x cases device matrix) at the named layers.
+
+        deepnet/dbm.py:340-398 (Inference / WriteRepresentationToDisk) without the disk writer:
+        per minibatch a positive phase with train=False, then each layer's state transposed to
+        (cases x dims).  With input_recon the input is also reconstructed (evaluate=True) and
+        the summed squared error returned under the key 'error'.
+        """
+        B = batchsize or self.batchsize
+        n = data.shape[1] // B
+        reps = dict((name, np.zeros((n * B, self.GetLayerByName(name).numdims), np.float32)) for name in layernames)
+        err = 0.0
+        for b in range(n):
+            self.SetBatch([data.slice(b * B, (b + 1) * B)])
+            losses = self.PositivePhase(train=False, evaluate=input_recon)
+            err += float(np.sum(losses)) if losses else 0.0
+            for name in layernames:
+                reps[name][b * B:(b + 1) * B, :] = np.array(self.GetLayerByName(name).state.asarray()).T
+        if input_recon:
+            reps["error"] = err
+        return reps
+
     def SetBatch(self, data_by_layer):
         """Stand-in for GetTrainBatch (deepnet/neuralnet.py:628-632): data is a device matrix per input."""
         for node, d in zip(self.input_datalayer, data_by_layer):

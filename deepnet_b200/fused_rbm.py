@@ -197,6 +197,46 @@ class FusedRBM(object):
         self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
                  l1=l1, w_lo=Wl)
 
+    def Inference(self, data, input_recon=False):
+        """Hidden representation of `data` (V x cases device matrix), minibatch by minibatch:
+        the inference-only positive phase of deepnet/dbm.py:340-398 (extract_rbm_representation.py)
+        as one fused product per minibatch.  Returns (cases x H) host array, and with input_recon
+        also the summed squared error of the input reconstructed from the hidden means."""
+        cm, B, W, Wl = self.cm, self.B, self.W, self.W_lo
+        n = data.shape[1] // B
+        rep = np.zeros((n * B, self.H), np.float32)
+        err = 0.0
+        soft = self.visible == REPLICATED_SOFTMAX
+        for b in range(n):
+            v0 = data.slice(b * B, (b + 1) * B)
+            if soft:
+                v0.sum(axis=0, target=self.NN)
+                self.NN.add(self.tiny)
+                up = [(Wl.T, v0), (W.T, v0)]
+            elif self.binary_data:
+                up = [(Wl.T, v0), (W.T, v0)]
+            else:
+                v0.split_tf32(self.data_lo)
+                up = [(Wl.T, v0), (W.T, self.data_lo), (W.T, v0)]
+            cm.fused_gemm(up, out=self.h_pos, out_lo=self.h_pos_lo, bias=self.bh, activation=1,
+                          col_scale=self.NN if soft else None)
+            if input_recon:
+                down = [(Wl, self.h_pos), (W, self.h_pos_lo), (W, self.h_pos)]
+                if soft:
+                    cm.fused_gemm(down, out=self.v_neg_lo, bias=self.bv, activation=0)
+                    self.v_neg_lo.softmax_scaled(self.NN, target=self.v_neg)
+                    self.v_neg.div_by_row(self.NN, target=self.v_negn)
+                    cm._check(cm._lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat, self.loss_acc.p_mat))
+                else:
+                    cm.fused_gemm(down, out=self.v_neg, out_lo=self.v_neg_lo, bias=self.bv,
+                                  activation=self._act(self.visible))
+                    cm._check(cm._lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat, self.loss_acc.p_mat))
+            rep[b * B:(b + 1) * B, :] = np.array(self.h_pos.asarray()).T
+        if input_recon:
+            err = self.read_loss()
+            return rep, err
+        return rep
+
     def read_loss(self, reset=True):
         """Sum of squared reconstruction errors accumulated since the last reset (blocks)."""
         v = float(np.array(self.loss_acc.asarray())[0, 0])

@@ -178,6 +178,26 @@ def test_fused_dbm_matches_oracle(cm, oracle):
     assert cm.read_status() == 0
 
 
+@pytest.mark.parametrize("config,scale,cases", [(0, 0.25, 300), (1, 0.0625, 512), (2, 0.02, 200)])
+def test_inference_path_matches_oracle(cm, oracle, config, scale, cases):
+    # representation extraction: positive phase only, no sampling, no statistics (deepnet/dbm.py:340-398)
+    cfg = configs.build(config, cases=cases, dims_scale=scale)
+    B = cfg["batchsize"]
+    mo = dbm.DBM(oracle, cfg["layers"], cfg["edges"], cfg["hyperparams"], B, cfg["optimizer"], seed=cfg["seed"])
+    want = mo.Inference(oracle.CUDAMatrix(cfg["data"]), ["h"], input_recon=True)
+    mg = dbm.DBM(cm, cfg["layers"], cfg["edges"], cfg["hyperparams"], B, cfg["optimizer"], seed=cfg["seed"])
+    got = mg.Inference(cm.CUDAMatrix(cfg["data"]), ["h"], input_recon=True)
+    assert relerr(got["h"], want["h"]) < TOL
+    assert abs(got["error"] - want["error"]) < 1e-5 * want["error"]
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"], visible=cfg["layers"][0]["activation"],
+                   binary_data=(config != 1), seed=cfg["seed"])
+    rep, err = eng.Inference(cm.CUDAMatrix(cfg["data"]), input_recon=True)
+    assert rep.shape == want["h"].shape
+    assert relerr(rep, want["h"]) < TOL
+    assert abs(err - want["error"]) < 1e-5 * want["error"]
+
+
 def test_reconstruction_error_curve_within_two_percent(cm, oracle):
     cases, steps = 1000, 60
     cfg = configs.build(0, cases=cases, dims_scale=0.25)
