@@ -34,7 +34,10 @@ namespace {
 constexpr int BM = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
 constexpr int kMaxStages = 8;
-constexpr int kStageBudget = 225 * 1024;      // shared memory available to the operand ring
+constexpr int kStageBudget = 193 * 1024;      // shared memory available to the operand ring
+constexpr int kOutStageBytes = 32 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
+constexpr int kOutCols = 4;                    // columns per staged batch (one Philox block)
+constexpr int kOutArrays = 4;                  // out, out_hi, out_lo, sample
 
 // One operand tile of a k-block: where it comes from and how tcgen05 must read it.
 struct TcOperand {
@@ -61,7 +64,7 @@ struct TcGroup {
 };
 
 struct TcParams {
-  CUtensorMap maps[2 * kMaxPass];
+  CUtensorMap maps[2 * kMaxPass + kOutArrays];   // operands, then the outputs an activation epilogue stores
   TcGroup group[kMaxPass];
   int ngroups;
   int M, N, tiles_m, tiles_n;
@@ -70,6 +73,7 @@ struct TcParams {
   uint32_t stage_bytes;    // ring pitch
   int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
   GemmEpilogue epi;
+  int out_map[kOutArrays];   // tensor maps (indices into maps) of out, out_hi, out_lo, sample for TMA stores; -1 = absent
   int* status;
 #ifdef B200_GEMM_TIMING
   unsigned long long* dbg;   // per CTA: issuer total, wait-full, wait-tmem-empty; producer wait-empty; epilogue wait
@@ -119,6 +123,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar));
+}
+
+// Shared -> global tile store (clipped at the tensor's edges), tracked by bulk async-groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+               "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -245,7 +266,7 @@ template <int BN>
 struct TcConfig {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kColsPerWarp = BN / 2;   // each lane quarter is shared by two epilogue warps
-  static constexpr int kSmemBytes = kStageBudget + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStageBudget + kOutStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // Epilogue variants, chosen on the host.  The common cases are compiled without run-time
@@ -263,7 +284,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   using Cfg = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + kStageBudget;
+  const uint32_t out_stage_base = smem_base + kStageBudget;
+  const uint32_t bar_base = out_stage_base + kOutStageBytes;
   // barrier layout (8 bytes each): full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
@@ -552,65 +574,82 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             for (int j = 0; j < COLS; j++)
               if (j < ncols) out[j * ldo] = alpha * accum[j] + beta * out[j * ldo];
           }
-        } else if (kEpi == kEpiSigLo || kEpi == kEpiSigLoSample || kEpi == kEpiLinLo) {
-          // host guarantees: bias, out, out_lo set; beta = 0; no col_scale, no out_hi
-          const long off = (long)nc * e.ldo + m, ldo = e.ldo;
-          float* const out = e.out + off;
-          float* const out_lo = e.out_lo + off;
-          float* const smp = kEpi == kEpiSigLoSample ? e.sample + off : nullptr;
-          const float alpha = e.alpha, bias = e.bias[m];
-          const int ncols = pN - nc < COLS ? pN - nc : COLS;
-          const PhiloxKey key = e.key;
-          const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
+        }
+      }
+      if (kEpi != kEpiPlain) {
+        // Activation epilogues leave through shared memory and TMA stores.  Per-thread global
+        // stores (three arrays, 128 columns, 32 KB apart) cost 55 us per tile here against 7 us
+        // for the arithmetic; a batch of four columns (one Philox block) is staged as
+        // [array][column][128 rows], and one thread of each column-half group of four warps
+        // sends it on with cp.async.bulk.tensor while the next batch is computed (two buffers).
+        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias, out, out_lo set; beta = 0;
+                                                    // no col_scale, no out_hi
+        const bool row_ok = m < pM;
+        const int hf = ew >> 2;                     // column half = store group
+        const bool leader = (ew & 3) == 0 && lane == 0;
+        const int row = wq * 32 + lane;             // row of the CTA's 128
+        const float alpha = e.alpha, beta = spec ? 0.0f : e.beta;
+        const float bias = ((spec || e.bias) && row_ok) ? e.bias[m] : 0.0f;
+        const bool logistic = spec ? (kEpi != kEpiLinLo) : (e.activation == 1);
+        const bool draw = spec ? (kEpi == kEpiSigLoSample) : (e.sample != nullptr);
+        const bool has_out = spec || e.out != nullptr;
+        const bool has_hi = !spec && e.out_hi != nullptr;
+        const bool has_lo = spec || e.out_lo != nullptr;
+        const PhiloxKey key = e.key;
+        const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
+        const long off = (long)nc * e.ldo + m, ldo = e.ldo;
+        const int m_tile = tm * TILE_M + (int)rank * BM;     // first row of this CTA's part of the tile
+        constexpr uint32_t kArrayBytes = kOutCols * BM * 4;   // one array of a batch
+        constexpr uint32_t kBufBytes = kOutArrays * kArrayBytes;
+        const uint32_t group_base = out_stage_base + (uint32_t)hf * 2u * kBufBytes;
 #pragma unroll
-          for (int g4 = 0; g4 < COLS / 4; g4++) {
-            if (4 * g4 < ncols) {
-              uint4 w = make_uint4(0, 0, 0, 0);
-              if (kEpi == kEpiSigLoSample) w = philox4x32_10((uint32_t)m, cblk0 + g4, key);
+        for (int g4 = 0; g4 < COLS / 4; g4++) {
+          const int c0 = nc + 4 * g4;               // first global column of the batch
+          float x[4];
 #pragma unroll
-              for (int j = 0; j < 4; j++) {
-                if (4 * g4 + j < ncols) {
-                  float x = alpha * accum[4 * g4 + j] + bias;
-                  if (kEpi != kEpiLinLo) x = sigmoid_accurate(x);
-                  float hi, lo;
-                  split_tf32(x, hi, lo);
-                  out[(4 * g4 + j) * ldo] = x;
-                  out_lo[(4 * g4 + j) * ldo] = lo;
-                  if (kEpi == kEpiSigLoSample)
-                    smp[(4 * g4 + j) * ldo] = word_to_uniform(pick_word(w, j)) < x ? 1.0f : 0.0f;
-                }
-              }
+          for (int j = 0; j < 4; j++) {
+            float t = alpha * accum[4 * g4 + j];
+            if (!spec) {
+              if (beta != 0.0f && row_ok && c0 + j < pN) t += beta * e.out[off + (long)(4 * g4 + j) * ldo];
+              if (e.bias) t += e.col_scale ? (c0 + j < pN ? bias * e.col_scale[c0 + j] : 0.0f) : bias;
+            } else {
+              t += bias;
+            }
+            x[j] = logistic ? sigmoid_accurate(t) : t;
+          }
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (draw) w = philox4x32_10((uint32_t)m, cblk0 + g4, key);
+          // buffer (g4 & 1) is free once the stores of batch g4 - 2 have read it (the leader waited)
+          named_bar_sync(1 + hf, 128);
+          const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes + (uint32_t)row * 4u;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const uint32_t a = buf + (uint32_t)j * (BM * 4);
+            float hi, lo;
+            split_tf32(x[j], hi, lo);
+            if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x[j]) : "memory");
+            if (has_hi) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + kArrayBytes), "f"(hi) : "memory");
+            if (has_lo) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 2 * kArrayBytes), "f"(lo) : "memory");
+            if (draw) {
+              const float sbit = word_to_uniform(pick_word(w, j)) < x[j] ? 1.0f : 0.0f;
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 3 * kArrayBytes), "f"(sbit) : "memory");
             }
           }
-        } else {
-          float bias = 0.0f;
-          if (e.bias) bias = e.bias[m];
-#pragma unroll
-          for (int g4 = 0; g4 < COLS / 4; g4++) {
-            uint4 w = make_uint4(0, 0, 0, 0);
-            if (e.sample && nc + 4 * g4 < pN)
-              w = philox4x32_10((uint32_t)m, (uint32_t)((nc + 4 * g4 + e.col0) >> 2), e.key);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const int n = nc + 4 * g4 + j;
-              if (n < pN) {
-                const long idx = (long)n * e.ldo + m;
-                float x = e.alpha * accum[4 * g4 + j];
-                if (e.beta != 0.0f) x += e.beta * e.out[idx];
-                if (e.bias) x += e.col_scale ? bias * e.col_scale[n] : bias;
-                if (e.activation == 1) x = sigmoid_accurate(x);
-                if (e.out) e.out[idx] = x;
-                if (e.out_hi || e.out_lo) {
-                  float hi, lo;
-                  split_tf32(x, hi, lo);
-                  if (e.out_hi) e.out_hi[idx] = hi;
-                  if (e.out_lo) e.out_lo[idx] = lo;
-                }
-                if (e.sample) e.sample[idx] = word_to_uniform(pick_word(w, j)) < x ? 1.0f : 0.0f;
-              }
-            }
+          fence_async_smem();                       // generic-proxy writes visible to the TMA engine
+          named_bar_sync(1 + hf, 128);
+          if (leader && c0 < pN && m_tile < pM) {
+            const uint32_t src = group_base + (uint32_t)(g4 & 1) * kBufBytes;
+            if (has_out) tma_store_2d(&p.maps[p.out_map[0]], m_tile, c0, src);
+            if (has_hi) tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, src + kArrayBytes);
+            if (has_lo) tma_store_2d(&p.maps[p.out_map[2]], m_tile, c0, src + 2 * kArrayBytes);
+            if (draw) tma_store_2d(&p.maps[p.out_map[3]], m_tile, c0, src + 3 * kArrayBytes);
+          }
+          if (leader) {
+            tma_store_commit();
+            tma_store_wait_read<1>();               // the other buffer's stores have read it
           }
         }
+        if (leader) tma_store_wait_all();           // results are in memory before the kernel can end
       }
 #ifdef B200_GEMM_TIMING
       t_epi += clock64() - t_e0;
@@ -662,7 +701,7 @@ struct MapKey {
   const void* ptr;
   uint64_t d0, d1, ld;
   uint32_t b0, b1;
-  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle
+  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle, 3: none (output tiles)
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
   }
@@ -704,7 +743,8 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
   const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swz == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                                 : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
+                                 : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B)),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
@@ -753,6 +793,8 @@ bool fill_operand(TcOperand& op, CUtensorMap* map_slot, int map_index, const Gem
 inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
   return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
 }
+
+static_assert(sizeof(TcParams) <= 4096, "kernel parameter block");
 
 template <int BN, int kEpi, bool kTwo>
 int launch_tc(TcParams& p) {
@@ -819,6 +861,15 @@ bool gemm_tc_supported(const GemmProblem& g) {
     if (!tma_ok(g.pass[q].a) || !tma_ok(g.pass[q].b) || g.pass[q].k <= 0) return false;
   }
   if (g.epi.sample && (g.epi.col0 & 3)) return false;
+  // activation epilogues store whole column segments with TMA: 16-byte aligned columns
+  const GemmEpilogue& e = g.epi;
+  const bool plain = !e.bias && e.activation == 0 && !e.out_hi && !e.out_lo && !e.sample && e.out;
+  if (!plain) {
+    if (e.ldo % 4 != 0) return false;
+    const float* outs[kOutArrays] = {e.out, e.out_hi, e.out_lo, e.sample};
+    for (const float* o : outs)
+      if ((uintptr_t)o & 15) return false;
+  }
   return encode_fn() != nullptr;
 }
 
@@ -944,6 +995,17 @@ int gemm_tc(const GemmProblem& g) {
     }
   }
   const GemmEpilogue& e = g.epi;
+  {
+    // outputs of the activation epilogues: M x N, columns ldo apart, stored as 128-row x 4-column boxes
+    const float* outs[kOutArrays] = {e.out, e.out_hi, e.out_lo, e.sample};
+    for (int i = 0; i < kOutArrays; i++) {
+      p.out_map[i] = -1;
+      if (!outs[i]) continue;
+      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)e.ldo, BM, kOutCols, 3))
+        return set_error("cuTensorMapEncodeTiled failed for an output");
+      p.out_map[i] = nmaps++;
+    }
+  }
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.out_hi && !e.out_lo && !e.sample && e.out) {
     epi = kEpiPlain;
