@@ -97,11 +97,29 @@ __device__ __forceinline__ uint32_t pick_word(const uint4& w, int i) {
   return i == 0 ? w.x : (i == 1 ? w.y : (i == 2 ? w.z : w.w));
 }
 
-// 1 / (1 + exp(-x)) with the accurate expf (the reference's fast __expf of
-// cudamat_kernels.cu:404 would miss the 1e-5 relative bound against libm).
-// The reciprocal is the correctly rounded one, which for a numerator of exactly 1 equals the
-// IEEE quotient 1.0f / (1.0f + expf(-x)) bit for bit, without the division's slow path.
-__device__ __forceinline__ float sigmoid_accurate(float x) { return __frcp_rn(1.0f + expf(-x)); }
+// 1 / (1 + exp(-x)) to about 4e-7 relative (the reference's fast __expf of
+// cudamat_kernels.cu:404 loses up to 5e-6 at large |x| and would miss the 1e-5 bound against
+// libm).  exp(-x) = 2^y with y = -x * log2(e): the rounding of that product (exact residual
+// by fma) and the part of log2(e) a float drops are folded back as 2^y * (1 + r * ln 2), so
+// only the two special-function units' own errors remain (ex2.approx 2 ulp, rcp.approx
+// 1 ulp).  Branch-free: libm's expf and the correctly rounded reciprocal, with their range
+// checks and slow paths, made the tensor-core epilogue three times slower.  Saturates like
+// the quotient: 2^y = inf gives 0, a flushed 2^y gives 1, NaN stays NaN.
+__device__ __forceinline__ float sigmoid_accurate(float x) {
+  const float kL = -1.4426950408889634f;        // -log2(e) rounded to float
+  const float kLlo = -1.9259629911e-8f;         // -(log2(e) - float(log2(e)))
+  const float y = x * kL;
+  float r = fmaf(x, kL, -y);
+  r = fmaf(x, kLlo, r);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y));
+  // r is finite and tiny whenever e is finite and non-zero; e = inf or 0 must stay so
+  const float corr = (fabsf(y) < 126.0f) ? r * 0.6931471805599453f : 0.0f;
+  e = fmaf(e, corr, e);
+  float p;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(1.0f + e));
+  return p;
+}
 
 // Split x = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits zero)
 // and lo = x - hi (exact in fp32).  The tensor core reads only the TF32 bits of lo.

@@ -25,6 +25,11 @@ def test_unary_and_scalar_ops(cm, oracle, shape):
     g, o = both(cm, oracle, a)
     np.testing.assert_allclose(get(cm.sigmoid(g, target=cm.empty(shape))),
                                get(oracle.sigmoid(o, target=oracle.empty(shape))), rtol=1e-6, atol=1e-7)
+    # the whole finite range of exp(-x): saturation at both ends, no NaN
+    w = np.linspace(-100, 100, int(np.prod(shape)), dtype=np.float32).reshape(shape)
+    gw, ow = both(cm, oracle, w)
+    np.testing.assert_allclose(get(cm.sigmoid(gw, target=cm.empty(shape))),
+                               get(oracle.sigmoid(ow, target=oracle.empty(shape))), rtol=1e-6, atol=1.2e-38)  # results below the smallest normal are flushed
     np.testing.assert_allclose(get(cm.exp(g, target=cm.empty(shape))), np.exp(a), rtol=1e-6)
     np.testing.assert_allclose(get(cm.log_1_plus_exp(g, target=cm.empty(shape))),
                                get(oracle.log_1_plus_exp(o, target=oracle.empty(shape))), rtol=1e-5, atol=1e-6)
