@@ -1,6 +1,7 @@
 // Description of one fused matrix product shared by the tensor-core and the SIMT
 // kernels:  out = act(alpha * sum_p (+/-) op(A_p) . op(B_p) + beta * out + bias (x) scale)
-// with optional TF32 hi/lo split outputs and a Bernoulli draw of the result.
+// with an optional Bernoulli draw of the result and the bfloat16 companions ("aux" matrices)
+// that later products read.
 #pragma once
 #include "common.cuh"
 
@@ -14,9 +15,11 @@ struct GemmOperand {
   const float* ptr;
   int ld;
   int trans;
+  int bf16;   // 1: ptr addresses bfloat16 elements (one plane of an aux matrix) and ld counts them
 };
 
-// One term of the sum: op(a) is M x k, op(b) is k x N.
+// One term of the sum: op(a) is M x k, op(b) is k x N; both operands fp32 (read as TF32 on the
+// tensor cores) or both bfloat16.
 struct GemmPass {
   GemmOperand a, b;
   int k;
@@ -29,10 +32,11 @@ struct GemmEpilogue {
   const float* col_scale;  // N entries or null: the bias of column n is bias[m] * col_scale[n]
   int activation;          // 0 identity, 1 logistic
   float* out;              // M x N result (may be null when only split/sample outputs are wanted)
-  float* out_hi;           // TF32-exact high part of the result, or null
-  float* out_lo;           // result - out_hi, or null
+  float* out_aux;          // aux matrix (two bfloat16 planes, see split_aux) of the result, or null
   float* sample;           // Bernoulli(result) draw, or null
-  int ldo;                 // leading dimension of every output
+  float* sample_aux;       // aux matrix of the draw (only plane 1 is written: a 0/1 value has no low part), or null
+  int ldo;                 // leading dimension of every fp32 output
+  int ld_aux;              // floats per column of the aux outputs (rows rounded up to 8)
   PhiloxKey key;           // random stream of this call (used when sample != null)
   int col0;                // global column of output column 0
 };
@@ -63,13 +67,16 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc,
   if (e.bias) v += e.col_scale ? e.bias[m] * e.col_scale[n] : e.bias[m];
   if (e.activation == 1) v = sigmoid_accurate(v);
   if (e.out) e.out[idx] = v;
-  if (e.out_hi || e.out_lo) {
-    float hi, lo;
-    split_tf32(v, hi, lo);
-    if (e.out_hi) e.out_hi[idx] = hi;
-    if (e.out_lo) e.out_lo[idx] = lo;
+  const long aidx = (long)n * 2 * e.ld_aux + m;   // 16-bit word of plane 0
+  if (e.out_aux) {
+    uint16_t lo16, b16;
+    split_aux(v, lo16, b16);
+    reinterpret_cast<uint16_t*>(e.out_aux)[aidx] = lo16;
+    reinterpret_cast<uint16_t*>(e.out_aux)[aidx + e.ld_aux] = b16;
   }
-  if (e.sample) e.sample[idx] = u < v ? 1.0f : 0.0f;
+  const float s = u < v ? 1.0f : 0.0f;
+  if (e.sample) e.sample[idx] = s;
+  if (e.sample_aux) reinterpret_cast<uint16_t*>(e.sample_aux)[aidx + e.ld_aux] = s != 0.0f ? 0x3f80 : 0;
 }
 #endif
 

@@ -13,13 +13,17 @@ constexpr int TM = 64, TN = 64, TK = 16;
 __device__ __forceinline__ float as_operand(float x, int tf32) {
   return tf32 ? __uint_as_float(__float_as_uint(x) & 0xffffe000u) : x;
 }
+__device__ __forceinline__ float element(const GemmOperand& o, long i, int tf32) {
+  if (o.bf16) return bf16_to_float(reinterpret_cast<const uint16_t*>(o.ptr)[i]);
+  return as_operand(o.ptr[i], tf32);
+}
 __device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K, int tf32) {
   if (m >= M || k >= K) return 0.0f;
-  return as_operand(a.trans ? a.ptr[(long)m * a.ld + k] : a.ptr[(long)k * a.ld + m], tf32);
+  return element(a, a.trans ? (long)m * a.ld + k : (long)k * a.ld + m, tf32);
 }
 __device__ __forceinline__ float load_b(const GemmOperand& b, int k, int n, int K, int N, int tf32) {
   if (n >= N || k >= K) return 0.0f;
-  return as_operand(b.trans ? b.ptr[(long)k * b.ld + n] : b.ptr[(long)n * b.ld + k], tf32);
+  return element(b, b.trans ? (long)k * b.ld + n : (long)n * b.ld + k, tf32);
 }
 
 __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmProblem g) {
@@ -77,7 +81,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
       const int m = m0 + tx + 16 * i;
       if (m >= g.M) continue;
       float u = 0.0f;
-      if (e.sample) {
+      if (e.sample || e.sample_aux) {
         const int gc = n + e.col0;
         const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), e.key);
         u = word_to_uniform(pick_word(w, gc & 3));

@@ -37,29 +37,33 @@ constexpr int kMaxStages = 8;
 constexpr int kStageBudget = 193 * 1024;      // shared memory available to the operand ring
 constexpr int kOutStageBytes = 32 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
 constexpr int kOutCols = 4;                    // columns per staged batch (one Philox block)
-constexpr int kOutArrays = 4;                  // out, out_hi, out_lo, sample
+constexpr int kOutArrays = 5;                  // out, aux plane 0, aux plane 1, sample, plane 1 of the sample's aux
+constexpr int kMaxOperands = 3;                // distinct A (or B) tiles a k-block stages: x, and the two planes of its aux
 
 // One operand tile of a k-block: where it comes from and how tcgen05 must read it.
 struct TcOperand {
   int map;                 // index into TcParams::maps
-  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as 32-wide boxes)
+  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as 128-byte wide boxes)
+  int nboxes;              // TMA boxes per tile: 1 when K is contiguous, rows / box_rows otherwise
+  int box_rows;            // rows of M/N per box of an MN-major tile: 32 floats or 64 bfloat16
   uint32_t desc_hi;        // upper 32 bits of the shared-memory matrix descriptor
   uint32_t desc_lo;        // leading-byte-offset field (bits 16-29 of the low word)
-  uint32_t adv;            // descriptor advance per K = 8 step, in 16-byte units
+  uint32_t adv;            // descriptor advance per MMA (K = 8 floats or 16 bfloat16), in 16-byte units
   uint32_t smem_off;       // byte offset of the tile inside a stage
 };
 struct TcMma {
   int a, b;                // operand slots of the group
+  int f16;                 // 0: kind::tf32 (K = 8 per instruction), 1: kind::f16 on bfloat16 (K = 16)
   uint32_t idesc;          // tcgen05 instruction descriptor (carries the negate bit)
 };
 // A group = the passes that walk the same K range together.  Each k-block stages every
-// distinct operand tile once (at most two A and two B tiles: x and its TF32 remainder)
-// and issues all the group's products from that one stage.
+// distinct operand tile once (x and the two bfloat16 planes of its aux matrix, for A and
+// for B) and issues all the group's products from that one stage.
 struct TcGroup {
   int k_iters;             // ceil(k / bk)
   int nA, nB, nmma;
   uint32_t stage_tx;       // bytes TMA delivers per k-block
-  TcOperand A[2], B[2];
+  TcOperand A[kMaxOperands], B[kMaxOperands];
   TcMma mma[4];
 };
 
@@ -73,7 +77,7 @@ struct TcParams {
   uint32_t stage_bytes;    // ring pitch
   int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
   GemmEpilogue epi;
-  int out_map[kOutArrays];   // tensor maps (indices into maps) of out, out_hi, out_lo, sample for TMA stores; -1 = absent
+  int out_map[kOutArrays];   // tensor maps (indices into maps) of the outputs stored by TMA; -1 = absent
   int* status;
 #ifdef B200_GEMM_TIMING
   unsigned long long* dbg;   // per CTA: issuer total, wait-full, wait-tmem-empty; producer wait-empty; epilogue wait
@@ -162,6 +166,14 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
+}
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -204,6 +216,14 @@ __device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, 
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 // Arrives (once all earlier MMAs of this thread are done) on the barrier at this offset in
@@ -271,10 +291,11 @@ struct TcConfig {
 
 // Epilogue variants, chosen on the host.  The common cases are compiled without run-time
 // branches (they are instruction-bound otherwise):
-//   kEpiPlain   out = alpha * acc (+ beta * out)                      (`dot`, statistics)
-//   kEpiAct     out = act(alpha * acc + bias), out_lo = its TF32 remainder (act by kSigmoid)
-//   kEpiSample  kEpiAct plus sample = Bernoulli(out)
-//   kEpiGeneric every option tested at run time
+//   kEpiPlain        out = alpha * acc (+ beta * out)                  (`dot`, statistics)
+//   kEpiSigLo        out = logistic(alpha * acc + bias) and its aux matrix
+//   kEpiSigLoSample  kEpiSigLo plus sample = Bernoulli(out) and the sample's aux matrix
+//   kEpiLinLo        out = alpha * acc + bias and its aux matrix
+//   kEpiGeneric      every option tested at run time
 enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSigLo = 2, kEpiSigLoSample = 3, kEpiLinLo = 4 };
 
 // kTwo: two CTAs of a cluster share one 256 x BN tile (cta_group::2): each stages its own 128
@@ -339,14 +360,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // The whole warp runs the loop; lane l issues (at most) one box per k-block: operand l / 8
-    // (A0, A1, B0, B1), box l % 8 of it.  The refill of a freed stage is on the critical path of
-    // a ring this shallow, so every constant sits in registers and a lane issues one copy only.
+    // The whole warp runs the loop; copy u = 8 * operand + box (operands A0..A2, B0..B2, up to 8
+    // boxes each) is issued by lane u % 32, so a lane issues at most two copies per k-block.  The
+    // refill of a freed stage is on the critical path of a ring this shallow: every constant
+    // sits in registers.
     {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const int opi = lane >> 3, box = lane & 7;
       long long t_empty = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
@@ -356,18 +377,27 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           const TcGroup& gr = p.group[q];
           const int k_iters = gr.k_iters;
           const uint32_t tx = kTwo ? 2 * gr.stage_tx : gr.stage_tx;
-          // this lane's copy, if any
-          const bool is_a = opi < 2;
-          const int slot = is_a ? opi : opi - 2;
-          bool active = slot < (is_a ? gr.nA : gr.nB);
-          TcOperand op = gr.A[0];
-          if (active) op = is_a ? gr.A[slot] : gr.B[slot];
-          const int nboxes = op.mn ? (is_a ? BM / 32 : BN_LOCAL / 32) : 1;
-          active = active && box < nboxes;
-          const CUtensorMap* map = &p.maps[op.map];
-          const int row0 = (is_a ? m0 : n0) + (op.mn ? 32 * box : 0);
-          const uint32_t dst_off = op.smem_off + (op.mn ? (uint32_t)(box * bk * 128) : 0u);
-          const int mn = op.mn;
+          // this lane's copies, if any
+          bool active[2];
+          const CUtensorMap* map[2];
+          int row0[2], mn[2];
+          uint32_t dst_off[2];
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            const int u = lane + 32 * c, opi = u >> 3, box = u & 7;
+            const bool is_a = opi < kMaxOperands;
+            const int slot = is_a ? opi : opi - kMaxOperands;
+            active[c] = opi < 2 * kMaxOperands && slot < (is_a ? gr.nA : gr.nB);
+            TcOperand op = gr.A[0];
+            if (active[c]) op = is_a ? gr.A[slot] : gr.B[slot];
+            // a B tile has BN_LOCAL rows, an A tile BM: B's box count scales with it
+            const int nboxes = op.mn ? (is_a ? BM : BN_LOCAL) / op.box_rows : 1;
+            active[c] = active[c] && box < nboxes;
+            map[c] = &p.maps[op.map];
+            row0[c] = (is_a ? m0 : n0) + (op.mn ? op.box_rows * box : 0);
+            dst_off[c] = op.smem_off + (op.mn ? (uint32_t)(box * bk * 128) : 0u);
+            mn[c] = op.mn;
+          }
           for (int kb = 0; kb < k_iters; kb++) {
             if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag))) {
               ok = false;
@@ -378,12 +408,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             const uint32_t bar = full_bar(stage);
             // the leader's barrier collects the bytes of both CTAs of a pair
             if (lane == 0 && rank == 0) mbar_expect_tx(bar, tx);
-            if (active) {
-              const uint32_t dst = smem_base + stage * stage_bytes + dst_off;
-              const int k0 = kb * bk;
-              const int x = mn ? row0 : k0, y = mn ? k0 : row0;
-              if (kTwo) tma_load_2d_pair(dst, map, x, y, bar);
-              else tma_load_2d(dst, map, x, y, bar);
+            const int k0 = kb * bk;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+              if (active[c]) {
+                const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
+                const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
+                if (kTwo) tma_load_2d_pair(dst, map[c], x, y, bar);
+                else tma_load_2d(dst, map[c], x, y, bar);
+              }
             }
             if (++stage == num_stages) {
               stage = 0;
@@ -426,10 +459,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           // per-product constants live in registers, the k-loop only adds the stage address.
           const int nm = gr.nmma, k_iters = gr.k_iters;
           uint32_t a_lo[4], b_lo[4], a_hi[4], b_hi[4], a_adv[4], b_adv[4], idesc[4];
+          bool f16[4];
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             a_lo[i] = b_lo[i] = a_hi[i] = b_hi[i] = a_adv[i] = b_adv[i] = idesc[i] = 0;
+            f16[i] = false;
             if (i < nm) {
+              f16[i] = gr.mma[i].f16 != 0;
               const TcOperand oa = gr.A[gr.mma[i].a];
               const TcOperand ob = gr.B[gr.mma[i].b];
               a_lo[i] = oa.desc_lo + (oa.smem_off >> 4);
@@ -468,14 +504,28 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             for (int i = 0; i < 4; i++) {
               if (i < nm) {
                 const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
+                if (f16[i]) {
+                  // bfloat16: K = 16 per instruction, half as many instructions per k-block
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                  if (j < ksteps) {
-                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
-                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
-                    if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    fresh = 0;
+                  for (int j = 0; j < 2; j++) {
+                    if (2 * j < ksteps) {
+                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                      if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                      else mma_f16(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                      fresh = 0;
+                    }
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 4; j++) {
+                    if (j < ksteps) {
+                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                      if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                      else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                      fresh = 0;
+                    }
                   }
                 }
               }
@@ -582,8 +632,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         // for the arithmetic; a batch of four columns (one Philox block) is staged as
         // [array][column][128 rows], and one thread of each column-half group of four warps
         // sends it on with cp.async.bulk.tensor while the next batch is computed (two buffers).
-        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias, out, out_lo set; beta = 0;
-                                                    // no col_scale, no out_hi
+        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias, out, out_aux set; beta = 0;
+                                                    // no col_scale; a draw comes with its aux
         const bool row_ok = m < pM;
         const int hf = ew >> 2;                     // column half = store group
         const bool leader = (ew & 3) == 0 && lane == 0;
@@ -591,16 +641,21 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         const float alpha = e.alpha, beta = spec ? 0.0f : e.beta;
         const float bias = ((spec || e.bias) && row_ok) ? e.bias[m] : 0.0f;
         const bool logistic = spec ? (kEpi != kEpiLinLo) : (e.activation == 1);
-        const bool draw = spec ? (kEpi == kEpiSigLoSample) : (e.sample != nullptr);
+        const bool draw = spec ? (kEpi == kEpiSigLoSample) : (e.sample != nullptr || e.sample_aux != nullptr);
         const bool has_out = spec || e.out != nullptr;
-        const bool has_hi = !spec && e.out_hi != nullptr;
-        const bool has_lo = spec || e.out_lo != nullptr;
+        const bool has_aux = spec || e.out_aux != nullptr;
+        const bool has_smp = spec ? draw : e.sample != nullptr;
+        const bool has_smp_aux = spec ? draw : e.sample_aux != nullptr;
         const PhiloxKey key = e.key;
         const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
         const long off = (long)nc * e.ldo + m, ldo = e.ldo;
         const int m_tile = tm * TILE_M + (int)rank * BM;     // first row of this CTA's part of the tile
-        constexpr uint32_t kArrayBytes = kOutCols * BM * 4;   // one array of a batch
-        constexpr uint32_t kBufBytes = kOutArrays * kArrayBytes;
+        // one staged batch: [out f32][aux plane 0 bf16][aux plane 1 bf16][sample f32][sample bf16],
+        // each kOutCols columns of BM rows
+        constexpr uint32_t kF32 = kOutCols * BM * 4, kB16 = kOutCols * BM * 2;
+        constexpr uint32_t kOffLo = kF32, kOffB = kF32 + kB16, kOffSmp = kF32 + 2 * kB16, kOffSmpB = 2 * kF32 + 2 * kB16;
+        constexpr uint32_t kBufBytes = 2 * kF32 + 3 * kB16;
+        static_assert(4 * kBufBytes <= kOutStageBytes, "epilogue staging");
         const uint32_t group_base = out_stage_base + (uint32_t)hf * 2u * kBufBytes;
 #pragma unroll
         for (int g4 = 0; g4 < COLS / 4; g4++) {
@@ -621,28 +676,34 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           if (draw) w = philox4x32_10((uint32_t)m, cblk0 + g4, key);
           // buffer (g4 & 1) is free once the stores of batch g4 - 2 have read it (the leader waited)
           named_bar_sync(1 + hf, 128);
-          const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes + (uint32_t)row * 4u;
+          const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes;
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            const uint32_t a = buf + (uint32_t)j * (BM * 4);
-            float hi, lo;
-            split_tf32(x[j], hi, lo);
-            if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x[j]) : "memory");
-            if (has_hi) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + kArrayBytes), "f"(hi) : "memory");
-            if (has_lo) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 2 * kArrayBytes), "f"(lo) : "memory");
+            const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u, a16 = buf + (uint32_t)(j * BM + row) * 2u;
+            if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32), "f"(x[j]) : "memory");
+            if (has_aux) {
+              uint16_t lo16, b16;
+              split_aux(x[j], lo16, b16);
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffLo), "h"(lo16) : "memory");
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffB), "h"(b16) : "memory");
+            }
             if (draw) {
-              const float sbit = word_to_uniform(pick_word(w, j)) < x[j] ? 1.0f : 0.0f;
-              asm volatile("st.shared.f32 [%0], %1;" ::"r"(a + 3 * kArrayBytes), "f"(sbit) : "memory");
+              const bool on = word_to_uniform(pick_word(w, j)) < x[j];
+              if (has_smp) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kOffSmp), "f"(on ? 1.0f : 0.0f) : "memory");
+              if (has_smp_aux)
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffSmpB), "h"((uint16_t)(on ? 0x3f80 : 0)) : "memory");
             }
           }
           fence_async_smem();                       // generic-proxy writes visible to the TMA engine
           named_bar_sync(1 + hf, 128);
           if (leader && c0 < pN && m_tile < pM) {
-            const uint32_t src = group_base + (uint32_t)(g4 & 1) * kBufBytes;
-            if (has_out) tma_store_2d(&p.maps[p.out_map[0]], m_tile, c0, src);
-            if (has_hi) tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, src + kArrayBytes);
-            if (has_lo) tma_store_2d(&p.maps[p.out_map[2]], m_tile, c0, src + 2 * kArrayBytes);
-            if (draw) tma_store_2d(&p.maps[p.out_map[3]], m_tile, c0, src + 3 * kArrayBytes);
+            if (has_out) tma_store_2d(&p.maps[p.out_map[0]], m_tile, c0, buf);
+            if (has_aux) {
+              tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, buf + kOffLo);
+              tma_store_2d(&p.maps[p.out_map[2]], m_tile, c0, buf + kOffB);
+            }
+            if (has_smp) tma_store_2d(&p.maps[p.out_map[3]], m_tile, c0, buf + kOffSmp);
+            if (has_smp_aux) tma_store_2d(&p.maps[p.out_map[4]], m_tile, c0, buf + kOffSmpB);
           }
           if (leader) {
             tma_store_commit();
@@ -702,8 +763,10 @@ struct MapKey {
   uint64_t d0, d1, ld;
   uint32_t b0, b1;
   int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle, 3: none (output tiles)
+  int bf16;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz &&
+           bf16 == o.bf16;
   }
 };
 struct MapKeyHash {
@@ -712,21 +775,22 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.d0;
     h = h * 1000003u ^ k.d1;
     h = h * 1000003u ^ k.ld;
-    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 2 | (uint32_t)k.swz);
+    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 3 | (uint32_t)k.swz << 1 | (uint32_t)k.bf16);
     return h;
   }
 };
 
-// 2-D fp32 map: inner (contiguous) extent d0, outer extent d1 with a stride of ld floats,
-// box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of 16-byte chunks
-// (K-major tiles, 32 floats of K per row); 2: 64-byte swizzle (K-major, 16 floats per row);
-// 1: 128-byte swizzle of 32-byte chunks, the only shared-memory layout tcgen05 accepts for
-// MN-major 32-bit operands.  Encoded maps are cached.
-bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
-              int swz) {
+// 2-D map over fp32 or bfloat16 elements: inner (contiguous) extent d0, outer extent d1 with a
+// stride of ld elements, box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of
+// 16-byte chunks (K-major fp32 tiles, 32 floats of K per row; MN-major bfloat16 tiles, 64 per
+// row); 2: 64-byte swizzle (K-major, 16 floats or 32 bfloat16 per row); 1: 128-byte swizzle of
+// 32-byte chunks, the only shared-memory layout tcgen05 accepts for MN-major 32-bit operands;
+// 3: none (output tiles).  Encoded maps are cached.
+bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+              int swz, int bf16) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  const MapKey key{ptr, d0, d1, ld, b0, b1, swz};
+  const MapKey key{ptr, d0, d1, ld, b0, b1, swz, bf16};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -736,17 +800,16 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {d0, d1};
-  const cuuint64_t strides[1] = {ld * sizeof(float)};
+  const cuuint64_t strides[1] = {ld * (bf16 ? 2 : 4)};
   const cuuint32_t box[2] = {b0, b1};
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUresult r = fn(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr,
+                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swz == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                  : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
                                              : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B)),
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, m);
@@ -754,18 +817,25 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
   return true;
 }
 
-inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0); }
+// TMA needs a 16-byte aligned base and column stride.
+inline bool tma_ok(const GemmOperand& o) {
+  return (o.ld % (o.bf16 ? 8 : 4) == 0) && (((uintptr_t)o.ptr & 15) == 0);
+}
 
 // Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
 // 16-byte units), descriptor version 1 for sm_100 (bits 46-47), layout type in bits 61-63.
-//  K-major, 32 floats of K per row: rows of 128 B, 8-row groups 1024 B apart, 128B swizzle (type 2).
-//  K-major, 16 floats of K per row: rows of 64 B, 8-row groups 512 B apart, 64B swizzle (type 4).
+//  K-major, rows of 128 B (32 floats of K): 8-row groups 1024 B apart, 128B swizzle (type 2).
+//  K-major, rows of 64 B (16 floats or 32 bfloat16 of K): 8-row groups 512 B apart, 64B swizzle (type 4).
 //  MN-major 32-bit: rows (one k each) of 128 B = 32 floats along M/N, 4-row groups 512 B apart,
 //                   128B swizzle with 32-byte atoms (type 1).
-// The lower word carries the start address and the leading byte offset.
+//  MN-major 16-bit: rows (one k each) of 128 B = 64 bfloat16 along M/N, 8-row groups 1024 B apart,
+//                   128B swizzle (type 2).
+// The lower word carries the start address and the leading byte offset (for MN-major tiles the
+// distance between two 128-byte wide column blocks = one TMA box = bk rows of 128 B).
 constexpr uint32_t kDescHiK32 = (1024u >> 4) | (1u << 14) | (2u << 29);
 constexpr uint32_t kDescHiK16 = (512u >> 4) | (1u << 14) | (4u << 29);
 constexpr uint32_t kDescHiMN = (512u >> 4) | (1u << 14) | (1u << 29);
+constexpr uint32_t kDescHiMN16 = (1024u >> 4) | (1u << 14) | (2u << 29);
 
 // Fills the tcgen05 view of one operand; `rows` = extent of the tile along M or N.
 bool fill_operand(TcOperand& op, CUtensorMap* map_slot, int map_index, const GemmOperand& src, bool is_a, int mn_extent,
@@ -776,25 +846,33 @@ bool fill_operand(TcOperand& op, CUtensorMap* map_slot, int map_index, const Gem
   op.map = map_index;
   bool ok;
   if (op.mn) {
-    ok = make_map(map_slot, src.ptr, (uint64_t)mn_extent, (uint64_t)k, (uint64_t)src.ld, 32, (uint32_t)bk, 1);
-    op.desc_hi = kDescHiMN;
-    op.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;  // distance between 32-float chunks = bk rows x 128 B
-    op.adv = 1024u >> 4;                             // K = 8 step: 8 rows of 128 B
+    op.box_rows = src.bf16 ? 64 : 32;                // 128 bytes of M/N per box row
+    op.nboxes = rows / op.box_rows;
+    ok = make_map(map_slot, src.ptr, (uint64_t)mn_extent, (uint64_t)k, (uint64_t)src.ld, (uint32_t)op.box_rows,
+                  (uint32_t)bk, src.bf16 ? 0 : 1, src.bf16);
+    op.desc_hi = src.bf16 ? kDescHiMN16 : kDescHiMN;
+    op.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;  // distance between column blocks = bk rows x 128 B
+    op.adv = (src.bf16 ? 2048u : 1024u) >> 4;        // one MMA reads 16 (bfloat16) or 8 (fp32) rows of 128 B
   } else {
+    op.box_rows = rows;
+    op.nboxes = 1;
+    const bool row128 = !src.bf16 && bk == 32;       // bytes of K per row: 128 (32 floats) or 64
     ok = make_map(map_slot, src.ptr, (uint64_t)k, (uint64_t)mn_extent, (uint64_t)src.ld, (uint32_t)bk, (uint32_t)rows,
-                  bk == 32 ? 0 : 2);
-    op.desc_hi = bk == 32 ? kDescHiK32 : kDescHiK16;
+                  row128 ? 0 : 2, src.bf16);
+    op.desc_hi = row128 ? kDescHiK32 : kDescHiK16;
     op.desc_lo = 1u << 16;                           // leading byte offset is unused for swizzled K-major tiles
-    op.adv = 32u >> 4;                               // K = 8 step: 32 bytes inside the swizzled row
+    op.adv = 32u >> 4;                               // one MMA reads 32 bytes of K inside the swizzled row
   }
   return ok;
 }
 
+inline uint32_t tile_bytes(const GemmOperand& o, int rows, int bk) { return (uint32_t)rows * bk * (o.bf16 ? 2 : 4); }
+
 inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
-  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
+  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.bf16 == b.bf16;
 }
 
-static_assert(sizeof(TcParams) <= 4096, "kernel parameter block");
+static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
 
 template <int BN, int kEpi, bool kTwo>
 int launch_tc(TcParams& p) {
@@ -859,14 +937,16 @@ bool gemm_tc_supported(const GemmProblem& g) {
   if (g.M <= 0 || g.N <= 0 || g.npass <= 0 || g.npass > kMaxPass) return false;
   for (int q = 0; q < g.npass; q++) {
     if (!tma_ok(g.pass[q].a) || !tma_ok(g.pass[q].b) || g.pass[q].k <= 0) return false;
+    if (g.pass[q].a.bf16 != g.pass[q].b.bf16) return false;
   }
-  if (g.epi.sample && (g.epi.col0 & 3)) return false;
-  // activation epilogues store whole column segments with TMA: 16-byte aligned columns
   const GemmEpilogue& e = g.epi;
-  const bool plain = !e.bias && e.activation == 0 && !e.out_hi && !e.out_lo && !e.sample && e.out;
+  if ((e.sample || e.sample_aux) && (e.col0 & 3)) return false;
+  // activation epilogues store whole column segments with TMA: 16-byte aligned columns (the
+  // planes of an aux matrix are, its columns being a multiple of 8 floats)
+  const bool plain = !e.bias && e.activation == 0 && !e.out_aux && !e.sample && !e.sample_aux && e.out;
   if (!plain) {
-    if (e.ldo % 4 != 0) return false;
-    const float* outs[kOutArrays] = {e.out, e.out_hi, e.out_lo, e.sample};
+    if (e.ldo % 4 != 0 || e.ld_aux % 8 != 0) return false;
+    const float* outs[4] = {e.out, e.out_aux, e.sample, e.sample_aux};
     for (const float* o : outs)
       if ((uintptr_t)o & 15) return false;
   }
@@ -896,8 +976,8 @@ int gemm_tc(const GemmProblem& g) {
   // ---- group consecutive passes that share K and need at most two distinct A and B operands
   struct HostGroup {
     int k, nA, nB, nmma;
-    GemmOperand A[2], B[2];
-    int ma[4], mb[4], neg[4];
+    GemmOperand A[kMaxOperands], B[kMaxOperands];
+    int ma[4], mb[4], neg[4], f16[4];
   } hg[kMaxPass];
   int ngroups = 0;
   for (int q = 0; q < g.npass; q++) {
@@ -910,10 +990,10 @@ int gemm_tc(const GemmProblem& g) {
         for (int i = 0; i < h.nA; i++) if (same_operand(h.A[i], ps.a)) ia = i;
         for (int i = 0; i < h.nB; i++) if (same_operand(h.B[i], ps.b)) ib = i;
         const int needA = ia < 0 ? 1 : 0, needB = ib < 0 ? 1 : 0;
-        if (h.nA + needA <= 2 && h.nB + needB <= 2) {
+        if (h.nA + needA <= kMaxOperands && h.nB + needB <= kMaxOperands) {
           if (ia < 0) { ia = h.nA; h.A[h.nA++] = ps.a; }
           if (ib < 0) { ib = h.nB; h.B[h.nB++] = ps.b; }
-          h.ma[h.nmma] = ia; h.mb[h.nmma] = ib; h.neg[h.nmma] = ps.negate;
+          h.ma[h.nmma] = ia; h.mb[h.nmma] = ib; h.neg[h.nmma] = ps.negate; h.f16[h.nmma] = ps.a.bf16;
           h.nmma++;
           placed = true;
         }
@@ -927,29 +1007,26 @@ int gemm_tc(const GemmProblem& g) {
       h.B[0] = ps.b;
       h.ma[0] = h.mb[0] = 0;
       h.neg[0] = ps.negate;
+      h.f16[0] = ps.a.bf16;
     }
   }
-  // ---- ring geometry: 32 floats of K per k-block (one 128-byte swizzle row); 16-float blocks
-  // double the stage count but measured slower (64-byte rows, twice the MMA and TMA issues)
-  auto stage_bytes_for = [&](int bk) {
-    uint32_t mx = 0;
-    for (int q = 0; q < ngroups; q++) {
-      const uint32_t b = (uint32_t)(hg[q].nA * BM + hg[q].nB * BN_LOCAL) * bk * 4;
-      if (b > mx) mx = b;
-    }
-    return mx;
-  };
-  static int forced_bk = -1, chunk_k = 0;
-  if (forced_bk < 0) {
-    const char* e = getenv("B200_GEMM_BK");
-    forced_bk = e ? atoi(e) : 0;
+  // ---- ring geometry: 32 elements of K per k-block (one 128-byte swizzle row of floats); 16
+  // doubles the stage count but measured slower (64-byte rows, twice the MMA and TMA issues)
+  const int bk = 32;
+  p.bk = bk;
+  uint32_t stage_bytes = 0;
+  for (int q = 0; q < ngroups; q++) {
+    uint32_t b = 0;
+    for (int i = 0; i < hg[q].nA; i++) b += tile_bytes(hg[q].A[i], BM, bk);
+    for (int i = 0; i < hg[q].nB; i++) b += tile_bytes(hg[q].B[i], BN_LOCAL, bk);
+    if (b > stage_bytes) stage_bytes = b;
+  }
+  static int chunk_k = -1;
+  if (chunk_k < 0) {
     const char* c = getenv("B200_CHUNK_K");
     chunk_k = c ? atoi(c) : 0;
   }
-  int bk = 32;
-  if (forced_bk == 16 || forced_bk == 32) bk = forced_bk;
-  p.bk = bk;
-  p.stage_bytes = stage_bytes_for(bk);
+  p.stage_bytes = stage_bytes;
   p.num_stages = (int)(kStageBudget / p.stage_bytes);
   if (p.num_stages > kMaxStages) p.num_stages = kMaxStages;
   if (p.num_stages < 1) return ERROR_UNSUPPORTED;
@@ -974,44 +1051,54 @@ int gemm_tc(const GemmProblem& g) {
         return set_error("cuTensorMapEncodeTiled failed for operand A");
       nmaps++;
       tg.A[i].smem_off = off;
-      off += (uint32_t)BM * bk * 4;
+      off += tile_bytes(h.A[i], BM, bk);
     }
     for (int i = 0; i < h.nB; i++) {
       if (!fill_operand(tg.B[i], &p.maps[nmaps], nmaps, h.B[i], false, g.N, h.k, BN_LOCAL, bk))
         return set_error("cuTensorMapEncodeTiled failed for operand B");
       nmaps++;
       tg.B[i].smem_off = off;
-      off += (uint32_t)BN_LOCAL * bk * 4;
+      off += tile_bytes(h.B[i], BN_LOCAL, bk);
     }
     tg.stage_tx = off;
     for (int i = 0; i < h.nmma; i++) {
       tg.mma[i].a = h.ma[i];
       tg.mma[i].b = h.mb[i];
-      // instruction descriptor: D fp32 (bit 4), A and B TF32 (value 2 at bits 7 and 10), negate A
-      // (bit 13), A / B MN-major (bits 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
-      tg.mma[i].idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((h.neg[i] ? 1u : 0u) << 13) |
+      tg.mma[i].f16 = h.f16[i];
+      // instruction descriptor: D fp32 (bit 4), A and B format at bits 7 and 10 (TF32 = 2 for
+      // kind::tf32, BF16 = 1 for kind::f16), negate A (bit 13), A / B MN-major (bits 15 / 16),
+      // N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t fmt = h.f16[i] ? 1u : 2u;
+      tg.mma[i].idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((h.neg[i] ? 1u : 0u) << 13) |
                         ((uint32_t)tg.A[h.ma[i]].mn << 15) | ((uint32_t)tg.B[h.mb[i]].mn << 16) |
                         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((two ? 2 * BM : BM) >> 4) << 24);
     }
   }
   const GemmEpilogue& e = g.epi;
-  {
-    // outputs of the activation epilogues: M x N, columns ldo apart, stored as 128-row x 4-column boxes
-    const float* outs[kOutArrays] = {e.out, e.out_hi, e.out_lo, e.sample};
+  int epi = kEpiGeneric;
+  if (!e.bias && e.activation == 0 && !e.out_aux && !e.sample && !e.sample_aux && e.out) {
+    epi = kEpiPlain;
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out && e.out_aux) {
+    if (e.activation == 1 && e.sample && e.sample_aux) epi = kEpiSigLoSample;
+    else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSigLo;
+    else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLinLo;
+  }
+  for (int i = 0; i < kOutArrays; i++) p.out_map[i] = -1;
+  if (epi != kEpiPlain) {
+    // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns: M x N floats
+    // with columns ldo apart, or one bfloat16 plane of an aux matrix (columns 2 ld_aux bfloat16
+    // apart, plane 1 starting ld_aux bfloat16 into the column)
+    const uint16_t* oa = reinterpret_cast<const uint16_t*>(e.out_aux);
+    const uint16_t* sa = reinterpret_cast<const uint16_t*>(e.sample_aux);
+    const void* outs[kOutArrays] = {e.out, oa, oa ? oa + e.ld_aux : nullptr, e.sample, sa ? sa + e.ld_aux : nullptr};
+    const int is16[kOutArrays] = {0, 1, 1, 0, 1};
     for (int i = 0; i < kOutArrays; i++) {
-      p.out_map[i] = -1;
       if (!outs[i]) continue;
-      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)e.ldo, BM, kOutCols, 3))
+      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)(is16[i] ? 2 * e.ld_aux : e.ldo), BM,
+                    kOutCols, 3, is16[i]))
         return set_error("cuTensorMapEncodeTiled failed for an output");
       p.out_map[i] = nmaps++;
     }
-  }
-  int epi = kEpiGeneric;
-  if (!e.bias && e.activation == 0 && !e.out_hi && !e.out_lo && !e.sample && e.out) {
-    epi = kEpiPlain;
-  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out && e.out_lo && !e.out_hi) {
-    if (e.activation == 1) epi = e.sample ? kEpiSigLoSample : kEpiSigLo;
-    else if (!e.sample) epi = kEpiLinLo;
   }
 #define B200_TC_CASE(BNV, TWO)                                            \
   switch (epi) {                                                          \
