@@ -5,7 +5,7 @@ dot (:1579), vdot (:1596), sigmoid/exp/log_1_plus_exp (:1607-1700), cuda_set_dev
 cublas_init/shutdown, cuda_sync_threads, so deepnet's dbm.py / layer.py / edge.py /
 parameter.py run on it unchanged.  Matrices are float32, column-major; `.T` and
 `slice` are non-owning views.  Extra entry points (fused_gemm, momentum_update,
-split_bf16, dp_*) have no counterpart in the reference.
+split_tf32, dp_*) have no counterpart in the reference.
 
 There is no CPU fallback: importing works without a GPU (so the symbols can be
 inspected), but the first operation fails loudly if the library or a device is missing.
@@ -45,14 +45,13 @@ class rnd_struct(ct.Structure):
 
 class _Pass(ct.Structure):
     _fields_ = [("a", ct.POINTER(cudamat)), ("b", ct.POINTER(cudamat)), ("negate", ct.c_int),
-                ("a_plane", ct.c_int), ("b_plane", ct.c_int), ("a_rows", ct.c_int), ("b_rows", ct.c_int)]
+                ("a_part", ct.c_int), ("b_part", ct.c_int)]
 
 
 class _FusedGemm(ct.Structure):
     _fields_ = [("npass", ct.c_int), ("passes", _Pass * MAX_PASS), ("alpha", ct.c_float), ("beta", ct.c_float),
                 ("bias", ct.POINTER(cudamat)), ("col_scale", ct.POINTER(cudamat)), ("activation", ct.c_int),
-                ("out", ct.POINTER(cudamat)), ("out_aux", ct.POINTER(cudamat)), ("sample", ct.POINTER(cudamat)),
-                ("sample_aux", ct.POINTER(cudamat))]
+                ("out", ct.POINTER(cudamat)), ("sample", ct.POINTER(cudamat))]
 
 
 _lib.get_last_cuda_error.restype = ct.c_char_p
@@ -474,21 +473,12 @@ class CUDAMatrix(object):
         return target
 
     # -- fused entry points (no counterpart in the reference API) -------------
-    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None):
-        """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter.
-
-        w_aux (optional) receives the aux matrix of the updated parameter (see `split_bf16`)."""
+    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0):
+        """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter."""
         _check(_lib.momentum_update(self.p_mat, delta.p_mat, grad.p_mat if grad is not None else None, suff.p_mat,
-                                    w_aux.p_mat if w_aux is not None else None,
                                     ct.c_float(inv_batch), ct.c_float(momentum), ct.c_float(eps), ct.c_float(l2),
                                     ct.c_float(l1)))
         return self
-
-    def split_bf16(self, aux):
-        """Fills `aux` (from `empty_aux(self.shape)`) with the two bfloat16 planes the split
-        products read: plane 0 = bf16(self - tf32(self)), plane 1 = bf16(self).  Returns aux."""
-        _check(_lib.split_bf16(self.p_mat, aux.p_mat))
-        return aux
 
     def split_tf32(self, lo, hi=None):
         """lo = self - tf32(self); hi (optional) = self with the low 13 mantissa bits cleared."""
@@ -515,98 +505,51 @@ class TransposedCUDAMatrix(CUDAMatrix):
         pass
 
 
-class AuxMatrix(CUDAMatrix):
-    """The bfloat16 companion of a rows x cols matrix (see `CUDAMatrix.split_bf16`): storage of
-    lda x cols floats, lda = rows rounded up to 8; column c holds lda bfloat16 of plane 0
-    (bf16(x - tf32(x))) and lda of plane 1 (bf16(x)), the first `rows` of each in use.
-    `.lo` / `.b` name the planes as `fused_gemm` operands; assign() copies the storage."""
+# What of an fp32 matrix a term of `fused_gemm` multiplies (derived inside the kernel from the
+# matrix itself): x read as TF32, x - tf32(x) read as TF32, bfloat16(x - tf32(x)), bfloat16(x).
+PART_X, PART_LO32, PART_LO16, PART_B16 = 0, 1, 2, 3
 
-    def __init__(self, shape):
-        _require_device()
-        self.rows, self.cols = int(shape[0]), int(shape[1])
-        self.mat = cudamat()
-        _check(_lib.init_empty(ct.pointer(self.mat), ct.c_int((self.rows + 7) // 8 * 8), ct.c_int(self.cols)))
-        self.p_mat = ct.pointer(self.mat)
-        self.numpy_array = None
 
-    @property
-    def lo(self):
-        return AuxPlane(self, 0, self.rows)
+class Part(object):
+    """A part of a matrix (or of its transpose) as a `fused_gemm` operand."""
 
-    @property
-    def b(self):
-        return AuxPlane(self, 1, self.rows)
+    def __init__(self, mat, part):
+        self.mat, self.part, self.p_mat = mat, part, mat.p_mat
 
     @property
     def T(self):
-        """The aux matrix of the transposed matrix: `.lo` / `.b` give transposed plane operands."""
-        return _AuxTransposed(self)
-
-    def planes(self):
-        """Host copy of the two planes as float32 arrays (rows x cols each)."""
-        raw = np.array(self.asarray(), copy=True)                       # lda x cols floats
-        words = np.ascontiguousarray(raw.T).view(np.uint16)             # cols x (2 lda) bfloat16
-        lda = raw.shape[0]
-        f = lambda w: (np.ascontiguousarray(w).astype(np.uint32) << 16).view(np.float32).T[:self.rows]
-        return f(words[:, :lda]), f(words[:, lda:])
+        return Part(self.mat.T, self.part)
 
 
-class _AuxTransposed(object):
-    def __init__(self, aux):
-        self.aux = aux
-        self.view = TransposedCUDAMatrix(aux.mat)
-        self.view._parent = aux
-
-    @property
-    def lo(self):
-        return AuxPlane(self.view, 0, self.aux.rows)
-
-    @property
-    def b(self):
-        return AuxPlane(self.view, 1, self.aux.rows)
-
-    @property
-    def T(self):
-        return self.aux
+def lo32(x):
+    return Part(x, PART_LO32)
 
 
-def empty_aux(shape):
-    """Zero-filled aux matrix for a matrix of this shape."""
-    return AuxMatrix(shape)
+def lo16(x):
+    return Part(x, PART_LO16)
 
 
-class AuxPlane(object):
-    """One bfloat16 plane of an aux matrix (`a.lo`, `a.b`) or of its transpose: a `fused_gemm` operand."""
-
-    def __init__(self, mat, plane, rows):
-        self.mat, self.plane, self.rows = mat, plane, rows
-        self.p_mat = mat.p_mat
-
-    @property
-    def T(self):
-        t = TransposedCUDAMatrix(self.mat.mat)
-        t._parent = self.mat
-        return AuxPlane(t, self.plane, self.rows)
+def b16(x):
+    return Part(x, PART_B16)
 
 
-def split_passes(w, w_aux, x, x_aux, negate=0, exact_x=False):
-    """The terms of op(w) . x at fp32 grade, small terms first: the bfloat16 correction products
-    over the aux matrices, then the TF32 product.  `exact_x`: x is exact in TF32 (0/1 data and
-    samples), so only w's low part needs a correction (x_aux still supplies its plane 1)."""
-    if exact_x:
-        return [(w_aux.lo, x_aux.b, negate), (w, x, negate)]
-    return [(w_aux.lo, x_aux.b, negate), (w_aux.b, x_aux.lo, negate), (w, x, negate)]
-
-
-def tf32_passes(a, a_lo, b, b_lo, negate=0):
-    """The terms of a . b with every term a TF32 product (a_lo, b_lo from `split_tf32`; either
-    may be None when that operand is exact in TF32): 2^-20 per term, for products whose
-    difference is wanted (positive minus negative statistics)."""
+def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16"):
+    """The terms of a . b at fp32 grade, small terms first.  terms="bf16": the corrections are
+    bfloat16 products, lo16(a).b16(b) + b16(a).lo16(b) (twice the TF32 rate; 2^-18 per term);
+    terms="tf32": TF32 products lo32(a).b + a.lo32(b) (2^-20 per term: for products whose
+    difference is wanted, like positive minus negative statistics).  exact_a / exact_b: that
+    operand is exact in TF32 (0/1 data and samples, small counts), its low part is skipped."""
     p = []
-    if a_lo is not None:
-        p.append((a_lo, b, negate))
-    if b_lo is not None:
-        p.append((a, b_lo, negate))
+    if terms == "bf16":
+        if not exact_a:
+            p.append((lo16(a), b16(b), negate))
+        if not exact_b:
+            p.append((b16(a), lo16(b), negate))
+    else:
+        if not exact_a:
+            p.append((lo32(a), b, negate))
+        if not exact_b:
+            p.append((a, lo32(b), negate))
     p.append((a, b, negate))
     return p
 
@@ -689,16 +632,14 @@ def correct_preds(mat, p, target=None, cutoff=0.5):
     return target
 
 
-def fused_gemm(passes, out=None, out_aux=None, sample=None, sample_aux=None, bias=None, col_scale=None,
-               activation=0, alpha=1.0, beta=0.0):
+def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activation=0, alpha=1.0, beta=0.0):
     """out = act(alpha * sum_p (+/-) a_p . b_p + beta * out + bias (x) col_scale) in one kernel.
 
-    `passes` is a list of (a, b) or (a, b, negate); a and b may be `.T` views, and are either
-    both fp32 matrices (a TF32 product on the tensor cores) or both planes of aux matrices
-    (`m_aux.lo`, `m_aux.b`: a bfloat16 product).  Optional outputs: the aux matrix of the result,
-    a Bernoulli draw of it (consumes one sampling call of the global random state) and the
-    draw's aux matrix.  Replaces the dot / add_dot / add_col_vec / sigmoid / sample_bernoulli
-    group of deepnet/dbm.py:88-105.
+    `passes` is a list of (a, b) or (a, b, negate); a and b are fp32 matrices, `.T` views, or
+    parts of them (`lo32(x)`, `lo16(x)`, `b16(x)`, see `split_passes`); both operands of a
+    term are fp32-wide (a TF32 product) or both bfloat16.  Optional output: a Bernoulli draw
+    of the result (consumes one sampling call of the global random state).  Replaces the dot /
+    add_dot / add_col_vec / sigmoid / sample_bernoulli group of deepnet/dbm.py:88-105.
     """
     f = _FusedGemm()
     f.npass = len(passes)
@@ -707,13 +648,11 @@ def fused_gemm(passes, out=None, out_aux=None, sample=None, sample_aux=None, bia
     for i, p in enumerate(passes):
         f.passes[i].a = p[0].p_mat
         f.passes[i].b = p[1].p_mat
-        pa, pb = isinstance(p[0], AuxPlane), isinstance(p[1], AuxPlane)
-        f.passes[i].a_plane, f.passes[i].a_rows = (p[0].plane, p[0].rows) if pa else (-1, 0)
-        f.passes[i].b_plane, f.passes[i].b_rows = (p[1].plane, p[1].rows) if pb else (-1, 0)
+        f.passes[i].a_part = p[0].part if isinstance(p[0], Part) else PART_X
+        f.passes[i].b_part = p[1].part if isinstance(p[1], Part) else PART_X
         f.passes[i].negate = int(p[2]) if len(p) > 2 else 0
     f.alpha, f.beta, f.activation = alpha, beta, activation
-    for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("out_aux", out_aux),
-                    ("sample", sample), ("sample_aux", sample_aux)):
+    for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("sample", sample)):
         if m is not None:
             setattr(f, name, m.p_mat)
     _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))

@@ -136,23 +136,6 @@ __device__ __forceinline__ uint16_t float_to_bf16(float x) {
 }
 __device__ __forceinline__ float bf16_to_float(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
-// The low-order companion of a rows x cols matrix x that the tensor-core products read ("aux"
-// matrix): lda x cols floats of storage, lda = rows rounded up to a multiple of 8 (so that both
-// planes of every column start on 16 bytes, as TMA requires); column c holds two runs of lda
-// bfloat16, the first `rows` of each in use,
-//   plane 0: bf16(x - tf32(x))   the part of x a TF32 operand drops
-//   plane 1: bf16(x)
-// so that  a . b ~= tf32(a) . tf32(b)  +  plane0(a) . plane1(b)  +  plane1(a) . plane0(b)
-// (one TF32 product and two bfloat16 products at twice the TF32 rate, all into one fp32
-// accumulator; what is left out is of relative order 2^-18 per term, rounded, not truncated).
-// Element (r, c) of plane p is 16-bit word  c * 2 * lda + p * lda + r  of the aux storage.
-__host__ __device__ inline int aux_rows(int rows) { return (rows + 7) & ~7; }
-__device__ __forceinline__ void split_aux(float x, uint16_t& lo16, uint16_t& b16) {
-  float hi, lo;
-  split_tf32(x, hi, lo);
-  lo16 = float_to_bf16(lo);
-  b16 = float_to_bf16(x);
-}
 #endif
 
 }  // namespace b200

@@ -1,7 +1,6 @@
 // Description of one fused matrix product shared by the tensor-core and the SIMT
 // kernels:  out = act(alpha * sum_p (+/-) op(A_p) . op(B_p) + beta * out + bias (x) scale)
-// with an optional Bernoulli draw of the result and the bfloat16 companions ("aux" matrices)
-// that later products read.
+// with an optional Bernoulli draw of the result.
 #pragma once
 #include "common.cuh"
 
@@ -9,17 +8,30 @@ namespace b200 {
 
 constexpr int kMaxPass = 8;
 
-// A column-major matrix in device memory: element (r, c) at ptr[c * ld + r].
+// Which part of an fp32 matrix x a term multiplies.  The kernels derive the parts from x
+// on the fly (the tensor-core kernel in shared memory, next to the tile TMA delivered), so
+// only x itself lives in device memory:
+//   kPartX     x, read as TF32 on the tensor cores (the hardware drops the low 13 mantissa bits)
+//   kPartLo32  x - tf32(x), read as TF32 (keeps 10 of its up to 13 significant bits)
+//   kPartLo16  bfloat16(x - tf32(x))
+//   kPartB16   bfloat16(x)
+// so that, small terms first,
+//   a . b ~= lo32(a).x(b) + x(a).lo32(b) + x(a).x(b)      three TF32 products, 2^-20 per term
+//   a . b ~= lo16(a).b16(b) + b16(a).lo16(b) + x(a).x(b)  one TF32 + two bfloat16 products
+//                                                        (twice the TF32 rate), 2^-18 per term
+// accumulate into one fp32 accumulator.  Both operands of a term are of the same width.
+enum { kPartX = 0, kPartLo32 = 1, kPartLo16 = 2, kPartB16 = 3 };
+
+// A column-major fp32 matrix in device memory: element (r, c) at ptr[c * ld + r].
 // trans = 1 means the product uses its transpose.
 struct GemmOperand {
   const float* ptr;
   int ld;
   int trans;
-  int bf16;   // 1: ptr addresses bfloat16 elements (one plane of an aux matrix) and ld counts them
+  int part;
 };
 
-// One term of the sum: op(a) is M x k, op(b) is k x N; both operands fp32 (read as TF32 on the
-// tensor cores) or both bfloat16.
+// One term of the sum: op(a) is M x k, op(b) is k x N.
 struct GemmPass {
   GemmOperand a, b;
   int k;
@@ -32,11 +44,8 @@ struct GemmEpilogue {
   const float* col_scale;  // N entries or null: the bias of column n is bias[m] * col_scale[n]
   int activation;          // 0 identity, 1 logistic
   float* out;              // M x N result (may be null when only split/sample outputs are wanted)
-  float* out_aux;          // aux matrix (two bfloat16 planes, see split_aux) of the result, or null
   float* sample;           // Bernoulli(result) draw, or null
-  float* sample_aux;       // aux matrix of the draw (only plane 1 is written: a 0/1 value has no low part), or null
-  int ldo;                 // leading dimension of every fp32 output
-  int ld_aux;              // floats per column of the aux outputs (rows rounded up to 8)
+  int ldo;                 // leading dimension of every output
   PhiloxKey key;           // random stream of this call (used when sample != null)
   int col0;                // global column of output column 0
 };
@@ -44,8 +53,8 @@ struct GemmEpilogue {
 struct GemmProblem {
   int M, N;
   int npass;
-  // 1: operands are read as TF32 (low 13 mantissa bits ignored), the meaning of a pass on
-  // the tensor cores, which the CUDA-core kernel then reproduces; 0: full fp32 operands.
+  // 1: part kPartX is read as TF32 (low 13 mantissa bits ignored), its meaning on the tensor
+  // cores, which the CUDA-core kernel then reproduces; 0: kPartX is the full fp32 value.
   int tf32_operands;
   GemmPass pass[kMaxPass];
   GemmEpilogue epi;
@@ -67,16 +76,7 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc,
   if (e.bias) v += e.col_scale ? e.bias[m] * e.col_scale[n] : e.bias[m];
   if (e.activation == 1) v = sigmoid_accurate(v);
   if (e.out) e.out[idx] = v;
-  const long aidx = (long)n * 2 * e.ld_aux + m;   // 16-bit word of plane 0
-  if (e.out_aux) {
-    uint16_t lo16, b16;
-    split_aux(v, lo16, b16);
-    reinterpret_cast<uint16_t*>(e.out_aux)[aidx] = lo16;
-    reinterpret_cast<uint16_t*>(e.out_aux)[aidx + e.ld_aux] = b16;
-  }
-  const float s = u < v ? 1.0f : 0.0f;
-  if (e.sample) e.sample[idx] = s;
-  if (e.sample_aux) reinterpret_cast<uint16_t*>(e.sample_aux)[aidx + e.ld_aux] = s != 0.0f ? 0x3f80 : 0;
+  if (e.sample) e.sample[idx] = u < v ? 1.0f : 0.0f;
 }
 #endif
 

@@ -14,8 +14,11 @@ __device__ __forceinline__ float as_operand(float x, int tf32) {
   return tf32 ? __uint_as_float(__float_as_uint(x) & 0xffffe000u) : x;
 }
 __device__ __forceinline__ float element(const GemmOperand& o, long i, int tf32) {
-  if (o.bf16) return bf16_to_float(reinterpret_cast<const uint16_t*>(o.ptr)[i]);
-  return as_operand(o.ptr[i], tf32);
+  const float x = o.ptr[i];
+  if (o.part == kPartX) return as_operand(x, tf32);
+  if (o.part == kPartB16) return bf16_to_float(float_to_bf16(x));
+  const float lo = x - as_operand(x, 1);
+  return o.part == kPartLo32 ? as_operand(lo, 1) : bf16_to_float(float_to_bf16(lo));
 }
 __device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K, int tf32) {
   if (m >= M || k >= K) return 0.0f;
@@ -81,7 +84,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
       const int m = m0 + tx + 16 * i;
       if (m >= g.M) continue;
       float u = 0.0f;
-      if (e.sample || e.sample_aux) {
+      if (e.sample) {
         const int gc = n + e.col0;
         const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), e.key);
         u = word_to_uniform(pick_word(w, gc & 3));

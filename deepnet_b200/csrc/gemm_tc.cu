@@ -1,22 +1,27 @@
-// Tensor-core matrix product for sm_100a: tcgen05.mma kind::tf32 with the accumulator
-// in tensor memory, operands staged in 128-byte-swizzled shared memory by TMA
-// (cp.async.bulk.tensor, one copy per CTA, never multicast), a fused epilogue read back
-// with tcgen05.ld.  It replaces the cublasSgemm behind `dot` (cudamat/cudamat.cu:1671-1696)
-// and the separate bias / sigmoid / Bernoulli passes that follow it in
-// deepnet/dbm.py:88-105 and deepnet/logistic_layer.py:11-15.
+// Tensor-core matrix product for sm_100a: tcgen05.mma (kind::tf32 and kind::f16 on bfloat16,
+// mixed in one accumulator) with the accumulator in tensor memory, fp32 operand tiles staged
+// in swizzled shared memory by TMA (cp.async.bulk.tensor, one copy per CTA, never multicast),
+// a fused epilogue read back with tcgen05.ld and stored by TMA.  It replaces the cublasSgemm
+// behind `dot` (cudamat/cudamat.cu:1671-1696) and the separate bias / sigmoid / Bernoulli
+// passes that follow it in deepnet/dbm.py:88-105 and deepnet/logistic_layer.py:11-15.
 //
-// fp32-grade accuracy comes from the caller's pass list: x = hi + lo with hi exact in
-// TF32, and hi*hi + hi*lo + lo*hi accumulate into ONE fp32 accumulator (a k-loop over
-// "passes x K").  A pass may be negated (instruction-descriptor bit), which folds
-// positive-minus-negative statistics into one kernel.
+// fp32-grade accuracy comes from the caller's term list over PARTS of the fp32 operands
+// (x as TF32, x - tf32(x) as TF32 or bfloat16, bfloat16(x)), all accumulating into ONE fp32
+// accumulator.  Only x is read from memory: the delivery of operand tiles to the SMs (about
+// 60 GB/s per SM) bounds this kernel, not the tensor pipe, so four converter warps derive the
+// other parts from the staged fp32 tile in shared memory, in the layout TMA would have
+// produced, and the MMA issuer consumes a stage once they are done.  A term may be negated
+// (instruction-descriptor bit), which folds positive-minus-negative statistics into one kernel.
 //
-// Kernel shape: persistent, one CTA per SM, 320 threads:
-//   warp 0     : TMA producer (one lane)       -> ring of kStages {A tile, B tile}
-//   warp 1     : TMEM allocation + MMA issuer (one lane), tcgen05.commit frees stages
-//   warps 2..9 : epilogue; two warps share each TMEM lane quarter (half the columns each).
-//                They fold every finished 128-deep chunk of the product into fp32
-//                registers (two TMEM accumulators ping-pong with the MMA issuer) and run
-//                the fused epilogue from those registers at the end of the tile.
+// Kernel shape: persistent, one CTA per SM (or a pair of CTAs on a 256-row tile), 512 threads
+// (registers move from the first two warpgroups to the epilogue's with setmaxnreg):
+//   warp 0      : TMA producer                    -> ring of stages {A tile, B tile}
+//   warp 1      : TMEM allocation + MMA issuer (one lane), tcgen05.commit frees stages
+//   warps 4..7  : converters: fp32 tile -> the derived tiles of the stage
+//   warps 8..15 : epilogue; two warps share each TMEM lane quarter (half the columns each).
+//                 They fold every finished chunk of the product into fp32 registers (two TMEM
+//                 accumulators ping-pong with the MMA issuer) and run the fused epilogue from
+//                 those registers at the end of the tile.
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, drains
 // and frees its tensor memory and returns.
 #include <cuda.h>
@@ -34,37 +39,51 @@ namespace {
 constexpr int BM = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
 constexpr int kMaxStages = 8;
-constexpr int kStageBudget = 193 * 1024;      // shared memory available to the operand ring
-constexpr int kOutStageBytes = 32 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
+constexpr int kStageBudget = 209 * 1024;      // shared memory available to the operand ring
+constexpr int kOutStageBytes = 16 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
 constexpr int kOutCols = 4;                    // columns per staged batch (one Philox block)
-constexpr int kOutArrays = 5;                  // out, aux plane 0, aux plane 1, sample, plane 1 of the sample's aux
-constexpr int kMaxOperands = 3;                // distinct A (or B) tiles a k-block stages: x, and the two planes of its aux
+constexpr int kOutArrays = 2;                  // out, sample
+constexpr int kMaxTiles = 8;                   // tiles of a stage: A and B as loaded + up to three derived parts each
+constexpr int kMaxMma = 4;                     // terms issued from one stage
+constexpr uint32_t kNoTile = 0xffffffffu;
 
-// One operand tile of a k-block: where it comes from and how tcgen05 must read it.
-struct TcOperand {
-  int map;                 // index into TcParams::maps
-  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as 128-byte wide boxes)
-  int nboxes;              // TMA boxes per tile: 1 when K is contiguous, rows / box_rows otherwise
-  int box_rows;            // rows of M/N per box of an MN-major tile: 32 floats or 64 bfloat16
+// How tcgen05 reads one staged tile.
+struct TcTile {
   uint32_t desc_hi;        // upper 32 bits of the shared-memory matrix descriptor
   uint32_t desc_lo;        // leading-byte-offset field (bits 16-29 of the low word)
   uint32_t adv;            // descriptor advance per MMA (K = 8 floats or 16 bfloat16), in 16-byte units
   uint32_t smem_off;       // byte offset of the tile inside a stage
 };
+// One fp32 operand tile of a k-block as TMA loads it.
+struct TcLoad {
+  int map;                 // index into TcParams::maps
+  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as boxes of 32 floats x bk)
+  int is_a;
+  uint32_t smem_off;
+};
+// The parts derived from a loaded tile (offsets inside the stage, kNoTile = not wanted).
+struct TcConv {
+  uint32_t src_off;
+  uint32_t lo32_off, lo16_off, b16_off;
+  int mn;
+  int is_a;
+};
 struct TcMma {
-  int a, b;                // operand slots of the group
+  int a, b;                // tiles of the group
   int f16;                 // 0: kind::tf32 (K = 8 per instruction), 1: kind::f16 on bfloat16 (K = 16)
   uint32_t idesc;          // tcgen05 instruction descriptor (carries the negate bit)
 };
-// A group = the passes that walk the same K range together.  Each k-block stages every
-// distinct operand tile once (x and the two bfloat16 planes of its aux matrix, for A and
-// for B) and issues all the group's products from that one stage.
+// A group = the terms over one pair of fp32 operands (and so one K range).  Each k-block stages
+// the two fp32 tiles once, the converters add the derived parts, and all the group's products
+// are issued from that one stage.
 struct TcGroup {
   int k_iters;             // ceil(k / bk)
-  int nA, nB, nmma;
-  uint32_t stage_tx;       // bytes TMA delivers per k-block
-  TcOperand A[kMaxOperands], B[kMaxOperands];
-  TcMma mma[4];
+  int nconv, nmma;
+  uint32_t stage_tx;       // bytes TMA delivers per k-block and CTA
+  TcLoad load[2];          // A, B
+  TcConv conv[2];
+  TcTile tile[kMaxTiles];
+  TcMma mma[kMaxMma];
 };
 
 struct TcParams {
@@ -189,16 +208,6 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Shared-window addresses carry the CTA's rank within the pair in bit 24; clearing it names the
-// same location in the pair's leader (rank 0).
-constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
-// Loads into THIS CTA's shared memory, completes the transaction on the LEADER's mbarrier.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
-          "r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar & kPeerBitMask));
-}
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -233,12 +242,16 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask)
                "h"(cta_mask)
                : "memory");
 }
-// Arrive on the barrier at this offset in the pair's leader.
+// Arrive on the barrier at this offset in the pair's leader.  Default semantics (release at
+// CTA scope), as a consumer releasing a stage to its producer does: a cluster-scope release
+// costs about 0.5 us per arrive here, more than a whole k-block.  What the leader's tensor core
+// then reads from this CTA's shared memory was made visible to the async proxy by the proxy
+// fence that precedes the arrive.
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
   asm volatile(
       "{\n\t.reg .b32 ra;\n\t"
       "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar)
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar)
       : "memory");
 }
 
@@ -280,7 +293,13 @@ __device__ __forceinline__ void tile_coords_g(int t, int tiles_m, int tiles_n, i
 // (two of them ping-pong) and the epilogue warps add the finished chunk into fp32
 // registers with ordinary rounding while the next chunk is being multiplied.
 constexpr int kEpiWarps = 8;
-constexpr int kThreadsTc = 32 * (2 + kEpiWarps);
+constexpr int kConvWarps = 4;
+constexpr int kFirstConvWarp = 4, kFirstEpiWarp = kFirstConvWarp + kConvWarps;   // warps 2, 3 only hold their place
+constexpr int kThreadsTc = 32 * (kFirstEpiWarp + kEpiWarps);
+// Registers per thread: the kernel starts with 65536 / 512 = 128 everywhere; the two epilogue
+// warpgroups (128 accumulator columns per thread) grow to kEpiRegs with what the other two give up.
+constexpr int kEpiRegs = 176, kOtherRegs = 80;
+static_assert(kFirstEpiWarp == 8 && kEpiWarps == 8 && kEpiRegs + kOtherRegs <= 256, "register split between warpgroups");
 
 template <int BN>
 struct TcConfig {
@@ -291,12 +310,64 @@ struct TcConfig {
 
 // Epilogue variants, chosen on the host.  The common cases are compiled without run-time
 // branches (they are instruction-bound otherwise):
-//   kEpiPlain        out = alpha * acc (+ beta * out)                  (`dot`, statistics)
-//   kEpiSigLo        out = logistic(alpha * acc + bias) and its aux matrix
-//   kEpiSigLoSample  kEpiSigLo plus sample = Bernoulli(out) and the sample's aux matrix
-//   kEpiLinLo        out = alpha * acc + bias and its aux matrix
-//   kEpiGeneric      every option tested at run time
-enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSigLo = 2, kEpiSigLoSample = 3, kEpiLinLo = 4 };
+//   kEpiPlain      out = alpha * acc (+ beta * out)                  (`dot`, statistics)
+//   kEpiSig        out = logistic(alpha * acc + bias)
+//   kEpiSigSample  kEpiSig plus sample = Bernoulli(out)
+//   kEpiLin        out = alpha * acc + bias
+//   kEpiGeneric    every option tested at run time
+enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSig = 2, kEpiSigSample = 3, kEpiLin = 4 };
+
+// Two packed bfloat16 (round to nearest even): `lo` goes to the lower address.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+// (volatile keeps these in program order among themselves and with the barrier operations; no
+// memory clobber, so that the arithmetic between them can be scheduled freely)
+__device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w));
+}
+__device__ __forceinline__ void sts128u(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w));
+}
+__device__ __forceinline__ float tf32_rest(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+// Derives the wanted parts of sixteen elements: four 16-byte chunks of the fp32 tile at s[0..3]
+// (s[0], s[1] are eight consecutive elements, s[2], s[3] the next eight).  x - tf32(x) goes as
+// fp32 to the same places of the lo32 tile (d32 - src apart), and as bfloat16 / bfloat16(x) to one
+// 16-byte chunk per eight elements of the lo16 / b16 tiles.  All loads are issued first.
+__device__ __forceinline__ void convert16(const uint32_t (&s)[4], bool lo32, uint32_t d32_minus_src, bool lo16,
+                                          uint32_t d_lo16_0, uint32_t d_lo16_1, bool b16, uint32_t d_b16_0,
+                                          uint32_t d_b16_1) {
+  float4 x[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) x[i] = lds128(s[i]);
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+    l[i] = make_float4(tf32_rest(x[i].x), tf32_rest(x[i].y), tf32_rest(x[i].z), tf32_rest(x[i].w));
+  if (lo32) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) sts128(s[i] + d32_minus_src, l[i]);
+  }
+  if (lo16) {
+    sts128u(d_lo16_0, make_uint4(pack_bf16(l[0].x, l[0].y), pack_bf16(l[0].z, l[0].w), pack_bf16(l[1].x, l[1].y),
+                                 pack_bf16(l[1].z, l[1].w)));
+    sts128u(d_lo16_1, make_uint4(pack_bf16(l[2].x, l[2].y), pack_bf16(l[2].z, l[2].w), pack_bf16(l[3].x, l[3].y),
+                                 pack_bf16(l[3].z, l[3].w)));
+  }
+  if (b16) {
+    sts128u(d_b16_0, make_uint4(pack_bf16(x[0].x, x[0].y), pack_bf16(x[0].z, x[0].w), pack_bf16(x[1].x, x[1].y),
+                                pack_bf16(x[1].z, x[1].w)));
+    sts128u(d_b16_1, make_uint4(pack_bf16(x[2].x, x[2].y), pack_bf16(x[2].z, x[2].w), pack_bf16(x[3].x, x[3].y),
+                                pack_bf16(x[3].z, x[3].w)));
+  }
+}
 
 // kTwo: two CTAs of a cluster share one 256 x BN tile (cta_group::2): each stages its own 128
 // rows of A and half of B's rows, the leader issues the MMAs for both.
@@ -307,11 +378,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t out_stage_base = smem_base + kStageBudget;
   const uint32_t bar_base = out_stage_base + kOutStageBytes;
-  // barrier layout (8 bytes each): full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2]
+  // barrier layout (8 bytes each): full[kMaxStages], empty[kMaxStages], ready[kMaxStages], tmem_full[2], tmem_empty[2]
+  //   full  : this CTA's TMA copies of the stage have landed            (producer -> converters)
+  //   ready : the derived tiles of the stage are written, in both CTAs   (converters -> issuer of the leader)
+  //   empty : the MMAs that read the stage are done                      (issuer -> producer, both CTAs)
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  auto ready_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * kMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * kMaxStages + 2 + a); };
+  static_assert(8 * (3 * kMaxStages + 4) <= 256, "barrier area");
   const int num_stages = p.num_stages;
   const uint32_t stage_bytes = p.stage_bytes;
   const int bk = p.bk;
@@ -331,6 +407,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     for (int s = 0; s < kMaxStages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(ready_bar(s), kTwo ? 2 * kConvWarps : kConvWarps);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
@@ -358,16 +435,20 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   for (int q = 0; q < p.ngroups; q++) total_k_iters += p.group[q].k_iters;
   const int kChunkIters = p.chunk_iters;
 
+  // Every warpgroup (four warps) passes ONE setmaxnreg instruction, at the top of its branch.
+  if (warp < kFirstConvWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // The whole warp runs the loop; copy u = 8 * operand + box (operands A0..A2, B0..B2, up to 8
-    // boxes each) is issued by lane u % 32, so a lane issues at most two copies per k-block.  The
-    // refill of a freed stage is on the critical path of a ring this shallow: every constant
-    // sits in registers.
+    // The whole warp runs the loop; lane l issues (at most) one box per k-block: operand l / 16
+    // (A, B), box l % 16 of it (an MN-major tile comes as boxes of 32 floats x bk).  The refill of
+    // a freed stage is on the critical path of a ring this shallow, so every constant sits in
+    // registers and a lane issues one copy only.
     {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const int opi = lane >> 4, box = lane & 15;
       long long t_empty = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
@@ -376,28 +457,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
           const int k_iters = gr.k_iters;
-          const uint32_t tx = kTwo ? 2 * gr.stage_tx : gr.stage_tx;
-          // this lane's copies, if any
-          bool active[2];
-          const CUtensorMap* map[2];
-          int row0[2], mn[2];
-          uint32_t dst_off[2];
-#pragma unroll
-          for (int c = 0; c < 2; c++) {
-            const int u = lane + 32 * c, opi = u >> 3, box = u & 7;
-            const bool is_a = opi < kMaxOperands;
-            const int slot = is_a ? opi : opi - kMaxOperands;
-            active[c] = opi < 2 * kMaxOperands && slot < (is_a ? gr.nA : gr.nB);
-            TcOperand op = gr.A[0];
-            if (active[c]) op = is_a ? gr.A[slot] : gr.B[slot];
-            // a B tile has BN_LOCAL rows, an A tile BM: B's box count scales with it
-            const int nboxes = op.mn ? (is_a ? BM : BN_LOCAL) / op.box_rows : 1;
-            active[c] = active[c] && box < nboxes;
-            map[c] = &p.maps[op.map];
-            row0[c] = (is_a ? m0 : n0) + (op.mn ? op.box_rows * box : 0);
-            dst_off[c] = op.smem_off + (op.mn ? (uint32_t)(box * bk * 128) : 0u);
-            mn[c] = op.mn;
-          }
+          const TcLoad ld = gr.load[opi];
+          const int nboxes = ld.mn ? (ld.is_a ? BM / 32 : BN_LOCAL / 32) : 1;
+          const bool active = box < nboxes;
+          const CUtensorMap* map = &p.maps[ld.map];
+          const int row0 = (ld.is_a ? m0 : n0) + (ld.mn ? 32 * box : 0);
+          const uint32_t dst_off = ld.smem_off + (ld.mn ? (uint32_t)(box * bk * 128) : 0u);
+          const int mn = ld.mn;
           for (int kb = 0; kb < k_iters; kb++) {
             if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag))) {
               ok = false;
@@ -406,17 +472,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               break;
             }
             const uint32_t bar = full_bar(stage);
-            // the leader's barrier collects the bytes of both CTAs of a pair
-            if (lane == 0 && rank == 0) mbar_expect_tx(bar, tx);
-            const int k0 = kb * bk;
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-              if (active[c]) {
-                const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
-                const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
-                if (kTwo) tma_load_2d_pair(dst, map[c], x, y, bar);
-                else tma_load_2d(dst, map[c], x, y, bar);
-              }
+            if (lane == 0) mbar_expect_tx(bar, gr.stage_tx);
+            __syncwarp();   // the expectation is posted before any copy can complete
+            if (active) {
+              const uint32_t dst = smem_base + stage * stage_bytes + dst_off;
+              const int k0 = kb * bk;
+              const int x = mn ? row0 : k0, y = mn ? k0 : row0;
+              tma_load_2d(dst, map, x, y, bar);
             }
             if (++stage == num_stages) {
               stage = 0;
@@ -447,7 +509,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const int ksteps = bk / 8;
       long long t_full = 0, t_tempty = 0;
       const long long t_start = clock64();
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
@@ -458,22 +519,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           // The issuing thread must launch an MMA every ~70 ns to keep the tensor pipe busy: all
           // per-product constants live in registers, the k-loop only adds the stage address.
           const int nm = gr.nmma, k_iters = gr.k_iters;
-          uint32_t a_lo[4], b_lo[4], a_hi[4], b_hi[4], a_adv[4], b_adv[4], idesc[4];
-          bool f16[4];
+          uint32_t a_lo[kMaxMma], b_lo[kMaxMma], a_hi[kMaxMma], b_hi[kMaxMma], a_adv[kMaxMma], b_adv[kMaxMma],
+              idesc[kMaxMma];
+          bool f16[kMaxMma];
 #pragma unroll
-          for (int i = 0; i < 4; i++) {
+          for (int i = 0; i < kMaxMma; i++) {
             a_lo[i] = b_lo[i] = a_hi[i] = b_hi[i] = a_adv[i] = b_adv[i] = idesc[i] = 0;
             f16[i] = false;
             if (i < nm) {
               f16[i] = gr.mma[i].f16 != 0;
-              const TcOperand oa = gr.A[gr.mma[i].a];
-              const TcOperand ob = gr.B[gr.mma[i].b];
-              a_lo[i] = oa.desc_lo + (oa.smem_off >> 4);
-              b_lo[i] = ob.desc_lo + (ob.smem_off >> 4);
-              a_hi[i] = oa.desc_hi;
-              b_hi[i] = ob.desc_hi;
-              a_adv[i] = oa.adv;
-              b_adv[i] = ob.adv;
+              const TcTile ta = gr.tile[gr.mma[i].a];
+              const TcTile tb = gr.tile[gr.mma[i].b];
+              a_lo[i] = ta.desc_lo + (ta.smem_off >> 4);
+              b_lo[i] = tb.desc_lo + (tb.smem_off >> 4);
+              a_hi[i] = ta.desc_hi;
+              b_hi[i] = tb.desc_hi;
+              a_adv[i] = ta.adv;
+              b_adv[i] = tb.adv;
               idesc[i] = gr.mma[i].idesc;
             }
           }
@@ -490,42 +552,40 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               tc_fence_after();
               fresh = 1;
             }
-            if (!TIMED_WAIT(t_full, mbar_wait(full_bar(stage), phase, &abort_flag))) {
+            // the stage is loaded and converted in both CTAs
+            if (!TIMED_WAIT(t_full, mbar_wait(ready_bar(stage), phase, &abort_flag))) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 3);
               abort_flag = 1;
               break;
             }
-            // No tcgen05 fence here: the stage was filled by TMA (async proxy, ordered by the
-            // mbarrier); a fence per k-block would make the issuer wait for the MMAs in flight.
+            // No tcgen05 fence here: a fence per k-block would make the issuer wait for the MMAs in
+            // flight.  The tiles were written through the async proxy (TMA) or made visible to it by
+            // the converters' proxy fence, ordered by the mbarriers.
             const uint32_t d_tmem = tmem_base + acc * BN;
             const uint32_t sb = (smem_base + stage * stage_bytes) >> 4;   // stage address, 16-byte units
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 0; i < kMaxMma; i++) {
               if (i < nm) {
                 const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
                 if (f16[i]) {
-                  // bfloat16: K = 16 per instruction, half as many instructions per k-block
+                  // bfloat16: K = 16 per instruction, two instructions per k-block of 32
 #pragma unroll
                   for (int j = 0; j < 2; j++) {
-                    if (2 * j < ksteps) {
-                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
-                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
-                      if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                      else mma_f16(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                      fresh = 0;
-                    }
+                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                    if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    else mma_f16(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    fresh = 0;
                   }
                 } else {
 #pragma unroll
                   for (int j = 0; j < 4; j++) {
-                    if (j < ksteps) {
-                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
-                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
-                      if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                      else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                      fresh = 0;
-                    }
+                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                    if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
+                    fresh = 0;
                   }
                 }
               }
@@ -558,10 +618,108 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       (void)t_full; (void)t_tempty; (void)t_start;
 #endif
     }
+  }   // warps 2, 3: nothing to do
+  } else if (warp < kFirstEpiWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+    // ------------------------------------------------------------ converters
+    // For every k-block: wait for this CTA's fp32 tiles, write the derived tiles next to them in
+    // the layout TMA would have produced for a tensor of that element type, make them visible to
+    // the tensor core (async proxy) and arrive on the leader's `ready` barrier.
+    //   K-major fp32 tile : rows of 128 B (32 floats of K), 16-byte chunk c of row r at c ^ (r & 7)
+    //   K-major bf16 tile : rows of 64 B, chunk c of row r at c ^ ((r >> 1) & 3)
+    //   MN-major fp32 tile: boxes of bk rows (one k each) of 128 B = 32 floats of M/N, 32-byte
+    //                       group g of row k at g ^ (k & 3)
+    //   MN-major bf16 tile: boxes of bk rows of 128 B = 64 bfloat16 of M/N (two fp32 boxes side
+    //                       by side), 16-byte chunk c of row k at c ^ (k & 7)
+    // A tile has as many units as rows of M/N (a row of a K-major tile, one k-row of one box of an
+    // MN-major tile), each of four 8-element pieces; thread ct takes units ct, ct + 64, ...
+    const int ct = threadIdx.x - 32 * kFirstConvWarp;
+    constexpr int kConvThreads = 32 * kConvWarps;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    long long t_cfull = 0, t_conv = 0;
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int q = 0; q < p.ngroups && ok; q++) {
+        const TcGroup& gr = p.group[q];
+        const int k_iters = gr.k_iters, nconv = gr.nconv;
+        const TcConv c0 = gr.conv[0], c1 = gr.conv[1];
+        for (int kb = 0; kb < k_iters; kb++) {
+          if (!TIMED_WAIT(t_cfull, mbar_wait(full_bar(stage), phase, &abort_flag))) {
+            ok = false;
+            if (!abort_flag) atomicCAS(p.status, 0, 5);
+            abort_flag = 1;
+            break;
+          }
+          const uint32_t sbase = smem_base + stage * stage_bytes;
+#ifdef B200_GEMM_TIMING
+          const long long t_c0 = clock64();
+#endif
+#pragma unroll
+          for (int ci = 0; ci < 2; ci++) {
+            if (ci < nconv) {
+              const TcConv cv = ci == 0 ? c0 : c1;
+              const int units = cv.is_a ? BM : BN_LOCAL;
+              const bool w32 = cv.lo32_off != kNoTile, w16 = cv.lo16_off != kNoTile, wb = cv.b16_off != kNoTile;
+              const uint32_t src = sbase + cv.src_off, d32 = sbase + cv.lo32_off, d16 = sbase + cv.lo16_off,
+                             db = sbase + cv.b16_off;
+              const uint32_t d32_minus_src = d32 - src;
+              for (int u = ct; u < units; u += kConvThreads) {
+                if (!cv.mn) {
+                  const uint32_t r = (uint32_t)u, sw = r & 7u, sw16 = (r >> 1) & 3u;
+                  const uint32_t row32 = src + r * 128u, row16 = r * 64u;
+#pragma unroll
+                  for (uint32_t h = 0; h < 2; h++) {   // half a row: 16 elements of K
+                    const uint32_t sa[4] = {row32 + (((4 * h) ^ sw) << 4), row32 + (((4 * h + 1) ^ sw) << 4),
+                                            row32 + (((4 * h + 2) ^ sw) << 4), row32 + (((4 * h + 3) ^ sw) << 4)};
+                    const uint32_t o0 = row16 + (((2 * h) ^ sw16) << 4), o1 = row16 + (((2 * h + 1) ^ sw16) << 4);
+                    convert16(sa, w32, d32_minus_src, w16, d16 + o0, d16 + o1, wb, db + o0, db + o1);
+                  }
+                } else {
+                  const uint32_t box = (uint32_t)u >> 5, k = (uint32_t)u & 31u;
+                  const uint32_t row32 = src + box * (uint32_t)(bk * 128) + k * 128u;
+                  const uint32_t row16 = (box >> 1) * (uint32_t)(bk * 128) + k * 128u;
+#pragma unroll
+                  for (uint32_t h = 0; h < 2; h++) {   // half a k-row of the box: 16 elements of M/N
+                    const uint32_t g0 = row32 + (((2 * h) ^ (k & 3u)) << 5), g1 = row32 + (((2 * h + 1) ^ (k & 3u)) << 5);
+                    const uint32_t sa[4] = {g0, g0 + 16u, g1, g1 + 16u};
+                    const uint32_t c0 = (box & 1u) * 4u + 2 * h;
+                    const uint32_t o0 = row16 + ((c0 ^ (k & 7u)) << 4), o1 = row16 + (((c0 + 1) ^ (k & 7u)) << 4);
+                    convert16(sa, w32, d32_minus_src, w16, d16 + o0, d16 + o1, wb, db + o0, db + o1);
+                  }
+                }
+              }
+            }
+          }
+          fence_async_smem();   // the derived tiles are read through the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            if (kTwo) mbar_arrive_leader(ready_bar(stage));
+            else mbar_arrive(ready_bar(stage));
+          }
+#ifdef B200_GEMM_TIMING
+          t_conv += clock64() - t_c0;
+#endif
+          if (++stage == num_stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+#ifdef B200_GEMM_TIMING
+    if (p.dbg && ct == 0) {
+      p.dbg[blockIdx.x * 8 + 6] = (unsigned long long)t_cfull;
+      p.dbg[blockIdx.x * 8 + 7] = (unsigned long long)t_conv;
+    }
+#else
+    (void)t_cfull; (void)t_conv;
+#endif
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
     // ------------------------------------------------------------ epilogue warps
     constexpr int COLS = Cfg::kColsPerWarp;
-    const int ew = warp - 2;
+    const int ew = warp - kFirstEpiWarp;
     const int wq = warp & 3;          // TMEM lane quarter this warp may read
     const int col_base = (ew >> 2) * COLS;
     uint32_t chunk = 0;
@@ -632,29 +790,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         // for the arithmetic; a batch of four columns (one Philox block) is staged as
         // [array][column][128 rows], and one thread of each column-half group of four warps
         // sends it on with cp.async.bulk.tensor while the next batch is computed (two buffers).
-        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias, out, out_aux set; beta = 0;
-                                                    // no col_scale; a draw comes with its aux
+        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias and out set; beta = 0; no col_scale
         const bool row_ok = m < pM;
         const int hf = ew >> 2;                     // column half = store group
         const bool leader = (ew & 3) == 0 && lane == 0;
         const int row = wq * 32 + lane;             // row of the CTA's 128
         const float alpha = e.alpha, beta = spec ? 0.0f : e.beta;
         const float bias = ((spec || e.bias) && row_ok) ? e.bias[m] : 0.0f;
-        const bool logistic = spec ? (kEpi != kEpiLinLo) : (e.activation == 1);
-        const bool draw = spec ? (kEpi == kEpiSigLoSample) : (e.sample != nullptr || e.sample_aux != nullptr);
+        const bool logistic = spec ? (kEpi != kEpiLin) : (e.activation == 1);
+        const bool draw = spec ? (kEpi == kEpiSigSample) : (e.sample != nullptr);
         const bool has_out = spec || e.out != nullptr;
-        const bool has_aux = spec || e.out_aux != nullptr;
-        const bool has_smp = spec ? draw : e.sample != nullptr;
-        const bool has_smp_aux = spec ? draw : e.sample_aux != nullptr;
         const PhiloxKey key = e.key;
         const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
         const long off = (long)nc * e.ldo + m, ldo = e.ldo;
         const int m_tile = tm * TILE_M + (int)rank * BM;     // first row of this CTA's part of the tile
-        // one staged batch: [out f32][aux plane 0 bf16][aux plane 1 bf16][sample f32][sample bf16],
-        // each kOutCols columns of BM rows
-        constexpr uint32_t kF32 = kOutCols * BM * 4, kB16 = kOutCols * BM * 2;
-        constexpr uint32_t kOffLo = kF32, kOffB = kF32 + kB16, kOffSmp = kF32 + 2 * kB16, kOffSmpB = 2 * kF32 + 2 * kB16;
-        constexpr uint32_t kBufBytes = 2 * kF32 + 3 * kB16;
+        // one staged batch: [out][sample], each kOutCols columns of BM rows of fp32
+        constexpr uint32_t kArrayBytes = kOutCols * BM * 4;
+        constexpr uint32_t kBufBytes = kOutArrays * kArrayBytes;
         static_assert(4 * kBufBytes <= kOutStageBytes, "epilogue staging");
         const uint32_t group_base = out_stage_base + (uint32_t)hf * 2u * kBufBytes;
 #pragma unroll
@@ -679,31 +831,18 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes;
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u, a16 = buf + (uint32_t)(j * BM + row) * 2u;
+            const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u;
             if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32), "f"(x[j]) : "memory");
-            if (has_aux) {
-              uint16_t lo16, b16;
-              split_aux(x[j], lo16, b16);
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffLo), "h"(lo16) : "memory");
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffB), "h"(b16) : "memory");
-            }
             if (draw) {
-              const bool on = word_to_uniform(pick_word(w, j)) < x[j];
-              if (has_smp) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kOffSmp), "f"(on ? 1.0f : 0.0f) : "memory");
-              if (has_smp_aux)
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffSmpB), "h"((uint16_t)(on ? 0x3f80 : 0)) : "memory");
+              const float sbit = word_to_uniform(pick_word(w, j)) < x[j] ? 1.0f : 0.0f;
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kArrayBytes), "f"(sbit) : "memory");
             }
           }
           fence_async_smem();                       // generic-proxy writes visible to the TMA engine
           named_bar_sync(1 + hf, 128);
           if (leader && c0 < pN && m_tile < pM) {
             if (has_out) tma_store_2d(&p.maps[p.out_map[0]], m_tile, c0, buf);
-            if (has_aux) {
-              tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, buf + kOffLo);
-              tma_store_2d(&p.maps[p.out_map[2]], m_tile, c0, buf + kOffB);
-            }
-            if (has_smp) tma_store_2d(&p.maps[p.out_map[3]], m_tile, c0, buf + kOffSmp);
-            if (has_smp_aux) tma_store_2d(&p.maps[p.out_map[4]], m_tile, c0, buf + kOffSmpB);
+            if (draw) tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, buf + kArrayBytes);
           }
           if (leader) {
             tma_store_commit();
@@ -717,7 +856,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
 #endif
     }
 #ifdef B200_GEMM_TIMING
-    if (p.dbg && threadIdx.x == 64) {
+    if (p.dbg && threadIdx.x == 32 * kFirstEpiWarp) {
       p.dbg[blockIdx.x * 8 + 4] = (unsigned long long)t_tfull;
       p.dbg[blockIdx.x * 8 + 5] = (unsigned long long)t_epi;
     }
@@ -762,11 +901,9 @@ struct MapKey {
   const void* ptr;
   uint64_t d0, d1, ld;
   uint32_t b0, b1;
-  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle, 3: none (output tiles)
-  int bf16;
+  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 3: none (output tiles)
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz &&
-           bf16 == o.bf16;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
   }
 };
 struct MapKeyHash {
@@ -775,22 +912,21 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.d0;
     h = h * 1000003u ^ k.d1;
     h = h * 1000003u ^ k.ld;
-    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 3 | (uint32_t)k.swz << 1 | (uint32_t)k.bf16);
+    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 2 | (uint32_t)k.swz);
     return h;
   }
 };
 
-// 2-D map over fp32 or bfloat16 elements: inner (contiguous) extent d0, outer extent d1 with a
-// stride of ld elements, box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of
-// 16-byte chunks (K-major fp32 tiles, 32 floats of K per row; MN-major bfloat16 tiles, 64 per
-// row); 2: 64-byte swizzle (K-major, 16 floats or 32 bfloat16 per row); 1: 128-byte swizzle of
-// 32-byte chunks, the only shared-memory layout tcgen05 accepts for MN-major 32-bit operands;
-// 3: none (output tiles).  Encoded maps are cached.
-bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
-              int swz, int bf16) {
+// 2-D fp32 map: inner (contiguous) extent d0, outer extent d1 with a stride of ld floats,
+// box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of 16-byte chunks
+// (K-major tiles, 32 floats of K per row); 1: 128-byte swizzle of 32-byte chunks, the only
+// shared-memory layout tcgen05 accepts for MN-major 32-bit operands; 3: none (output tiles).
+// Encoded maps are cached.
+bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+              int swz) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  const MapKey key{ptr, d0, d1, ld, b0, b1, swz, bf16};
+  const MapKey key{ptr, d0, d1, ld, b0, b1, swz};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -800,15 +936,14 @@ bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint6
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {d0, d1};
-  const cuuint64_t strides[1] = {ld * (bf16 ? 2 : 4)};
+  const cuuint64_t strides[1] = {ld * sizeof(float)};
   const cuuint32_t box[2] = {b0, b1};
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  const CUresult r = fn(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr,
-                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swz == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                                 : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                             : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B)),
+                                 : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
@@ -818,58 +953,41 @@ bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint6
 }
 
 // TMA needs a 16-byte aligned base and column stride.
-inline bool tma_ok(const GemmOperand& o) {
-  return (o.ld % (o.bf16 ? 8 : 4) == 0) && (((uintptr_t)o.ptr & 15) == 0);
-}
+inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0); }
 
 // Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
 // 16-byte units), descriptor version 1 for sm_100 (bits 46-47), layout type in bits 61-63.
-//  K-major, rows of 128 B (32 floats of K): 8-row groups 1024 B apart, 128B swizzle (type 2).
-//  K-major, rows of 64 B (16 floats or 32 bfloat16 of K): 8-row groups 512 B apart, 64B swizzle (type 4).
-//  MN-major 32-bit: rows (one k each) of 128 B = 32 floats along M/N, 4-row groups 512 B apart,
-//                   128B swizzle with 32-byte atoms (type 1).
-//  MN-major 16-bit: rows (one k each) of 128 B = 64 bfloat16 along M/N, 8-row groups 1024 B apart,
-//                   128B swizzle (type 2).
+//  K-major fp32, rows of 128 B (32 floats of K): 8-row groups 1024 B apart, 128B swizzle (type 2).
+//  K-major bf16, rows of 64 B (32 bfloat16 of K): 8-row groups 512 B apart, 64B swizzle (type 4).
+//  MN-major fp32: rows (one k each) of 128 B = 32 floats along M/N, 4-row groups 512 B apart,
+//                 128B swizzle with 32-byte atoms (type 1).
+//  MN-major bf16: rows (one k each) of 128 B = 64 bfloat16 along M/N, 8-row groups 1024 B apart,
+//                 128B swizzle (type 2).
 // The lower word carries the start address and the leading byte offset (for MN-major tiles the
-// distance between two 128-byte wide column blocks = one TMA box = bk rows of 128 B).
+// distance between two 128-byte wide column blocks = bk rows of 128 B).
 constexpr uint32_t kDescHiK32 = (1024u >> 4) | (1u << 14) | (2u << 29);
 constexpr uint32_t kDescHiK16 = (512u >> 4) | (1u << 14) | (4u << 29);
 constexpr uint32_t kDescHiMN = (512u >> 4) | (1u << 14) | (1u << 29);
 constexpr uint32_t kDescHiMN16 = (1024u >> 4) | (1u << 14) | (2u << 29);
 
-// Fills the tcgen05 view of one operand; `rows` = extent of the tile along M or N.
-bool fill_operand(TcOperand& op, CUtensorMap* map_slot, int map_index, const GemmOperand& src, bool is_a, int mn_extent,
-                  int k, int rows, int bk) {
-  // op(A) is M x k: trans -> stored k x M, k contiguous (K-major); else M contiguous.
-  // op(B) is k x N: not trans -> stored k x N, k contiguous (K-major); trans -> N contiguous.
-  op.mn = is_a ? (src.trans ? 0 : 1) : (src.trans ? 1 : 0);
-  op.map = map_index;
-  bool ok;
-  if (op.mn) {
-    op.box_rows = src.bf16 ? 64 : 32;                // 128 bytes of M/N per box row
-    op.nboxes = rows / op.box_rows;
-    ok = make_map(map_slot, src.ptr, (uint64_t)mn_extent, (uint64_t)k, (uint64_t)src.ld, (uint32_t)op.box_rows,
-                  (uint32_t)bk, src.bf16 ? 0 : 1, src.bf16);
-    op.desc_hi = src.bf16 ? kDescHiMN16 : kDescHiMN;
-    op.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;  // distance between column blocks = bk rows x 128 B
-    op.adv = (src.bf16 ? 2048u : 1024u) >> 4;        // one MMA reads 16 (bfloat16) or 8 (fp32) rows of 128 B
+// The tcgen05 view of a staged tile of fp32 (as loaded, or the lo32 part) or of bfloat16 (a derived part).
+TcTile tile_view(bool mn, bool bf16, int bk, uint32_t smem_off) {
+  TcTile t;
+  t.smem_off = smem_off;
+  if (mn) {
+    t.desc_hi = bf16 ? kDescHiMN16 : kDescHiMN;
+    t.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;   // distance between column blocks = bk rows x 128 B
+    t.adv = (bf16 ? 2048u : 1024u) >> 4;             // one MMA reads 16 (bfloat16) or 8 (fp32) rows of 128 B
   } else {
-    op.box_rows = rows;
-    op.nboxes = 1;
-    const bool row128 = !src.bf16 && bk == 32;       // bytes of K per row: 128 (32 floats) or 64
-    ok = make_map(map_slot, src.ptr, (uint64_t)k, (uint64_t)mn_extent, (uint64_t)src.ld, (uint32_t)bk, (uint32_t)rows,
-                  row128 ? 0 : 2, src.bf16);
-    op.desc_hi = row128 ? kDescHiK32 : kDescHiK16;
-    op.desc_lo = 1u << 16;                           // leading byte offset is unused for swizzled K-major tiles
-    op.adv = 32u >> 4;                               // one MMA reads 32 bytes of K inside the swizzled row
+    t.desc_hi = bf16 ? kDescHiK16 : kDescHiK32;
+    t.desc_lo = 1u << 16;                            // leading byte offset is unused for swizzled K-major tiles
+    t.adv = 32u >> 4;                                // one MMA reads 32 bytes of K inside the swizzled row
   }
-  return ok;
+  return t;
 }
 
-inline uint32_t tile_bytes(const GemmOperand& o, int rows, int bk) { return (uint32_t)rows * bk * (o.bf16 ? 2 : 4); }
-
 inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
-  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.bf16 == b.bf16;
+  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
 }
 
 static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
@@ -936,19 +1054,17 @@ int launch_tc(TcParams& p) {
 bool gemm_tc_supported(const GemmProblem& g) {
   if (g.M <= 0 || g.N <= 0 || g.npass <= 0 || g.npass > kMaxPass) return false;
   for (int q = 0; q < g.npass; q++) {
-    if (!tma_ok(g.pass[q].a) || !tma_ok(g.pass[q].b) || g.pass[q].k <= 0) return false;
-    if (g.pass[q].a.bf16 != g.pass[q].b.bf16) return false;
+    const GemmPass& ps = g.pass[q];
+    if (!tma_ok(ps.a) || !tma_ok(ps.b) || ps.k <= 0) return false;
+    if ((ps.a.part >= kPartLo16) != (ps.b.part >= kPartLo16)) return false;
   }
   const GemmEpilogue& e = g.epi;
-  if ((e.sample || e.sample_aux) && (e.col0 & 3)) return false;
-  // activation epilogues store whole column segments with TMA: 16-byte aligned columns (the
-  // planes of an aux matrix are, its columns being a multiple of 8 floats)
-  const bool plain = !e.bias && e.activation == 0 && !e.out_aux && !e.sample && !e.sample_aux && e.out;
+  if (e.sample && (e.col0 & 3)) return false;
+  // activation epilogues store whole column segments with TMA: 16-byte aligned columns
+  const bool plain = !e.bias && e.activation == 0 && !e.sample && e.out;
   if (!plain) {
-    if (e.ldo % 4 != 0 || e.ld_aux % 8 != 0) return false;
-    const float* outs[4] = {e.out, e.out_aux, e.sample, e.sample_aux};
-    for (const float* o : outs)
-      if ((uintptr_t)o & 15) return false;
+    if (e.ldo % 4 != 0) return false;
+    if (((uintptr_t)e.out | (uintptr_t)e.sample) & 15) return false;
   }
   return encode_fn() != nullptr;
 }
@@ -957,75 +1073,116 @@ int gemm_tc(const GemmProblem& g) {
   if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
   static int pair_mode = -1;   // B200_GEMM_2CTA=0 keeps one CTA per tile
+  static int chunk_k = 0;
   if (pair_mode < 0) {
     const char* e = getenv("B200_GEMM_2CTA");
     pair_mode = e ? atoi(e) : 1;
+    const char* c = getenv("B200_CHUNK_K");
+    chunk_k = c ? atoi(c) : 0;
   }
   // pairs of CTAs (cta_group::2) on 256-row tiles when the product has at least two row tiles
   const bool two = pair_mode != 0 && BN == 256 && g.M > BM;
   const int BN_LOCAL = two ? BN / 2 : BN;      // rows of B staged per CTA
+  // 32 elements of K per k-block (one 128-byte swizzle row of floats); 16 doubles the stage count
+  // but measured slower (64-byte rows, twice the MMA and TMA issues)
+  const int bk = 32;
   TcParams p;
   p.M = g.M;
   p.N = g.N;
+  p.bk = bk;
   p.epi = g.epi;
   p.status = status_word();
 #ifdef B200_GEMM_TIMING
   p.dbg = (unsigned long long*)workspace(7, 8 * 512 * sizeof(unsigned long long));
 #endif
 
-  // ---- group consecutive passes that share K and need at most two distinct A and B operands
-  struct HostGroup {
-    int k, nA, nB, nmma;
-    GemmOperand A[kMaxOperands], B[kMaxOperands];
-    int ma[4], mb[4], neg[4], f16[4];
-  } hg[kMaxPass];
-  int ngroups = 0;
+  // ---- group consecutive terms over the same two fp32 matrices (at most kMaxMma of them)
+  int ngroups = 0, nmaps = 0;
+  uint32_t stage_bytes = 0;
+  const GemmPass* first_of[kMaxPass];
   for (int q = 0; q < g.npass; q++) {
     const GemmPass& ps = g.pass[q];
-    bool placed = false;
     if (ngroups > 0) {
-      HostGroup& h = hg[ngroups - 1];
-      if (h.k == ps.k && h.nmma < 4) {
-        int ia = -1, ib = -1;
-        for (int i = 0; i < h.nA; i++) if (same_operand(h.A[i], ps.a)) ia = i;
-        for (int i = 0; i < h.nB; i++) if (same_operand(h.B[i], ps.b)) ib = i;
-        const int needA = ia < 0 ? 1 : 0, needB = ib < 0 ? 1 : 0;
-        if (h.nA + needA <= kMaxOperands && h.nB + needB <= kMaxOperands) {
-          if (ia < 0) { ia = h.nA; h.A[h.nA++] = ps.a; }
-          if (ib < 0) { ib = h.nB; h.B[h.nB++] = ps.b; }
-          h.ma[h.nmma] = ia; h.mb[h.nmma] = ib; h.neg[h.nmma] = ps.negate; h.f16[h.nmma] = ps.a.bf16;
-          h.nmma++;
-          placed = true;
-        }
+      const GemmPass& f = *first_of[ngroups - 1];
+      if (same_operand(f.a, ps.a) && same_operand(f.b, ps.b) && f.k == ps.k && p.group[ngroups - 1].nmma < kMaxMma) {
+        p.group[ngroups - 1].nmma++;
+        continue;
       }
     }
-    if (!placed) {
-      HostGroup& h = hg[ngroups++];
-      h.k = ps.k;
-      h.nA = h.nB = h.nmma = 1;
-      h.A[0] = ps.a;
-      h.B[0] = ps.b;
-      h.ma[0] = h.mb[0] = 0;
-      h.neg[0] = ps.negate;
-      h.f16[0] = ps.a.bf16;
+    first_of[ngroups] = &ps;
+    p.group[ngroups].nmma = 1;
+    ngroups++;
+  }
+  int q0 = 0;
+  for (int gi = 0; gi < ngroups; gi++) {
+    TcGroup& tg = p.group[gi];
+    const GemmPass& f = g.pass[q0];
+    tg.k_iters = (f.k + bk - 1) / bk;
+    // op(A) is M x k: trans -> stored k x M, k contiguous (K-major); else M contiguous.
+    // op(B) is k x N: not trans -> stored k x N, k contiguous (K-major); trans -> N contiguous.
+    const bool mn[2] = {f.a.trans == 0, f.b.trans != 0};
+    const GemmOperand* src[2] = {&f.a, &f.b};
+    const int rows[2] = {BM, BN_LOCAL}, extent[2] = {g.M, g.N};
+    // which parts the group's terms read
+    bool want[2][4] = {{false, false, false, false}, {false, false, false, false}};
+    for (int i = 0; i < tg.nmma; i++) {
+      want[0][g.pass[q0 + i].a.part] = true;
+      want[1][g.pass[q0 + i].b.part] = true;
     }
+    uint32_t off = 0;
+    int tile_of[2][4];
+    int ntiles = 0;
+    tg.nconv = 0;
+    for (int o = 0; o < 2; o++) {   // the loaded tiles first
+      TcLoad& ld = tg.load[o];
+      ld.map = nmaps;
+      ld.mn = mn[o];
+      ld.is_a = o == 0;
+      ld.smem_off = off;
+      const bool ok = mn[o] ? make_map(&p.maps[nmaps], src[o]->ptr, (uint64_t)extent[o], (uint64_t)f.k,
+                                       (uint64_t)src[o]->ld, 32, (uint32_t)bk, 1)
+                            : make_map(&p.maps[nmaps], src[o]->ptr, (uint64_t)f.k, (uint64_t)extent[o],
+                                       (uint64_t)src[o]->ld, (uint32_t)bk, (uint32_t)rows[o], 0);
+      if (!ok) return set_error("cuTensorMapEncodeTiled failed for an operand");
+      nmaps++;
+      tile_of[o][kPartX] = ntiles;
+      tg.tile[ntiles++] = tile_view(mn[o], false, bk, off);
+      off += (uint32_t)rows[o] * bk * 4;
+    }
+    tg.stage_tx = off;
+    for (int o = 0; o < 2; o++) {   // then the derived ones
+      if (!want[o][kPartLo32] && !want[o][kPartLo16] && !want[o][kPartB16]) continue;
+      TcConv& cv = tg.conv[tg.nconv++];
+      cv.src_off = tg.load[o].smem_off;
+      cv.mn = mn[o];
+      cv.is_a = o == 0;
+      cv.lo32_off = cv.lo16_off = cv.b16_off = kNoTile;
+      for (int part = kPartLo32; part <= kPartB16; part++) {
+        if (!want[o][part]) continue;
+        const bool bf16 = part != kPartLo32;
+        (part == kPartLo32 ? cv.lo32_off : (part == kPartLo16 ? cv.lo16_off : cv.b16_off)) = off;
+        tile_of[o][part] = ntiles;
+        tg.tile[ntiles++] = tile_view(mn[o], bf16, bk, off);
+        off += (uint32_t)rows[o] * bk * (bf16 ? 2 : 4);
+      }
+    }
+    if (off > stage_bytes) stage_bytes = off;
+    for (int i = 0; i < tg.nmma; i++) {
+      const GemmPass& ps = g.pass[q0 + i];
+      TcMma& m = tg.mma[i];
+      m.a = tile_of[0][ps.a.part];
+      m.b = tile_of[1][ps.b.part];
+      m.f16 = ps.a.part >= kPartLo16;
+      // instruction descriptor: D fp32 (bit 4), A and B format at bits 7 and 10 (TF32 = 2 for
+      // kind::tf32, BF16 = 1 for kind::f16), negate A (bit 13), A / B MN-major (bits 15 / 16),
+      // N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t fmt = m.f16 ? 1u : 2u;
+      m.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((ps.negate ? 1u : 0u) << 13) | ((mn[0] ? 1u : 0u) << 15) |
+                ((mn[1] ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((two ? 2 * BM : BM) >> 4) << 24);
+    }
+    q0 += tg.nmma;
   }
-  // ---- ring geometry: 32 elements of K per k-block (one 128-byte swizzle row of floats); 16
-  // doubles the stage count but measured slower (64-byte rows, twice the MMA and TMA issues)
-  const int bk = 32;
-  p.bk = bk;
-  uint32_t stage_bytes = 0;
-  for (int q = 0; q < ngroups; q++) {
-    uint32_t b = 0;
-    for (int i = 0; i < hg[q].nA; i++) b += tile_bytes(hg[q].A[i], BM, bk);
-    for (int i = 0; i < hg[q].nB; i++) b += tile_bytes(hg[q].B[i], BN_LOCAL, bk);
-    if (b > stage_bytes) stage_bytes = b;
-  }
-  static int chunk_k = -1;
-  if (chunk_k < 0) {
-    const char* c = getenv("B200_CHUNK_K");
-    chunk_k = c ? atoi(c) : 0;
-  }
+  p.ngroups = ngroups;
   p.stage_bytes = stage_bytes;
   p.num_stages = (int)(kStageBudget / p.stage_bytes);
   if (p.num_stages > kMaxStages) p.num_stages = kMaxStages;
@@ -1036,77 +1193,33 @@ int gemm_tc(const GemmProblem& g) {
   // (measured 2e-7 absolute on the probabilities), which costs 8 % less time.
   const int ck = chunk_k >= 16 ? chunk_k : (g.epi.activation == 1 ? 512 : 128);
   p.chunk_iters = ck / bk < 1 ? 1 : ck / bk;
-  p.ngroups = ngroups;
-  int nmaps = 0;
-  for (int q = 0; q < ngroups; q++) {
-    const HostGroup& h = hg[q];
-    TcGroup& tg = p.group[q];
-    tg.k_iters = (h.k + bk - 1) / bk;
-    tg.nA = h.nA;
-    tg.nB = h.nB;
-    tg.nmma = h.nmma;
-    uint32_t off = 0;
-    for (int i = 0; i < h.nA; i++) {
-      if (!fill_operand(tg.A[i], &p.maps[nmaps], nmaps, h.A[i], true, g.M, h.k, BM, bk))
-        return set_error("cuTensorMapEncodeTiled failed for operand A");
-      nmaps++;
-      tg.A[i].smem_off = off;
-      off += tile_bytes(h.A[i], BM, bk);
-    }
-    for (int i = 0; i < h.nB; i++) {
-      if (!fill_operand(tg.B[i], &p.maps[nmaps], nmaps, h.B[i], false, g.N, h.k, BN_LOCAL, bk))
-        return set_error("cuTensorMapEncodeTiled failed for operand B");
-      nmaps++;
-      tg.B[i].smem_off = off;
-      off += tile_bytes(h.B[i], BN_LOCAL, bk);
-    }
-    tg.stage_tx = off;
-    for (int i = 0; i < h.nmma; i++) {
-      tg.mma[i].a = h.ma[i];
-      tg.mma[i].b = h.mb[i];
-      tg.mma[i].f16 = h.f16[i];
-      // instruction descriptor: D fp32 (bit 4), A and B format at bits 7 and 10 (TF32 = 2 for
-      // kind::tf32, BF16 = 1 for kind::f16), negate A (bit 13), A / B MN-major (bits 15 / 16),
-      // N >> 3 at bit 17, M >> 4 at bit 24
-      const uint32_t fmt = h.f16[i] ? 1u : 2u;
-      tg.mma[i].idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((h.neg[i] ? 1u : 0u) << 13) |
-                        ((uint32_t)tg.A[h.ma[i]].mn << 15) | ((uint32_t)tg.B[h.mb[i]].mn << 16) |
-                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((two ? 2 * BM : BM) >> 4) << 24);
-    }
-  }
+
   const GemmEpilogue& e = g.epi;
   int epi = kEpiGeneric;
-  if (!e.bias && e.activation == 0 && !e.out_aux && !e.sample && !e.sample_aux && e.out) {
+  if (!e.bias && e.activation == 0 && !e.sample && e.out) {
     epi = kEpiPlain;
-  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out && e.out_aux) {
-    if (e.activation == 1 && e.sample && e.sample_aux) epi = kEpiSigLoSample;
-    else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSigLo;
-    else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLinLo;
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out) {
+    if (e.activation == 1) epi = e.sample ? kEpiSigSample : kEpiSig;
+    else if (!e.sample) epi = kEpiLin;
   }
   for (int i = 0; i < kOutArrays; i++) p.out_map[i] = -1;
   if (epi != kEpiPlain) {
-    // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns: M x N floats
-    // with columns ldo apart, or one bfloat16 plane of an aux matrix (columns 2 ld_aux bfloat16
-    // apart, plane 1 starting ld_aux bfloat16 into the column)
-    const uint16_t* oa = reinterpret_cast<const uint16_t*>(e.out_aux);
-    const uint16_t* sa = reinterpret_cast<const uint16_t*>(e.sample_aux);
-    const void* outs[kOutArrays] = {e.out, oa, oa ? oa + e.ld_aux : nullptr, e.sample, sa ? sa + e.ld_aux : nullptr};
-    const int is16[kOutArrays] = {0, 1, 1, 0, 1};
+    // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns
+    const float* outs[kOutArrays] = {e.out, e.sample};
     for (int i = 0; i < kOutArrays; i++) {
       if (!outs[i]) continue;
-      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)(is16[i] ? 2 * e.ld_aux : e.ldo), BM,
-                    kOutCols, 3, is16[i]))
+      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)e.ldo, BM, kOutCols, 3))
         return set_error("cuTensorMapEncodeTiled failed for an output");
       p.out_map[i] = nmaps++;
     }
   }
-#define B200_TC_CASE(BNV, TWO)                                            \
-  switch (epi) {                                                          \
-    case kEpiPlain: return launch_tc<BNV, kEpiPlain, TWO>(p);             \
-    case kEpiSigLo: return launch_tc<BNV, kEpiSigLo, TWO>(p);             \
-    case kEpiSigLoSample: return launch_tc<BNV, kEpiSigLoSample, TWO>(p); \
-    case kEpiLinLo: return launch_tc<BNV, kEpiLinLo, TWO>(p);             \
-    default: return launch_tc<BNV, kEpiGeneric, TWO>(p);                  \
+#define B200_TC_CASE(BNV, TWO)                                        \
+  switch (epi) {                                                      \
+    case kEpiPlain: return launch_tc<BNV, kEpiPlain, TWO>(p);         \
+    case kEpiSig: return launch_tc<BNV, kEpiSig, TWO>(p);             \
+    case kEpiSigSample: return launch_tc<BNV, kEpiSigSample, TWO>(p); \
+    case kEpiLin: return launch_tc<BNV, kEpiLin, TWO>(p);             \
+    default: return launch_tc<BNV, kEpiGeneric, TWO>(p);              \
   }
   if (BN == 256 && two) { B200_TC_CASE(256, true) }
   if (BN == 256) { B200_TC_CASE(256, false) }

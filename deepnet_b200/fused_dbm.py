@@ -6,8 +6,8 @@ Gibbs sweeps on persistent particles, :240-261 updates), but a layer update - th
 with BOTH neighbouring layers, bias, logistic, Bernoulli draw - is one `fused_gemm` call whose
 pass list mixes the two inner dimensions, and positive-minus-negative edge statistics are one
 call per edge.  Split-TF32 as in fused_rbm: a real-valued matrix x is multiplied as
-x.y (TF32) + lo_x.y + x.lo_y (bfloat16 planes of the aux matrices); a binary one (data, samples)
-needs no low-part term.
+x.y plus correction terms over its low part x - tf32(x), which the kernel derives from x itself;
+a binary one (data, samples) has no low part.
 """
 import numpy as np
 
@@ -21,76 +21,60 @@ class FusedDBM(object):
         self.L = len(sizes)
         cm.CUDAMatrix.init_random(seed)
         z = lambda r, c: cm.empty((r, c))
-        za = lambda r, c: cm.empty_aux((r, c))
         B = batchsize
-        self.W, self.W_aux, self.dW, self.suff_W = [], [], [], []
+        self.W, self.dW, self.suff_W = [], [], []
         for i, w in enumerate(weights):
             w = np.asarray(w, np.float32)
             assert w.shape == (sizes[i], sizes[i + 1])
-            W = cm.CUDAMatrix(w)
-            self.W.append(W)
-            self.W_aux.append(W.split_bf16(za(*w.shape)))   # bfloat16 planes read by the correction products
+            self.W.append(cm.CUDAMatrix(w))
             self.dW.append(z(*w.shape))
             self.suff_W.append(z(*w.shape))
         self.b = [z(n, 1) for n in sizes]
         self.db = [z(n, 1) for n in sizes]
         self.suff_b = [z(n, 1) for n in sizes]
         self.pos = [z(n, B) for n in sizes]
-        self.pos_aux = [za(n, B) for n in sizes]
         self.neg = [z(n, B) for n in sizes]
-        self.neg_aux = [za(n, B) for n in sizes]
         self.neg_sample = [z(n, B) for n in sizes]
-        self.neg_sample_aux = [za(n, B) for n in sizes]
-        self.data_aux = za(sizes[0], B)
-        # fp32 low parts of the statistics operands (every term of that product is a TF32 product)
-        self.pos_lo = [z(n, B) for n in sizes]
-        self.neg_lo = [z(n, B) for n in sizes]
         self.loss_acc = z(1, 1)
         self._sched = Parameter(cm, hyperparams)
         self.kernel_launches = 0
 
-    def _update_layer(self, j, below, above, out, out_aux, sample, sample_aux):
+    def _update_layer(self, j, below, above, out, sample):
         """state_j = sigmoid(W[j-1]' below + W[j] above + b_j) (deepnet/dbm.py:82-105), optional draw.
-        below / above = (state, its aux matrix, exact): exact states (0/1) need no low-part term."""
+        below / above = (state, exact): exact states (0/1) have no low part."""
         P = self.cm.split_passes
         passes = []
         if below is not None:
-            passes += P(self.W[j - 1].T, self.W_aux[j - 1].T, below[0], below[1], exact_x=below[2])
+            passes += P(self.W[j - 1].T, below[0], exact_b=below[1])
         if above is not None:
-            passes += P(self.W[j], self.W_aux[j], above[0], above[1], exact_x=above[2])
-        self.cm.fused_gemm(passes, out=out, out_aux=out_aux, sample=sample, sample_aux=sample_aux, bias=self.b[j],
-                           activation=1)
+            passes += P(self.W[j], above[0], exact_b=above[1])
+        self.cm.fused_gemm(passes, out=out, sample=sample, bias=self.b[j], activation=1)
         self.kernel_launches += 1
 
     def TrainOneBatch(self, step, data):
         cm, L, hyp = self.cm, self.L, self.hyp
         self.kernel_launches = 0
-        pos, pos_aux, neg, neg_aux = self.pos, self.pos_aux, self.neg, self.neg_aux
-        ns, ns_aux = self.neg_sample, self.neg_sample_aux
-        data_aux = data.split_bf16(self.data_aux)
+        pos, neg, ns = self.pos, self.neg, self.neg_sample
         # ---- positive phase: data clamped, hidden layers start at zero, mean-field sweeps
         for j in range(1, L):
             pos[j].assign(0)
-            pos_aux[j].assign(0)
         for _ in range(hyp.mf_steps):
             for j in range(1, L):
-                below = (data, data_aux, True) if j == 1 else (pos[j - 1], pos_aux[j - 1], False)
-                above = (pos[j + 1], pos_aux[j + 1], False) if j < L - 1 else None
-                self._update_layer(j, below, above, pos[j], pos_aux[j], None, None)
+                below = (data, True) if j == 1 else (pos[j - 1], False)
+                above = (pos[j + 1], False) if j < L - 1 else None
+                self._update_layer(j, below, above, pos[j], None)
         # bias statistics of the positive phase (the visible state is the data here)
         data.sum(axis=1, target=self.suff_b[0])
         for j in range(1, L):
             pos[j].sum(axis=1, target=self.suff_b[j])
         # PCD reports the reconstruction of the input from the first hidden layer (deepnet/dbm.py:163-166)
-        self._update_layer(0, None, (pos[1], pos_aux[1], False), pos[0], pos_aux[0], None, None)
+        self._update_layer(0, None, (pos[1], False), pos[0], None)
         cm._check(cm._lib.add_sq_diff(pos[0].p_mat, data.p_mat, self.loss_acc.p_mat))
         # ---- particles start from the positive states at step 0 (deepnet/dbm.py:169-181, 270-271)
         if step == 0:
             for j in range(L):
                 neg[j].assign(pos[j])
-                neg_aux[j].assign(pos_aux[j])
                 neg[j].sample_bernoulli(target=ns[j])
-                ns[j].split_bf16(ns_aux[j])
         # ---- negative phase: Gibbs sweeps on the particles, neighbours' samples as input
         gibbs = hyp.gibbs_steps
         if hyp.start_step_up_cd_after > 0 and hyp.start_step_up_cd_after < step:
@@ -98,25 +82,17 @@ class FusedDBM(object):
         for _ in range(gibbs):
             for j in range(L):
                 # the visible "sample" is its mean (sample_input off), so it carries a low part
-                below = None if j == 0 else ((neg[0], neg_aux[0], False) if j == 1 else (ns[j - 1], ns_aux[j - 1], True))
-                above = (ns[j + 1], ns_aux[j + 1], True) if j < L - 1 else None
-                self._update_layer(j, below, above, neg[j], neg_aux[j], ns[j] if j > 0 else None,
-                                   ns_aux[j] if j > 0 else None)
+                below = None if j == 0 else ((neg[0], False) if j == 1 else (ns[j - 1], True))
+                above = (ns[j + 1], True) if j < L - 1 else None
+                self._update_layer(j, below, above, neg[j], ns[j] if j > 0 else None)
         # ---- statistics pos - neg and updates
         for j in range(L):
             self.suff_b[j].add_sums(neg[j], axis=1, mult=-1.0)
         for i in range(L - 1):
-            # the difference of two nearly equal products: all-TF32 terms on fp32 low parts
-            T = cm.tf32_passes
-            if i == 0:
-                for j in range(L):
-                    if j > 0:
-                        pos[j].split_tf32(self.pos_lo[j])
-                    neg[j].split_tf32(self.neg_lo[j])
-            plo, nlo = self.pos_lo, self.neg_lo
-            # the data are exact: only the hidden means carry a low part
-            p = T(data if i == 0 else pos[i], None if i == 0 else plo[i], pos[i + 1].T, plo[i + 1].T)
-            n = T(neg[i], nlo[i], neg[i + 1].T, nlo[i + 1].T, negate=1)
+            # the difference of two nearly equal products: TF32 correction terms; the data are exact
+            P = cm.split_passes
+            p = P(data if i == 0 else pos[i], pos[i + 1].T, exact_a=(i == 0), terms="tf32")
+            n = P(neg[i], neg[i + 1].T, negate=1, terms="tf32")
             cm.fused_gemm(p + n, out=self.suff_W[i])
         inv_b = 1.0 / self.B
         mom, eps = self._sched.GetMomentumAndEpsilon(step)
@@ -126,8 +102,7 @@ class FusedDBM(object):
         for j in range(L):
             self.b[j].momentum_update(self.db[j], None, self.suff_b[j], inv_b, mom, eps)
         for i in range(L - 1):
-            self.W[i].momentum_update(self.dW[i], None, self.suff_W[i], inv_b, mom, eps, l2=l2, l1=l1,
-                                      w_aux=self.W_aux[i])
+            self.W[i].momentum_update(self.dW[i], None, self.suff_W[i], inv_b, mom, eps, l2=l2, l1=l1)
 
     def read_loss(self, reset=True):
         v = float(np.array(self.loss_acc.asarray())[0, 0])

@@ -5,7 +5,7 @@ call for the positive hidden sample, one per Gibbs step), but every group of
 reference calls is one kernel:
 
   dot + add_col_vec + sigmoid + sample_bernoulli   -> fused_gemm (bias, activation, Bernoulli in the
-      (deepnet/dbm.py:88-105, logistic_layer.py:11-15)  epilogue; TF32 hi/lo split of the result written too)
+      (deepnet/dbm.py:88-105, logistic_layer.py:11-15)  epilogue)
   dot(v, h.T) and add_dot(..., mult=-1)            -> one fused_gemm with negated passes
       (deepnet/edge.py:236,242)
   add_mult / mult / add_mult / assign(0)           -> momentum_update (one pass over W)
@@ -14,9 +14,11 @@ reference calls is one kernel:
       (deepnet/logistic_layer.py:48-52)
 
 fp32-grade products: the tensor core reads an fp32 operand as TF32 (low 13 mantissa
-bits ignored), so x serves as its own high part and only lo = x - tf32(x) is kept
-beside it; x.y ~= lo_x.y + x.lo_y + x.y.  Binary matrices (data, Bernoulli samples)
-have lo = 0 and need one pass fewer.
+bits ignored); the kernel derives lo = x - tf32(x) from the staged tile of x and adds the
+correction terms lo_x.y + x.lo_y to x.y - as bfloat16 products (twice the TF32 rate) for
+the activation products, as TF32 products for the statistics, whose positive and negative
+halves nearly cancel.  Binary matrices (data, Bernoulli samples) have lo = 0 and need one
+term fewer.  Only fp32 matrices live in device memory.
 
 With more than one rank the sufficient statistics of the ranks' minibatch shards are
 summed by one NCCL all-reduce of a packed buffer before the update.
@@ -39,12 +41,9 @@ class FusedRBM(object):
         cm.CUDAMatrix.init_random(seed)
         cm.set_rng_column_offset(rank * batchsize)
         z = lambda r, c: cm.empty((r, c))
-        za = lambda r, c: cm.empty_aux((r, c))      # bfloat16 companions of the product operands
         w = np.asarray(weight, np.float32)
         assert w.shape == (V, H)
         self.W = cm.CUDAMatrix(w)
-        self.W_aux = za(V, H)                     # bfloat16 planes of W read by the correction products
-        self.W.split_bf16(self.W_aux)
         self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
         self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
         self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
@@ -54,21 +53,15 @@ class FusedRBM(object):
         self.suff_bv = self.pack.slice(V * H, V * H + V)
         self.suff_bh = self.pack.slice(V * H + V, V * H + V + H)
         B = batchsize
-        self.data_aux = za(V, B)
-        self.h_pos, self.h_pos_aux = z(H, B), za(H, B)
-        self.h_samp, self.h_samp_aux = z(H, B), za(H, B)
-        self.v_neg, self.v_neg_aux = z(V, B), za(V, B)
-        self.h_neg, self.h_neg_aux = z(H, B), za(H, B)
-        # fp32 low parts of the four operands of the statistics product (all-TF32 terms there)
-        self.v_pos_lo = None if binary_data and visible != REPLICATED_SOFTMAX else z(V, B)
-        self.h_pos_lo, self.v_neg_lo, self.h_neg_lo = z(H, B), z(V, B), z(H, B)
+        self.h_pos, self.h_samp = z(H, B), z(H, B)
+        self.v_neg, self.h_neg = z(V, B), z(H, B)
         self.loss_acc = z(1, 1)
         if visible == REPLICATED_SOFTMAX:
             # document lengths, length-normalised visible states (the statistics use state / NN,
             # deepnet/edge.py:225-228) and the multinomial sample fed upward
             self.NN = z(1, B)
             self.v0n, self.v_negn = z(V, B), z(V, B)
-            self.v_samp, self.v_samp_aux = z(V, B), za(V, B)
+            self.v_samp = z(V, B)
             self.v_act = z(V, B)                  # W h + b_v before the softmax
             self.tiny = 1e-10
         self._sched = Parameter(cm, self.hyp)
@@ -96,38 +89,30 @@ class FusedRBM(object):
             return self._train_replicated_softmax(step, data)
         cm, k = self.cm, self.hyp.gibbs_steps
         V, H, B = self.V, self.H, self.B
-        W, Wa = self.W, self.W_aux
-        P = cm.split_passes
-        v0, v0a = data, self.data_aux
+        W, P = self.W, cm.split_passes
+        v0 = data
         self.kernel_launches = 0
         gf = 2.0 * V * H * B                      # algorithmic flops of one product
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         lib = cm._lib
+        exact = self.binary_data                  # 0/1 data have no low part
         # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
-        exact = self.binary_data
-        self._op("split", 0, 2 * vb, v0.split_bf16, v0a)
-        self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, P(W.T, Wa.T, v0, v0a, exact_x=exact), out=self.h_pos,
-                 out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
+        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=exact), out=self.h_pos, sample=self.h_samp,
+                 bias=self.bh, activation=1)
         # negative phase: k Gibbs steps, visible mean fed upward (sample_input off)
         for i in range(k):
-            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, P(W, Wa, self.h_samp, self.h_samp_aux, exact_x=True),
-                     out=self.v_neg, out_aux=self.v_neg_aux, bias=self.bv, activation=self._act(self.visible))
+            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True), out=self.v_neg, bias=self.bv,
+                     activation=self._act(self.visible))
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1          # add_sq_diff is two launches
-            self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, P(W.T, Wa.T, self.v_neg, self.v_neg_aux), out=self.h_neg,
-                     out_aux=self.h_neg_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
-        # statistics: pos - neg in one product (the difference of two nearly equal products: every
-        # term a TF32 product, on fp32 low parts split off here); bias statistics by row sums
-        T = cm.tf32_passes
-        if not exact:
-            self._op("split", 0, 2 * vb, v0.split_tf32, self.v_pos_lo)
-        self._op("split", 0, 2 * hb, self.h_pos.split_tf32, self.h_pos_lo)
-        self._op("split", 0, 2 * vb, self.v_neg.split_tf32, self.v_neg_lo)
-        self._op("split", 0, 2 * hb, self.h_neg.split_tf32, self.h_neg_lo)
-        pos = T(v0, None if exact else self.v_pos_lo, self.h_pos.T, self.h_pos_lo.T)
-        neg = T(self.v_neg, self.v_neg_lo, self.h_neg.T, self.h_neg_lo.T, negate=1)
+            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_neg), out=self.h_neg, sample=self.h_samp,
+                     bias=self.bh, activation=1)
+        # statistics: pos - neg in one product: the difference of two nearly equal products, so its
+        # correction terms are TF32 products too; bias statistics by row sums
+        pos = P(v0, self.h_pos.T, exact_a=exact, terms="tf32")
+        neg = P(self.v_neg, self.h_neg.T, negate=1, terms="tf32")
         self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
         self._op("row_sum", 0, vb, v0.sum, axis=1, target=self.suff_bv)
         self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_neg, axis=1, mult=-1.0)
@@ -145,8 +130,8 @@ class FusedRBM(object):
         eh = self.ehyp
         l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1, w_aux=Wa)
+        self._op("update_W", 0, 5 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1)
 
     def _train_replicated_softmax(self, step, data):
         """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:
@@ -156,43 +141,33 @@ class FusedRBM(object):
         multinomial draw and one for the hidden draw."""
         cm, k = self.cm, self.hyp.gibbs_steps
         V, H, B = self.V, self.H, self.B
-        W, Wa = self.W, self.W_aux
-        P = cm.split_passes
+        W, P = self.W, cm.split_passes
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         lib = cm._lib
         self.kernel_launches = 0
-        v0, v0a = data, self.data_aux                          # integer counts: exact in TF32
+        v0 = data                                              # integer counts: exact in TF32
         # GetData: NN = column sums + tiny; v0n = data / NN for the statistics
         self._op("col_sum", 0, vb, v0.sum, axis=0, target=self.NN)
         self._op("add_scalar", 0, 8.0 * B, self.NN.add, self.tiny)
         self._op("div_by_row", 0, 2 * vb, v0.div_by_row, self.NN, target=self.v0n)
-        self._op("split", 0, 2 * vb, v0.split_bf16, v0a)
         # positive phase: hidden bias is scaled by the document length (deepnet/dbm.py:101-104)
-        self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, P(W.T, Wa.T, v0, v0a, exact_x=True), out=self.h_pos,
-                 out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh,
-                 col_scale=self.NN, activation=1)
+        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=True), out=self.h_pos, sample=self.h_samp,
+                 bias=self.bh, col_scale=self.NN, activation=1)
         for i in range(k):
             # visible: NN * softmax(W h + b_v)
-            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, Wa, self.h_samp, self.h_samp_aux, exact_x=True),
-                     out=self.v_act, bias=self.bv, activation=0)
+            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True), out=self.v_act, bias=self.bv,
+                     activation=0)
             self._op("softmax", 0, 2 * vb, self.v_act.softmax_scaled, self.NN, target=self.v_neg)
             self._op("div_by_row", 0, 2 * vb, self.v_neg.div_by_row, self.NN, target=self.v_negn)
             if i == 0:   # squared error between state / NN and the counts (replicated_softmax_layer.py:128-135)
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
             self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
-            self._op("split", 0, 2 * vb, self.v_samp.split_bf16, self.v_samp_aux)
-            self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, P(W.T, Wa.T, self.v_samp, self.v_samp_aux, exact_x=True),
-                     out=self.h_neg, out_aux=self.h_neg_aux, sample=self.h_samp, sample_aux=self.h_samp_aux,
-                     bias=self.bh, col_scale=self.NN, activation=1)
-        T = cm.tf32_passes
-        self._op("split", 0, 2 * vb, self.v0n.split_tf32, self.v_pos_lo)
-        self._op("split", 0, 2 * hb, self.h_pos.split_tf32, self.h_pos_lo)
-        self._op("split", 0, 2 * vb, self.v_negn.split_tf32, self.v_neg_lo)
-        self._op("split", 0, 2 * hb, self.h_neg.split_tf32, self.h_neg_lo)
-        pos = T(self.v0n, self.v_pos_lo, self.h_pos.T, self.h_pos_lo.T)
-        neg = T(self.v_negn, self.v_neg_lo, self.h_neg.T, self.h_neg_lo.T, negate=1)
+            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_samp, exact_b=True), out=self.h_neg,
+                     sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
+        pos = P(self.v0n, self.h_pos.T, terms="tf32")
+        neg = P(self.v_negn, self.h_neg.T, negate=1, terms="tf32")
         self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
         self._op("row_sum", 0, vb, self.v0n.sum, axis=1, target=self.suff_bv)
         self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_negn, axis=1, mult=-1.0)
@@ -208,16 +183,15 @@ class FusedRBM(object):
         eh = self.ehyp
         l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1, w_aux=Wa)
+        self._op("update_W", 0, 5 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1)
 
     def Inference(self, data, input_recon=False):
         """Hidden representation of `data` (V x cases device matrix), minibatch by minibatch:
         the inference-only positive phase of deepnet/dbm.py:340-398 (extract_rbm_representation.py)
         as one fused product per minibatch.  Returns (cases x H) host array, and with input_recon
         also the summed squared error of the input reconstructed from the hidden means."""
-        cm, B, W, Wa = self.cm, self.B, self.W, self.W_aux
-        P = cm.split_passes
+        cm, B, W, P = self.cm, self.B, self.W, self.cm.split_passes
         n = data.shape[1] // B
         rep = np.zeros((n * B, self.H), np.float32)
         err = 0.0
@@ -227,20 +201,17 @@ class FusedRBM(object):
             if soft:
                 v0.sum(axis=0, target=self.NN)
                 self.NN.add(self.tiny)
-            v0.split_bf16(self.data_aux)
-            up = P(W.T, Wa.T, v0, self.data_aux, exact_x=soft or self.binary_data)
-            cm.fused_gemm(up, out=self.h_pos, out_aux=self.h_pos_aux, bias=self.bh, activation=1,
+            cm.fused_gemm(P(W.T, v0, exact_b=soft or self.binary_data), out=self.h_pos, bias=self.bh, activation=1,
                           col_scale=self.NN if soft else None)
             if input_recon:
-                down = P(W, Wa, self.h_pos, self.h_pos_aux)
+                down = P(W, self.h_pos)
                 if soft:
                     cm.fused_gemm(down, out=self.v_act, bias=self.bv, activation=0)
                     self.v_act.softmax_scaled(self.NN, target=self.v_neg)
                     self.v_neg.div_by_row(self.NN, target=self.v_negn)
                     cm._check(cm._lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat, self.loss_acc.p_mat))
                 else:
-                    cm.fused_gemm(down, out=self.v_neg, out_aux=self.v_neg_aux, bias=self.bv,
-                                  activation=self._act(self.visible))
+                    cm.fused_gemm(down, out=self.v_neg, bias=self.bv, activation=self._act(self.visible))
                     cm._check(cm._lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat, self.loss_acc.p_mat))
             rep[b * B:(b + 1) * B, :] = np.array(self.h_pos.asarray()).T
         if input_recon:

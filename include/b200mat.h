@@ -157,26 +157,24 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha);
 
 /* ================= additions: no counterpart in the reference ======================== */
 
-/* The low-order companion ("aux matrix") of a rows x cols fp32 matrix x, read by the split
- * products: lda x cols floats of storage, lda = rows rounded up to a multiple of 8; column c
- * holds lda bfloat16 of plane 0, bf16(x - tf32(x)), then lda bfloat16 of plane 1, bf16(x)
- * (the first `rows` of each in use).  With it
- *   a . b ~= tf32(a) . tf32(b) + plane0(a) . plane1(b) + plane1(a) . plane0(b)
- * is one TF32 product plus two bfloat16 products (twice the TF32 rate) into one fp32
- * accumulator; the terms left out are of relative order 2^-18, rounded to nearest.
- * An aux handle is an ordinary cudamat of lda x cols. */
-int split_bf16(cudamat* x, cudamat* aux);
+/* What of an fp32 matrix x a term of a fused product multiplies.  The kernels derive the
+ * parts from x on the fly, only x lives in device memory:
+ *   B200_PART_X     x, read as TF32 on the tensor cores (the low 13 mantissa bits are dropped)
+ *   B200_PART_LO32  x - tf32(x), read as TF32
+ *   B200_PART_LO16  bfloat16(x - tf32(x))
+ *   B200_PART_B16   bfloat16(x)
+ * a . b ~= lo32(a).x(b) + x(a).lo32(b) + x(a).x(b)       three TF32 products, 2^-20 per term, or
+ * a . b ~= lo16(a).b16(b) + b16(a).lo16(b) + x(a).x(b)   one TF32 + two bfloat16 products (twice
+ *                                                        the TF32 rate), 2^-18 per term. */
+enum { B200_PART_X = 0, B200_PART_LO32 = 1, B200_PART_LO16 = 2, B200_PART_B16 = 3 };
 
 /* One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
- * a_plane / b_plane: -1 = the handle is an fp32 matrix (a TF32 product); 0 or 1 = the handle
- * is an aux matrix and the term reads that bfloat16 plane, a_rows / b_rows then being the
- * rows of the matrix the aux belongs to.  Both operands of a term are of the same kind. */
+ * Both parts of a term are fp32-wide (X, LO32) or both bfloat16 (LO16, B16). */
 typedef struct b200_pass {
   cudamat* a;
   cudamat* b;
   int negate;
-  int a_plane, b_plane;
-  int a_rows, b_rows;
+  int a_part, b_part;
 } b200_pass;
 
 /* out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale).
@@ -191,20 +189,18 @@ typedef struct b200_fused_gemm {
   cudamat* col_scale;    /* 1 x N or NULL: bias of column n is bias[m] * col_scale[n] */
   int activation;        /* 0 identity, 1 logistic */
   cudamat* out;          /* M x N or NULL */
-  cudamat* out_aux;      /* aux matrix of the result, or NULL */
   cudamat* sample;       /* Bernoulli(result): consumes one sampling call, or NULL */
-  cudamat* sample_aux;   /* aux matrix of the draw (plane 1 only: a 0/1 value has no low part), or NULL */
 } b200_fused_gemm;
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f);
 
-/* lo = x - tf32(x); hi (may be NULL) = tf32(x): the fp32 form of the split. */
+/* lo = x - tf32(x); hi (may be NULL) = tf32(x): the split the kernels apply on the fly. */
 int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
 
 /* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass over the parameter:
  * grad += -inv_batch * suff; delta = momentum*delta + l2*w + l1*sign(w) + grad;
- * w -= eps*delta; grad = 0; w_aux = aux matrix of the new w.  grad, w_aux may be NULL. */
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, float inv_batch,
-                    float momentum, float eps, float l2, float l1);
+ * w -= eps*delta; grad = 0.  grad may be NULL. */
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, float inv_batch, float momentum,
+                    float eps, float l2, float l1);
 
 /* Has no counterpart in the reference.  add_sum_by_axis for callers that must never reach
  * cudaMalloc (a host that gave the whole device to its own memory pool, or a loop that cannot

@@ -88,11 +88,6 @@ def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases):
     assert relerr(get(eng.v_neg), get(mo.GetLayerByName("v").state)) < TOL
     np.testing.assert_array_equal(get(eng.h_samp), get(mo.GetLayerByName("h").sample))  # Bernoulli bits
     assert np.abs(get(eng.bh) - get(mo.GetLayerByName("h").params["bias"])).max() < 1e-6
-    w = get(eng.W)       # the weights' bfloat16 planes follow every update
-    hi = (w.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
-    lo_plane, b_plane = eng.W_aux.planes()
-    assert np.abs(lo_plane - (w - hi)).max() <= np.abs(w - hi).max() * 2.0 ** -8
-    assert np.abs(b_plane - w).max() <= np.abs(w).max() * 2.0 ** -8
     assert cm.read_status() == 0
 
 

@@ -114,43 +114,40 @@ def tf32_trunc(x):
     return (np.ascontiguousarray(x, np.float32).view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
 
 
-@pytest.mark.parametrize("shape", [(100, 33), (500, 100), (128, 256), (7, 5)])
-def test_split_bf16_planes(cm, shape):
-    rng = np.random.default_rng(12)
-    x = (rng.standard_normal(shape) * 10.0 ** rng.integers(-3, 4, shape)).astype(np.float32)
-    aux = cm.CUDAMatrix(x).split_bf16(cm.empty_aux(shape))
-    lo, b = aux.planes()
-    np.testing.assert_array_equal(lo, bf16_round(x - tf32_trunc(x)))
-    np.testing.assert_array_equal(b, bf16_round(x))
+def part_values(x, part):
+    """What the kernels multiply for each operand part (float32)."""
+    if part == 0:
+        return tf32_trunc(x)
+    lo = (x - tf32_trunc(x)).astype(np.float32)
+    if part == 1:
+        return tf32_trunc(lo)
+    return bf16_round(lo) if part == 2 else bf16_round(x)
 
 
 @pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
-@pytest.mark.parametrize("m,n,k", [(500, 300, 784), (128, 64, 96), (260, 36, 40), (1000, 520, 4100)])
-def test_bf16_plane_product_all_layouts(cm, path, ta, tb, m, n, k):
-    """One bfloat16 pass = the exact product of the planes' bfloat16 values (fp32 accumulation)."""
+@pytest.mark.parametrize("m,n,k", [(500, 300, 784), (128, 64, 96), (260, 36, 40), (1000, 520, 2100)])
+def test_operand_parts_in_all_layouts(cm, path, ta, tb, m, n, k):
+    """One term over parts of the operands = the exact product of the parts' values (fp32
+    accumulation): the converter warps write what TMA would have delivered, in all four layouts."""
     rng = np.random.default_rng(13)
     A = rng.standard_normal((m, k)).astype(np.float32)
     B = rng.standard_normal((k, n)).astype(np.float32)
     cm.set_gemm_path(path)
     sa, sb = (A.T if ta else A), (B.T if tb else B)          # stored forms
     ga, gb = cm.CUDAMatrix(np.asfortranarray(sa)), cm.CUDAMatrix(np.asfortranarray(sb))
-    xa, xb = ga.split_bf16(cm.empty_aux(sa.shape)), gb.split_bf16(cm.empty_aux(sb.shape))
-    for pa, pb in ((1, 1), (0, 1), (1, 0)):
-        opa = (xa.b if pa else xa.lo)
-        opb = (xb.b if pb else xb.lo)
+    oa, ob = (ga.T if ta else ga), (gb.T if tb else gb)
+    for pa, pb in ((0, 0), (1, 0), (0, 1), (3, 3), (2, 3), (3, 2)):
         out = cm.empty((m, n))
-        cm.fused_gemm([(opa.T if ta else opa, opb.T if tb else opb)], out=out)
-        fa = bf16_round(A) if pa else bf16_round(A - tf32_trunc(A))
-        fb = bf16_round(B) if pb else bf16_round(B - tf32_trunc(B))
-        want = fa.astype(np.float64) @ fb.astype(np.float64)
+        cm.fused_gemm([(cm.Part(oa, pa), cm.Part(ob, pb))], out=out)
+        want = part_values(A, pa).astype(np.float64) @ part_values(B, pb).astype(np.float64)
         assert relerr(get(out), want) < 5e-6, (pa, pb)   # fp32 accumulation of k mixed-sign terms
     assert cm.read_status() == 0
 
 
 @pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("m,n,k", [(500, 100, 784), (128, 256, 64), (260, 36, 40), (1024, 512, 2048)])
-def test_fused_epilogue_bias_logistic_sample_split(cm, oracle, path, m, n, k):
+def test_fused_epilogue_bias_logistic_sample(cm, oracle, path, m, n, k):
     rng = np.random.default_rng(9)
     W = (rng.standard_normal((k, m)) * 0.1).astype(np.float32)
     X = (rng.random((k, n)) < 0.3).astype(np.float32)
@@ -160,42 +157,36 @@ def test_fused_epilogue_bias_logistic_sample_split(cm, oracle, path, m, n, k):
     cm.CUDAMatrix.init_random(seed)
     oracle.EigenMatrix.init_random(seed)
     w, x, bias = cm.CUDAMatrix(W), cm.CUDAMatrix(X), cm.CUDAMatrix(b)
-    w_aux, x_aux = w.split_bf16(cm.empty_aux(W.shape)), x.split_bf16(cm.empty_aux(X.shape))
     out, smp = cm.empty((m, n)), cm.empty((m, n))
-    out_aux, smp_aux = cm.empty_aux((m, n)), cm.empty_aux((m, n))
-    cm.fused_gemm(cm.split_passes(w.T, w_aux.T, x, x_aux, exact_x=True), out=out, out_aux=out_aux, sample=smp,
-                  sample_aux=smp_aux, bias=bias, activation=1, alpha=1.0)
+    cm.fused_gemm(cm.split_passes(w.T, x, exact_b=True), out=out, sample=smp, bias=bias, activation=1, alpha=1.0)
     pre = W.astype(np.float64).T @ X + b
     want = 1 / (1 + np.exp(-pre))
     got = get(out)
     assert relerr(got, want) < TOL
-    lo, bb = out_aux.planes()
-    np.testing.assert_array_equal(lo, bf16_round(got - tf32_trunc(got)))
-    np.testing.assert_array_equal(bb, bf16_round(got))
     # the draw thresholds the probabilities the kernel itself produced against the shared
     # uniforms of call 0: bit-exact with the oracle fed the same probabilities
     want_s = get(oracle.EigenMatrix(got).sample_bernoulli(target=oracle.empty((m, n))))
     np.testing.assert_array_equal(get(smp), want_s)
-    np.testing.assert_array_equal(smp_aux.planes()[1], want_s)
     assert cm.CUDAMatrix.rnd_state.calls == 1
     assert cm.read_status() == 0
 
 
 @pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("terms", ["bf16", "tf32"])
 @pytest.mark.parametrize("m,n,k", [(512, 256, 4096), (500, 100, 784)])
-def test_split_product_is_fp32_grade(cm, path, m, n, k):
-    """tf32 + two bfloat16 correction products against the float64 product of same-sign operands
+def test_split_product_is_fp32_grade(cm, path, terms, m, n, k):
+    """x.y plus its two correction terms against the float64 product of same-sign operands
     (the worst case for a truncating or biased scheme)."""
     rng = np.random.default_rng(14)
     A = rng.random((m, k)).astype(np.float32)
     B = rng.random((k, n)).astype(np.float32)
     cm.set_gemm_path(path)
-    ga, gb = cm.CUDAMatrix(A), cm.CUDAMatrix(B)
-    xa, xb = ga.split_bf16(cm.empty_aux(A.shape)), gb.split_bf16(cm.empty_aux(B.shape))
     out = cm.empty((m, n))
-    cm.fused_gemm(cm.split_passes(ga, xa, gb, xb), out=out)
-    # the CUDA-core kernel adds k same-sign terms one by one in fp32
-    assert relerr(get(out), A.astype(np.float64) @ B.astype(np.float64)) < (2e-6 if path == 1 else 3e-5)
+    cm.fused_gemm(cm.split_passes(cm.CUDAMatrix(A), cm.CUDAMatrix(B), terms=terms), out=out)
+    # the CUDA-core kernel adds k same-sign terms one by one in fp32; the TF32 correction terms
+    # truncate x - tf32(x) to 10 bits (a one-sided error on same-sign data), the bfloat16 ones round
+    tol = 3e-5 if path == 2 else (3e-6 if terms == "tf32" else 2e-6)
+    assert relerr(get(out), A.astype(np.float64) @ B.astype(np.float64)) < tol
 
 
 @pytest.mark.parametrize("path", [1, 2])
@@ -231,12 +222,8 @@ def test_momentum_update_is_bit_exact(cm, oracle, shape, with_grad):
     wo.momentum_update(do, go, oracle.EigenMatrix(s0), *args, l2=2e-4, l1=1e-3)
     wg, dg = cm.CUDAMatrix(w0), cm.CUDAMatrix(d0)
     gg = cm.CUDAMatrix(g0) if with_grad else None
-    aux = cm.empty_aux(shape)
-    wg.momentum_update(dg, gg, cm.CUDAMatrix(s0), *args, l2=2e-4, l1=1e-3, w_aux=aux)
+    wg.momentum_update(dg, gg, cm.CUDAMatrix(s0), *args, l2=2e-4, l1=1e-3)
     np.testing.assert_array_equal(get(wg), get(wo))
     np.testing.assert_array_equal(get(dg), get(do))
     if with_grad:
         assert not get(gg).any()
-    lo, b = aux.planes()
-    np.testing.assert_array_equal(lo, bf16_round(get(wg) - tf32_trunc(get(wg))))
-    np.testing.assert_array_equal(b, bf16_round(get(wg)))
