@@ -28,6 +28,7 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "gemm.cuh"
@@ -516,96 +517,114 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         uint32_t fresh = 1;
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
-          // The issuing thread must launch an MMA every ~70 ns to keep the tensor pipe busy: all
-          // per-product constants live in registers, the k-loop only adds the stage address.
-          const int nm = gr.nmma, k_iters = gr.k_iters;
-          uint32_t a_lo[kMaxMma], b_lo[kMaxMma], a_hi[kMaxMma], b_hi[kMaxMma], a_adv[kMaxMma], b_adv[kMaxMma],
-              idesc[kMaxMma];
-          bool f16[kMaxMma];
+          // The issuing thread must launch an MMA every ~70 ns to keep the tensor pipe busy, and what
+          // it does between two k-blocks is not hidden behind the pipe: all per-product constants
+          // live in registers, the k-loop only adds the stage address, and the common term lists
+          // (count and which terms are bfloat16 known at compile time) run as straight-line code.
+          auto run_group = [&](auto nm_c, auto mask_c) {
+            constexpr int kNm = decltype(nm_c)::value;       // -1: count and kinds read from the group
+            constexpr int kMask = decltype(mask_c)::value;   // bit i: term i is a bfloat16 product
+            const int nm = kNm >= 0 ? kNm : gr.nmma;
+            const int k_iters = gr.k_iters;
+            uint32_t a_lo[kMaxMma], b_lo[kMaxMma], a_hi[kMaxMma], b_hi[kMaxMma], a_adv[kMaxMma], b_adv[kMaxMma],
+                idesc[kMaxMma];
+            bool f16[kMaxMma];
 #pragma unroll
-          for (int i = 0; i < kMaxMma; i++) {
-            a_lo[i] = b_lo[i] = a_hi[i] = b_hi[i] = a_adv[i] = b_adv[i] = idesc[i] = 0;
-            f16[i] = false;
-            if (i < nm) {
-              f16[i] = gr.mma[i].f16 != 0;
-              const TcTile ta = gr.tile[gr.mma[i].a];
-              const TcTile tb = gr.tile[gr.mma[i].b];
-              a_lo[i] = ta.desc_lo + (ta.smem_off >> 4);
-              b_lo[i] = tb.desc_lo + (tb.smem_off >> 4);
-              a_hi[i] = ta.desc_hi;
-              b_hi[i] = tb.desc_hi;
-              a_adv[i] = ta.adv;
-              b_adv[i] = tb.adv;
-              idesc[i] = gr.mma[i].idesc;
+            for (int i = 0; i < kMaxMma; i++) {
+              a_lo[i] = b_lo[i] = a_hi[i] = b_hi[i] = a_adv[i] = b_adv[i] = idesc[i] = 0;
+              f16[i] = false;
+              if (i < nm) {
+                f16[i] = kNm >= 0 ? ((kMask >> i) & 1) != 0 : gr.mma[i].f16 != 0;
+                const TcTile ta = gr.tile[gr.mma[i].a];
+                const TcTile tb = gr.tile[gr.mma[i].b];
+                a_lo[i] = ta.desc_lo + (ta.smem_off >> 4);
+                b_lo[i] = tb.desc_lo + (tb.smem_off >> 4);
+                a_hi[i] = ta.desc_hi;
+                b_hi[i] = tb.desc_hi;
+                a_adv[i] = ta.adv;
+                b_adv[i] = tb.adv;
+                idesc[i] = gr.mma[i].idesc;
+              }
             }
-          }
-          for (int kb = 0; kb < k_iters; kb++) {
-            const int acc = chunk & 1;
-            if (in_chunk == 0) {
-              // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
-              if (!TIMED_WAIT(t_tempty, mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag))) {
+            for (int kb = 0; kb < k_iters; kb++) {
+              const int acc = chunk & 1;
+              if (in_chunk == 0) {
+                // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
+                if (!TIMED_WAIT(t_tempty, mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag))) {
+                  ok = false;
+                  if (!abort_flag) atomicCAS(p.status, 0, 2);
+                  abort_flag = 1;
+                  break;
+                }
+                tc_fence_after();
+                fresh = 1;
+              }
+              // the stage is loaded and converted in both CTAs
+              if (!TIMED_WAIT(t_full, mbar_wait(ready_bar(stage), phase, &abort_flag))) {
                 ok = false;
-                if (!abort_flag) atomicCAS(p.status, 0, 2);
+                if (!abort_flag) atomicCAS(p.status, 0, 3);
                 abort_flag = 1;
                 break;
               }
-              tc_fence_after();
-              fresh = 1;
-            }
-            // the stage is loaded and converted in both CTAs
-            if (!TIMED_WAIT(t_full, mbar_wait(ready_bar(stage), phase, &abort_flag))) {
-              ok = false;
-              if (!abort_flag) atomicCAS(p.status, 0, 3);
-              abort_flag = 1;
-              break;
-            }
-            // No tcgen05 fence here: a fence per k-block would make the issuer wait for the MMAs in
-            // flight.  The tiles were written through the async proxy (TMA) or made visible to it by
-            // the converters' proxy fence, ordered by the mbarriers.
-            const uint32_t d_tmem = tmem_base + acc * BN;
-            const uint32_t sb = (smem_base + stage * stage_bytes) >> 4;   // stage address, 16-byte units
+              // No tcgen05 fence here: a fence per k-block would make the issuer wait for the MMAs in
+              // flight.  The tiles were written through the async proxy (TMA) or made visible to it by
+              // the converters' proxy fence, ordered by the mbarriers.
+              const uint32_t d_tmem = tmem_base + acc * BN;
+              const uint32_t sb = (smem_base + stage * stage_bytes) >> 4;   // stage address, 16-byte units
 #pragma unroll
-            for (int i = 0; i < kMaxMma; i++) {
-              if (i < nm) {
-                const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
-                if (f16[i]) {
-                  // bfloat16: K = 16 per instruction, two instructions per k-block of 32
+              for (int i = 0; i < kMaxMma; i++) {
+                if (i < nm) {
+                  const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
+                  if (f16[i]) {
+                    // bfloat16: K = 16 per instruction, two instructions per k-block of 32
 #pragma unroll
-                  for (int j = 0; j < 2; j++) {
-                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
-                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
-                    if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    else mma_f16(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    fresh = 0;
-                  }
-                } else {
+                    for (int j = 0; j < 2; j++) {
+                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                      const uint32_t accumulate = (i == 0 && j == 0) ? (fresh ^ 1u) : 1u;
+                      if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      else mma_f16(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                    }
+                  } else {
 #pragma unroll
-                  for (int j = 0; j < 4; j++) {
-                    const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
-                    const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
-                    if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], fresh ^ 1u);
-                    fresh = 0;
+                    for (int j = 0; j < 4; j++) {
+                      const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
+                      const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
+                      const uint32_t accumulate = (i == 0 && j == 0) ? (fresh ^ 1u) : 1u;
+                      if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                    }
                   }
                 }
               }
+              fresh = 0;
+              // the stage is free (in both CTAs of a pair) once these MMAs have read it
+              if (kTwo) mma_commit_pair(empty_bar(stage), 3);
+              else mma_commit(empty_bar(stage));
+              if (++stage == num_stages) {
+                stage = 0;
+                phase ^= 1u;
+              }
+              in_tile++;
+              if (++in_chunk == kChunkIters || in_tile == total_k_iters) {
+                // chunk complete: hand it to the epilogue warps (of both CTAs)
+                if (kTwo) mma_commit_pair(tfull_bar(acc), 3);
+                else mma_commit(tfull_bar(acc));
+                chunk++;
+                in_chunk = 0;
+              }
             }
-            // the stage is free (in both CTAs of a pair) once these MMAs have read it
-            if (kTwo) mma_commit_pair(empty_bar(stage), 3);
-            else mma_commit(empty_bar(stage));
-            if (++stage == num_stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            in_tile++;
-            if (++in_chunk == kChunkIters || in_tile == total_k_iters) {
-              // chunk complete: hand it to the epilogue warps (of both CTAs)
-              if (kTwo) mma_commit_pair(tfull_bar(acc), 3);
-              else mma_commit(tfull_bar(acc));
-              chunk++;
-              in_chunk = 0;
-            }
-          }
+          };
+          int mask = 0;
+          for (int i = 0; i < gr.nmma; i++) mask |= (gr.mma[i].f16 != 0 ? 1 : 0) << i;
+          using std::integral_constant;
+          const int shape = gr.nmma * 16 + mask;
+          if (shape == 3 * 16 + 3) run_group(integral_constant<int, 3>{}, integral_constant<int, 3>{});        // lo16.b16, b16.lo16, x.x
+          else if (shape == 2 * 16 + 1) run_group(integral_constant<int, 2>{}, integral_constant<int, 1>{});   // lo16.b16, x.x
+          else if (shape == 3 * 16) run_group(integral_constant<int, 3>{}, integral_constant<int, 0>{});       // three TF32 terms
+          else if (shape == 2 * 16) run_group(integral_constant<int, 2>{}, integral_constant<int, 0>{});
+          else if (shape == 1 * 16) run_group(integral_constant<int, 1>{}, integral_constant<int, 0>{});
+          else run_group(integral_constant<int, -1>{}, integral_constant<int, 0>{});
         }
       }
 #ifdef B200_GEMM_TIMING
