@@ -199,6 +199,17 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- two-CTA (cta_group::2) forms: the pair of CTAs of a cluster works on one 256-row tile.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -349,9 +360,11 @@ __device__ __forceinline__ void convert16(const uint32_t (&s)[4], bool lo32, uin
   float4 x[4], l[4];
 #pragma unroll
   for (int i = 0; i < 4; i++) x[i] = lds128(s[i]);
+  if (lo32 || lo16) {
 #pragma unroll
-  for (int i = 0; i < 4; i++)
-    l[i] = make_float4(tf32_rest(x[i].x), tf32_rest(x[i].y), tf32_rest(x[i].z), tf32_rest(x[i].w));
+    for (int i = 0; i < 4; i++)
+      l[i] = make_float4(tf32_rest(x[i].x), tf32_rest(x[i].y), tf32_rest(x[i].z), tf32_rest(x[i].w));
+  }
   if (lo32) {
 #pragma unroll
     for (int i = 0; i < 4; i++) sts128(s[i] + d32_minus_src, l[i]);
@@ -505,7 +518,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (the pair's leader only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loops and one elected lane issues: computed by a single diverged
+    // lane, every operand of a tcgen05.mma has to be moved from that lane's registers to the
+    // uniform registers the instruction reads, about 50 ns per MMA whatever its size, and the
+    // issuing thread, not the tensor pipe, bounds the kernel.
+    if (rank == 0) {
+      const bool elected = elect_one();
       uint32_t chunk = 0;
       int stage = 0;
       uint32_t phase = 0;
@@ -582,8 +600,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
                       const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
                       const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
                       const uint32_t accumulate = (i == 0 && j == 0) ? (fresh ^ 1u) : 1u;
-                      if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
-                      else mma_f16(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      if (elected) {
+                        if (kTwo) mma_f16_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                        else mma_f16(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      }
                     }
                   } else {
 #pragma unroll
@@ -591,16 +611,20 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
                       const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
                       const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
                       const uint32_t accumulate = (i == 0 && j == 0) ? (fresh ^ 1u) : 1u;
-                      if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
-                      else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      if (elected) {
+                        if (kTwo) mma_tf32_pair(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                        else mma_tf32(d_tmem, a_desc, b_desc, idesc[i], accumulate);
+                      }
                     }
                   }
                 }
               }
               fresh = 0;
               // the stage is free (in both CTAs of a pair) once these MMAs have read it
-              if (kTwo) mma_commit_pair(empty_bar(stage), 3);
-              else mma_commit(empty_bar(stage));
+              if (elected) {
+                if (kTwo) mma_commit_pair(empty_bar(stage), 3);
+                else mma_commit(empty_bar(stage));
+              }
               if (++stage == num_stages) {
                 stage = 0;
                 phase ^= 1u;
@@ -608,8 +632,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               in_tile++;
               if (++in_chunk == kChunkIters || in_tile == total_k_iters) {
                 // chunk complete: hand it to the epilogue warps (of both CTAs)
-                if (kTwo) mma_commit_pair(tfull_bar(acc), 3);
-                else mma_commit(tfull_bar(acc));
+                if (elected) {
+                  if (kTwo) mma_commit_pair(tfull_bar(acc), 3);
+                  else mma_commit(tfull_bar(acc));
+                }
                 chunk++;
                 in_chunk = 0;
               }
@@ -628,7 +654,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         }
       }
 #ifdef B200_GEMM_TIMING
-      if (p.dbg) {
+      if (p.dbg && elected) {
         p.dbg[blockIdx.x * 8 + 0] = (unsigned long long)(clock64() - t_start);
         p.dbg[blockIdx.x * 8 + 1] = (unsigned long long)t_full;
         p.dbg[blockIdx.x * 8 + 2] = (unsigned long long)t_tempty;
