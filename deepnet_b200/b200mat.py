@@ -45,13 +45,15 @@ class rnd_struct(ct.Structure):
 
 class _Pass(ct.Structure):
     _fields_ = [("a", ct.POINTER(cudamat)), ("b", ct.POINTER(cudamat)), ("negate", ct.c_int),
-                ("a_part", ct.c_int), ("b_part", ct.c_int)]
+                ("a_part", ct.c_int), ("b_part", ct.c_int),
+                ("a_aux", ct.POINTER(cudamat)), ("b_aux", ct.POINTER(cudamat))]
 
 
 class _FusedGemm(ct.Structure):
     _fields_ = [("npass", ct.c_int), ("passes", _Pass * MAX_PASS), ("alpha", ct.c_float), ("beta", ct.c_float),
                 ("bias", ct.POINTER(cudamat)), ("col_scale", ct.POINTER(cudamat)), ("activation", ct.c_int),
-                ("out", ct.POINTER(cudamat)), ("sample", ct.POINTER(cudamat))]
+                ("out", ct.POINTER(cudamat)), ("out_aux", ct.POINTER(cudamat)), ("sample", ct.POINTER(cudamat)),
+                ("sample_aux", ct.POINTER(cudamat))]
 
 
 _lib.get_last_cuda_error.restype = ct.c_char_p
@@ -473,12 +475,21 @@ class CUDAMatrix(object):
         return target
 
     # -- fused entry points (no counterpart in the reference API) -------------
-    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0):
-        """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter."""
+    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None):
+        """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter.
+        w_aux (optional, from `empty_aux`) receives the bfloat16 parts of the updated parameter."""
         _check(_lib.momentum_update(self.p_mat, delta.p_mat, grad.p_mat if grad is not None else None, suff.p_mat,
+                                    w_aux.p_mat if w_aux is not None else None,
                                     ct.c_float(inv_batch), ct.c_float(momentum), ct.c_float(eps), ct.c_float(l2),
                                     ct.c_float(l1)))
         return self
+
+    def split_bf16(self, aux):
+        """Fills `aux` (from `empty_aux(self.shape)`) with the bfloat16 parts of self that the
+        correction terms of a product read: plane 0 = bf16(self - tf32(self)), plane 1 =
+        bf16(self).  Returns aux."""
+        _check(_lib.split_bf16(self.p_mat, aux.p_mat))
+        return aux
 
     def split_tf32(self, lo, hi=None):
         """lo = self - tf32(self); hi (optional) = self with the low 13 mantissa bits cleared."""
@@ -505,52 +516,85 @@ class TransposedCUDAMatrix(CUDAMatrix):
         pass
 
 
-# What of an fp32 matrix a term of `fused_gemm` multiplies (derived inside the kernel from the
-# matrix itself): x read as TF32, x - tf32(x) read as TF32, bfloat16(x - tf32(x)), bfloat16(x).
+class AuxMatrix(CUDAMatrix):
+    """The bfloat16 parts of a rows x cols matrix kept in device memory (see `split_bf16`):
+    storage of lda x cols floats, lda = rows rounded up to 8; column c holds lda bfloat16 of
+    plane 0 (bf16(x - tf32(x))) and lda of plane 1 (bf16(x)), the first `rows` of each in use.
+    Passed as `a_aux` / `b_aux` of a term, written as `out_aux` / `sample_aux` / `w_aux`."""
+
+    def __init__(self, shape):
+        _require_device()
+        self.rows, self.cols = int(shape[0]), int(shape[1])
+        self.mat = cudamat()
+        _check(_lib.init_empty(ct.pointer(self.mat), ct.c_int((self.rows + 7) // 8 * 8), ct.c_int(self.cols)))
+        self.p_mat = ct.pointer(self.mat)
+        self.numpy_array = None
+
+    def planes(self):
+        """Host copy of the two planes as float32 arrays (rows x cols each)."""
+        raw = np.array(self.asarray(), copy=True)                       # lda x cols floats
+        words = np.ascontiguousarray(raw.T).view(np.uint16)             # cols x (2 lda) bfloat16
+        lda = raw.shape[0]
+        f = lambda w: (np.ascontiguousarray(w).astype(np.uint32) << 16).view(np.float32).T[:self.rows]
+        return f(words[:, :lda]), f(words[:, lda:])
+
+
+def empty_aux(shape):
+    """Zero-filled aux matrix for a matrix of this shape."""
+    return AuxMatrix(shape)
+
+
+# What of an fp32 matrix a term of `fused_gemm` multiplies: x read as TF32, x - tf32(x) read as
+# TF32, bfloat16(x - tf32(x)), bfloat16(x).  The kernel derives the parts from the matrix itself,
+# or reads the two bfloat16 ones from the matrix's aux when one is given.
 PART_X, PART_LO32, PART_LO16, PART_B16 = 0, 1, 2, 3
 
 
 class Part(object):
-    """A part of a matrix (or of its transpose) as a `fused_gemm` operand."""
+    """A part of a matrix (or of its transpose) as a `fused_gemm` operand; aux: its AuxMatrix."""
 
-    def __init__(self, mat, part):
-        self.mat, self.part, self.p_mat = mat, part, mat.p_mat
+    def __init__(self, mat, part, aux=None):
+        self.mat, self.part, self.aux, self.p_mat = mat, part, aux, mat.p_mat
 
     @property
     def T(self):
-        return Part(self.mat.T, self.part)
+        return Part(self.mat.T, self.part, self.aux)
 
 
 def lo32(x):
     return Part(x, PART_LO32)
 
 
-def lo16(x):
-    return Part(x, PART_LO16)
+def lo16(x, aux=None):
+    return Part(x, PART_LO16, aux)
 
 
-def b16(x):
-    return Part(x, PART_B16)
+def b16(x, aux=None):
+    return Part(x, PART_B16, aux)
 
 
-def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16"):
+def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16", a_aux=None, b_aux=None):
     """The terms of a . b at fp32 grade, small terms first.  terms="bf16": the corrections are
     bfloat16 products, lo16(a).b16(b) + b16(a).lo16(b) (twice the TF32 rate; 2^-18 per term);
     terms="tf32": TF32 products lo32(a).b + a.lo32(b) (2^-20 per term: for products whose
     difference is wanted, like positive minus negative statistics).  exact_a / exact_b: that
-    operand is exact in TF32 (0/1 data and samples, small counts), its low part is skipped."""
+    operand is exact in TF32 (0/1 data and samples, small counts), its low part is skipped.
+    a_aux / b_aux: AuxMatrix of a / b (of the untransposed matrix): the bfloat16 parts are read
+    from it instead of being derived in the kernel, which the big products need to run at the
+    tensor pipe's rate."""
     p = []
     if terms == "bf16":
         if not exact_a:
-            p.append((lo16(a), b16(b), negate))
+            p.append((lo16(a, a_aux), b16(b, b_aux), negate))
         if not exact_b:
-            p.append((b16(a), lo16(b), negate))
+            p.append((b16(a, a_aux), lo16(b, b_aux), negate))
+        p.append((Part(a, PART_X, a_aux), Part(b, PART_X, b_aux), negate))
     else:
         if not exact_a:
             p.append((lo32(a), b, negate))
         if not exact_b:
             p.append((a, lo32(b), negate))
-    p.append((a, b, negate))
+        p.append((a, b, negate))
     return p
 
 
@@ -632,14 +676,16 @@ def correct_preds(mat, p, target=None, cutoff=0.5):
     return target
 
 
-def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activation=0, alpha=1.0, beta=0.0):
+def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activation=0, alpha=1.0, beta=0.0,
+               out_aux=None, sample_aux=None):
     """out = act(alpha * sum_p (+/-) a_p . b_p + beta * out + bias (x) col_scale) in one kernel.
 
     `passes` is a list of (a, b) or (a, b, negate); a and b are fp32 matrices, `.T` views, or
     parts of them (`lo32(x)`, `lo16(x)`, `b16(x)`, see `split_passes`); both operands of a
-    term are fp32-wide (a TF32 product) or both bfloat16.  Optional output: a Bernoulli draw
-    of the result (consumes one sampling call of the global random state).  Replaces the dot /
-    add_dot / add_col_vec / sigmoid / sample_bernoulli group of deepnet/dbm.py:88-105.
+    term are fp32-wide (a TF32 product) or both bfloat16.  Optional outputs: a Bernoulli draw
+    of the result (consumes one sampling call of the global random state) and the aux matrices
+    (bfloat16 parts) of result and draw.  Replaces the dot / add_dot / add_col_vec / sigmoid /
+    sample_bernoulli group of deepnet/dbm.py:88-105.
     """
     f = _FusedGemm()
     f.npass = len(passes)
@@ -648,11 +694,15 @@ def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activat
     for i, p in enumerate(passes):
         f.passes[i].a = p[0].p_mat
         f.passes[i].b = p[1].p_mat
-        f.passes[i].a_part = p[0].part if isinstance(p[0], Part) else PART_X
-        f.passes[i].b_part = p[1].part if isinstance(p[1], Part) else PART_X
+        for side, op in (("a", p[0]), ("b", p[1])):
+            is_part = isinstance(op, Part)
+            setattr(f.passes[i], side + "_part", op.part if is_part else PART_X)
+            if is_part and op.aux is not None:
+                setattr(f.passes[i], side + "_aux", op.aux.p_mat)
         f.passes[i].negate = int(p[2]) if len(p) > 2 else 0
     f.alpha, f.beta, f.activation = alpha, beta, activation
-    for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("sample", sample)):
+    for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("sample", sample),
+                    ("out_aux", out_aux), ("sample_aux", sample_aux)):
         if m is not None:
             setattr(f, name, m.p_mat)
     _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))

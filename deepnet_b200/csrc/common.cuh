@@ -136,6 +136,22 @@ __device__ __forceinline__ uint16_t float_to_bf16(float x) {
 }
 __device__ __forceinline__ float bf16_to_float(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
+// The bfloat16 companion ("aux matrix") of a rows x cols fp32 matrix x, for products that read
+// the bfloat16 parts of x from memory instead of deriving them from x in the kernel: lda x cols
+// floats of storage, lda = rows rounded up to a multiple of 8 (both planes of every column then
+// start on 16 bytes, as TMA requires); column c holds two runs of lda bfloat16, the first
+// `rows` of each in use,
+//   plane 0: bf16(x - tf32(x))      plane 1: bf16(x)
+// Element (r, c) of plane p is 16-bit word  c * 2 * lda + p * lda + r  of the aux storage.
+__device__ __forceinline__ void split_aux(float x, uint16_t& lo16, uint16_t& b16) {
+  float hi, lo;
+  split_tf32(x, hi, lo);
+  lo16 = float_to_bf16(lo);
+  b16 = float_to_bf16(x);
+}
+
 #endif
+
+__host__ __device__ inline int aux_rows(int rows) { return (rows + 7) & ~7; }
 
 }  // namespace b200

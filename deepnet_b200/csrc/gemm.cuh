@@ -1,6 +1,7 @@
 // Description of one fused matrix product shared by the tensor-core and the SIMT
 // kernels:  out = act(alpha * sum_p (+/-) op(A_p) . op(B_p) + beta * out + bias (x) scale)
-// with an optional Bernoulli draw of the result.
+// with an optional Bernoulli draw of the result, and optionally the aux matrices (bfloat16
+// parts) of result and draw for the products that read them next.
 #pragma once
 #include "common.cuh"
 
@@ -20,6 +21,9 @@ constexpr int kMaxPass = 8;
 //   a . b ~= lo16(a).b16(b) + b16(a).lo16(b) + x(a).x(b)  one TF32 + two bfloat16 products
 //                                                        (twice the TF32 rate), 2^-18 per term
 // accumulate into one fp32 accumulator.  Both operands of a term are of the same width.
+// The bfloat16 parts may instead be READ from an aux matrix of x kept in device memory (see
+// split_aux): deriving them costs shared-memory bandwidth (the fp32 tile is read and two tiles
+// are written, next to the tensor core's own operand reads), which bounds the big products.
 enum { kPartX = 0, kPartLo32 = 1, kPartLo16 = 2, kPartB16 = 3 };
 
 // A column-major fp32 matrix in device memory: element (r, c) at ptr[c * ld + r].
@@ -29,6 +33,8 @@ struct GemmOperand {
   int ld;
   int trans;
   int part;
+  const float* aux;   // aux matrix of the same matrix (or null: bfloat16 parts are derived from ptr)
+  int lda;            // floats per column of aux
 };
 
 // One term of the sum: op(a) is M x k, op(b) is k x N.
@@ -44,8 +50,11 @@ struct GemmEpilogue {
   const float* col_scale;  // N entries or null: the bias of column n is bias[m] * col_scale[n]
   int activation;          // 0 identity, 1 logistic
   float* out;              // M x N result (may be null when only split/sample outputs are wanted)
+  float* out_aux;          // aux matrix of the result, or null
   float* sample;           // Bernoulli(result) draw, or null
-  int ldo;                 // leading dimension of every output
+  float* sample_aux;       // aux matrix of the draw (only plane 1 is written: a 0/1 value has no low part), or null
+  int ldo;                 // leading dimension of every fp32 output
+  int ld_aux;              // floats per column of the aux outputs (rows rounded up to 8)
   PhiloxKey key;           // random stream of this call (used when sample != null)
   int col0;                // global column of output column 0
 };
@@ -76,7 +85,16 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc,
   if (e.bias) v += e.col_scale ? e.bias[m] * e.col_scale[n] : e.bias[m];
   if (e.activation == 1) v = sigmoid_accurate(v);
   if (e.out) e.out[idx] = v;
-  if (e.sample) e.sample[idx] = u < v ? 1.0f : 0.0f;
+  const long aidx = (long)n * 2 * e.ld_aux + m;   // 16-bit word of plane 0
+  if (e.out_aux) {
+    uint16_t lo16, b16;
+    split_aux(v, lo16, b16);
+    reinterpret_cast<uint16_t*>(e.out_aux)[aidx] = lo16;
+    reinterpret_cast<uint16_t*>(e.out_aux)[aidx + e.ld_aux] = b16;
+  }
+  const float s = u < v ? 1.0f : 0.0f;
+  if (e.sample) e.sample[idx] = s;
+  if (e.sample_aux) reinterpret_cast<uint16_t*>(e.sample_aux)[aidx + e.ld_aux] = s != 0.0f ? 0x3f80 : 0;
 }
 #endif
 

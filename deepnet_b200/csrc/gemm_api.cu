@@ -14,13 +14,19 @@ constexpr long kTcMinWork = 1L << 21;  // below this many multiply-adds `dot` st
 
 inline int lead(const cudamat* m) { return m->is_trans ? m->size[1] : m->size[0]; }
 inline int nonlead(const cudamat* m) { return m->is_trans ? m->size[0] : m->size[1]; }
-inline GemmOperand operand(const cudamat* m, int part) {
+inline GemmOperand operand(const cudamat* m, int part, const cudamat* aux = nullptr) {
   GemmOperand o;
   o.ptr = m->data_device;
   o.ld = m->size[0];
   o.trans = m->is_trans;
   o.part = part;
+  o.aux = aux ? aux->data_device : nullptr;
+  o.lda = aux ? aux->size[0] : 0;
   return o;
+}
+// An aux handle holds aux_rows(rows) x cols floats.
+inline bool aux_shape_ok(const cudamat* aux, const cudamat* m) {
+  return aux->on_device && aux->size[0] == aux_rows(m->size[0]) && aux->size[1] == m->size[1];
 }
 
 int run(const GemmProblem& g) {
@@ -59,6 +65,42 @@ __global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float*
   }
 }
 
+// aux matrix of x (rows x cols, contiguous columns): both bfloat16 planes in one pass.
+__global__ void __launch_bounds__(256) k_split_aux(const float* x, uint16_t* aux, int rows, int lda, long n,
+                                                   bool vec) {
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  if (vec) {   // rows % 4 == 0: four consecutive elements share a column
+    for (long i = tid; i < (n >> 2); i += nth) {
+      const float4 v = reinterpret_cast<const float4*>(x)[i];
+      const long e = i << 2, c = e / rows, r = e - c * rows;
+      ushort4 l, b;
+      split_aux(v.x, l.x, b.x); split_aux(v.y, l.y, b.y); split_aux(v.z, l.z, b.z); split_aux(v.w, l.w, b.w);
+      uint16_t* dst = aux + c * 2 * lda + r;
+      *reinterpret_cast<ushort4*>(dst) = l;
+      *reinterpret_cast<ushort4*>(dst + lda) = b;
+    }
+  } else {
+    for (long i = tid; i < n; i += nth) {
+      const long c = i / rows, r = i - c * rows;
+      uint16_t l, b;
+      split_aux(x[i], l, b);
+      aux[c * 2 * lda + r] = l;
+      aux[c * 2 * lda + lda + r] = b;
+    }
+  }
+}
+
+// aux holds aux_rows(rows) floats per column.
+int launch_split_aux(const float* x, float* aux, int rows, long n) {
+  if (n == 0) return 0;
+  const bool vec = (rows % 4 == 0) && ((((uintptr_t)x) & 15) == 0) && ((((uintptr_t)aux) & 7) == 0);
+  long blocks = ((vec ? n / 4 : n) + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  if (blocks < 1) blocks = 1;
+  k_split_aux<<<(int)blocks, 256, 0, stream()>>>(x, reinterpret_cast<uint16_t*>(aux), rows, aux_rows(rows), n, vec);
+  return check_launch();
+}
+
 int launch_split(const float* x, float* hi, float* lo, long n) {
   if (n == 0) return 0;
   const bool vec = (((uintptr_t)x | (uintptr_t)hi | (uintptr_t)lo) & 15) == 0;
@@ -81,14 +123,13 @@ __device__ __forceinline__ void update_one(float& w, float& d, float g, float su
   w = __fadd_rn(w, __fmul_rn(d, neps));
 }
 
-template <bool kHasGrad>
-__global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff, long n,
-                                                bool vec, float ninv_batch, float momentum, float neps, float l2,
-                                                float l1) {
+template <bool kHasGrad, bool kAux>
+__global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff,
+                                                uint16_t* w_aux, int rows, int lda, long n, bool vec,
+                                                float ninv_batch, float momentum, float neps, float l2, float l1) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
-  if (vec) {
-    const long n4 = n >> 2;
-    for (long i = tid; i < n4; i += nth) {
+  if (vec) {   // n % 4 == 0, and with an aux rows % 4 == 0: four consecutive elements share a column
+    for (long i = tid; i < (n >> 2); i += nth) {
       float4 W = reinterpret_cast<float4*>(w)[i];
       float4 D = reinterpret_cast<float4*>(delta)[i];
       const float4 S = reinterpret_cast<const float4*>(suff)[i];
@@ -101,12 +142,14 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       reinterpret_cast<float4*>(w)[i] = W;
       reinterpret_cast<float4*>(delta)[i] = D;
       if (kHasGrad) reinterpret_cast<float4*>(grad)[i] = make_float4(0, 0, 0, 0);
-    }
-    for (long i = (n4 << 2) + tid; i < n; i += nth) {
-      float W = w[i], D = delta[i];
-      update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
-      w[i] = W; delta[i] = D;
-      if (kHasGrad) grad[i] = 0.0f;
+      if (kAux) {
+        const long e = i << 2, c = e / rows, r = e - c * rows;
+        ushort4 L, B;
+        split_aux(W.x, L.x, B.x); split_aux(W.y, L.y, B.y); split_aux(W.z, L.z, B.z); split_aux(W.w, L.w, B.w);
+        uint16_t* dst = w_aux + c * 2 * lda + r;
+        *reinterpret_cast<ushort4*>(dst) = L;
+        *reinterpret_cast<ushort4*>(dst + lda) = B;
+      }
     }
   } else {
     for (long i = tid; i < n; i += nth) {
@@ -114,6 +157,13 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
       w[i] = W; delta[i] = D;
       if (kHasGrad) grad[i] = 0.0f;
+      if (kAux) {
+        const long c = i / rows, r = i - c * rows;
+        uint16_t L, B;
+        split_aux(W, L, B);
+        w_aux[c * 2 * lda + r] = L;
+        w_aux[c * 2 * lda + lda + r] = B;
+      }
     }
   }
 }
@@ -122,12 +172,15 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
 
 // One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
 // a_part / b_part choose what of each fp32 matrix the term multiplies (kPartX, kPartLo32:
-// a TF32 product; kPartLo16, kPartB16: a bfloat16 product); both of one width.
+// a TF32 product; kPartLo16, kPartB16: a bfloat16 product); both of one width.  a_aux / b_aux:
+// the aux matrix of a / b (or null): its bfloat16 parts are then read from there.
 struct b200_pass {
   cudamat* a;
   cudamat* b;
   int negate;
   int a_part, b_part;
+  cudamat* a_aux;
+  cudamat* b_aux;
 };
 // out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale)
 struct b200_fused_gemm {
@@ -138,7 +191,9 @@ struct b200_fused_gemm {
   cudamat* col_scale;  // 1 x N or null
   int activation;      // 0 identity, 1 logistic
   cudamat* out;        // M x N or null
+  cudamat* out_aux;    // aux matrix of the result, or null
   cudamat* sample;     // Bernoulli(result), or null
+  cudamat* sample_aux; // aux matrix of the draw, or null
 };
 
 extern "C" {
@@ -163,6 +218,14 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo) {
   return launch_split(x->data_device, hi ? hi->data_device : nullptr, lo->data_device, numel(x));
 }
 
+// aux = the bfloat16 planes of x (see split_aux in common.cuh); aux holds aux_rows(rows) x cols floats.
+int split_bf16(cudamat* x, cudamat* aux) {
+  if (!x->on_device || !aux->on_device) return ERROR_NOT_ON_DEVICE;
+  if (x->is_trans || aux->is_trans) return ERROR_TRANSPOSED;
+  if (!aux_shape_ok(aux, x)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  return launch_split_aux(x->data_device, aux->data_device, x->size[0], numel(x));
+}
+
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   if (f->npass <= 0 || f->npass > kMaxPass) return ERROR_UNSUPPORTED;
   GemmProblem g;
@@ -176,8 +239,10 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
     if (lead(a) != g.M || nonlead(b) != g.N || nonlead(a) != lead(b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
     const int pa = f->pass[q].a_part, pb = f->pass[q].b_part;
     if (pa < 0 || pa > 3 || pb < 0 || pb > 3 || (pa >= kPartLo16) != (pb >= kPartLo16)) return ERROR_UNSUPPORTED;
-    g.pass[q].a = operand(a, pa);
-    g.pass[q].b = operand(b, pb);
+    const cudamat *xa = f->pass[q].a_aux, *xb = f->pass[q].b_aux;
+    if ((xa && !aux_shape_ok(xa, a)) || (xb && !aux_shape_ok(xb, b))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    g.pass[q].a = operand(a, pa, xa);
+    g.pass[q].b = operand(b, pb, xb);
     g.pass[q].k = nonlead(a);
     g.pass[q].negate = f->pass[q].negate;
   }
@@ -187,18 +252,22 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   e.bias = nullptr;
   e.col_scale = nullptr;
   e.activation = f->activation;
-  e.out = e.sample = nullptr;
+  e.out = e.out_aux = e.sample = e.sample_aux = nullptr;
   e.ldo = g.M;
+  e.ld_aux = aux_rows(g.M);
   e.col0 = rng_col0();
-  cudamat* outs[2] = {f->out, f->sample};
-  for (int i = 0; i < 2; i++) {
+  cudamat* outs[4] = {f->out, f->out_aux, f->sample, f->sample_aux};
+  for (int i = 0; i < 4; i++) {
     if (!outs[i]) continue;
     if (!outs[i]->on_device) return ERROR_NOT_ON_DEVICE;
     if (outs[i]->is_trans) return ERROR_TRANSPOSED;
-    if (outs[i]->size[0] != g.M || outs[i]->size[1] != g.N) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    const int want_rows = (i & 1) ? e.ld_aux : g.M;   // aux handles hold the rounded-up rows
+    if (outs[i]->size[0] != want_rows || outs[i]->size[1] != g.N) return ERROR_INCOMPATIBLE_DIMENSIONS;
   }
   if (f->out) e.out = f->out->data_device;
+  if (f->out_aux) e.out_aux = f->out_aux->data_device;
   if (f->sample) e.sample = f->sample->data_device;
+  if (f->sample_aux) e.sample_aux = f->sample_aux->data_device;
   if (e.beta != 0.0f && !e.out) return ERROR_UNSUPPORTED;
   if (f->bias) {
     if (!f->bias->on_device) return ERROR_NOT_ON_DEVICE;
@@ -211,7 +280,7 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
     e.col_scale = f->col_scale->data_device;
   }
   e.key = make_philox_key(0, 0);
-  if (f->sample) {
+  if (f->sample || f->sample_aux) {
     if (!rnd_state) return ERROR_GENERIC;
     e.key = make_philox_key(rnd_state->seed, rnd_state->calls);
     rnd_state->calls += 1;
@@ -236,8 +305,9 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
   e.bias = e.col_scale = nullptr;
   e.activation = 0;
   e.out = target->data_device;
-  e.sample = nullptr;
+  e.out_aux = e.sample = e.sample_aux = nullptr;
   e.ldo = m;
+  e.ld_aux = aux_rows(m);
   e.col0 = 0;
   e.key = make_philox_key(0, 0);
   g.npass = 1;
@@ -275,28 +345,35 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 
 // deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass over the parameter:
 //   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
-//   w -= eps * delta; grad = 0.
+//   w -= eps * delta; grad = 0; and, when w_aux is given, the aux matrix of the new w.
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
-// without grad, 28 with.
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, float inv_batch, float momentum,
-                    float eps, float l2, float l1) {
+// without grad and aux; +8 with grad, +4 with w_aux.
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, float inv_batch,
+                    float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
   if (!same_shape(w, delta) || !same_shape(w, suff)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (grad && (!grad->on_device || !same_shape(w, grad))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (w_aux && (w->is_trans || !aux_shape_ok(w_aux, w))) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const long n = numel(w);
   if (n == 0) return 0;
   uintptr_t bits = (uintptr_t)w->data_device | (uintptr_t)delta->data_device | (uintptr_t)suff->data_device;
   if (grad) bits |= (uintptr_t)grad->data_device;
-  const bool vec = (bits & 15) == 0;
-  long blocks = ((vec ? (n + 3) / 4 : n) + 255) / 256;
+  if (w_aux) bits |= (uintptr_t)w_aux->data_device;
+  const int rows = w->size[0];
+  const bool vec = (bits & 15) == 0 && n % 4 == 0 && (!w_aux || rows % 4 == 0);
+  long blocks = ((vec ? n / 4 : n) + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  if (blocks < 1) blocks = 1;
   float* gp = grad ? grad->data_device : nullptr;
-  if (grad)
-    k_update<true><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, n, vec,
-                                                      -inv_batch, momentum, -eps, l2, l1);
-  else
-    k_update<false><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, n,
-                                                       vec, -inv_batch, momentum, -eps, l2, l1);
+  uint16_t* ap = w_aux ? reinterpret_cast<uint16_t*>(w_aux->data_device) : nullptr;
+#define LAUNCH_UPDATE(G, A)                                                                                       \
+  k_update<G, A><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, ap, \
+                                                    rows, aux_rows(rows), n, vec, -inv_batch, momentum, -eps, l2, l1)
+  if (grad && w_aux) LAUNCH_UPDATE(true, true);
+  else if (grad) LAUNCH_UPDATE(true, false);
+  else if (w_aux) LAUNCH_UPDATE(false, true);
+  else LAUNCH_UPDATE(false, false);
+#undef LAUNCH_UPDATE
   return check_launch();
 }
 

@@ -13,8 +13,13 @@ constexpr int TM = 64, TN = 64, TK = 16;
 __device__ __forceinline__ float as_operand(float x, int tf32) {
   return tf32 ? __uint_as_float(__float_as_uint(x) & 0xffffe000u) : x;
 }
-__device__ __forceinline__ float element(const GemmOperand& o, long i, int tf32) {
-  const float x = o.ptr[i];
+// Element (r, c) of the stored matrix, as the part the term reads.
+__device__ __forceinline__ float element(const GemmOperand& o, int r, int c, int tf32) {
+  if (o.part >= kPartLo16 && o.aux) {
+    const long w = (long)c * 2 * o.lda + (o.part == kPartB16 ? o.lda : 0) + r;
+    return bf16_to_float(reinterpret_cast<const uint16_t*>(o.aux)[w]);
+  }
+  const float x = o.ptr[(long)c * o.ld + r];
   if (o.part == kPartX) return as_operand(x, tf32);
   if (o.part == kPartB16) return bf16_to_float(float_to_bf16(x));
   const float lo = x - as_operand(x, 1);
@@ -22,11 +27,11 @@ __device__ __forceinline__ float element(const GemmOperand& o, long i, int tf32)
 }
 __device__ __forceinline__ float load_a(const GemmOperand& a, int m, int k, int M, int K, int tf32) {
   if (m >= M || k >= K) return 0.0f;
-  return element(a, a.trans ? (long)m * a.ld + k : (long)k * a.ld + m, tf32);
+  return a.trans ? element(a, k, m, tf32) : element(a, m, k, tf32);
 }
 __device__ __forceinline__ float load_b(const GemmOperand& b, int k, int n, int K, int N, int tf32) {
   if (n >= N || k >= K) return 0.0f;
-  return element(b, b.trans ? (long)k * b.ld + n : (long)n * b.ld + k, tf32);
+  return b.trans ? element(b, n, k, tf32) : element(b, k, n, tf32);
 }
 
 __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmProblem g) {
@@ -84,7 +89,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const __grid_constant__ GemmP
       const int m = m0 + tx + 16 * i;
       if (m >= g.M) continue;
       float u = 0.0f;
-      if (e.sample) {
+      if (e.sample || e.sample_aux) {
         const int gc = n + e.col0;
         const uint4 w = philox4x32_10((uint32_t)m, (uint32_t)(gc >> 2), e.key);
         u = word_to_uniform(pick_word(w, gc & 3));

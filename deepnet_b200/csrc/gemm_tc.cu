@@ -40,10 +40,11 @@ namespace {
 constexpr int BM = 128;
 constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
 constexpr int kMaxStages = 8;
-constexpr int kStageBudget = 209 * 1024;      // shared memory available to the operand ring
-constexpr int kOutStageBytes = 16 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
+constexpr int kStageBudget = 193 * 1024;      // shared memory available to the operand ring
+constexpr int kOutStageBytes = 32 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
 constexpr int kOutCols = 4;                    // columns per staged batch (one Philox block)
-constexpr int kOutArrays = 2;                  // out, sample
+constexpr int kOutArrays = 5;                  // out, its aux planes 0 and 1, sample, plane 1 of the sample's aux
+constexpr int kMaxLoads = 6;                   // A and B as fp32, and up to two bfloat16 planes of each from their aux
 constexpr int kMaxTiles = 8;                   // tiles of a stage: A and B as loaded + up to three derived parts each
 constexpr int kMaxMma = 4;                     // terms issued from one stage
 constexpr uint32_t kNoTile = 0xffffffffu;
@@ -55,11 +56,12 @@ struct TcTile {
   uint32_t adv;            // descriptor advance per MMA (K = 8 floats or 16 bfloat16), in 16-byte units
   uint32_t smem_off;       // byte offset of the tile inside a stage
 };
-// One fp32 operand tile of a k-block as TMA loads it.
+// One operand tile of a k-block as TMA loads it: fp32, or one bfloat16 plane of an aux matrix.
 struct TcLoad {
   int map;                 // index into TcParams::maps
-  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as boxes of 32 floats x bk)
+  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as boxes of 128 bytes x bk)
   int is_a;
+  int box_rows;            // rows of M/N per box of an MN-major tile: 32 floats or 64 bfloat16
   uint32_t smem_off;
 };
 // The parts derived from a loaded tile (offsets inside the stage, kNoTile = not wanted).
@@ -79,16 +81,16 @@ struct TcMma {
 // are issued from that one stage.
 struct TcGroup {
   int k_iters;             // ceil(k / bk)
-  int nconv, nmma;
+  int nload, nconv, nmma;
   uint32_t stage_tx;       // bytes TMA delivers per k-block and CTA
-  TcLoad load[2];          // A, B
+  TcLoad load[kMaxLoads];
   TcConv conv[2];
   TcTile tile[kMaxTiles];
   TcMma mma[kMaxMma];
 };
 
 struct TcParams {
-  CUtensorMap maps[2 * kMaxPass + kOutArrays];   // operands, then the outputs an activation epilogue stores
+  CUtensorMap maps[2 * kMaxPass + kOutArrays];   // operands (fp32, aux planes; at most two per term), then the outputs an activation epilogue stores
   TcGroup group[kMaxPass];
   int ngroups;
   int M, N, tiles_m, tiles_n;
@@ -454,15 +456,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // The whole warp runs the loop; lane l issues (at most) one box per k-block: operand l / 16
-    // (A, B), box l % 16 of it (an MN-major tile comes as boxes of 32 floats x bk).  The refill of
-    // a freed stage is on the critical path of a ring this shallow, so every constant sits in
-    // registers and a lane issues one copy only.
+    // The whole warp runs the loop; copy u = 8 * load + box (up to six loads of up to 8 boxes: an
+    // MN-major tile comes as boxes of 128 bytes x bk) is issued by lane u % 32, so a lane issues at
+    // most two copies per k-block.  The refill of a freed stage is on the critical path of a ring
+    // this shallow: every constant sits in registers.
     {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const int opi = lane >> 4, box = lane & 15;
       long long t_empty = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
@@ -471,13 +472,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
           const int k_iters = gr.k_iters;
-          const TcLoad ld = gr.load[opi];
-          const int nboxes = ld.mn ? (ld.is_a ? BM / 32 : BN_LOCAL / 32) : 1;
-          const bool active = box < nboxes;
-          const CUtensorMap* map = &p.maps[ld.map];
-          const int row0 = (ld.is_a ? m0 : n0) + (ld.mn ? 32 * box : 0);
-          const uint32_t dst_off = ld.smem_off + (ld.mn ? (uint32_t)(box * bk * 128) : 0u);
-          const int mn = ld.mn;
+          bool active[2];
+          const CUtensorMap* map[2];
+          int row0[2], mn[2];
+          uint32_t dst_off[2];
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            const int u = lane + 32 * c, li = u >> 3, box = u & 7;
+            active[c] = li < gr.nload;
+            const TcLoad ld = gr.load[active[c] ? li : 0];
+            const int nboxes = ld.mn ? (ld.is_a ? BM : BN_LOCAL) / ld.box_rows : 1;
+            active[c] = active[c] && box < nboxes;
+            map[c] = &p.maps[ld.map];
+            row0[c] = (ld.is_a ? m0 : n0) + (ld.mn ? ld.box_rows * box : 0);
+            dst_off[c] = ld.smem_off + (ld.mn ? (uint32_t)(box * bk * 128) : 0u);
+            mn[c] = ld.mn;
+          }
           for (int kb = 0; kb < k_iters; kb++) {
             if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag))) {
               ok = false;
@@ -488,11 +498,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             const uint32_t bar = full_bar(stage);
             if (lane == 0) mbar_expect_tx(bar, gr.stage_tx);
             __syncwarp();   // the expectation is posted before any copy can complete
-            if (active) {
-              const uint32_t dst = smem_base + stage * stage_bytes + dst_off;
-              const int k0 = kb * bk;
-              const int x = mn ? row0 : k0, y = mn ? k0 : row0;
-              tma_load_2d(dst, map, x, y, bar);
+            const int k0 = kb * bk;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+              if (active[c]) {
+                const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
+                const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
+                tma_load_2d(dst, map[c], x, y, bar);
+              }
             }
             if (++stage == num_stages) {
               stage = 0;
@@ -843,15 +856,20 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         const float alpha = e.alpha, beta = spec ? 0.0f : e.beta;
         const float bias = ((spec || e.bias) && row_ok) ? e.bias[m] : 0.0f;
         const bool logistic = spec ? (kEpi != kEpiLin) : (e.activation == 1);
-        const bool draw = spec ? (kEpi == kEpiSigSample) : (e.sample != nullptr);
+        const bool draw = spec ? (kEpi == kEpiSigSample) : (e.sample != nullptr || e.sample_aux != nullptr);
         const bool has_out = spec || e.out != nullptr;
+        const bool has_aux = e.out_aux != nullptr;
+        const bool has_smp = spec ? draw : e.sample != nullptr;
+        const bool has_smp_aux = draw && e.sample_aux != nullptr;
         const PhiloxKey key = e.key;
         const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
         const long off = (long)nc * e.ldo + m, ldo = e.ldo;
         const int m_tile = tm * TILE_M + (int)rank * BM;     // first row of this CTA's part of the tile
-        // one staged batch: [out][sample], each kOutCols columns of BM rows of fp32
-        constexpr uint32_t kArrayBytes = kOutCols * BM * 4;
-        constexpr uint32_t kBufBytes = kOutArrays * kArrayBytes;
+        // one staged batch: [out f32][aux plane 0 bf16][aux plane 1 bf16][sample f32][sample bf16],
+        // each kOutCols columns of BM rows
+        constexpr uint32_t kF32 = kOutCols * BM * 4, kB16 = kOutCols * BM * 2;
+        constexpr uint32_t kOffLo = kF32, kOffB = kF32 + kB16, kOffSmp = kF32 + 2 * kB16, kOffSmpB = 2 * kF32 + 2 * kB16;
+        constexpr uint32_t kBufBytes = 2 * kF32 + 3 * kB16;
         static_assert(4 * kBufBytes <= kOutStageBytes, "epilogue staging");
         const uint32_t group_base = out_stage_base + (uint32_t)hf * 2u * kBufBytes;
 #pragma unroll
@@ -876,18 +894,31 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes;
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u;
+            const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u, a16 = buf + (uint32_t)(j * BM + row) * 2u;
             if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32), "f"(x[j]) : "memory");
+            if (has_aux) {
+              const float lo = tf32_rest(x[j]);
+              const uint32_t lo16 = pack_bf16(lo, 0.0f), b16 = pack_bf16(x[j], 0.0f);
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffLo), "h"((uint16_t)lo16) : "memory");
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffB), "h"((uint16_t)b16) : "memory");
+            }
             if (draw) {
-              const float sbit = word_to_uniform(pick_word(w, j)) < x[j] ? 1.0f : 0.0f;
-              asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kArrayBytes), "f"(sbit) : "memory");
+              const bool on = word_to_uniform(pick_word(w, j)) < x[j];
+              if (has_smp) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kOffSmp), "f"(on ? 1.0f : 0.0f) : "memory");
+              if (has_smp_aux)
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffSmpB), "h"((uint16_t)(on ? 0x3f80 : 0)) : "memory");
             }
           }
           fence_async_smem();                       // generic-proxy writes visible to the TMA engine
           named_bar_sync(1 + hf, 128);
           if (leader && c0 < pN && m_tile < pM) {
             if (has_out) tma_store_2d(&p.maps[p.out_map[0]], m_tile, c0, buf);
-            if (draw) tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, buf + kArrayBytes);
+            if (has_aux) {
+              tma_store_2d(&p.maps[p.out_map[1]], m_tile, c0, buf + kOffLo);
+              tma_store_2d(&p.maps[p.out_map[2]], m_tile, c0, buf + kOffB);
+            }
+            if (has_smp) tma_store_2d(&p.maps[p.out_map[3]], m_tile, c0, buf + kOffSmp);
+            if (has_smp_aux) tma_store_2d(&p.maps[p.out_map[4]], m_tile, c0, buf + kOffSmpB);
           }
           if (leader) {
             tma_store_commit();
@@ -946,9 +977,11 @@ struct MapKey {
   const void* ptr;
   uint64_t d0, d1, ld;
   uint32_t b0, b1;
-  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 3: none (output tiles)
+  int swz;  // 0: 128B swizzle, 1: 128B swizzle with 32B atoms, 2: 64B swizzle, 3: none (output tiles)
+  int bf16;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && swz == o.swz &&
+           bf16 == o.bf16;
   }
 };
 struct MapKeyHash {
@@ -957,21 +990,22 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.d0;
     h = h * 1000003u ^ k.d1;
     h = h * 1000003u ^ k.ld;
-    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 2 | (uint32_t)k.swz);
+    h = h * 1000003u ^ ((uint64_t)k.b0 << 32 | k.b1 << 3 | (uint32_t)k.swz << 1 | (uint32_t)k.bf16);
     return h;
   }
 };
 
-// 2-D fp32 map: inner (contiguous) extent d0, outer extent d1 with a stride of ld floats,
-// box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of 16-byte chunks
-// (K-major tiles, 32 floats of K per row); 1: 128-byte swizzle of 32-byte chunks, the only
-// shared-memory layout tcgen05 accepts for MN-major 32-bit operands; 3: none (output tiles).
-// Encoded maps are cached.
-bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
-              int swz) {
+// 2-D map over fp32 or bfloat16 elements: inner (contiguous) extent d0, outer extent d1 with a
+// stride of ld elements, box b0 x b1, zero fill outside the tensor.  swz 0: 128-byte swizzle of
+// 16-byte chunks (K-major fp32 tiles, 32 floats of K per row; MN-major bfloat16 tiles, 64 per
+// row); 2: 64-byte swizzle (K-major bfloat16, 32 per row); 1: 128-byte swizzle of 32-byte
+// chunks, the only shared-memory layout tcgen05 accepts for MN-major 32-bit operands;
+// 3: none (output tiles).  Encoded maps are cached.
+bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+              int swz, int bf16) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  const MapKey key{ptr, d0, d1, ld, b0, b1, swz};
+  const MapKey key{ptr, d0, d1, ld, b0, b1, swz, bf16};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -981,14 +1015,15 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {d0, d1};
-  const cuuint64_t strides[1] = {ld * sizeof(float)};
+  const cuuint64_t strides[1] = {ld * (bf16 ? 2 : 4)};
   const cuuint32_t box[2] = {b0, b1};
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUresult r = fn(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr,
+                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swz == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                                 : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B),
+                                 : (swz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : (swz == 3 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B)),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
@@ -998,7 +1033,9 @@ bool make_map(CUtensorMap* out, const float* ptr, uint64_t d0, uint64_t d1, uint
 }
 
 // TMA needs a 16-byte aligned base and column stride.
-inline bool tma_ok(const GemmOperand& o) { return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0); }
+inline bool tma_ok(const GemmOperand& o) {
+  return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0) && (!o.aux || (o.lda % 8 == 0 && ((uintptr_t)o.aux & 15) == 0));
+}
 
 // Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
 // 16-byte units), descriptor version 1 for sm_100 (bits 46-47), layout type in bits 61-63.
@@ -1032,7 +1069,7 @@ TcTile tile_view(bool mn, bool bf16, int bk, uint32_t smem_off) {
 }
 
 inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
-  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans;
+  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.aux == b.aux && a.lda == b.lda;
 }
 
 static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
@@ -1104,12 +1141,13 @@ bool gemm_tc_supported(const GemmProblem& g) {
     if ((ps.a.part >= kPartLo16) != (ps.b.part >= kPartLo16)) return false;
   }
   const GemmEpilogue& e = g.epi;
-  if (e.sample && (e.col0 & 3)) return false;
-  // activation epilogues store whole column segments with TMA: 16-byte aligned columns
-  const bool plain = !e.bias && e.activation == 0 && !e.sample && e.out;
+  if ((e.sample || e.sample_aux) && (e.col0 & 3)) return false;
+  // activation epilogues store whole column segments with TMA: 16-byte aligned columns (the
+  // planes of an aux matrix are, its columns being a multiple of 8 floats)
+  const bool plain = !e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out;
   if (!plain) {
-    if (e.ldo % 4 != 0) return false;
-    if (((uintptr_t)e.out | (uintptr_t)e.sample) & 15) return false;
+    if (e.ldo % 4 != 0 || e.ld_aux % 8 != 0) return false;
+    if (((uintptr_t)e.out | (uintptr_t)e.sample | (uintptr_t)e.out_aux | (uintptr_t)e.sample_aux) & 15) return false;
   }
   return encode_fn() != nullptr;
 }
@@ -1177,28 +1215,51 @@ int gemm_tc(const GemmProblem& g) {
     uint32_t off = 0;
     int tile_of[2][4];
     int ntiles = 0;
-    tg.nconv = 0;
-    for (int o = 0; o < 2; o++) {   // the loaded tiles first
-      TcLoad& ld = tg.load[o];
-      ld.map = nmaps;
-      ld.mn = mn[o];
-      ld.is_a = o == 0;
-      ld.smem_off = off;
-      const bool ok = mn[o] ? make_map(&p.maps[nmaps], src[o]->ptr, (uint64_t)extent[o], (uint64_t)f.k,
-                                       (uint64_t)src[o]->ld, 32, (uint32_t)bk, 1)
-                            : make_map(&p.maps[nmaps], src[o]->ptr, (uint64_t)f.k, (uint64_t)extent[o],
-                                       (uint64_t)src[o]->ld, (uint32_t)bk, (uint32_t)rows[o], 0);
-      if (!ok) return set_error("cuTensorMapEncodeTiled failed for an operand");
+    tg.nload = tg.nconv = 0;
+    auto add_load = [&](int o, const void* ptr, uint64_t ld, bool bf16) {
+      TcLoad& l = tg.load[tg.nload++];
+      l.map = nmaps;
+      l.mn = mn[o];
+      l.is_a = o == 0;
+      l.box_rows = bf16 ? 64 : 32;                     // 128 bytes of M/N per box row
+      l.smem_off = off;
+      // K-major: one box of bk elements of K x the tile's rows; MN-major: boxes of 128 bytes x bk
+      const bool ok = mn[o] ? make_map(&p.maps[nmaps], ptr, (uint64_t)extent[o], (uint64_t)f.k, ld,
+                                       (uint32_t)l.box_rows, (uint32_t)bk, bf16 ? 0 : 1, bf16)
+                            : make_map(&p.maps[nmaps], ptr, (uint64_t)f.k, (uint64_t)extent[o], ld, (uint32_t)bk,
+                                       (uint32_t)rows[o], bf16 ? 2 : 0, bf16);
       nmaps++;
+      return ok;
+    };
+    uint32_t x_off[2] = {0, 0};
+    for (int o = 0; o < 2; o++) {   // the fp32 tiles first: wanted as they are, or as the source of derived parts
+      const bool from_aux = src[o]->aux != nullptr;
+      if (!(want[o][kPartX] || want[o][kPartLo32] || (!from_aux && (want[o][kPartLo16] || want[o][kPartB16])))) continue;
+      x_off[o] = off;
+      if (!add_load(o, src[o]->ptr, (uint64_t)src[o]->ld, false))
+        return set_error("cuTensorMapEncodeTiled failed for an operand");
       tile_of[o][kPartX] = ntiles;
       tg.tile[ntiles++] = tile_view(mn[o], false, bk, off);
       off += (uint32_t)rows[o] * bk * 4;
     }
+    for (int o = 0; o < 2; o++) {   // bfloat16 parts read from the operand's aux matrix
+      if (!src[o]->aux) continue;
+      for (int part = kPartLo16; part <= kPartB16; part++) {
+        if (!want[o][part]) continue;
+        const uint16_t* plane = reinterpret_cast<const uint16_t*>(src[o]->aux) + (part == kPartB16 ? src[o]->lda : 0);
+        if (!add_load(o, plane, (uint64_t)(2 * src[o]->lda), true))
+          return set_error("cuTensorMapEncodeTiled failed for an aux plane");
+        tile_of[o][part] = ntiles;
+        tg.tile[ntiles++] = tile_view(mn[o], true, bk, off);
+        off += (uint32_t)rows[o] * bk * 2;
+        want[o][part] = false;   // not the converters' job
+      }
+    }
     tg.stage_tx = off;
-    for (int o = 0; o < 2; o++) {   // then the derived ones
+    for (int o = 0; o < 2; o++) {   // then the parts the converters derive
       if (!want[o][kPartLo32] && !want[o][kPartLo16] && !want[o][kPartB16]) continue;
       TcConv& cv = tg.conv[tg.nconv++];
-      cv.src_off = tg.load[o].smem_off;
+      cv.src_off = x_off[o];
       cv.mn = mn[o];
       cv.is_a = o == 0;
       cv.lo32_off = cv.lo16_off = cv.b16_off = kNoTile;
@@ -1241,19 +1302,26 @@ int gemm_tc(const GemmProblem& g) {
 
   const GemmEpilogue& e = g.epi;
   int epi = kEpiGeneric;
-  if (!e.bias && e.activation == 0 && !e.sample && e.out) {
+  if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
     epi = kEpiPlain;
   } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out) {
-    if (e.activation == 1) epi = e.sample ? kEpiSigSample : kEpiSig;
-    else if (!e.sample) epi = kEpiLin;
+    if (e.activation == 1 && e.sample) epi = kEpiSigSample;
+    else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
+    else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;
   }
   for (int i = 0; i < kOutArrays; i++) p.out_map[i] = -1;
   if (epi != kEpiPlain) {
-    // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns
-    const float* outs[kOutArrays] = {e.out, e.sample};
+    // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns: M x N floats
+    // with columns ldo apart, or one bfloat16 plane of an aux matrix (columns 2 ld_aux bfloat16
+    // apart, plane 1 starting ld_aux bfloat16 into the column)
+    const uint16_t* oa = reinterpret_cast<const uint16_t*>(e.out_aux);
+    const uint16_t* sa = reinterpret_cast<const uint16_t*>(e.sample_aux);
+    const void* outs[kOutArrays] = {e.out, oa, oa ? oa + e.ld_aux : nullptr, e.sample, sa ? sa + e.ld_aux : nullptr};
+    const int is16[kOutArrays] = {0, 1, 1, 0, 1};
     for (int i = 0; i < kOutArrays; i++) {
       if (!outs[i]) continue;
-      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)e.ldo, BM, kOutCols, 3))
+      if (!make_map(&p.maps[nmaps], outs[i], (uint64_t)g.M, (uint64_t)g.N, (uint64_t)(is16[i] ? 2 * e.ld_aux : e.ldo), BM,
+                    kOutCols, 3, is16[i]))
         return set_error("cuTensorMapEncodeTiled failed for an output");
       p.out_map[i] = nmaps++;
     }

@@ -22,11 +22,12 @@ class FusedDBM(object):
         cm.CUDAMatrix.init_random(seed)
         z = lambda r, c: cm.empty((r, c))
         B = batchsize
-        self.W, self.dW, self.suff_W = [], [], []
+        self.W, self.W_aux, self.dW, self.suff_W = [], [], [], []
         for i, w in enumerate(weights):
             w = np.asarray(w, np.float32)
             assert w.shape == (sizes[i], sizes[i + 1])
             self.W.append(cm.CUDAMatrix(w))
+            self.W_aux.append(self.W[-1].split_bf16(cm.empty_aux(w.shape)))   # bfloat16 parts, rewritten by the update
             self.dW.append(z(*w.shape))
             self.suff_W.append(z(*w.shape))
         self.b = [z(n, 1) for n in sizes]
@@ -45,9 +46,9 @@ class FusedDBM(object):
         P = self.cm.split_passes
         passes = []
         if below is not None:
-            passes += P(self.W[j - 1].T, below[0], exact_b=below[1])
+            passes += P(self.W[j - 1].T, below[0], exact_b=below[1], a_aux=self.W_aux[j - 1])
         if above is not None:
-            passes += P(self.W[j], above[0], exact_b=above[1])
+            passes += P(self.W[j], above[0], exact_b=above[1], a_aux=self.W_aux[j])
         self.cm.fused_gemm(passes, out=out, sample=sample, bias=self.b[j], activation=1)
         self.kernel_launches += 1
 
@@ -102,7 +103,8 @@ class FusedDBM(object):
         for j in range(L):
             self.b[j].momentum_update(self.db[j], None, self.suff_b[j], inv_b, mom, eps)
         for i in range(L - 1):
-            self.W[i].momentum_update(self.dW[i], None, self.suff_W[i], inv_b, mom, eps, l2=l2, l1=l1)
+            self.W[i].momentum_update(self.dW[i], None, self.suff_W[i], inv_b, mom, eps, l2=l2, l1=l1,
+                                      w_aux=self.W_aux[i])
 
     def read_loss(self, reset=True):
         v = float(np.array(self.loss_acc.asarray())[0, 0])

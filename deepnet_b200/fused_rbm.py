@@ -18,7 +18,10 @@ bits ignored); the kernel derives lo = x - tf32(x) from the staged tile of x and
 correction terms lo_x.y + x.lo_y to x.y - as bfloat16 products (twice the TF32 rate) for
 the activation products, as TF32 products for the statistics, whose positive and negative
 halves nearly cancel.  Binary matrices (data, Bernoulli samples) have lo = 0 and need one
-term fewer.  Only fp32 matrices live in device memory.
+term fewer.  For the big products the bfloat16 parts come from aux matrices kept beside W
+(rewritten by the update) and beside the states (written by the epilogue that produced
+them): deriving them in the kernel costs shared-memory bandwidth next to the tensor core's
+own operand reads.
 
 With more than one rank the sufficient statistics of the ranks' minibatch shards are
 summed by one NCCL all-reduce of a packed buffer before the update.
@@ -44,6 +47,9 @@ class FusedRBM(object):
         w = np.asarray(weight, np.float32)
         assert w.shape == (V, H)
         self.W = cm.CUDAMatrix(w)
+        # bfloat16 parts of W kept in memory (rewritten by every update): the big products read
+        # them instead of deriving them, as they do for the states that feed the next product
+        self.W_aux = self.W.split_bf16(cm.empty_aux((V, H)))
         self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
         self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
         self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
@@ -53,8 +59,10 @@ class FusedRBM(object):
         self.suff_bv = self.pack.slice(V * H, V * H + V)
         self.suff_bh = self.pack.slice(V * H + V, V * H + V + H)
         B = batchsize
-        self.h_pos, self.h_samp = z(H, B), z(H, B)
-        self.v_neg, self.h_neg = z(V, B), z(H, B)
+        za = lambda r, c: cm.empty_aux((r, c))
+        self.h_pos, self.h_samp, self.h_samp_aux = z(H, B), z(H, B), za(H, B)
+        self.v_neg, self.v_neg_aux, self.h_neg = z(V, B), za(V, B), z(H, B)
+        self.data_aux = za(V, B)
         self.loss_acc = z(1, 1)
         if visible == REPLICATED_SOFTMAX:
             # document lengths, length-normalised visible states (the statistics use state / NN,
@@ -89,7 +97,7 @@ class FusedRBM(object):
             return self._train_replicated_softmax(step, data)
         cm, k = self.cm, self.hyp.gibbs_steps
         V, H, B = self.V, self.H, self.B
-        W, P = self.W, cm.split_passes
+        W, Wa, P = self.W, self.W_aux, cm.split_passes
         v0 = data
         self.kernel_launches = 0
         gf = 2.0 * V * H * B                      # algorithmic flops of one product
@@ -97,18 +105,20 @@ class FusedRBM(object):
         lib = cm._lib
         exact = self.binary_data                  # 0/1 data have no low part
         # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
-        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=exact), out=self.h_pos, sample=self.h_samp,
-                 bias=self.bh, activation=1)
+        self._op("split", 0, 2 * vb, v0.split_bf16, self.data_aux)
+        self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux),
+                 out=self.h_pos, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
         # negative phase: k Gibbs steps, visible mean fed upward (sample_input off)
         for i in range(k):
-            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True), out=self.v_neg, bias=self.bv,
-                     activation=self._act(self.visible))
+            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm,
+                     P(W, self.h_samp, exact_b=True, a_aux=Wa, b_aux=self.h_samp_aux), out=self.v_neg,
+                     out_aux=self.v_neg_aux, bias=self.bv, activation=self._act(self.visible))
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1          # add_sq_diff is two launches
-            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_neg), out=self.h_neg, sample=self.h_samp,
-                     bias=self.bh, activation=1)
+            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, self.v_neg, a_aux=Wa, b_aux=self.v_neg_aux),
+                     out=self.h_neg, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
         # statistics: pos - neg in one product: the difference of two nearly equal products, so its
         # correction terms are TF32 products too; bias statistics by row sums
         pos = P(v0, self.h_pos.T, exact_a=exact, terms="tf32")
@@ -130,8 +140,8 @@ class FusedRBM(object):
         eh = self.ehyp
         l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 5 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1)
+        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1, w_aux=Wa)
 
     def _train_replicated_softmax(self, step, data):
         """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:
@@ -141,7 +151,7 @@ class FusedRBM(object):
         multinomial draw and one for the hidden draw."""
         cm, k = self.cm, self.hyp.gibbs_steps
         V, H, B = self.V, self.H, self.B
-        W, P = self.W, cm.split_passes
+        W, Wa, P = self.W, self.W_aux, cm.split_passes   # the small state matrices' parts are derived in the kernel
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         lib = cm._lib
@@ -152,20 +162,20 @@ class FusedRBM(object):
         self._op("add_scalar", 0, 8.0 * B, self.NN.add, self.tiny)
         self._op("div_by_row", 0, 2 * vb, v0.div_by_row, self.NN, target=self.v0n)
         # positive phase: hidden bias is scaled by the document length (deepnet/dbm.py:101-104)
-        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=True), out=self.h_pos, sample=self.h_samp,
-                 bias=self.bh, col_scale=self.NN, activation=1)
+        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=True, a_aux=Wa), out=self.h_pos,
+                 sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
         for i in range(k):
             # visible: NN * softmax(W h + b_v)
-            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True), out=self.v_act, bias=self.bv,
-                     activation=0)
+            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True, a_aux=Wa), out=self.v_act,
+                     bias=self.bv, activation=0)
             self._op("softmax", 0, 2 * vb, self.v_act.softmax_scaled, self.NN, target=self.v_neg)
             self._op("div_by_row", 0, 2 * vb, self.v_neg.div_by_row, self.NN, target=self.v_negn)
             if i == 0:   # squared error between state / NN and the counts (replicated_softmax_layer.py:128-135)
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
             self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
-            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_samp, exact_b=True), out=self.h_neg,
-                     sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
+            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_samp, exact_b=True, a_aux=Wa),
+                     out=self.h_neg, sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
         pos = P(self.v0n, self.h_pos.T, terms="tf32")
         neg = P(self.v_negn, self.h_neg.T, negate=1, terms="tf32")
         self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
@@ -183,15 +193,15 @@ class FusedRBM(object):
         eh = self.ehyp
         l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 5 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1)
+        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1, w_aux=Wa)
 
     def Inference(self, data, input_recon=False):
         """Hidden representation of `data` (V x cases device matrix), minibatch by minibatch:
         the inference-only positive phase of deepnet/dbm.py:340-398 (extract_rbm_representation.py)
         as one fused product per minibatch.  Returns (cases x H) host array, and with input_recon
         also the summed squared error of the input reconstructed from the hidden means."""
-        cm, B, W, P = self.cm, self.B, self.W, self.cm.split_passes
+        cm, B, W, Wa, P = self.cm, self.B, self.W, self.W_aux, self.cm.split_passes
         n = data.shape[1] // B
         rep = np.zeros((n * B, self.H), np.float32)
         err = 0.0
@@ -201,10 +211,10 @@ class FusedRBM(object):
             if soft:
                 v0.sum(axis=0, target=self.NN)
                 self.NN.add(self.tiny)
-            cm.fused_gemm(P(W.T, v0, exact_b=soft or self.binary_data), out=self.h_pos, bias=self.bh, activation=1,
+            cm.fused_gemm(P(W.T, v0, exact_b=soft or self.binary_data, a_aux=Wa), out=self.h_pos, bias=self.bh, activation=1,
                           col_scale=self.NN if soft else None)
             if input_recon:
-                down = P(W, self.h_pos)
+                down = P(W, self.h_pos, a_aux=Wa)
                 if soft:
                     cm.fused_gemm(down, out=self.v_act, bias=self.bv, activation=0)
                     self.v_act.softmax_scaled(self.NN, target=self.v_neg)

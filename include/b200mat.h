@@ -168,13 +168,24 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha);
  *                                                        the TF32 rate), 2^-18 per term. */
 enum { B200_PART_X = 0, B200_PART_LO32 = 1, B200_PART_LO16 = 2, B200_PART_B16 = 3 };
 
+/* The bfloat16 parts of a rows x cols fp32 matrix x kept in device memory ("aux matrix"), for
+ * the big products: deriving the parts in the kernel costs shared-memory bandwidth next to the
+ * tensor core's own operand reads.  lda x cols floats of storage, lda = rows rounded up to a
+ * multiple of 8; column c holds lda bfloat16 of plane 0, bf16(x - tf32(x)), then lda bfloat16
+ * of plane 1, bf16(x) (the first `rows` of each in use).  An aux handle is an ordinary cudamat
+ * of lda x cols. */
+int split_bf16(cudamat* x, cudamat* aux);
+
 /* One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
- * Both parts of a term are fp32-wide (X, LO32) or both bfloat16 (LO16, B16). */
+ * Both parts of a term are fp32-wide (X, LO32) or both bfloat16 (LO16, B16).  a_aux / b_aux:
+ * NULL, or the aux matrix of a / b, from which the bfloat16 parts are then read. */
 typedef struct b200_pass {
   cudamat* a;
   cudamat* b;
   int negate;
   int a_part, b_part;
+  cudamat* a_aux;
+  cudamat* b_aux;
 } b200_pass;
 
 /* out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale).
@@ -189,7 +200,9 @@ typedef struct b200_fused_gemm {
   cudamat* col_scale;    /* 1 x N or NULL: bias of column n is bias[m] * col_scale[n] */
   int activation;        /* 0 identity, 1 logistic */
   cudamat* out;          /* M x N or NULL */
+  cudamat* out_aux;      /* aux matrix of the result, or NULL */
   cudamat* sample;       /* Bernoulli(result): consumes one sampling call, or NULL */
+  cudamat* sample_aux;   /* aux matrix of the draw (plane 1 only: a 0/1 value has no low part), or NULL */
 } b200_fused_gemm;
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f);
 
@@ -198,9 +211,9 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
 
 /* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass over the parameter:
  * grad += -inv_batch * suff; delta = momentum*delta + l2*w + l1*sign(w) + grad;
- * w -= eps*delta; grad = 0.  grad may be NULL. */
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, float inv_batch, float momentum,
-                    float eps, float l2, float l1);
+ * w -= eps*delta; grad = 0; w_aux = aux matrix of the new w.  grad, w_aux may be NULL. */
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, float inv_batch,
+                    float momentum, float eps, float l2, float l1);
 
 /* Has no counterpart in the reference.  add_sum_by_axis for callers that must never reach
  * cudaMalloc (a host that gave the whole device to its own memory pool, or a loop that cannot

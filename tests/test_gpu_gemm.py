@@ -145,6 +145,43 @@ def test_operand_parts_in_all_layouts(cm, path, ta, tb, m, n, k):
     assert cm.read_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(100, 33), (500, 100), (128, 256), (7, 5)])
+def test_split_bf16_planes(cm, shape):
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal(shape) * 10.0 ** rng.integers(-3, 4, shape)).astype(np.float32)
+    aux = cm.CUDAMatrix(x).split_bf16(cm.empty_aux(shape))
+    lo, b = aux.planes()
+    np.testing.assert_array_equal(lo, bf16_round(x - tf32_trunc(x)))
+    np.testing.assert_array_equal(b, bf16_round(x))
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(500, 300, 784), (260, 36, 40), (1000, 520, 2100)])
+def test_bfloat16_parts_read_from_aux_matrices(cm, path, ta, tb, m, n, k):
+    """The bfloat16 parts loaded from aux matrices give the same products as the parts the
+    kernel derives, in all four layouts, also with the aux of one operand only."""
+    rng = np.random.default_rng(15)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    cm.set_gemm_path(path)
+    sa, sb = (A.T if ta else A), (B.T if tb else B)          # stored forms
+    ga, gb = cm.CUDAMatrix(np.asfortranarray(sa)), cm.CUDAMatrix(np.asfortranarray(sb))
+    xa, xb = ga.split_bf16(cm.empty_aux(sa.shape)), gb.split_bf16(cm.empty_aux(sb.shape))
+    oa, ob = (ga.T if ta else ga), (gb.T if tb else gb)
+    for pa, pb in ((3, 3), (2, 3), (3, 2)):
+        want = part_values(A, pa).astype(np.float64) @ part_values(B, pb).astype(np.float64)
+        for aux_a, aux_b in ((xa, xb), (xa, None), (None, xb)):
+            out = cm.empty((m, n))
+            cm.fused_gemm([(cm.Part(oa, pa, aux_a), cm.Part(ob, pb, aux_b))], out=out)
+            assert relerr(get(out), want) < 5e-6, (pa, pb)
+    # the full term list of a split product, every bfloat16 part from memory
+    out = cm.empty((m, n))
+    cm.fused_gemm(cm.split_passes(oa, ob, a_aux=xa, b_aux=xb), out=out)
+    assert relerr(get(out), A.astype(np.float64) @ B.astype(np.float64)) < (2e-6 if path == 1 else 1e-5)
+    assert cm.read_status() == 0
+
+
 @pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("m,n,k", [(500, 100, 784), (128, 256, 64), (260, 36, 40), (1024, 512, 2048)])
 def test_fused_epilogue_bias_logistic_sample(cm, oracle, path, m, n, k):
@@ -158,15 +195,22 @@ def test_fused_epilogue_bias_logistic_sample(cm, oracle, path, m, n, k):
     oracle.EigenMatrix.init_random(seed)
     w, x, bias = cm.CUDAMatrix(W), cm.CUDAMatrix(X), cm.CUDAMatrix(b)
     out, smp = cm.empty((m, n)), cm.empty((m, n))
-    cm.fused_gemm(cm.split_passes(w.T, x, exact_b=True), out=out, sample=smp, bias=bias, activation=1, alpha=1.0)
+    out_aux, smp_aux = cm.empty_aux((m, n)), cm.empty_aux((m, n))
+    w_aux, x_aux = w.split_bf16(cm.empty_aux(W.shape)), x.split_bf16(cm.empty_aux(X.shape))
+    cm.fused_gemm(cm.split_passes(w.T, x, exact_b=True, a_aux=w_aux, b_aux=x_aux), out=out, sample=smp,
+                  out_aux=out_aux, sample_aux=smp_aux, bias=bias, activation=1, alpha=1.0)
     pre = W.astype(np.float64).T @ X + b
     want = 1 / (1 + np.exp(-pre))
     got = get(out)
     assert relerr(got, want) < TOL
+    lo, bb = out_aux.planes()                       # the bfloat16 parts of the result
+    np.testing.assert_array_equal(lo, bf16_round(got - tf32_trunc(got)))
+    np.testing.assert_array_equal(bb, bf16_round(got))
     # the draw thresholds the probabilities the kernel itself produced against the shared
     # uniforms of call 0: bit-exact with the oracle fed the same probabilities
     want_s = get(oracle.EigenMatrix(got).sample_bernoulli(target=oracle.empty((m, n))))
     np.testing.assert_array_equal(get(smp), want_s)
+    np.testing.assert_array_equal(smp_aux.planes()[1], want_s)
     assert cm.CUDAMatrix.rnd_state.calls == 1
     assert cm.read_status() == 0
 
@@ -222,8 +266,12 @@ def test_momentum_update_is_bit_exact(cm, oracle, shape, with_grad):
     wo.momentum_update(do, go, oracle.EigenMatrix(s0), *args, l2=2e-4, l1=1e-3)
     wg, dg = cm.CUDAMatrix(w0), cm.CUDAMatrix(d0)
     gg = cm.CUDAMatrix(g0) if with_grad else None
-    wg.momentum_update(dg, gg, cm.CUDAMatrix(s0), *args, l2=2e-4, l1=1e-3)
+    aux = cm.empty_aux(shape)
+    wg.momentum_update(dg, gg, cm.CUDAMatrix(s0), *args, l2=2e-4, l1=1e-3, w_aux=aux)
     np.testing.assert_array_equal(get(wg), get(wo))
     np.testing.assert_array_equal(get(dg), get(do))
     if with_grad:
         assert not get(gg).any()
+    lo, b = aux.planes()
+    np.testing.assert_array_equal(lo, bf16_round(get(wg) - tf32_trunc(get(wg))))
+    np.testing.assert_array_equal(b, bf16_round(get(wg)))
