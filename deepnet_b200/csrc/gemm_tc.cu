@@ -1295,9 +1295,10 @@ int gemm_tc(const GemmProblem& g) {
   if (p.num_stages < 1) return ERROR_UNSUPPORTED;
   // Products folded in tensor memory before they join the fp32 registers.  128 keeps linear
   // outputs (statistics, `dot`) within 2e-6 of the largest entry at K = 4096..8192; behind a
-  // logistic epilogue the slope <= 1/4 and the small pre-activations leave room for 512
-  // (measured 2e-7 absolute on the probabilities), which costs 8 % less time.
-  const int ck = chunk_k >= 16 ? chunk_k : (g.epi.activation == 1 ? 512 : 128);
+  // logistic epilogue the slope <= 1/4 and the small pre-activations leave room for 1024
+  // (a few 1e-7 absolute on the probabilities).  Long chunks also cover the tile epilogue: the
+  // issuer runs two chunks ahead of the epilogue warps, which are busy for ~20 us per tile.
+  const int ck = chunk_k >= 16 ? chunk_k : (g.epi.activation == 1 ? 1024 : 128);
   p.chunk_iters = ck / bk < 1 ? 1 : ck / bk;
 
   const GemmEpilogue& e = g.epi;
