@@ -235,9 +235,9 @@ def run_ours(args):
                       frac=round(achieved / peaks["tensor"], 4),
                       # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
                       # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
-                      traffic=3.17e9 if config == 4 else None,
+                      traffic=2.80e9 if config == 4 else None,
                       kernel="k_gemm_tc<256, sigmoid+Bernoulli> (tcgen05 kind::tf32 + 2 x kind::f16 bf16 "
-                             "correction terms per k-block, derived in shared memory)",
+                             "correction terms per k-block, paired CTAs)",
                       peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
                                   "and one TF32 + two bf16 terms make one fp32-grade product" % peaks["source"],
                       launches=up[0], ms_per_launch=round(up[1] / up[0], 4),

@@ -848,7 +848,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         // for the arithmetic; a batch of four columns (one Philox block) is staged as
         // [array][column][128 rows], and one thread of each column-half group of four warps
         // sends it on with cp.async.bulk.tensor while the next batch is computed (two buffers).
-        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias and out set; beta = 0; no col_scale
+        const bool spec = kEpi != kEpiGeneric;      // specialised variants: bias set; beta = 0; no col_scale
         const bool row_ok = m < pM;
         const int hf = ew >> 2;                     // column half = store group
         const bool leader = (ew & 3) == 0 && lane == 0;
@@ -857,7 +857,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         const float bias = ((spec || e.bias) && row_ok) ? e.bias[m] : 0.0f;
         const bool logistic = spec ? (kEpi != kEpiLin) : (e.activation == 1);
         const bool draw = spec ? (kEpi == kEpiSigSample) : (e.sample != nullptr || e.sample_aux != nullptr);
-        const bool has_out = spec || e.out != nullptr;
+        const bool has_out = e.out != nullptr;
         const bool has_aux = e.out_aux != nullptr;
         const bool has_smp = spec ? draw : e.sample != nullptr;
         const bool has_smp_aux = draw && e.sample_aux != nullptr;
@@ -1305,7 +1305,7 @@ int gemm_tc(const GemmProblem& g) {
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
     epi = kEpiPlain;
-  } else if (e.bias && !e.col_scale && e.beta == 0.0f && e.out) {
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample)) {
     if (e.activation == 1 && e.sample) epi = kEpiSigSample;
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;

@@ -117,8 +117,10 @@ class FusedRBM(object):
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1          # add_sq_diff is two launches
+            # the hidden means are only read after the last step (statistics); before that the draw suffices
             self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, self.v_neg, a_aux=Wa, b_aux=self.v_neg_aux),
-                     out=self.h_neg, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
+                     out=self.h_neg if i == k - 1 else None, sample=self.h_samp, sample_aux=self.h_samp_aux,
+                     bias=self.bh, activation=1)
         # statistics: pos - neg in one product: the difference of two nearly equal products, so its
         # correction terms are TF32 products too; bias statistics by row sums
         pos = P(v0, self.h_pos.T, exact_a=exact, terms="tf32")
