@@ -26,6 +26,8 @@ own operand reads.
 With more than one rank the sufficient statistics of the ranks' minibatch shards are
 summed by one NCCL all-reduce of a packed buffer before the update.
 """
+import os
+
 import numpy as np
 
 from .dbm import LINEAR, LOGISTIC, REPLICATED_SOFTMAX, Parameter
@@ -50,6 +52,10 @@ class FusedRBM(object):
         # bfloat16 parts of W kept in memory (rewritten by every update): the big products read
         # them instead of deriving them, as they do for the states that feed the next product
         self.W_aux = self.W.split_bf16(cm.empty_aux((V, H)))
+        # ... and for the states only when the products are big: a small model is bound by launch
+        # latency, where the extra split launch and the wider epilogue cost more than they save
+        env = os.environ.get("B200_RBM_STATE_AUX")
+        self.state_aux = (V * H * batchsize >= 1 << 32) if env is None else env != "0"
         self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
         self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
         self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
@@ -105,21 +111,25 @@ class FusedRBM(object):
         lib = cm._lib
         exact = self.binary_data                  # 0/1 data have no low part
         # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
-        self._op("split", 0, 2 * vb, v0.split_bf16, self.data_aux)
-        self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux),
-                 out=self.h_pos, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1)
+        sa = self.state_aux
+        if sa:
+            self._op("split", 0, 2 * vb, v0.split_bf16, self.data_aux)
+        h_samp_aux, v_neg_aux = (self.h_samp_aux, self.v_neg_aux) if sa else (None, None)
+        self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm,
+                 P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux if sa else None),
+                 out=self.h_pos, sample=self.h_samp, sample_aux=h_samp_aux, bias=self.bh, activation=1)
         # negative phase: k Gibbs steps, visible mean fed upward (sample_input off)
         for i in range(k):
             self._op("gemm_down", gf, 2 * vb, cm.fused_gemm,
-                     P(W, self.h_samp, exact_b=True, a_aux=Wa, b_aux=self.h_samp_aux), out=self.v_neg,
-                     out_aux=self.v_neg_aux, bias=self.bv, activation=self._act(self.visible))
+                     P(W, self.h_samp, exact_b=True, a_aux=Wa, b_aux=h_samp_aux), out=self.v_neg,
+                     out_aux=v_neg_aux, bias=self.bv, activation=self._act(self.visible))
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1          # add_sq_diff is two launches
             # the hidden means are only read after the last step (statistics); before that the draw suffices
-            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, self.v_neg, a_aux=Wa, b_aux=self.v_neg_aux),
-                     out=self.h_neg if i == k - 1 else None, sample=self.h_samp, sample_aux=self.h_samp_aux,
+            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, self.v_neg, a_aux=Wa, b_aux=v_neg_aux),
+                     out=self.h_neg if i == k - 1 else None, sample=self.h_samp, sample_aux=h_samp_aux,
                      bias=self.bh, activation=1)
         # statistics: pos - neg in one product: the difference of two nearly equal products, so its
         # correction terms are TF32 products too; bias statistics by row sums
