@@ -7,11 +7,13 @@
 //
 // fp32-grade accuracy comes from the caller's term list over PARTS of the fp32 operands
 // (x as TF32, x - tf32(x) as TF32 or bfloat16, bfloat16(x)), all accumulating into ONE fp32
-// accumulator.  Only x is read from memory: the delivery of operand tiles to the SMs (about
-// 60 GB/s per SM) bounds this kernel, not the tensor pipe, so four converter warps derive the
-// other parts from the staged fp32 tile in shared memory, in the layout TMA would have
-// produced, and the MMA issuer consumes a stage once they are done.  A term may be negated
-// (instruction-descriptor bit), which folds positive-minus-negative statistics into one kernel.
+// accumulator.  The parts other than x reach shared memory in one of two ways: four converter
+// warps derive them from the staged fp32 tile, in the layout TMA would have produced (nothing
+// but x in device memory; costs shared-memory bandwidth next to the tensor core's own operand
+// reads), or TMA loads the bfloat16 ones from an aux matrix kept beside x (what the big
+// products of the training step use).  The MMA issuer consumes a stage once its loads have
+// landed and the converters are done with it.  A term may be negated (instruction-descriptor
+// bit), which folds positive-minus-negative statistics into one kernel.
 //
 // Kernel shape: persistent, one CTA per SM (or a pair of CTAs on a 256-row tile), 512 threads
 // (registers move from the first two warpgroups to the epilogue's with setmaxnreg):
@@ -77,8 +79,8 @@ struct TcMma {
   uint32_t idesc;          // tcgen05 instruction descriptor (carries the negate bit)
 };
 // A group = the terms over one pair of fp32 operands (and so one K range).  Each k-block stages
-// the two fp32 tiles once, the converters add the derived parts, and all the group's products
-// are issued from that one stage.
+// every tile the terms read once (the fp32 tiles and aux planes by TMA, derived parts by the
+// converters), and all the group's products are issued from that one stage.
 struct TcGroup {
   int k_iters;             // ceil(k / bk)
   int nload, nconv, nmma;
