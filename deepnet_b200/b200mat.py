@@ -53,7 +53,8 @@ class _FusedGemm(ct.Structure):
     _fields_ = [("npass", ct.c_int), ("passes", _Pass * MAX_PASS), ("alpha", ct.c_float), ("beta", ct.c_float),
                 ("bias", ct.POINTER(cudamat)), ("col_scale", ct.POINTER(cudamat)), ("activation", ct.c_int),
                 ("out", ct.POINTER(cudamat)), ("out_aux", ct.POINTER(cudamat)), ("sample", ct.POINTER(cudamat)),
-                ("sample_aux", ct.POINTER(cudamat))]
+                ("sample_aux", ct.POINTER(cudamat)), ("scale_exp", ct.POINTER(cudamat)),
+                ("scale_exp_const", ct.c_int), ("aux_f16", ct.c_int), ("aux_exp", ct.c_int)]
 
 
 _lib.get_last_cuda_error.restype = ct.c_char_p
@@ -475,11 +476,13 @@ class CUDAMatrix(object):
         return target
 
     # -- fused entry points (no counterpart in the reference API) -------------
-    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None):
+    def momentum_update(self, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None, w_scale=None):
         """deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one kernel; self is the parameter.
-        w_aux (optional, from `empty_aux`) receives the bfloat16 parts of the updated parameter."""
+        w_aux (optional, from `empty_aux`) receives the bfloat16 parts of the updated parameter, or,
+        with w_scale (the 1 x 4 device matrix of `f16_scale_state`), its scaled half-precision form."""
         _check(_lib.momentum_update(self.p_mat, delta.p_mat, grad.p_mat if grad is not None else None, suff.p_mat,
                                     w_aux.p_mat if w_aux is not None else None,
+                                    w_scale.p_mat if w_scale is not None else None,
                                     ct.c_float(inv_batch), ct.c_float(momentum), ct.c_float(eps), ct.c_float(l2),
                                     ct.c_float(l1)))
         return self
@@ -489,6 +492,14 @@ class CUDAMatrix(object):
         correction terms of a product read: plane 0 = bf16(self - tf32(self)), plane 1 =
         bf16(self).  Returns aux."""
         _check(_lib.split_bf16(self.p_mat, aux.p_mat))
+        return aux
+
+    def split_f16(self, aux, exp_dev=None, exp_const=0):
+        """Fills `aux` with self in scaled half-precision form: with xs = self * 2^(exp_dev + exp_const)
+        (exp_dev: 1 x 1 device matrix or None), plane 1 = fp16(xs), plane 0 = fp16(xs - plane 1).
+        Returns aux."""
+        _check(_lib.split_f16(self.p_mat, aux.p_mat, exp_dev.p_mat if exp_dev is not None else None,
+                              ct.c_int(int(exp_const))))
         return aux
 
     def split_tf32(self, lo, hi=None):
@@ -547,7 +558,7 @@ def empty_aux(shape):
 # What of an fp32 matrix a term of `fused_gemm` multiplies: x read as TF32, x - tf32(x) read as
 # TF32, bfloat16(x - tf32(x)), bfloat16(x).  The kernel derives the parts from the matrix itself,
 # or reads the two bfloat16 ones from the matrix's aux when one is given.
-PART_X, PART_LO32, PART_LO16, PART_B16 = 0, 1, 2, 3
+PART_X, PART_LO32, PART_LO16, PART_B16, PART_F16LO, PART_F16HI = 0, 1, 2, 3, 4, 5
 
 
 class Part(object):
@@ -571,6 +582,29 @@ def lo16(x, aux=None):
 
 def b16(x, aux=None):
     return Part(x, PART_B16, aux)
+
+
+def f16_passes(a, a_aux, b, b_aux, negate=0, exact_a=False, exact_b=False):
+    """The terms of a . b over aux matrices in scaled half-precision form (`split_f16`): with
+    x * 2^e = hi + lo,  a . b * 2^(ea + eb) ~= hi(a).lo(b) + lo(a).hi(b) + hi(a).hi(b), three
+    half-precision products (no TF32 term, no fp32 operand read), below 2^-21 per term.  The
+    caller passes the exponent sum to `fused_gemm` (scale_exp / scale_exp_const).  exact_a /
+    exact_b: that operand is exact in fp16 (0/1 data and samples), its lo plane is not read."""
+    p = []
+    if not exact_b:
+        p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16LO, b_aux), negate))
+    if not exact_a:
+        p.append((Part(a, PART_F16LO, a_aux), Part(b, PART_F16HI, b_aux), negate))
+    p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16HI, b_aux), negate))
+    return p
+
+
+def f16_scale_state(max_abs):
+    """The 1 x 4 device matrix `momentum_update` keeps for a parameter in scaled half-precision
+    form: {exponent in use, exponent of the next update, running max |w| (bits), -}; exponents
+    put the largest magnitude at or below 2^13.  `.slice(0, 1)` is the `scale_exp` of a product."""
+    e = float(np.floor(np.log2(8192.0 / max(float(max_abs), 1e-30))))
+    return CUDAMatrix(np.array([[e, e, 0.0, 0.0]], np.float32))
 
 
 def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16", a_aux=None, b_aux=None):
@@ -677,14 +711,17 @@ def correct_preds(mat, p, target=None, cutoff=0.5):
 
 
 def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activation=0, alpha=1.0, beta=0.0,
-               out_aux=None, sample_aux=None):
+               out_aux=None, sample_aux=None, scale_exp=None, scale_exp_const=0, aux_f16=False, aux_exp=0):
     """out = act(alpha * sum_p (+/-) a_p . b_p + beta * out + bias (x) col_scale) in one kernel.
 
     `passes` is a list of (a, b) or (a, b, negate); a and b are fp32 matrices, `.T` views, or
     parts of them (`lo32(x)`, `lo16(x)`, `b16(x)`, see `split_passes`); both operands of a
     term are fp32-wide (a TF32 product) or both bfloat16.  Optional outputs: a Bernoulli draw
     of the result (consumes one sampling call of the global random state) and the aux matrices
-    (bfloat16 parts) of result and draw.  Replaces the dot / add_dot / add_col_vec / sigmoid /
+    (bfloat16 parts) of result and draw.  With operands in scaled half-precision form
+    (`f16_passes`) the terms carry 2^(scale_exp + scale_exp_const) (scale_exp: 1 x 1 device matrix
+    or None), which the kernel divides out; aux_f16: the aux outputs are written in that form
+    with exponent aux_exp.  Replaces the dot / add_dot / add_col_vec / sigmoid /
     sample_bernoulli group of deepnet/dbm.py:88-105.
     """
     f = _FusedGemm()
@@ -701,8 +738,9 @@ def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activat
                 setattr(f.passes[i], side + "_aux", op.aux.p_mat)
         f.passes[i].negate = int(p[2]) if len(p) > 2 else 0
     f.alpha, f.beta, f.activation = alpha, beta, activation
+    f.scale_exp_const, f.aux_f16, f.aux_exp = int(scale_exp_const), int(bool(aux_f16)), int(aux_exp)
     for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("sample", sample),
-                    ("out_aux", out_aux), ("sample_aux", sample_aux)):
+                    ("out_aux", out_aux), ("sample_aux", sample_aux), ("scale_exp", scale_exp)):
         if m is not None:
             setattr(f, name, m.p_mat)
     _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))

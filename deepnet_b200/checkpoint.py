@@ -295,4 +295,4 @@ def load_into_rbm(engine, model, visible=None, hidden=None):
     engine.W.overwrite(np.asfortranarray(w))
     engine.bv.overwrite(np.asfortranarray(model.get_layer_param(visible).reshape(engine.V, 1)))
     engine.bh.overwrite(np.asfortranarray(model.get_layer_param(hidden).reshape(engine.H, 1)))
-    engine.W.split_bf16(engine.W_aux)
+    engine.refresh_weight_aux()

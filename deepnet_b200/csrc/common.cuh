@@ -1,6 +1,7 @@
 // Shared declarations of the b200mat library: the matrix handle, error codes, the
 // library stream, launch helpers and the counter-based random stream.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -149,6 +150,25 @@ __device__ __forceinline__ void split_aux(float x, uint16_t& lo16, uint16_t& b16
   lo16 = float_to_bf16(lo);
   b16 = float_to_bf16(x);
 }
+
+// The same storage can hold the SCALED HALF-PRECISION form of x instead: with xs = x * 2^e,
+//   plane 1: hi = fp16(xs)      plane 0: lo = fp16(xs - hi)
+// hi + lo carries 22 significant bits of xs, and
+//   a . b * 2^(ea + eb) ~= hi(a).hi(b) + hi(a).lo(b) + lo(a).hi(b)
+// is three half-precision products (K = 16 per tcgen05.mma, exact in the fp32 accumulator), no
+// TF32 term and no fp32 operand tile at all; what is left out (lo.lo and the rounding of lo) is
+// below 2^-21 of |a||b| per term.  e is chosen so that the largest |xs| stays well inside the
+// fp16 range (65504): a power of two, so the scaling is exact and the epilogue undoes it with
+// alpha * 2^-(ea + eb).  Entries more than 2^14 below the largest lose relative (not absolute)
+// precision in lo.
+__device__ __forceinline__ void split_f16(float x, float scale, uint16_t& lo, uint16_t& hi) {
+  const float xs = x * scale;
+  const __half h = __float2half_rn(xs);
+  const __half l = __float2half_rn(xs - __half2float(h));
+  hi = __half_as_ushort(h);
+  lo = __half_as_ushort(l);
+}
+__device__ __forceinline__ float f16_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 #endif
 

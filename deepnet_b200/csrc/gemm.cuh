@@ -24,7 +24,12 @@ constexpr int kMaxPass = 8;
 // The bfloat16 parts may instead be READ from an aux matrix of x kept in device memory (see
 // split_aux): deriving them costs shared-memory bandwidth (the fp32 tile is read and two tiles
 // are written, next to the tensor core's own operand reads), which bounds the big products.
-enum { kPartX = 0, kPartLo32 = 1, kPartLo16 = 2, kPartB16 = 3 };
+//   kPartF16Lo, kPartF16Hi  the two planes of an aux matrix in scaled half-precision form (see
+//                           split_f16): a . b * 2^(ea + eb) ~= hi.hi + hi.lo + lo.hi, read from memory only
+enum { kPartX = 0, kPartLo32 = 1, kPartLo16 = 2, kPartB16 = 3, kPartF16Lo = 4, kPartF16Hi = 5, kNumParts = 6 };
+inline bool part_is_16bit(int part) { return part >= kPartLo16; }
+inline bool part_is_f16(int part) { return part >= kPartF16Lo; }
+inline int part_plane(int part) { return (part == kPartB16 || part == kPartF16Hi) ? 1 : 0; }
 
 // A column-major fp32 matrix in device memory: element (r, c) at ptr[c * ld + r].
 // trans = 1 means the product uses its transpose.
@@ -51,6 +56,10 @@ struct GemmEpilogue {
   int activation;          // 0 identity, 1 logistic
   float* out;              // M x N result (may be null when only split/sample outputs are wanted)
   float* out_aux;          // aux matrix of the result, or null
+  int aux_f16;             // 1: aux outputs in scaled half-precision form (exponent aux_exp), 0: bfloat16 parts
+  int aux_exp;
+  const float* scale_exp;  // device scalar or null: the products carry a factor 2^(*scale_exp + scale_exp_const)
+  int scale_exp_const;     // (scaled half-precision operands), which the epilogue divides out of alpha
   float* sample;           // Bernoulli(result) draw, or null
   float* sample_aux;       // aux matrix of the draw (only plane 1 is written: a 0/1 value has no low part), or null
   int ldo;                 // leading dimension of every fp32 output
@@ -80,7 +89,7 @@ bool gemm_tc_supported(const GemmProblem& g);
 // `u` is the uniform of this element (only read when e.sample != null).
 __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc, int m, int n, float u) {
   const long idx = (long)n * e.ldo + m;
-  float v = e.alpha * acc;
+  float v = e.alpha * exp2f(-((e.scale_exp ? *e.scale_exp : 0.0f) + (float)e.scale_exp_const)) * acc;
   if (e.beta != 0.0f) v += e.beta * e.out[idx];
   if (e.bias) v += e.col_scale ? e.bias[m] * e.col_scale[n] : e.bias[m];
   if (e.activation == 1) v = sigmoid_accurate(v);
@@ -88,13 +97,17 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& e, float acc,
   const long aidx = (long)n * 2 * e.ld_aux + m;   // 16-bit word of plane 0
   if (e.out_aux) {
     uint16_t lo16, b16;
-    split_aux(v, lo16, b16);
+    if (e.aux_f16) split_f16(v, exp2f((float)e.aux_exp), lo16, b16);
+    else split_aux(v, lo16, b16);
     reinterpret_cast<uint16_t*>(e.out_aux)[aidx] = lo16;
     reinterpret_cast<uint16_t*>(e.out_aux)[aidx + e.ld_aux] = b16;
   }
   const float s = u < v ? 1.0f : 0.0f;
   if (e.sample) e.sample[idx] = s;
-  if (e.sample_aux) reinterpret_cast<uint16_t*>(e.sample_aux)[aidx + e.ld_aux] = s != 0.0f ? 0x3f80 : 0;
+  if (e.sample_aux) {
+    const uint16_t one = e.aux_f16 ? __half_as_ushort(__float2half_rn(exp2f((float)e.aux_exp))) : (uint16_t)0x3f80;
+    reinterpret_cast<uint16_t*>(e.sample_aux)[aidx + e.ld_aux] = s != 0.0f ? one : (uint16_t)0;
+  }
 }
 #endif
 

@@ -90,6 +90,33 @@ __global__ void __launch_bounds__(256) k_split_aux(const float* x, uint16_t* aux
   }
 }
 
+// aux matrix of x in scaled half-precision form (split_f16): scale = 2^(*exp_dev + exp_const).
+__global__ void __launch_bounds__(256) k_split_f16(const float* x, uint16_t* aux, int rows, int lda, long n, bool vec,
+                                                   const float* exp_dev, int exp_const) {
+  const float scale = exp2f((exp_dev ? *exp_dev : 0.0f) + (float)exp_const);
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  if (vec) {
+    for (long i = tid; i < (n >> 2); i += nth) {
+      const float4 v = reinterpret_cast<const float4*>(x)[i];
+      const long e = i << 2, c = e / rows, r = e - c * rows;
+      ushort4 l, h;
+      split_f16(v.x, scale, l.x, h.x); split_f16(v.y, scale, l.y, h.y);
+      split_f16(v.z, scale, l.z, h.z); split_f16(v.w, scale, l.w, h.w);
+      uint16_t* dst = aux + c * 2 * lda + r;
+      *reinterpret_cast<ushort4*>(dst) = l;
+      *reinterpret_cast<ushort4*>(dst + lda) = h;
+    }
+  } else {
+    for (long i = tid; i < n; i += nth) {
+      const long c = i / rows, r = i - c * rows;
+      uint16_t l, h;
+      split_f16(x[i], scale, l, h);
+      aux[c * 2 * lda + r] = l;
+      aux[c * 2 * lda + lda + r] = h;
+    }
+  }
+}
+
 // aux holds aux_rows(rows) floats per column.
 int launch_split_aux(const float* x, float* aux, int rows, long n) {
   if (n == 0) return 0;
@@ -123,11 +150,16 @@ __device__ __forceinline__ void update_one(float& w, float& d, float g, float su
   w = __fadd_rn(w, __fmul_rn(d, neps));
 }
 
-template <bool kHasGrad, bool kAux>
+// kAux: 0 no aux, 1 bfloat16 parts, 2 scaled half-precision form.  For 2, `scale` points at
+// {e_used, e_next, max |w| (bits), -}: the new w is split with 2^e_next and its largest magnitude
+// is gathered for the exponent after that (k_update_scale).
+template <bool kHasGrad, int kAux>
 __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff,
-                                                uint16_t* w_aux, int rows, int lda, long n, bool vec,
+                                                uint16_t* w_aux, float* scale, int rows, int lda, long n, bool vec,
                                                 float ninv_batch, float momentum, float neps, float l2, float l1) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  const float f16_scale = kAux == 2 ? exp2f(scale[1]) : 1.0f;
+  float wmax = 0.0f;
   if (vec) {   // n % 4 == 0, and with an aux rows % 4 == 0: four consecutive elements share a column
     for (long i = tid; i < (n >> 2); i += nth) {
       float4 W = reinterpret_cast<float4*>(w)[i];
@@ -145,7 +177,13 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       if (kAux) {
         const long e = i << 2, c = e / rows, r = e - c * rows;
         ushort4 L, B;
-        split_aux(W.x, L.x, B.x); split_aux(W.y, L.y, B.y); split_aux(W.z, L.z, B.z); split_aux(W.w, L.w, B.w);
+        if (kAux == 1) {
+          split_aux(W.x, L.x, B.x); split_aux(W.y, L.y, B.y); split_aux(W.z, L.z, B.z); split_aux(W.w, L.w, B.w);
+        } else {
+          split_f16(W.x, f16_scale, L.x, B.x); split_f16(W.y, f16_scale, L.y, B.y);
+          split_f16(W.z, f16_scale, L.z, B.z); split_f16(W.w, f16_scale, L.w, B.w);
+          wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(W.x), fabsf(W.y))), fmaxf(fabsf(W.z), fabsf(W.w)));
+        }
         uint16_t* dst = w_aux + c * 2 * lda + r;
         *reinterpret_cast<ushort4*>(dst) = L;
         *reinterpret_cast<ushort4*>(dst + lda) = B;
@@ -160,12 +198,31 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       if (kAux) {
         const long c = i / rows, r = i - c * rows;
         uint16_t L, B;
-        split_aux(W, L, B);
+        if (kAux == 1) {
+          split_aux(W, L, B);
+        } else {
+          split_f16(W, f16_scale, L, B);
+          wmax = fmaxf(wmax, fabsf(W));
+        }
         w_aux[c * 2 * lda + r] = L;
         w_aux[c * 2 * lda + lda + r] = B;
       }
     }
   }
+  if (kAux == 2) {   // non-negative floats order like their bit patterns
+    const unsigned m = __reduce_max_sync(0xffffffffu, __float_as_uint(wmax));
+    if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned*>(scale) + 2, m);
+  }
+}
+
+// After an update in scaled half-precision form: the exponent just used becomes the current one,
+// the next is chosen so that the largest |w| * 2^e stays at or below 2^13 (three binary orders
+// of headroom below the fp16 limit for the growth of one update), the maximum starts over.
+__global__ void k_update_scale(float* scale) {
+  scale[0] = scale[1];
+  const float m = __uint_as_float(reinterpret_cast<unsigned*>(scale)[2]);
+  if (m > 0.0f && m < 3.0e38f) scale[1] = floorf(log2f(8192.0f / m));
+  reinterpret_cast<unsigned*>(scale)[2] = 0u;
 }
 
 }  // namespace
@@ -194,6 +251,13 @@ struct b200_fused_gemm {
   cudamat* out_aux;    // aux matrix of the result, or null
   cudamat* sample;     // Bernoulli(result), or null
   cudamat* sample_aux; // aux matrix of the draw, or null
+  // scaled half-precision operands (parts kPartF16Lo / kPartF16Hi): the terms carry a factor
+  // 2^(*scale_exp + scale_exp_const) (scale_exp: 1 x 1 device matrix or null), divided out of alpha;
+  // aux_f16 != 0: out_aux / sample_aux are written in that form with exponent aux_exp
+  cudamat* scale_exp;
+  int scale_exp_const;
+  int aux_f16;
+  int aux_exp;
 };
 
 extern "C" {
@@ -226,6 +290,24 @@ int split_bf16(cudamat* x, cudamat* aux) {
   return launch_split_aux(x->data_device, aux->data_device, x->size[0], numel(x));
 }
 
+// aux = x in scaled half-precision form, scale 2^(*exp_dev + exp_const) (exp_dev: 1 x 1 device matrix or null).
+int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const) {
+  if (!x->on_device || !aux->on_device || (exp_dev && !exp_dev->on_device)) return ERROR_NOT_ON_DEVICE;
+  if (x->is_trans || aux->is_trans) return ERROR_TRANSPOSED;
+  if (!aux_shape_ok(aux, x)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const long n = numel(x);
+  if (n == 0) return 0;
+  const int rows = x->size[0];
+  const bool vec = (rows % 4 == 0) && ((((uintptr_t)x->data_device) & 15) == 0);
+  long blocks = ((vec ? n / 4 : n) + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  if (blocks < 1) blocks = 1;
+  k_split_f16<<<(int)blocks, 256, 0, stream()>>>(x->data_device, reinterpret_cast<uint16_t*>(aux->data_device), rows,
+                                                 aux_rows(rows), n, vec, exp_dev ? exp_dev->data_device : nullptr,
+                                                 exp_const);
+  return check_launch();
+}
+
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   if (f->npass <= 0 || f->npass > kMaxPass) return ERROR_UNSUPPORTED;
   GemmProblem g;
@@ -238,7 +320,10 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
     if (!a->on_device || !b->on_device) return ERROR_NOT_ON_DEVICE;
     if (lead(a) != g.M || nonlead(b) != g.N || nonlead(a) != lead(b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
     const int pa = f->pass[q].a_part, pb = f->pass[q].b_part;
-    if (pa < 0 || pa > 3 || pb < 0 || pb > 3 || (pa >= kPartLo16) != (pb >= kPartLo16)) return ERROR_UNSUPPORTED;
+    if (pa < 0 || pa >= kNumParts || pb < 0 || pb >= kNumParts) return ERROR_UNSUPPORTED;
+    // both operands of a term of one kind: fp32-wide, bfloat16, or scaled half precision (aux only)
+    if (part_is_16bit(pa) != part_is_16bit(pb) || part_is_f16(pa) != part_is_f16(pb)) return ERROR_UNSUPPORTED;
+    if (part_is_f16(pa) && (!f->pass[q].a_aux || !f->pass[q].b_aux)) return ERROR_UNSUPPORTED;
     const cudamat *xa = f->pass[q].a_aux, *xb = f->pass[q].b_aux;
     if ((xa && !aux_shape_ok(xa, a)) || (xb && !aux_shape_ok(xb, b))) return ERROR_INCOMPATIBLE_DIMENSIONS;
     g.pass[q].a = operand(a, pa, xa);
@@ -255,6 +340,14 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   e.out = e.out_aux = e.sample = e.sample_aux = nullptr;
   e.ldo = g.M;
   e.ld_aux = aux_rows(g.M);
+  e.aux_f16 = f->aux_f16;
+  e.aux_exp = f->aux_exp;
+  e.scale_exp = nullptr;
+  e.scale_exp_const = f->scale_exp_const;
+  if (f->scale_exp) {
+    if (!f->scale_exp->on_device) return ERROR_NOT_ON_DEVICE;
+    e.scale_exp = f->scale_exp->data_device;
+  }
   e.col0 = rng_col0();
   cudamat* outs[4] = {f->out, f->out_aux, f->sample, f->sample_aux};
   for (int i = 0; i < 4; i++) {
@@ -308,6 +401,8 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
   e.out_aux = e.sample = e.sample_aux = nullptr;
   e.ldo = m;
   e.ld_aux = aux_rows(m);
+  e.aux_f16 = e.aux_exp = e.scale_exp_const = 0;
+  e.scale_exp = nullptr;
   e.col0 = 0;
   e.key = make_philox_key(0, 0);
   g.npass = 1;
@@ -345,15 +440,18 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 
 // deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass over the parameter:
 //   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
-//   w -= eps * delta; grad = 0; and, when w_aux is given, the aux matrix of the new w.
+//   w -= eps * delta; grad = 0; and, when w_aux is given, the aux matrix of the new w: its
+//   bfloat16 parts, or with w_scale (1 x 4 device matrix {exponent in use, next exponent, max |w|
+//   bits, -}) its scaled half-precision form.
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
 // without grad and aux; +8 with grad, +4 with w_aux.
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, float inv_batch,
-                    float momentum, float eps, float l2, float l1) {
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                    float inv_batch, float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
   if (!same_shape(w, delta) || !same_shape(w, suff)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (grad && (!grad->on_device || !same_shape(w, grad))) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (w_aux && (w->is_trans || !aux_shape_ok(w_aux, w))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (w_scale && (!w_aux || !w_scale->on_device || numel(w_scale) < 4)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const long n = numel(w);
   if (n == 0) return 0;
   uintptr_t bits = (uintptr_t)w->data_device | (uintptr_t)delta->data_device | (uintptr_t)suff->data_device;
@@ -366,14 +464,24 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
   if (blocks < 1) blocks = 1;
   float* gp = grad ? grad->data_device : nullptr;
   uint16_t* ap = w_aux ? reinterpret_cast<uint16_t*>(w_aux->data_device) : nullptr;
+  float* sp = w_scale ? w_scale->data_device : nullptr;
+  const int mode = !w_aux ? 0 : (w_scale ? 2 : 1);
 #define LAUNCH_UPDATE(G, A)                                                                                       \
   k_update<G, A><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, ap, \
-                                                    rows, aux_rows(rows), n, vec, -inv_batch, momentum, -eps, l2, l1)
-  if (grad && w_aux) LAUNCH_UPDATE(true, true);
-  else if (grad) LAUNCH_UPDATE(true, false);
-  else if (w_aux) LAUNCH_UPDATE(false, true);
-  else LAUNCH_UPDATE(false, false);
+                                                    sp, rows, aux_rows(rows), n, vec, -inv_batch, momentum, -eps, l2, l1)
+  if (grad) {
+    if (mode == 2) LAUNCH_UPDATE(true, 2);
+    else if (mode == 1) LAUNCH_UPDATE(true, 1);
+    else LAUNCH_UPDATE(true, 0);
+  } else {
+    if (mode == 2) LAUNCH_UPDATE(false, 2);
+    else if (mode == 1) LAUNCH_UPDATE(false, 1);
+    else LAUNCH_UPDATE(false, 0);
+  }
 #undef LAUNCH_UPDATE
+  int err = check_launch();
+  if (err || mode != 2) return err;
+  k_update_scale<<<1, 1, 0, stream()>>>(sp);
   return check_launch();
 }
 

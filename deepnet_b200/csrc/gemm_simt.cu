@@ -16,9 +16,11 @@ __device__ __forceinline__ float as_operand(float x, int tf32) {
 // Element (r, c) of the stored matrix, as the part the term reads.
 __device__ __forceinline__ float element(const GemmOperand& o, int r, int c, int tf32) {
   if (o.part >= kPartLo16 && o.aux) {
-    const long w = (long)c * 2 * o.lda + (o.part == kPartB16 ? o.lda : 0) + r;
-    return bf16_to_float(reinterpret_cast<const uint16_t*>(o.aux)[w]);
+    const long w = (long)c * 2 * o.lda + ((o.part == kPartB16 || o.part == kPartF16Hi) ? o.lda : 0) + r;
+    const uint16_t bits = reinterpret_cast<const uint16_t*>(o.aux)[w];
+    return o.part >= kPartF16Lo ? f16_to_float(bits) : bf16_to_float(bits);
   }
+  if (o.part >= kPartF16Lo) return 0.0f;   // scaled half-precision parts exist in aux matrices only
   const float x = o.ptr[(long)c * o.ld + r];
   if (o.part == kPartX) return as_operand(x, tf32);
   if (o.part == kPartB16) return bf16_to_float(float_to_bf16(x));

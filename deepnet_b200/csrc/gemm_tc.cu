@@ -660,7 +660,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           for (int i = 0; i < gr.nmma; i++) mask |= (gr.mma[i].f16 != 0 ? 1 : 0) << i;
           using std::integral_constant;
           const int shape = gr.nmma * 16 + mask;
-          if (shape == 3 * 16 + 3) run_group(integral_constant<int, 3>{}, integral_constant<int, 3>{});        // lo16.b16, b16.lo16, x.x
+          if (shape == 3 * 16 + 7) run_group(integral_constant<int, 3>{}, integral_constant<int, 7>{});        // three half-precision terms
+          else if (shape == 2 * 16 + 3) run_group(integral_constant<int, 2>{}, integral_constant<int, 3>{});   // two
+          else if (shape == 3 * 16 + 3) run_group(integral_constant<int, 3>{}, integral_constant<int, 3>{});   // lo16.b16, b16.lo16, x.x
           else if (shape == 2 * 16 + 1) run_group(integral_constant<int, 2>{}, integral_constant<int, 1>{});   // lo16.b16, x.x
           else if (shape == 3 * 16) run_group(integral_constant<int, 3>{}, integral_constant<int, 0>{});       // three TF32 terms
           else if (shape == 2 * 16) run_group(integral_constant<int, 2>{}, integral_constant<int, 0>{});
@@ -785,7 +787,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     uint32_t chunk = 0;
     // A private copy: read through the parameter block, every field would have to be
     // reloaded after each store (the stores could alias it as far as the compiler knows).
-    const GemmEpilogue e = p.epi;
+    GemmEpilogue e = p.epi;
+    // scaled half-precision operands: the accumulator carries 2^(exponent sum); a power of two, exact
+    e.alpha *= exp2f(-((e.scale_exp ? *e.scale_exp : 0.0f) + (float)e.scale_exp_const));
+    const float aux_scale = exp2f((float)e.aux_exp);
+    const uint16_t aux_one = e.aux_f16 ? __half_as_ushort(__float2half_rn(aux_scale)) : (uint16_t)0x3f80;
     const int pM = p.M, pN = p.N;
     const int nchunks = (total_k_iters + kChunkIters - 1) / kChunkIters;
     bool ok = true;
@@ -899,16 +905,21 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             const uint32_t a32 = buf + (uint32_t)(j * BM + row) * 4u, a16 = buf + (uint32_t)(j * BM + row) * 2u;
             if (has_out) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32), "f"(x[j]) : "memory");
             if (has_aux) {
-              const float lo = tf32_rest(x[j]);
-              const uint32_t lo16 = pack_bf16(lo, 0.0f), b16 = pack_bf16(x[j], 0.0f);
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffLo), "h"((uint16_t)lo16) : "memory");
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffB), "h"((uint16_t)b16) : "memory");
+              uint16_t lo16, b16;
+              if (e.aux_f16) {
+                split_f16(x[j], aux_scale, lo16, b16);
+              } else {
+                lo16 = (uint16_t)pack_bf16(tf32_rest(x[j]), 0.0f);
+                b16 = (uint16_t)pack_bf16(x[j], 0.0f);
+              }
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffLo), "h"(lo16) : "memory");
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffB), "h"(b16) : "memory");
             }
             if (draw) {
               const bool on = word_to_uniform(pick_word(w, j)) < x[j];
               if (has_smp) asm volatile("st.shared.f32 [%0], %1;" ::"r"(a32 + kOffSmp), "f"(on ? 1.0f : 0.0f) : "memory");
               if (has_smp_aux)
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffSmpB), "h"((uint16_t)(on ? 0x3f80 : 0)) : "memory");
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(a16 + kOffSmpB), "h"((uint16_t)(on ? aux_one : 0)) : "memory");
             }
           }
           fence_async_smem();                       // generic-proxy writes visible to the TMA engine
@@ -1140,7 +1151,8 @@ bool gemm_tc_supported(const GemmProblem& g) {
   for (int q = 0; q < g.npass; q++) {
     const GemmPass& ps = g.pass[q];
     if (!tma_ok(ps.a) || !tma_ok(ps.b) || ps.k <= 0) return false;
-    if ((ps.a.part >= kPartLo16) != (ps.b.part >= kPartLo16)) return false;
+    if (part_is_16bit(ps.a.part) != part_is_16bit(ps.b.part) || part_is_f16(ps.a.part) != part_is_f16(ps.b.part)) return false;
+    if (part_is_f16(ps.a.part) && (!ps.a.aux || !ps.b.aux)) return false;
   }
   const GemmEpilogue& e = g.epi;
   if ((e.sample || e.sample_aux) && (e.col0 & 3)) return false;
@@ -1209,13 +1221,13 @@ int gemm_tc(const GemmProblem& g) {
     const GemmOperand* src[2] = {&f.a, &f.b};
     const int rows[2] = {BM, BN_LOCAL}, extent[2] = {g.M, g.N};
     // which parts the group's terms read
-    bool want[2][4] = {{false, false, false, false}, {false, false, false, false}};
+    bool want[2][kNumParts] = {};
     for (int i = 0; i < tg.nmma; i++) {
       want[0][g.pass[q0 + i].a.part] = true;
       want[1][g.pass[q0 + i].b.part] = true;
     }
     uint32_t off = 0;
-    int tile_of[2][4];
+    int tile_of[2][kNumParts];
     int ntiles = 0;
     tg.nload = tg.nconv = 0;
     auto add_load = [&](int o, const void* ptr, uint64_t ld, bool bf16) {
@@ -1246,9 +1258,9 @@ int gemm_tc(const GemmProblem& g) {
     }
     for (int o = 0; o < 2; o++) {   // bfloat16 parts read from the operand's aux matrix
       if (!src[o]->aux) continue;
-      for (int part = kPartLo16; part <= kPartB16; part++) {
+      for (int part = kPartLo16; part < kNumParts; part++) {
         if (!want[o][part]) continue;
-        const uint16_t* plane = reinterpret_cast<const uint16_t*>(src[o]->aux) + (part == kPartB16 ? src[o]->lda : 0);
+        const uint16_t* plane = reinterpret_cast<const uint16_t*>(src[o]->aux) + (part_plane(part) ? src[o]->lda : 0);
         if (!add_load(o, plane, (uint64_t)(2 * src[o]->lda), true))
           return set_error("cuTensorMapEncodeTiled failed for an aux plane");
         tile_of[o][part] = ntiles;
@@ -1280,11 +1292,11 @@ int gemm_tc(const GemmProblem& g) {
       TcMma& m = tg.mma[i];
       m.a = tile_of[0][ps.a.part];
       m.b = tile_of[1][ps.b.part];
-      m.f16 = ps.a.part >= kPartLo16;
+      m.f16 = part_is_16bit(ps.a.part);
       // instruction descriptor: D fp32 (bit 4), A and B format at bits 7 and 10 (TF32 = 2 for
-      // kind::tf32, BF16 = 1 for kind::f16), negate A (bit 13), A / B MN-major (bits 15 / 16),
-      // N >> 3 at bit 17, M >> 4 at bit 24
-      const uint32_t fmt = m.f16 ? 1u : 2u;
+      // kind::tf32; BF16 = 1, F16 = 0 for kind::f16), negate A (bit 13), A / B MN-major (bits
+      // 15 / 16), N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t fmt = part_is_f16(ps.a.part) ? 0u : (m.f16 ? 1u : 2u);
       m.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((ps.negate ? 1u : 0u) << 13) | ((mn[0] ? 1u : 0u) << 15) |
                 ((mn[1] ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((two ? 2 * BM : BM) >> 4) << 24);
     }

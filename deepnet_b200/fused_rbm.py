@@ -56,6 +56,15 @@ class FusedRBM(object):
         # latency, where the extra split launch and the wider epilogue cost more than they save
         env = os.environ.get("B200_RBM_STATE_AUX")
         self.state_aux = (V * H * batchsize >= 1 << 32) if env is None else env != "0"
+        # With 0/1 data and logistic units every operand's range is known, and the big products run
+        # on the scaled half-precision form of W and of the states (three fp16 terms, no TF32 term,
+        # no fp32 operand read): W * 2^e with e kept by the update kernel, states * 2^14.
+        self.f16 = (self.state_aux and binary_data and visible == LOGISTIC
+                    and os.environ.get("B200_RBM_F16", "1") != "0")
+        if self.f16:
+            self.W_scale = cm.f16_scale_state(float(np.abs(w).max()))
+            self.W_exp = self.W_scale.slice(0, 1)
+            self.W.split_f16(self.W_aux, exp_dev=self.W_exp)
         self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
         self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
         self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
@@ -69,6 +78,7 @@ class FusedRBM(object):
         self.h_pos, self.h_samp, self.h_samp_aux = z(H, B), z(H, B), za(H, B)
         self.v_neg, self.v_neg_aux, self.h_neg = z(V, B), za(V, B), z(H, B)
         self.data_aux = za(V, B)
+        self.h_pos_aux, self.h_neg_aux = (za(H, B), za(H, B)) if getattr(self, "f16", False) else (None, None)
         self.loss_acc = z(1, 1)
         if visible == REPLICATED_SOFTMAX:
             # document lengths, length-normalised visible states (the statistics use state / NN,
@@ -111,6 +121,8 @@ class FusedRBM(object):
         lib = cm._lib
         exact = self.binary_data                  # 0/1 data have no low part
         # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
+        if self.f16:
+            return self._train_f16(step, data)
         sa = self.state_aux
         if sa:
             self._op("split", 0, 2 * vb, v0.split_bf16, self.data_aux)
@@ -154,6 +166,59 @@ class FusedRBM(object):
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
         self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
                  l1=l1, w_aux=Wa)
+
+    def _train_f16(self, step, data):
+        """The binary-data, logistic-units CD-k update with every big product on scaled
+        half-precision operands: states and data as x * 2^14 = hi + lo in fp16 (written by the
+        producing epilogue, `split_f16` for the data), W as W * 2^e (written by the update kernel,
+        which also keeps e); a product is hi.lo + lo.hi + hi.hi, 0/1 operands need hi only."""
+        cm, k = self.cm, self.hyp.gibbs_steps
+        V, H, B = self.V, self.H, self.B
+        W, Wa, We, F = self.W, self.W_aux, self.W_exp, cm.f16_passes
+        E = 14                                     # exponent of every state: values in [0, 1]
+        v0, v0a = data, self.data_aux
+        gf = 2.0 * V * H * B
+        vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
+        lib = cm._lib
+        act = dict(scale_exp=We, scale_exp_const=E, aux_f16=True, aux_exp=E)
+        self._op("split", 0, 2 * vb, v0.split_f16, v0a, None, E)
+        # positive phase: h0 = sigmoid(W' v0 + b_h), its Bernoulli sample, and the parts of both
+        self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, F(W.T, Wa, v0, v0a, exact_b=True), out=self.h_pos,
+                 out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
+                 **act)
+        for i in range(k):
+            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, F(W, Wa, self.h_samp, self.h_samp_aux, exact_b=True),
+                     out=self.v_neg, out_aux=self.v_neg_aux, bias=self.bv, activation=1, **act)
+            if i == 0:
+                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
+                                                                                self.loss_acc.p_mat)))
+                self.kernel_launches += 1
+            last = i == k - 1
+            # the hidden means (and their parts) are only read after the last step, by the statistics
+            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, F(W.T, Wa, self.v_neg, self.v_neg_aux),
+                     out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
+                     sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1, **act)
+        pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
+        neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
+        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W, scale_exp_const=2 * E)
+        self._op("row_sum", 0, vb, v0.sum, axis=1, target=self.suff_bv)
+        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_neg, axis=1, mult=-1.0)
+        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
+        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
+        self.kernel_launches += 4
+        if self.world_size > 1:
+            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
+        inv_b = 1.0 / (self.B * self.world_size)
+        mom, eps = self._sched.GetMomentumAndEpsilon(step)
+        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
+        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
+        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
+        eh = self.ehyp
+        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
+        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
+        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
+                 l1=l1, w_aux=Wa, w_scale=self.W_scale)
+        self.kernel_launches += 1                  # the exponent bookkeeping launch
 
     def _train_replicated_softmax(self, step, data):
         """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:
@@ -208,12 +273,23 @@ class FusedRBM(object):
         self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
                  l1=l1, w_aux=Wa)
 
+    def refresh_weight_aux(self):
+        """Rebuilds the 16-bit parts of W after W was written from outside (a loaded checkpoint)."""
+        if self.f16:
+            w = np.array(self.W.asarray())
+            self.W_scale = self.cm.f16_scale_state(float(np.abs(w).max()))
+            self.W_exp = self.W_scale.slice(0, 1)
+            self.W.split_f16(self.W_aux, exp_dev=self.W_exp)
+        else:
+            self.W.split_bf16(self.W_aux)
+
     def Inference(self, data, input_recon=False):
         """Hidden representation of `data` (V x cases device matrix), minibatch by minibatch:
         the inference-only positive phase of deepnet/dbm.py:340-398 (extract_rbm_representation.py)
         as one fused product per minibatch.  Returns (cases x H) host array, and with input_recon
         also the summed squared error of the input reconstructed from the hidden means."""
-        cm, B, W, Wa, P = self.cm, self.B, self.W, self.W_aux, self.cm.split_passes
+        cm, B, W, P = self.cm, self.B, self.W, self.cm.split_passes
+        Wa = None if self.f16 else self.W_aux     # the bfloat16 parts exist only in that form of the aux
         n = data.shape[1] // B
         rep = np.zeros((n * B, self.H), np.float32)
         err = 0.0

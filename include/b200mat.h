@@ -166,7 +166,8 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha);
  * a . b ~= lo32(a).x(b) + x(a).lo32(b) + x(a).x(b)       three TF32 products, 2^-20 per term, or
  * a . b ~= lo16(a).b16(b) + b16(a).lo16(b) + x(a).x(b)   one TF32 + two bfloat16 products (twice
  *                                                        the TF32 rate), 2^-18 per term. */
-enum { B200_PART_X = 0, B200_PART_LO32 = 1, B200_PART_LO16 = 2, B200_PART_B16 = 3 };
+enum { B200_PART_X = 0, B200_PART_LO32 = 1, B200_PART_LO16 = 2, B200_PART_B16 = 3,
+       B200_PART_F16LO = 4, B200_PART_F16HI = 5 };
 
 /* The bfloat16 parts of a rows x cols fp32 matrix x kept in device memory ("aux matrix"), for
  * the big products: deriving the parts in the kernel costs shared-memory bandwidth next to the
@@ -175,6 +176,14 @@ enum { B200_PART_X = 0, B200_PART_LO32 = 1, B200_PART_LO16 = 2, B200_PART_B16 = 
  * of plane 1, bf16(x) (the first `rows` of each in use).  An aux handle is an ordinary cudamat
  * of lda x cols. */
 int split_bf16(cudamat* x, cudamat* aux);
+
+/* The same storage in SCALED HALF-PRECISION form: with xs = x * 2^e (e = *exp_dev + exp_const;
+ * exp_dev a 1 x 1 device matrix or NULL), plane 1 = hi = fp16(xs), plane 0 = lo = fp16(xs - hi).
+ *   a . b * 2^(ea + eb) ~= hi(a).lo(b) + lo(a).hi(b) + hi(a).hi(b)      (B200_PART_F16HI / _F16LO)
+ * is three half-precision products, no TF32 term and no fp32 operand read, below 2^-21 of
+ * |a||b| per term; the caller names the exponent sum in b200_fused_gemm and the kernel divides
+ * it out.  e must keep the largest |xs| inside the fp16 range (65504). */
+int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const);
 
 /* One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
  * Both parts of a term are fp32-wide (X, LO32) or both bfloat16 (LO16, B16).  a_aux / b_aux:
@@ -203,6 +212,10 @@ typedef struct b200_fused_gemm {
   cudamat* out_aux;      /* aux matrix of the result, or NULL */
   cudamat* sample;       /* Bernoulli(result): consumes one sampling call, or NULL */
   cudamat* sample_aux;   /* aux matrix of the draw (plane 1 only: a 0/1 value has no low part), or NULL */
+  cudamat* scale_exp;    /* scaled half-precision operands: the terms carry 2^(*scale_exp + scale_exp_const), */
+  int scale_exp_const;   /*   divided out by the kernel (scale_exp: 1 x 1 device matrix or NULL) */
+  int aux_f16;           /* != 0: out_aux / sample_aux in scaled half-precision form ... */
+  int aux_exp;           /*   ... with this exponent */
 } b200_fused_gemm;
 int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f);
 
@@ -211,9 +224,11 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
 
 /* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass over the parameter:
  * grad += -inv_batch * suff; delta = momentum*delta + l2*w + l1*sign(w) + grad;
- * w -= eps*delta; grad = 0; w_aux = aux matrix of the new w.  grad, w_aux may be NULL. */
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, float inv_batch,
-                    float momentum, float eps, float l2, float l1);
+ * w -= eps*delta; grad = 0; w_aux = aux matrix of the new w: its bfloat16 parts, or with w_scale
+ * (1 x 4 device matrix {exponent in use, exponent of the next update, max |w| bits, -}, kept by
+ * this call) its scaled half-precision form.  grad, w_aux, w_scale may be NULL. */
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                    float inv_batch, float momentum, float eps, float l2, float l1);
 
 /* Has no counterpart in the reference.  add_sum_by_axis for callers that must never reach
  * cudaMalloc (a host that gave the whole device to its own memory pool, or a loop that cannot

@@ -66,8 +66,14 @@ def test_replicated_softmax_step_matches_oracle(cm, oracle):
     assert relerr(get(mg.edge[0].params["weight"]), get(mo.edge[0].params["weight"])) < TOL
 
 
-@pytest.mark.parametrize("config,scale,cases", [(0, 0.25, 300), (1, 0.0625, 768), (0, 1.0, 200)])
-def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases):
+@pytest.mark.parametrize("config,scale,cases,form", [(0, 0.25, 300, "derived"), (1, 0.0625, 768, "derived"),
+                                                     (0, 1.0, 200, "derived"), (0, 0.25, 300, "bf16 aux"),
+                                                     (0, 0.25, 300, "f16"), (0, 1.0, 200, "f16")])
+def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases, form, monkeypatch):
+    # the three forms the products' operands take: parts derived in the kernel (small models),
+    # bfloat16 parts from aux matrices, scaled half precision (what the big binary model runs on)
+    monkeypatch.setenv("B200_RBM_STATE_AUX", "0" if form == "derived" else "1")
+    monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     cfg = configs.build(config, cases=cases, dims_scale=scale)
     B, steps = cfg["batchsize"], 3
     mo, lo = run_driver(oracle, cfg, cases, steps)
@@ -75,6 +81,7 @@ def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases):
     eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
                    edge_hyperparams=cfg["edges"][0].get("hyperparams"), visible=cfg["layers"][0]["activation"],
                    binary_data=(config != 1), seed=cfg["seed"])
+    assert eng.f16 == (form == "f16") and eng.state_aux == (form != "derived")
     data = cm.CUDAMatrix(cfg["data"])
     lg = []
     for step in range(steps):

@@ -182,6 +182,130 @@ def test_bfloat16_parts_read_from_aux_matrices(cm, path, ta, tb, m, n, k):
     assert cm.read_status() == 0
 
 
+def f16_planes(aux):
+    """(lo, hi) planes of an aux matrix in scaled half-precision form, as float32."""
+    raw = np.array(aux.asarray(), copy=True)
+    words = np.ascontiguousarray(raw.T).view(np.uint16)
+    lda = raw.shape[0]
+    f = lambda w: np.ascontiguousarray(w).view(np.float16).astype(np.float32).T[:aux.rows]
+    return f(words[:, :lda]), f(words[:, lda:])
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(500, 300, 784), (260, 36, 40), (1024, 512, 4096)])
+def test_scaled_half_precision_product_in_all_layouts(cm, path, ta, tb, m, n, k):
+    """x * 2^e = hi + lo in fp16: hi.lo + lo.hi + hi.hi, divided by 2^(ea + eb), is the product to
+    fp32 grade; the planes hold exactly the fp16 roundings."""
+    rng = np.random.default_rng(16)
+    A = (rng.standard_normal((m, k)) * 0.03).astype(np.float32)       # weights-like
+    B = rng.random((k, n)).astype(np.float32)                          # probabilities-like
+    cm.set_gemm_path(path)
+    sa, sb = (A.T if ta else A), (B.T if tb else B)
+    ga, gb = cm.CUDAMatrix(np.asfortranarray(sa)), cm.CUDAMatrix(np.asfortranarray(sb))
+    scale = cm.f16_scale_state(np.abs(A).max())
+    ea, eb = float(get(scale)[0, 0]), 14
+    assert np.abs(A).max() * 2.0 ** ea <= 8192 < np.abs(A).max() * 2.0 ** (ea + 1)
+    xa = ga.split_f16(cm.empty_aux(sa.shape), exp_dev=scale.slice(0, 1))
+    xb = gb.split_f16(cm.empty_aux(sb.shape), exp_const=eb)
+    lo, hi = f16_planes(xa)
+    want_hi = (sa * np.float32(2.0 ** ea)).astype(np.float16)
+    np.testing.assert_array_equal(hi, want_hi.astype(np.float32))
+    np.testing.assert_array_equal(lo, (sa * np.float32(2.0 ** ea) - want_hi.astype(np.float32)).astype(np.float16).astype(np.float32))
+    oa, ob = (ga.T if ta else ga), (gb.T if tb else gb)
+    out = cm.empty((m, n))
+    cm.fused_gemm(cm.f16_passes(oa, xa, ob, xb), out=out, scale_exp=scale.slice(0, 1), scale_exp_const=eb)
+    want = A.astype(np.float64) @ B.astype(np.float64)
+    assert relerr(get(out), want) < (1e-6 if path == 1 else 1e-5)
+    # a 0/1 operand needs its hi plane only
+    Bb = (rng.random((k, n)) < 0.3).astype(np.float32)
+    sbb = Bb.T if tb else Bb
+    gbb = cm.CUDAMatrix(np.asfortranarray(sbb))
+    xbb = gbb.split_f16(cm.empty_aux(sbb.shape), exp_const=eb)
+    cm.fused_gemm(cm.f16_passes(oa, xa, gbb.T if tb else gbb, xbb, exact_b=True), out=out,
+                  scale_exp=scale.slice(0, 1), scale_exp_const=eb)
+    assert relerr(get(out), A.astype(np.float64) @ Bb.astype(np.float64)) < (1e-6 if path == 1 else 1e-5)
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_scaled_half_precision_difference_of_products(cm, path):
+    """Positive minus negative statistics: two nearly equal products subtracted in one accumulator."""
+    rng = np.random.default_rng(17)
+    M, N, K = 512, 384, 1024
+    sig = lambda x: 1 / (1 + np.exp(-x))
+    Ap = sig(rng.standard_normal((M, K)) * 0.3).astype(np.float32)
+    Bp = sig(rng.standard_normal((K, N)) * 0.3).astype(np.float32)
+    An = (Ap + rng.standard_normal((M, K)).astype(np.float32) * 0.02).clip(0, 1).astype(np.float32)
+    Bn = (Bp + rng.standard_normal((K, N)).astype(np.float32) * 0.02).clip(0, 1).astype(np.float32)
+    cm.set_gemm_path(path)
+    mats = [cm.CUDAMatrix(x) for x in (Ap, Bp, An, Bn)]
+    auxs = [g.split_f16(cm.empty_aux(g.shape), exp_const=14) for g in mats]
+    out = cm.empty((M, N))
+    P = cm.f16_passes
+    cm.fused_gemm(P(mats[0], auxs[0], mats[1], auxs[1]) + P(mats[2], auxs[2], mats[3], auxs[3], negate=1), out=out,
+                  scale_exp_const=28)
+    want = Ap.astype(np.float64) @ Bp.astype(np.float64) - An.astype(np.float64) @ Bn.astype(np.float64)
+    # each product is ~256, their difference ~1: 5e-5 of the difference is 2e-7 of the products,
+    # the grade of an fp32 product (numpy's float32 matmul is at 2e-4 here)
+    f32 = Ap @ Bp - An @ Bn
+    # (the CUDA-core kernel adds the 1024 same-sign terms of each product one by one in fp32)
+    assert relerr(get(out), want) < (min(1e-4, relerr(f32, want)) if path == 1 else 3e-3)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(500, 100, 784), (1024, 512, 2048)])
+def test_fused_epilogue_writes_scaled_half_precision_aux(cm, oracle, path, m, n, k):
+    rng = np.random.default_rng(18)
+    W = (rng.standard_normal((k, m)) * 0.1).astype(np.float32)
+    X = (rng.random((k, n)) < 0.3).astype(np.float32)
+    b = rng.standard_normal((m, 1)).astype(np.float32)
+    cm.set_gemm_path(path)
+    cm.CUDAMatrix.init_random(99)
+    oracle.EigenMatrix.init_random(99)
+    w, x, bias = cm.CUDAMatrix(W), cm.CUDAMatrix(X), cm.CUDAMatrix(b)
+    scale = cm.f16_scale_state(np.abs(W).max())
+    w_aux = w.split_f16(cm.empty_aux(W.shape), exp_dev=scale.slice(0, 1))
+    x_aux = x.split_f16(cm.empty_aux(X.shape), exp_const=14)
+    out, smp = cm.empty((m, n)), cm.empty((m, n))
+    out_aux, smp_aux = cm.empty_aux((m, n)), cm.empty_aux((m, n))
+    cm.fused_gemm(cm.f16_passes(w.T, w_aux, x, x_aux, exact_b=True), out=out, sample=smp, out_aux=out_aux,
+                  sample_aux=smp_aux, bias=bias, activation=1, scale_exp=scale.slice(0, 1), scale_exp_const=14,
+                  aux_f16=True, aux_exp=14)
+    got = get(out)
+    assert relerr(got, 1 / (1 + np.exp(-(W.astype(np.float64).T @ X + b)))) < TOL
+    lo, hi = f16_planes(out_aux)
+    want_hi = (got * np.float32(16384)).astype(np.float16)
+    np.testing.assert_array_equal(hi, want_hi.astype(np.float32))
+    np.testing.assert_array_equal(lo, (got * np.float32(16384) - want_hi.astype(np.float32)).astype(np.float16).astype(np.float32))
+    want_s = get(oracle.EigenMatrix(got).sample_bernoulli(target=oracle.empty((m, n))))
+    np.testing.assert_array_equal(get(smp), want_s)
+    np.testing.assert_array_equal(f16_planes(smp_aux)[1], want_s * 16384)
+    assert cm.read_status() == 0
+
+
+def test_momentum_update_keeps_the_scaled_half_precision_form(cm):
+    rng = np.random.default_rng(19)
+    shape = (256, 96)
+    w0 = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    w, d = cm.CUDAMatrix(w0), cm.CUDAMatrix(np.zeros(shape, np.float32))
+    scale = cm.f16_scale_state(np.abs(w0).max())
+    aux = w.split_f16(cm.empty_aux(shape), exp_dev=scale.slice(0, 1))
+    for step in range(3):
+        s = cm.CUDAMatrix((rng.standard_normal(shape) * (5.0 if step == 1 else 0.1)).astype(np.float32))
+        e_next = float(get(scale)[0, 1])
+        w.momentum_update(d, None, s, 1.0 / 10, 0.5, 0.1, w_aux=aux, w_scale=scale)
+        now = get(w)
+        st = get(scale)
+        assert st[0, 0] == e_next                       # the aux was written with the announced exponent
+        lo, hi = f16_planes(aux)
+        want_hi = (now * np.float32(2.0 ** e_next)).astype(np.float16)
+        np.testing.assert_array_equal(hi, want_hi.astype(np.float32))
+        np.testing.assert_array_equal(lo, (now * np.float32(2.0 ** e_next) - want_hi.astype(np.float32)).astype(np.float16).astype(np.float32))
+        assert st[0, 1] == np.floor(np.log2(8192.0 / np.abs(now).max()))   # and the next one follows the new maximum
+        assert np.isfinite(hi).all()
+
+
 @pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("m,n,k", [(500, 100, 784), (128, 256, 64), (260, 36, 40), (1024, 512, 2048)])
 def test_fused_epilogue_bias_logistic_sample(cm, oracle, path, m, n, k):
