@@ -1319,7 +1319,7 @@ int gemm_tc(const GemmProblem& g) {
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
     epi = kEpiPlain;
-  } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample)) {
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample || e.out_aux)) {
     if (e.activation == 1 && e.sample) epi = kEpiSigSample;
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;

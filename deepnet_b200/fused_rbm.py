@@ -187,13 +187,16 @@ class FusedRBM(object):
                  out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                  **act)
         for i in range(k):
+            last = i == k - 1
+            # the fp32 visible means are read by the error of the first reconstruction and by the
+            # statistics after the last step; in between only their half-precision form is
             self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, F(W, Wa, self.h_samp, self.h_samp_aux, exact_b=True),
-                     out=self.v_neg, out_aux=self.v_neg_aux, bias=self.bv, activation=1, **act)
+                     out=self.v_neg if (i == 0 or last) else None, out_aux=self.v_neg_aux, bias=self.bv, activation=1,
+                     **act)
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1
-            last = i == k - 1
             # the hidden means (and their parts) are only read after the last step, by the statistics
             self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, F(W.T, Wa, self.v_neg, self.v_neg_aux),
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
