@@ -100,6 +100,8 @@ struct TcParams {
   int num_stages;          // ring depth
   uint32_t stage_bytes;    // ring pitch
   int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
+  int direct;              // 1: no group derives anything: the copies of both CTAs complete on the leader's `ready`
+                           //    barrier and the converter warps stay out of the way
   GemmEpilogue epi;
   int out_map[kOutArrays];   // tensor maps (indices into maps) of the outputs stored by TMA; -1 = absent
   int* status;
@@ -223,6 +225,16 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-window addresses carry the CTA's rank within the pair in bit 24; clearing it names the
+// same location in the pair's leader (rank 0).
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+// Loads into THIS CTA's shared memory, completes the transaction on the LEADER's mbarrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar & kPeerBitMask));
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
@@ -398,7 +410,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   const uint32_t bar_base = out_stage_base + kOutStageBytes;
   // barrier layout (8 bytes each): full[kMaxStages], empty[kMaxStages], ready[kMaxStages], tmem_full[2], tmem_empty[2]
   //   full  : this CTA's TMA copies of the stage have landed            (producer -> converters)
-  //   ready : the derived tiles of the stage are written, in both CTAs   (converters -> issuer of the leader)
+  //   ready : the derived tiles of the stage are written, in both CTAs   (converters -> issuer of the leader);
+  //           when nothing is derived (p.direct) the copies of both CTAs complete on it themselves
   //   empty : the MMAs that read the stage are done                      (issuer -> producer, both CTAs)
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
@@ -425,7 +438,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     for (int s = 0; s < kMaxStages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(ready_bar(s), kTwo ? 2 * kConvWarps : kConvWarps);
+      mbar_init(ready_bar(s), p.direct ? 1 : (kTwo ? 2 * kConvWarps : kConvWarps));
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
@@ -467,6 +480,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       long long t_empty = 0;
+      const bool direct = p.direct != 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -497,16 +511,31 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               abort_flag = 1;
               break;
             }
-            const uint32_t bar = full_bar(stage);
-            if (lane == 0) mbar_expect_tx(bar, gr.stage_tx);
-            __syncwarp();   // the expectation is posted before any copy can complete
             const int k0 = kb * bk;
+            if (direct) {
+              // nothing to derive: the leader's `ready` barrier collects the bytes of both CTAs
+              const uint32_t bar = ready_bar(stage);
+              if (lane == 0 && rank == 0) mbar_expect_tx(bar, kTwo ? 2 * gr.stage_tx : gr.stage_tx);
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-              if (active[c]) {
-                const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
-                const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
-                tma_load_2d(dst, map[c], x, y, bar);
+              for (int c = 0; c < 2; c++) {
+                if (active[c]) {
+                  const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
+                  const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
+                  if (kTwo) tma_load_2d_pair(dst, map[c], x, y, bar);
+                  else tma_load_2d(dst, map[c], x, y, bar);
+                }
+              }
+            } else {
+              const uint32_t bar = full_bar(stage);
+              if (lane == 0) mbar_expect_tx(bar, gr.stage_tx);
+              __syncwarp();   // the expectation is posted before any copy can complete
+#pragma unroll
+              for (int c = 0; c < 2; c++) {
+                if (active[c]) {
+                  const uint32_t dst = smem_base + stage * stage_bytes + dst_off[c];
+                  const int x = mn[c] ? row0[c] : k0, y = mn[c] ? k0 : row0[c];
+                  tma_load_2d(dst, map[c], x, y, bar);
+                }
               }
             }
             if (++stage == num_stages) {
@@ -525,7 +554,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         // let copies already issued land before the CTA leaves
         for (int s = 0; s < num_stages; s++) {
           for (uint32_t i = 0; i < 4096; i++) {
-            if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
+            const uint32_t bar = direct ? ready_bar(s) : full_bar(s);   // (a peer's copies report to the leader)
+            if (mbar_try_wait(bar, 0) || mbar_try_wait(bar, 1)) break;
             __nanosleep(100);
           }
         }
@@ -699,7 +729,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     constexpr int kConvThreads = 32 * kConvWarps;
     int stage = 0;
     uint32_t phase = 0;
-    bool ok = true;
+    bool ok = !p.direct;   // nothing to derive anywhere: the copies report to the issuer themselves
     long long t_cfull = 0, t_conv = 0;
     for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       for (int q = 0; q < p.ngroups && ok; q++) {
@@ -1303,6 +1333,9 @@ int gemm_tc(const GemmProblem& g) {
     q0 += tg.nmma;
   }
   p.ngroups = ngroups;
+  p.direct = 1;
+  for (int gi = 0; gi < ngroups; gi++)
+    if (p.group[gi].nconv > 0) p.direct = 0;
   p.stage_bytes = stage_bytes;
   p.num_stages = (int)(kStageBudget / p.stage_bytes);
   if (p.num_stages > kMaxStages) p.num_stages = kMaxStages;
