@@ -210,10 +210,11 @@ def run_ours(args):
     peaks = measured_peaks()
     gemm_ms = sum(v[1] for n, v in agg.items() if n.startswith("gemm"))
     gemm_flops = sum(v[2] for n, v in agg.items() if n.startswith("gemm"))
-    # tensor-pipe work per algorithmic product, in TF32-product equivalents (a bfloat16 correction
-    # term issues at twice the TF32 rate): up = x.y + two bf16 terms, down (0/1 samples) = x.y + one
-    # bf16 term, statistics = positive (0/1 data: 2 TF32 terms) + negative (3 TF32 terms)
-    passes = {"gemm_up": 2, "gemm_down": 1.5, "gemm_stats": 2.5}
+    # tensor-pipe work per algorithmic product, in half-precision terms (each the flops of the product
+    # at the fp16/bf16 rate): up = hi.lo + lo.hi + hi.hi, down (0/1 samples) = two terms, statistics =
+    # positive half (0/1 data) two + negative half three
+    kg = float(getattr(getattr(eng, "hyp", None), "gibbs_steps", 1))
+    passes = {"gemm_up": (3 * kg + 2) / (kg + 1), "gemm_down": 2, "gemm_stats": 2.5}   # the first up product reads 0/1 data
     hw_flops = sum(v[2] * passes.get(n, 1) for n, v in agg.items() if n.startswith("gemm"))
     kernels = {n: dict(launches=v[0], ms_per_launch=round(v[1] / v[0], 5),
                        tflops=round(v[2] / (v[1] * 1e-3) / 1e12, 2) if v[2] else None,
@@ -235,15 +236,15 @@ def run_ours(args):
                       frac=round(achieved / peaks["tensor"], 4),
                       # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at this workload
                       # (ncu capture summarised in profiles/k_gemm_tc_up_c4.md); other workloads: not captured
-                      traffic=2.80e9 if config == 4 else None,
-                      kernel="k_gemm_tc<256, sigmoid+Bernoulli> (tcgen05 kind::tf32 + 2 x kind::f16 bf16 "
-                             "correction terms per k-block, paired CTAs)",
-                      peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); TF32 issues at half that rate "
-                                  "and one TF32 + two bf16 terms make one fp32-grade product" % peaks["source"],
+                      traffic=1.43e9 if config == 4 else None,
+                      kernel="k_gemm_tc<256, sigmoid+Bernoulli> (tcgen05 kind::f16: three fp16 terms hi.lo + lo.hi "
+                             "+ hi.hi on x * 2^e = hi + lo per k-block, paired CTAs)",
+                      peak_source="%s bf16 dense sustained (MEASURED_PEAKS.json); three half-precision terms "
+                                  "make one fp32-grade product" % peaks["source"],
                       launches=up[0], ms_per_launch=round(up[1] / up[0], 4),
                       share_of_step=round(up[1] / ms, 4) if world == 1 else None,
                       all_gemm_algorithmic_tflops=round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 2),
-                      all_gemm_tf32_issued_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2),
+                      all_gemm_issued_f16_tflops=round(hw_flops / (gemm_ms * 1e-3) / 1e12, 2),
                       all_gemm_share_of_step=round(gemm_ms / ms, 4) if world == 1 else None)
 
     # ---- end to end: host batches in, loss out, every step --------------------------------
