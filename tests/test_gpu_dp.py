@@ -14,9 +14,14 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def test_two_gpu_shards_match_one_gpu(cm, tmp_path):
+@pytest.mark.parametrize("form", ["derived", "f16"])
+def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, monkeypatch):
     if cm._lib.b200_device_count() < 2:
         pytest.skip("needs two GPUs")
+    # "f16": the operand form of the big model (aux matrices in scaled half precision, W's exponent
+    # kept on each replica by its update kernel), forced here at test size
+    monkeypatch.setenv("B200_RBM_STATE_AUX", "1" if form == "f16" else "0")
+    monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path)], env=env)
              for r in range(2)]
@@ -33,6 +38,7 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path):
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, gb, cfg["edges"][0]["weight"], cfg["hyperparams"],
                    edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+    assert eng.f16 == (form == "f16")
     data = cm.CUDAMatrix(cfg["data"])
     for step in range(3):
         eng.TrainOneBatch(step, data.slice(step * gb, (step + 1) * gb))
