@@ -897,7 +897,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         const bool draw = spec ? (kEpi == kEpiSigSample) : (e.sample != nullptr || e.sample_aux != nullptr);
         const bool has_out = e.out != nullptr;
         const bool has_aux = e.out_aux != nullptr;
-        const bool has_smp = spec ? draw : e.sample != nullptr;
+        const bool has_smp = e.sample != nullptr;
         const bool has_smp_aux = draw && e.sample_aux != nullptr;
         const PhiloxKey key = e.key;
         const uint32_t cblk0 = (uint32_t)((nc + e.col0) >> 2);
@@ -1355,8 +1355,8 @@ int gemm_tc(const GemmProblem& g) {
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
     epi = kEpiPlain;
-  } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample || e.out_aux)) {
-    if (e.activation == 1 && e.sample) epi = kEpiSigSample;
+  } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample || e.out_aux || e.sample_aux)) {
+    if (e.activation == 1 && (e.sample || e.sample_aux)) epi = kEpiSigSample;
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;
   }
