@@ -161,8 +161,9 @@ __device__ __forceinline__ void split_aux(float x, uint16_t& lo16, uint16_t& b16
 // fp16 range (65504): a power of two, so the scaling is exact and the epilogue undoes it with
 // alpha * 2^-(ea + eb).  Entries more than 2^14 below the largest lose relative (not absolute)
 // precision in lo.
+// A value that outgrows its exponent saturates at the largest fp16 instead of becoming infinite.
 __device__ __forceinline__ void split_f16(float x, float scale, uint16_t& lo, uint16_t& hi) {
-  const float xs = x * scale;
+  const float xs = fminf(fmaxf(x * scale, -65504.0f), 65504.0f);
   const __half h = __float2half_rn(xs);
   const __half l = __float2half_rn(xs - __half2float(h));
   hi = __half_as_ushort(h);

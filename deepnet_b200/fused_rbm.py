@@ -201,7 +201,7 @@ class FusedRBM(object):
             # (the next product reads the draw's half-precision plane; the fp32 draw is kept for the caller)
             self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, F(W.T, Wa, self.v_neg, self.v_neg_aux),
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
-                     sample=self.h_samp if (last or os.environ.get('B200_TMP_KEEP')) else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
+                     sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
         pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
         neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
