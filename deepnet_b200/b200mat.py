@@ -601,8 +601,8 @@ def f16_passes(a, a_aux, b, b_aux, negate=0, exact_a=False, exact_b=False):
 
 def f16_scale_state(max_abs):
     """The 1 x 4 device matrix `momentum_update` keeps for a parameter in scaled half-precision
-    form: {exponent in use, exponent of the next update, running max |w| (bits), -}; exponents
-    put the largest magnitude at or below 2^13.  `.slice(0, 1)` is the `scale_exp` of a product."""
+    form: {exponent, -, max |w| of the running update (bits), -}; the exponent puts the largest
+    magnitude at or below 2^13.  `.slice(0, 1)` is the `scale_exp` of a product."""
     e = float(np.floor(np.log2(8192.0 / max(float(max_abs), 1e-30))))
     return CUDAMatrix(np.array([[e, e, 0.0, 0.0]], np.float32))
 

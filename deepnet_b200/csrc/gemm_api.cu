@@ -150,15 +150,14 @@ __device__ __forceinline__ void update_one(float& w, float& d, float g, float su
   w = __fadd_rn(w, __fmul_rn(d, neps));
 }
 
-// kAux: 0 no aux, 1 bfloat16 parts, 2 scaled half-precision form.  For 2, `scale` points at
-// {e_used, e_next, max |w| (bits), -}: the new w is split with 2^e_next and its largest magnitude
-// is gathered for the exponent after that (k_update_scale).
+// kAux: 0 no aux, 1 bfloat16 parts, 2 scaled half-precision form.  For 2 this pass only gathers the
+// largest |w| of the new parameter into scale[2] (`scale` = {exponent, -, max |w| bits, -});
+// k_update_scale turns it into the exponent and k_split_f16 writes the aux with it.
 template <bool kHasGrad, int kAux>
 __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff,
                                                 uint16_t* w_aux, float* scale, int rows, int lda, long n, bool vec,
                                                 float ninv_batch, float momentum, float neps, float l2, float l1) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
-  const float f16_scale = kAux == 2 ? exp2f(scale[1]) : 1.0f;
   float wmax = 0.0f;
   if (vec) {   // n % 4 == 0, and with an aux rows % 4 == 0: four consecutive elements share a column
     for (long i = tid; i < (n >> 2); i += nth) {
@@ -174,20 +173,15 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       reinterpret_cast<float4*>(w)[i] = W;
       reinterpret_cast<float4*>(delta)[i] = D;
       if (kHasGrad) reinterpret_cast<float4*>(grad)[i] = make_float4(0, 0, 0, 0);
-      if (kAux) {
+      if (kAux == 1) {
         const long e = i << 2, c = e / rows, r = e - c * rows;
         ushort4 L, B;
-        if (kAux == 1) {
-          split_aux(W.x, L.x, B.x); split_aux(W.y, L.y, B.y); split_aux(W.z, L.z, B.z); split_aux(W.w, L.w, B.w);
-        } else {
-          split_f16(W.x, f16_scale, L.x, B.x); split_f16(W.y, f16_scale, L.y, B.y);
-          split_f16(W.z, f16_scale, L.z, B.z); split_f16(W.w, f16_scale, L.w, B.w);
-          wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(W.x), fabsf(W.y))), fmaxf(fabsf(W.z), fabsf(W.w)));
-        }
+        split_aux(W.x, L.x, B.x); split_aux(W.y, L.y, B.y); split_aux(W.z, L.z, B.z); split_aux(W.w, L.w, B.w);
         uint16_t* dst = w_aux + c * 2 * lda + r;
         *reinterpret_cast<ushort4*>(dst) = L;
         *reinterpret_cast<ushort4*>(dst + lda) = B;
       }
+      if (kAux == 2) wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(W.x), fabsf(W.y))), fmaxf(fabsf(W.z), fabsf(W.w)));
     }
   } else {
     for (long i = tid; i < n; i += nth) {
@@ -195,18 +189,14 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
       update_one(W, D, kHasGrad ? grad[i] : 0.0f, suff[i], ninv_batch, momentum, neps, l2, l1);
       w[i] = W; delta[i] = D;
       if (kHasGrad) grad[i] = 0.0f;
-      if (kAux) {
+      if (kAux == 1) {
         const long c = i / rows, r = i - c * rows;
         uint16_t L, B;
-        if (kAux == 1) {
-          split_aux(W, L, B);
-        } else {
-          split_f16(W, f16_scale, L, B);
-          wmax = fmaxf(wmax, fabsf(W));
-        }
+        split_aux(W, L, B);
         w_aux[c * 2 * lda + r] = L;
         w_aux[c * 2 * lda + lda + r] = B;
       }
+      if (kAux == 2) wmax = fmaxf(wmax, fabsf(W));
     }
   }
   if (kAux == 2) {   // non-negative floats order like their bit patterns
@@ -215,13 +205,13 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
   }
 }
 
-// After an update in scaled half-precision form: the exponent just used becomes the current one,
-// the next is chosen so that the largest |w| * 2^e stays at or below 2^13 (three binary orders
-// of headroom below the fp16 limit for the growth of one update), the maximum starts over.
+// After an update in scaled half-precision form: the exponent that puts the largest |w| * 2^e at
+// or below 2^13 (the fp16 limit is just under 2^16), and the maximum starts over.  A parameter
+// that is all zero (or not finite) keeps its exponent.
 __global__ void k_update_scale(float* scale) {
-  scale[0] = scale[1];
   const float m = __uint_as_float(reinterpret_cast<unsigned*>(scale)[2]);
-  if (m > 0.0f && m < 3.0e38f) scale[1] = floorf(log2f(8192.0f / m));
+  if (m > 0.0f && m < 3.0e38f) scale[0] = fminf(fmaxf(floorf(log2f(8192.0f / m)), -100.0f), 100.0f);
+  scale[1] = scale[0];
   reinterpret_cast<unsigned*>(scale)[2] = 0u;
 }
 
@@ -441,10 +431,11 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 // deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 in one pass over the parameter:
 //   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
 //   w -= eps * delta; grad = 0; and, when w_aux is given, the aux matrix of the new w: its
-//   bfloat16 parts, or with w_scale (1 x 4 device matrix {exponent in use, next exponent, max |w|
-//   bits, -}) its scaled half-precision form.
+//   bfloat16 parts, or with w_scale (1 x 4 device matrix {exponent, -, max |w| bits, -}) its
+//   scaled half-precision form, with the exponent that fits the new w (the update gathers the
+//   largest |w|, then a second pass over w writes the aux).
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
-// without grad and aux; +8 with grad, +4 with w_aux.
+// without grad and aux; +8 with grad, +4 with the bfloat16 aux, +8 with the half-precision one.
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
                     float inv_batch, float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
@@ -482,6 +473,13 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
   int err = check_launch();
   if (err || mode != 2) return err;
   k_update_scale<<<1, 1, 0, stream()>>>(sp);
+  err = check_launch();
+  if (err) return err;
+  const bool svec = (rows % 4 == 0) && ((((uintptr_t)w->data_device) & 15) == 0);
+  long sblocks = ((svec ? n / 4 : n) + 255) / 256;
+  if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
+  if (sblocks < 1) sblocks = 1;
+  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, aux_rows(rows), n, svec, sp, 0);
   return check_launch();
 }
 

@@ -223,7 +223,7 @@ class FusedRBM(object):
         l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
         self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
                  l1=l1, w_aux=Wa, w_scale=self.W_scale)
-        self.kernel_launches += 1                  # the exponent bookkeeping launch
+        self.kernel_launches += 2                  # the exponent launch and the pass that writes W's aux
 
     def _train_replicated_softmax(self, step, data):
         """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:

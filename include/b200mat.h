@@ -225,8 +225,8 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
 /* deepnet/dbm.py:242,254 + deepnet/parameter.py:80-106 as one pass over the parameter:
  * grad += -inv_batch * suff; delta = momentum*delta + l2*w + l1*sign(w) + grad;
  * w -= eps*delta; grad = 0; w_aux = aux matrix of the new w: its bfloat16 parts, or with w_scale
- * (1 x 4 device matrix {exponent in use, exponent of the next update, max |w| bits, -}, kept by
- * this call) its scaled half-precision form.  grad, w_aux, w_scale may be NULL. */
+ * (1 x 4 device matrix {exponent, -, max |w| bits, -}, kept by this call: the exponent always
+ * fits the new w) its scaled half-precision form.  grad, w_aux, w_scale may be NULL. */
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
                     float inv_batch, float momentum, float eps, float l2, float l1);
 

@@ -98,6 +98,30 @@ def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases, form, mon
     assert cm.read_status() == 0
 
 
+def test_half_precision_engine_from_zero_weights(cm, oracle, monkeypatch):
+    """W's exponent follows the weights from nothing to their first values (the update gathers the
+    largest |W| and writes the half-precision form with the exponent that fits it)."""
+    monkeypatch.setenv("B200_RBM_STATE_AUX", "1")
+    monkeypatch.setenv("B200_RBM_F16", "1")
+    cfg = configs.build(0, cases=300, dims_scale=0.25)
+    cfg["edges"][0]["weight"] = np.zeros_like(cfg["edges"][0]["weight"])
+    B, steps = cfg["batchsize"], 3
+    mo, lo = run_driver(oracle, cfg, 300, steps)
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+    assert eng.f16
+    data = cm.CUDAMatrix(cfg["data"])
+    lg = []
+    for step in range(steps):
+        eng.TrainOneBatch(step, data.slice(step * B, (step + 1) * B))
+        lg.append(eng.read_loss())
+    np.testing.assert_allclose(lg, lo, rtol=1e-5)
+    assert relerr(get(eng.W), get(mo.edge[0].params["weight"])) < TOL
+    np.testing.assert_array_equal(get(eng.h_samp), get(mo.GetLayerByName("h").sample))
+    assert cm.read_status() == 0
+
+
 def test_fused_softmax_ops_match_the_call_sequence(cm, oracle):
     rng = np.random.default_rng(21)
     V, B = 400, 12
