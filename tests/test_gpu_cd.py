@@ -228,7 +228,10 @@ def test_inference_path_matches_oracle(cm, oracle, config, scale, cases):
     assert abs(err - want["error"]) < 1e-5 * want["error"]
 
 
-def test_reconstruction_error_curve_within_two_percent(cm, oracle):
+@pytest.mark.parametrize("form", ["derived", "f16"])
+def test_reconstruction_error_curve_within_two_percent(cm, oracle, form, monkeypatch):
+    monkeypatch.setenv("B200_RBM_STATE_AUX", "0" if form == "derived" else "1")
+    monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     cases, steps = 1000, 60
     cfg = configs.build(0, cases=cases, dims_scale=0.25)
     B = cfg["batchsize"]
@@ -258,6 +261,7 @@ def test_full_size_properties(cm):
     x = (rng.random((V, B), dtype=np.float32) < p).astype(np.float32)
     hyp = dbm.Hyperparams(base_epsilon=0.05, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=1)
     eng = FusedRBM(cm, V, H, B, W, hyp, seed=3004)
+    assert eng.f16                       # at this size every product runs on scaled half-precision operands
     data = cm.CUDAMatrix(x)
     eng.TrainOneBatch(0, data)
     h_pos, h_samp, v_neg = get(eng.h_pos), get(eng.h_samp), get(eng.v_neg)
