@@ -54,9 +54,10 @@ def test_per_call_driver_matches_golden_trace(cm, name, config, scale, cases, st
     assert cm.read_status() == 0
 
 
-def test_replicated_softmax_step_matches_oracle(cm, oracle):
-    # config 2 at 1/50 size: multinomial sampling of the visible layer (sample_input on)
-    cfg = configs.build(2, cases=200, dims_scale=0.02)
+@pytest.mark.parametrize("scale", [0.02, 1.0])
+def test_replicated_softmax_step_matches_oracle(cm, oracle, scale):
+    # config 2 at 1/50 size and at full size: multinomial sampling of the visible layer (sample_input on)
+    cfg = configs.build(2, cases=200, dims_scale=scale)
     mg, lg = run_driver(cm, cfg, 200, 2)
     mo, lo = run_driver(oracle, cfg, 200, 2)
     np.testing.assert_allclose(lg, lo, rtol=1e-4)
@@ -66,16 +67,27 @@ def test_replicated_softmax_step_matches_oracle(cm, oracle):
     assert relerr(get(mg.edge[0].params["weight"]), get(mo.edge[0].params["weight"])) < TOL
 
 
-@pytest.mark.parametrize("config,scale,cases,form", [(0, 0.25, 300, "derived"), (1, 0.0625, 768, "derived"),
-                                                     (0, 1.0, 200, "derived"), (0, 0.25, 300, "bf16 aux"),
-                                                     (0, 0.25, 300, "f16"), (0, 1.0, 200, "f16")])
-def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases, form, monkeypatch):
+@pytest.mark.parametrize("config,scale,cases,form,gibbs", [
+    (0, 0.25, 300, "derived", 1), (1, 0.0625, 768, "derived", 1), (0, 1.0, 200, "derived", 1),
+    (0, 0.25, 300, "bf16 aux", 1), (0, 0.25, 300, "f16", 1), (0, 1.0, 200, "f16", 1),
+    # configuration 1 at its full size (1024 x 4096, batch 256)
+    (1, 1.0, 512, "derived", 1), (1, 1.0, 512, "bf16 aux", 1),
+    # CD-k with k > 1: the intermediate Gibbs steps store only what the next product reads
+    (0, 0.25, 300, "derived", 3), (4, 0.03125, 384, "f16", 10), (4, 0.03125, 384, "bf16 aux", 10),
+    (4, 0.0625, 512, "f16", 10)])
+def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases, form, gibbs, monkeypatch):
     # the three forms the products' operands take: parts derived in the kernel (small models),
     # bfloat16 parts from aux matrices, scaled half precision (what the big binary model runs on)
     monkeypatch.setenv("B200_RBM_STATE_AUX", "0" if form == "derived" else "1")
     monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     cfg = configs.build(config, cases=cases, dims_scale=scale)
-    B, steps = cfg["batchsize"], 3
+    if config == 4:
+        # the benchmarked model (8192 x 8192, CD-10, batch 4096) shrunk until the CPU restatement
+        # runs it in seconds: 256 units a side at batch 128 (one CTA per tile) and 512 at batch 256
+        # (paired CTAs on 256 x 256 tiles, as at full size), the same ten Gibbs steps
+        cfg["batchsize"] = 128 if scale < 0.05 else 256
+    cfg["hyperparams"].gibbs_steps = gibbs
+    B, steps = cfg["batchsize"], (3 if gibbs <= 3 else 2)
     mo, lo = run_driver(oracle, cfg, cases, steps)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
@@ -157,10 +169,12 @@ def test_fused_softmax_ops_match_the_call_sequence(cm, oracle):
     assert cm.CUDAMatrix.rnd_state.calls == B
 
 
-def test_fused_engine_replicated_softmax_matches_oracle(cm, oracle):
-    # config 2 at 1/50 size through the fused engine against the call-by-call driver on the oracle
+@pytest.mark.parametrize("scale", [0.02, 1.0])
+def test_fused_engine_replicated_softmax_matches_oracle(cm, oracle, scale):
+    # config 2 at 1/50 size and at its full size (10 000 words, 512 hidden units, documents of about
+    # 100 words) through the fused engine against the call-by-call driver on the oracle
     cases = 200
-    cfg = configs.build(2, cases=cases, dims_scale=0.02)
+    cfg = configs.build(2, cases=cases, dims_scale=scale)
     B, steps = cfg["batchsize"], 2
     mo, lo = run_driver(oracle, cfg, cases, steps)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
@@ -251,43 +265,76 @@ def test_reconstruction_error_curve_within_two_percent(cm, oracle, form, monkeyp
     assert lg[-1] < 0.6 * lg[0]
 
 
+def _f16_planes(aux):
+    """(lo, hi) planes of an aux matrix in scaled half-precision form, as float32."""
+    raw = np.array(aux.asarray(), copy=True)
+    words = np.ascontiguousarray(raw.T).view(np.uint16)
+    lda = raw.shape[0]
+    f = lambda w: np.ascontiguousarray(w).view(np.float16).astype(np.float32).T[:aux.rows]
+    return f(words[:, :lda]), f(words[:, lda:])
+
+
 def test_full_size_properties(cm):
-    """Config 4 shapes (V = H = 8192, batch 4096): checks that do not need a CPU run of the step."""
+    """Config 4 as benchmarked (V = H = 8192, batch 4096, CD-10): checks that do not need a CPU run
+    of the step.  Every product kind of the update is pinned at inner dimension 8192 (4096 for
+    the statistics) against float64 dot products of the operands it actually read."""
     V = H = 8192
     B = 4096
     rng = np.random.default_rng(44)
     W = (rng.standard_normal((V, H)) * 0.01).astype(np.float32)
     p = rng.beta(0.3, 2.0, size=(V, 1)).astype(np.float32)
     x = (rng.random((V, B), dtype=np.float32) < p).astype(np.float32)
-    hyp = dbm.Hyperparams(base_epsilon=0.05, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=1)
+    hyp = dbm.Hyperparams(base_epsilon=0.05, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=10)
     eng = FusedRBM(cm, V, H, B, W, hyp, seed=3004)
     assert eng.f16                       # at this size every product runs on scaled half-precision operands
     data = cm.CUDAMatrix(x)
     eng.TrainOneBatch(0, data)
     h_pos, h_samp, v_neg = get(eng.h_pos), get(eng.h_samp), get(eng.v_neg)
-    # (1) sampled entries of the positive hidden activations against float64 dot products
+    sig = lambda t: 1 / (1 + np.exp(-t))
+    # (1) the two-term up product on 0/1 data: sampled entries of the positive hidden
+    # activations against float64 dot products
     idx = rng.integers(0, H, 200), rng.integers(0, B, 200)
     pre = np.einsum("ki,ki->i", W[:, idx[0]].astype(np.float64), x[:, idx[1]].astype(np.float64))
-    want = 1 / (1 + np.exp(-pre))
-    assert np.abs(h_pos[idx] - want).max() < TOL
-    # (2) Bernoulli draws are 0/1 and their mean tracks the mean probability (checksum of the draw)
-    assert set(np.unique(h_samp)) <= {0.0, 1.0}
-    # h_samp holds the draw of the negative-phase hidden state after the Gibbs step
+    assert np.abs(h_pos[idx] - sig(pre)).max() < TOL
+    # (1b) the three-term up product on probabilities: the last hidden means against the last
+    # visible means they were computed from (biases are still zero during the first update)
     h_neg = get(eng.h_neg)
+    pre = np.einsum("ki,ki->i", W[:, idx[0]].astype(np.float64), v_neg[:, idx[1]].astype(np.float64))
+    assert np.abs(h_neg[idx] - sig(pre)).max() < TOL
+    # (1c) what the next product would read of those visible means: their half-precision planes
+    lo, hi = _f16_planes(eng.v_neg_aux)
+    cols = slice(0, 64)
+    want_hi = (v_neg[:, cols] * np.float32(2.0 ** 14)).astype(np.float16).astype(np.float32)
+    np.testing.assert_array_equal(hi[:, cols], want_hi)
+    np.testing.assert_array_equal(lo[:, cols], (v_neg[:, cols] * np.float32(2.0 ** 14) - want_hi).astype(np.float16))
+    # (2) Bernoulli draws are 0/1 and their mean tracks the mean probability (checksum of the draw);
+    # h_samp holds the draw of the last negative-phase hidden state
+    assert set(np.unique(h_samp)) <= {0.0, 1.0}
     assert abs(h_samp.mean() - h_neg.mean()) < 5 * 0.5 / np.sqrt(h_samp.size)
+    np.testing.assert_array_equal(_f16_planes(eng.h_samp_aux)[1][:, cols], h_samp[:, cols] * 2.0 ** 14)
     # (3) statistics: row sums and the packed gradient against float64 on sampled entries
     sb = get(eng.suff_bh).ravel()
     np.testing.assert_allclose(sb, h_pos.astype(np.float64).sum(axis=1) - h_neg.astype(np.float64).sum(axis=1),
                                rtol=1e-5, atol=2e-3)
     ii, jj = rng.integers(0, V, 64), rng.integers(0, H, 64)
     want_s = (x[ii].astype(np.float64) * h_pos[jj]).sum(axis=1) - (v_neg[ii].astype(np.float64) * h_neg[jj]).sum(axis=1)
-    got_s = get(eng.suff_W)[ii, jj]
-    assert np.abs(got_s - want_s).max() < TOL * max(np.abs(want_s).max(), 1.0) * 10
+    suff = get(eng.suff_W)
+    got_s = suff[ii, jj]
+    assert np.abs(got_s - want_s).max() < TOL * np.abs(suff).max()     # gradients: 1e-5 of the largest
     # (4) the update applied what the statistics say: W1 = W0 - eps * (-(suff)/B) with zero history
     W1 = get(eng.W)
     want_w = W[ii, jj] - np.float32(0.05) * (-(got_s) / B)
     assert np.abs(W1[ii, jj] - want_w).max() < 1e-6
-    # (5) a zero learning rate leaves the parameters untouched (idempotence of the update path)
+    # (5) the down product (W read along its rows, 0/1 hidden draws, inner dimension 8192) on the
+    # updated parameters and their rewritten half-precision form
+    out = cm.empty((V, B))
+    cm.fused_gemm(cm.f16_passes(eng.W, eng.W_aux, eng.h_samp, eng.h_samp_aux, exact_b=True), out=out, bias=eng.bv,
+                  activation=1, scale_exp=eng.W_exp, scale_exp_const=14)
+    got_v, bv1 = get(out), get(eng.bv).ravel().astype(np.float64)
+    vi, vb = rng.integers(0, V, 200), rng.integers(0, B, 200)
+    pre = np.einsum("ik,ki->i", W1[vi, :].astype(np.float64), h_samp[:, vb].astype(np.float64)) + bv1[vi]
+    assert np.abs(got_v[vi, vb] - sig(pre)).max() < TOL
+    # (6) a zero learning rate leaves the parameters untouched (idempotence of the update path)
     eng.hyp.base_epsilon = 0.0
     eng.ehyp.base_epsilon = 0.0
     eng.TrainOneBatch(1, data)

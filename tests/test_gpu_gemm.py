@@ -398,3 +398,33 @@ def test_momentum_update_is_bit_exact(cm, oracle, shape, with_grad):
     lo, b = aux.planes()
     np.testing.assert_array_equal(lo, bf16_round(get(wg) - tf32_trunc(get(wg))))
     np.testing.assert_array_equal(b, bf16_round(get(wg)))
+
+
+@pytest.mark.parametrize("k,form", [(8192, "f16"), (8192, "tf32"), (10000, "tf32"), (10000, "bf16")])
+def test_long_same_sign_products_keep_the_bound(cm, k, form):
+    """The tensor core truncates its accumulator at every MMA, so a long same-sign sum drifts; the
+    kernel folds chunks of the product into fp32 registers (128 products for linear outputs, 2048
+    behind a logistic).  Worst case for that rule: all-positive operands at the longest inner
+    dimensions of the path (8192 hidden units, a 10 000-word vocabulary), linear and logistic."""
+    rng = np.random.default_rng(k)
+    m, n = 256, 512
+    A = (rng.random((k, m)) * 0.02).astype(np.float32)            # stored k x m, used transposed (the up product)
+    B = rng.random((k, n)).astype(np.float32)
+    b = (-(A.astype(np.float64).T @ B).mean(axis=1, keepdims=True)).astype(np.float32)   # centres the logistic
+    cm.set_gemm_path(1)
+    a, x, bias = cm.CUDAMatrix(A), cm.CUDAMatrix(B), cm.CUDAMatrix(b)
+    lin, sig = cm.empty((m, n)), cm.empty((m, n))
+    if form == "f16":
+        scale = cm.f16_scale_state(np.abs(A).max())
+        xa = a.split_f16(cm.empty_aux(A.shape), exp_dev=scale.slice(0, 1))
+        xb = x.split_f16(cm.empty_aux(B.shape), exp_const=14)
+        kw = dict(scale_exp=scale.slice(0, 1), scale_exp_const=14)
+        cm.fused_gemm(cm.f16_passes(a.T, xa, x, xb), out=lin, **kw)
+        cm.fused_gemm(cm.f16_passes(a.T, xa, x, xb), out=sig, bias=bias, activation=1, **kw)
+    else:
+        cm.fused_gemm(cm.split_passes(a.T, x, terms=form), out=lin)
+        cm.fused_gemm(cm.split_passes(a.T, x, terms=form), out=sig, bias=bias, activation=1)
+    pre = A.astype(np.float64).T @ B.astype(np.float64)
+    assert relerr(get(lin), pre) < (4e-6 if form != "bf16" else TOL)
+    assert np.abs(get(sig) - 1 / (1 + np.exp(-(pre + b)))).max() < TOL
+    assert cm.read_status() == 0

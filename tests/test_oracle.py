@@ -203,3 +203,60 @@ def test_cd_learning_reduces_reconstruction_error(oracle):
         m.SetBatch([data.slice(s, s + B)])
         losses.append(m.TrainOneBatch(step)[0])
     assert losses[-1] < 0.5 * losses[0]
+
+
+def _numpy_twin_cd1(w_vh, w_v, w_h, v_true, uniforms, epsilon):
+    """One minibatch of the reference's numpy RBM example (cudamat/examples/rbm_numpy.py:33-68)
+    restated for Python 3 in float64, from zero update history (so its momentum factor does not
+    enter) and with the uniforms passed in instead of drawn by np.random.rand (:52)."""
+    batch_size = v_true.shape[1]
+    v = v_true
+    h = 1. / (1 + np.exp(-(np.dot(w_vh.T, v) + w_h)))                    # :44
+    wu_vh = np.dot(v, h.T)                                               # :46-48
+    wu_v = v.sum(1)[:, np.newaxis]
+    wu_h = h.sum(1)[:, np.newaxis]
+    h = 1. * (h > uniforms)                                              # :51
+    v = 1. / (1 + np.exp(-(np.dot(w_vh, h) + w_v)))                      # :54-55
+    h = 1. / (1 + np.exp(-(np.dot(w_vh.T, v) + w_h)))
+    wu_vh = wu_vh - np.dot(v, h.T)                                       # :57-59
+    wu_v = wu_v - v.sum(1)[:, np.newaxis]
+    wu_h = wu_h - h.sum(1)[:, np.newaxis]
+    new = (w_vh + epsilon / batch_size * wu_vh, w_v + epsilon / batch_size * wu_v,   # :62-64
+           w_h + epsilon / batch_size * wu_h)
+    return dict(wu_vh=wu_vh, wu_v=wu_v, wu_h=wu_h, v=v, h=h, new=new, err=np.mean((v - v_true) ** 2))   # :66
+
+
+def test_cd1_step_matches_the_reference_numpy_twin(oracle):
+    """The one numerical twin of a CD-1 step the reference holds is its numpy RBM example.  From zero
+    update history, without weight decay and with momentum-free first step, the deepnet call
+    sequence restated in deepnet_b200/dbm.py over the oracle must give the example's positive minus
+    negative statistics, reconstruction and first parameter update."""
+    from deepnet_b200 import dbm, synthetic
+    V, H, B, seed, eps = 96, 80, 40, 77, 0.05
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((V, H)) * 0.1).astype(np.float32)
+    bv = (rng.standard_normal((V, 1)) * 0.1).astype(np.float32)
+    bh = (rng.standard_normal((H, 1)) * 0.1).astype(np.float32)
+    data, _ = synthetic.binary_data(V, B, 5)
+    hyp = dbm.Hyperparams(base_epsilon=eps, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=1)
+    layers = [dict(name="v", activation=dbm.LOGISTIC, numdims=V, is_input=True, bias=bv),
+              dict(name="h", activation=dbm.LOGISTIC, numdims=H, bias=bh)]
+    m = dbm.DBM(oracle, layers, [dict(node1="v", node2="h", weight=w)], hyp, B, dbm.CD, seed=seed)
+    m.SetBatch([oracle.CUDAMatrix(data)])
+    loss = m.TrainOneBatch(0)[0]
+    # the hidden draw is the first sampling call of the step: its uniforms are call 0 of the stream
+    oracle.EigenMatrix.init_random(seed=seed)
+    u = np.array(oracle.empty((H, B)).fill_with_rand().asarray(), np.float64)
+    twin = _numpy_twin_cd1(w.astype(np.float64), bv.astype(np.float64), bh.astype(np.float64),
+                           data.astype(np.float64), u, eps)
+    e, lv, lh = m.edge[0], m.GetLayerByName("v"), m.GetLayerByName("h")
+    scale = np.abs(twin["wu_vh"]).max()
+    assert np.abs(e.suff_stats.asarray() - twin["wu_vh"]).max() < 1e-5 * max(scale, 1.0)
+    assert np.abs(lv.suff_stats.asarray() - twin["wu_v"]).max() < 1e-5 * B
+    assert np.abs(lh.suff_stats.asarray() - twin["wu_h"]).max() < 1e-5 * B
+    assert np.abs(lv.state.asarray() - twin["v"]).max() < 1e-6        # reconstruction (mean-field)
+    assert np.abs(lh.state.asarray() - twin["h"]).max() < 1e-6
+    assert abs(loss / (V * B) - twin["err"]) < 1e-6                    # summed vs mean squared error
+    assert np.abs(e.params["weight"].asarray() - twin["new"][0]).max() < 1e-6
+    assert np.abs(lv.params["bias"].asarray() - twin["new"][1]).max() < 1e-6
+    assert np.abs(lh.params["bias"].asarray() - twin["new"][2]).max() < 1e-6
