@@ -98,10 +98,13 @@ _ERRORS = {
 
 def generate_exception(err_code):
     """Error-code mapping of cudamat/cudamat.py:101-123 (plus -10 NCCL, -11 device timeout)."""
+    text = _lib.get_last_cuda_error().decode("utf-8", "replace")     # reading it clears it
     if err_code in (-3, -10):
-        return CUDAMatException(("CUDA error: " if err_code == -3 else "NCCL error: ") +
-                                _lib.get_last_cuda_error().decode("utf-8", "replace"))
-    return CUDAMatException(_ERRORS.get(err_code, "error code %d" % err_code))
+        return CUDAMatException(("CUDA error: " if err_code == -3 else "NCCL error: ") + text)
+    msg = _ERRORS.get(err_code, "error code %d" % err_code)
+    if err_code == -9 and text and text != "no error":
+        msg += " " + text                                            # why the library refused
+    return CUDAMatException(msg)
 
 
 def _check(err_code):
@@ -119,6 +122,7 @@ def _require_device():
             raise CUDAMatException("no CUDA device is visible; b200mat has no CPU fallback")
         _check(_lib.cublas_init())
         _device_checked = True
+        cublas_init()
 
 
 class CUDAMatrix(object):
@@ -368,6 +372,19 @@ class CUDAMatrix(object):
     def apply_softmax(self, target=None):
         target = target or self
         _check(_lib.softmax(self.p_mat, target.p_mat))
+        return target
+
+    def norm_limit(self, norm, axis, target=None):
+        """cudamat/cudamat.py:1000-1016: columns longer than `norm` are scaled back to it (axis 0 only)."""
+        target = target or self
+        _check(_lib.normlimit_by_axis(self.p_mat, target.p_mat, ct.c_int(axis), ct.c_float(norm)))
+        return target
+
+    def transpose(self, target=None):
+        """cudamat/cudamat.py:422-433: target = self' as a dense matrix (a copy, not a view)."""
+        if target is None:
+            target = empty((self.shape[1], self.shape[0]))
+        _check(_lib.copy_transpose(self.p_mat, target.p_mat))
         return target
 
     # -- elementwise -------------------------------------------------------
@@ -751,15 +768,22 @@ def cuda_set_device(dev_id):
     _check(_lib.cuda_set_device(ct.c_int(dev_id)))
 
 
+MAX_ONES = 1024 * 256
+
+
 def cublas_init():
+    """cudamat/cudamat.py:1879-1885: brings the library up and fills `CUDAMatrix.ones`, the column
+    of ones the reference's callers multiply with for sums."""
     _require_device()
-    CUDAMatrix.ones = None
+    if CUDAMatrix.ones is None:
+        CUDAMatrix.ones = CUDAMatrix(np.ones((MAX_ONES, 1), dtype=np.float32, order="F"))
 
 
 init = cublas_init
 
 
 def cublas_shutdown():
+    CUDAMatrix.ones = None
     _lib.cublas_shutdown()
 
 
@@ -787,6 +811,12 @@ def set_rng_column_offset(col0):
 def read_status():
     """Non-zero if a kernel's bounded wait gave up since the last call (blocks)."""
     return _lib.b200_read_status()
+
+
+def set_wait_limit(iterations):
+    """Iterations a device-side wait may spin before its kernel gives up and records a status
+    (default 2^24, one to two seconds; 0 restores the default)."""
+    _check(_lib.b200_set_wait_limit(ct.c_uint(int(iterations))))
 
 
 class Event(object):

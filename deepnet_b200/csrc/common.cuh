@@ -43,11 +43,14 @@ namespace b200 {
 cudaStream_t stream();                 // the stream every operation of the library runs on
 cudaStream_t stream_if_initialised();  // the same, or the default stream when the library was never initialised
 int sm_count();                        // SMs of the current device
-int check_launch();                    // cudaGetLastError -> 0 or CUDA_ERROR (message kept)
+int check_launch();                    // cudaGetLastError -> 0 or CUDA_ERROR (message kept); CUDA_ERROR when the library failed to initialise
+int check_launch_any_stream();         // the same for entry points that also run without the library stream
 int set_error(const char* msg);        // records msg, returns CUDA_ERROR
 int rng_col0();                        // first global column of this process's minibatch shard
 void* workspace(int slot, size_t bytes);  // grow-only cached device scratch, slot 0..7
 int* status_word();                    // device int: non-zero after a bounded wait gave up
+bool initialised();                    // the library stream and status word exist (tries to create them)
+uint32_t wait_limit();                 // iterations a bounded device-side wait may spin (b200_set_wait_limit)
 
 inline long numel(const cudamat* m) { return (long)m->size[0] * m->size[1]; }
 inline bool same_shape(const cudamat* a, const cudamat* b) {

@@ -21,19 +21,39 @@ static void* g_ws[8] = {nullptr};
 static size_t g_ws_bytes[8] = {0};
 static std::mutex g_mu;
 
+static uint32_t g_wait_limit = 1u << 24;   // iterations of a bounded device-side wait: ~1-2 s
+
+// Creates the library stream and the device status word.  A failure (a device with no memory left,
+// a context in an error state) is recorded and leaves the library uninitialised: stream() then
+// returns null, status_word() null, and every entry point that launches reports CUDA_ERROR through
+// check_launch() / its own checks instead of running on a garbage stream.
 static void ensure_init() {
   if (g_stream) return;
   std::lock_guard<std::mutex> lock(g_mu);
   if (g_stream) return;
   int dev = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-  cudaMalloc(&g_status, sizeof(int));
-  cudaMemset(g_status, 0, sizeof(int));
-  cudaStream_t s;
-  cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    snprintf(g_err, sizeof(g_err), "library initialisation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return;
+  }
+  int* status = nullptr;
+  if (cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemset(status, 0, sizeof(int)) != cudaSuccess) {
+    snprintf(g_err, sizeof(g_err), "library initialisation failed (status word): %s",
+             cudaGetErrorString(cudaGetLastError()));
+    if (status) cudaFree(status);
+    return;
+  }
+  cudaStream_t s = nullptr;
+  if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess || !s) {
+    snprintf(g_err, sizeof(g_err), "library initialisation failed (stream): %s",
+             cudaGetErrorString(cudaGetLastError()));
+    cudaFree(status);
+    return;
+  }
+  g_status = status;
   g_own_stream = true;
-  g_stream = s;
+  g_stream = s;   // published last: a non-null stream means the library is usable
 }
 
 cudaStream_t stream() {
@@ -50,16 +70,25 @@ int* status_word() {
   ensure_init();
   return g_status;
 }
+bool initialised() {
+  ensure_init();
+  return g_stream != nullptr;
+}
+uint32_t wait_limit() { return g_wait_limit; }
 
 int set_error(const char* msg) {
-  snprintf(g_err, sizeof(g_err), "%s", msg);
+  if (msg != g_err) snprintf(g_err, sizeof(g_err), "%s", msg);
   return CUDA_ERROR;
 }
 
-int check_launch() {
+int check_launch_any_stream() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(cudaGetErrorString(e));
   return 0;
+}
+int check_launch() {
+  if (!g_stream) return set_error(g_err[0] ? g_err : "the library is not initialised");
+  return check_launch_any_stream();
 }
 
 void* workspace(int slot, size_t bytes) {
@@ -91,8 +120,15 @@ using namespace b200;
 
 extern "C" {
 
+// Text of the most recent failure.  Reading it clears it, so a later error of another kind (a raw
+// CUDA error with no recorded text) is not reported under this one's words.
 const char* get_last_cuda_error() {
-  if (g_err[0]) return g_err;
+  static char last[sizeof(g_err)];
+  if (g_err[0]) {
+    snprintf(last, sizeof(last), "%s", g_err);
+    g_err[0] = 0;
+    return last;
+  }
   return cudaGetErrorString(cudaGetLastError());
 }
 
@@ -100,6 +136,15 @@ const char* get_last_cuda_error() {
 // create the library stream and release cached scratch.
 int cublas_init() {
   ensure_init();
+  return g_stream ? 0 : CUDA_ERROR;
+}
+
+// Iterations a device-side wait (an mbarrier wait of the tensor-core product) may spin before
+// the kernel gives up, records where in the status word (b200_read_status) and returns.  The
+// default, 2^24, is one to two seconds; 0 restores it.  Failure-detection tests set a few
+// thousand iterations (milliseconds) so that a wait that cannot complete ends quickly.
+int b200_set_wait_limit(unsigned int iterations) {
+  g_wait_limit = iterations ? iterations : (1u << 24);
   return 0;
 }
 
@@ -182,8 +227,12 @@ void b200_event_destroy(void* ev) {
 // gave up (the value encodes where).  Blocks until the stream is idle.
 int b200_read_status() {
   int v = 0;
-  cudaStreamSynchronize(stream());
-  cudaMemcpy(&v, status_word(), sizeof(int), cudaMemcpyDeviceToHost);
+  if (!initialised()) return ERROR_GENERIC;
+  if (cudaStreamSynchronize(stream()) != cudaSuccess ||
+      cudaMemcpy(&v, status_word(), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    set_error(cudaGetErrorString(cudaGetLastError()));
+    return CUDA_ERROR;
+  }
   if (v) cudaMemset(status_word(), 0, sizeof(int));
   return v;
 }

@@ -40,7 +40,6 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128;
-constexpr uint32_t kSpinLimit = 1u << 24;     // bounded wait: ~1-2 s with the sleep below
 constexpr int kMaxStages = 8;
 constexpr int kStageBudget = 193 * 1024;      // shared memory available to the operand ring
 constexpr int kOutStageBytes = 32 * 1024;      // epilogue staging for TMA stores (two column halves x two buffers)
@@ -105,6 +104,7 @@ struct TcParams {
   GemmEpilogue epi;
   int out_map[kOutArrays];   // tensor maps (indices into maps) of the outputs stored by TMA; -1 = absent
   int* status;
+  uint32_t spin_limit;       // iterations a wait may spin before the kernel gives up (b200_set_wait_limit)
 #ifdef B200_GEMM_TIMING
   unsigned long long* dbg;   // per CTA: issuer total, wait-full, wait-tmem-empty; producer wait-empty; epilogue wait
 #endif
@@ -140,8 +140,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit ran out or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(40);
     if ((i & 1023) == 1023 && *abort_flag) return false;
@@ -422,6 +422,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   const int num_stages = p.num_stages;
   const uint32_t stage_bytes = p.stage_bytes;
   const int bk = p.bk;
+  const uint32_t spin_limit = p.spin_limit;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -505,7 +506,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             mn[c] = ld.mn;
           }
           for (int kb = 0; kb < k_iters; kb++) {
-            if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag))) {
+            if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, spin_limit))) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 1);
               abort_flag = 1;
@@ -613,7 +614,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
               const int acc = chunk & 1;
               if (in_chunk == 0) {
                 // a new chunk: its TMEM accumulator must have been drained by the epilogue warps
-                if (!TIMED_WAIT(t_tempty, mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag))) {
+                if (!TIMED_WAIT(t_tempty, mbar_wait(tempty_bar(acc), ((chunk >> 1) & 1u) ^ 1u, &abort_flag, spin_limit))) {
                   ok = false;
                   if (!abort_flag) atomicCAS(p.status, 0, 2);
                   abort_flag = 1;
@@ -623,7 +624,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
                 fresh = 1;
               }
               // the stage is loaded and converted in both CTAs
-              if (!TIMED_WAIT(t_full, mbar_wait(ready_bar(stage), phase, &abort_flag))) {
+              if (!TIMED_WAIT(t_full, mbar_wait(ready_bar(stage), phase, &abort_flag, spin_limit))) {
                 ok = false;
                 if (!abort_flag) atomicCAS(p.status, 0, 3);
                 abort_flag = 1;
@@ -737,7 +738,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
         const int k_iters = gr.k_iters, nconv = gr.nconv;
         const TcConv c0 = gr.conv[0], c1 = gr.conv[1];
         for (int kb = 0; kb < k_iters; kb++) {
-          if (!TIMED_WAIT(t_cfull, mbar_wait(full_bar(stage), phase, &abort_flag))) {
+          if (!TIMED_WAIT(t_cfull, mbar_wait(full_bar(stage), phase, &abort_flag, spin_limit))) {
             ok = false;
             if (!abort_flag) atomicCAS(p.status, 0, 5);
             abort_flag = 1;
@@ -834,7 +835,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       for (int j = 0; j < COLS; j++) accum[j] = 0.0f;
       for (int c = 0; c < nchunks; c++, chunk++) {
         const int acc = chunk & 1;
-        if (!TIMED_WAIT(t_tfull, mbar_wait(tfull_bar(acc), (chunk >> 1) & 1u, &abort_flag))) {
+        if (!TIMED_WAIT(t_tfull, mbar_wait(tfull_bar(acc), (chunk >> 1) & 1u, &abort_flag, spin_limit))) {
           if (!abort_flag) atomicCAS(p.status, 0, 4);
           abort_flag = 1;
           ok = false;
@@ -1117,36 +1118,53 @@ inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
 
 static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
 
+// Host-side failure injection for the bounded waits: the next tensor-core product is told to
+// expect this many more bytes per stage than its copies deliver, so the stage's barrier can
+// never complete, the waiting role runs into the wait limit, records a status word and the
+// kernel drains and returns.  Nothing traps, faults or spins without bound.
+int g_inject_stage_bytes = 0;
+
 template <int BN, int kEpi, bool kTwo>
 int launch_tc(TcParams& p) {
   using Cfg = TcConfig<BN>;
-  static bool attr_set = false;
-  static int max_pairs = 0;
+  // The shared-memory attribute of a kernel and the number of resident CTA pairs belong to a
+  // device, not to the process: kept per device ordinal for a host that drives several GPUs.
+  constexpr int kMaxDev = 64;
+  static bool attr_set[kMaxDev] = {false};
+  static int pairs_of[kMaxDev] = {0};
+  static std::mutex mu;
   auto kernel = k_gemm_tc<BN, kEpi, kTwo>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-      return set_error("cudaFuncSetAttribute(max dynamic shared memory) failed");
-    if (kTwo) {
-      // how many CTA pairs the device can keep resident at once (a pair needs two SMs of one TPC)
-      cudaLaunchConfig_t q = {};
-      q.gridDim = dim3(2 * (sm_count() / 2));
-      q.blockDim = dim3(kThreadsTc);
-      q.dynamicSmemBytes = Cfg::kSmemBytes;
-      cudaLaunchAttribute at[1];
-      at[0].id = cudaLaunchAttributeClusterDimension;
-      at[0].val.clusterDim.x = 2;
-      at[0].val.clusterDim.y = 1;
-      at[0].val.clusterDim.z = 1;
-      q.attrs = at;
-      q.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n < 1) {
-        cudaGetLastError();
-        return set_error("cudaOccupancyMaxActiveClusters failed for the paired-CTA product");
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return set_error("cudaGetDevice failed");
+  int max_pairs = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_set[dev]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+        return set_error("cudaFuncSetAttribute(max dynamic shared memory) failed");
+      if (kTwo) {
+        // how many CTA pairs the device can keep resident at once (a pair needs two SMs of one TPC)
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(2 * (sm_count() / 2));
+        q.blockDim = dim3(kThreadsTc);
+        q.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        q.attrs = at;
+        q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n < 1) {
+          cudaGetLastError();
+          return set_error("cudaOccupancyMaxActiveClusters failed for the paired-CTA product");
+        }
+        pairs_of[dev] = n;
       }
-      max_pairs = n;
+      attr_set[dev] = true;
     }
-    attr_set = true;
+    max_pairs = pairs_of[dev];
   }
   constexpr int TILE_M = kTwo ? 2 * BM : BM;
   p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
@@ -1219,6 +1237,8 @@ int gemm_tc(const GemmProblem& g) {
   p.bk = bk;
   p.epi = g.epi;
   p.status = status_word();
+  if (!p.status) return set_error("the library is not initialised (no device status word)");
+  p.spin_limit = wait_limit();
 #ifdef B200_GEMM_TIMING
   p.dbg = (unsigned long long*)workspace(7, 8 * 512 * sizeof(unsigned long long));
 #endif
@@ -1332,6 +1352,10 @@ int gemm_tc(const GemmProblem& g) {
     }
     q0 += tg.nmma;
   }
+  if (g_inject_stage_bytes) {
+    for (int gi = 0; gi < ngroups; gi++) p.group[gi].stage_tx += (uint32_t)g_inject_stage_bytes;
+    g_inject_stage_bytes = 0;
+  }
   p.ngroups = ngroups;
   p.direct = 1;
   for (int gi = 0; gi < ngroups; gi++)
@@ -1393,6 +1417,12 @@ int gemm_tc(const GemmProblem& g) {
 }
 
 }  // namespace b200
+
+// Test hook (see g_inject_stage_bytes): applies to the next tensor-core product only.
+extern "C" int b200_test_inject_stage_bytes(int extra_bytes) {
+  b200::g_inject_stage_bytes = extra_bytes > 0 ? extra_bytes : 0;
+  return 0;
+}
 
 #ifdef B200_GEMM_TIMING
 // Debug build only: copies the per-CTA cycle counters of the last launch (8 words per CTA).

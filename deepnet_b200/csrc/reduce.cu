@@ -3,6 +3,8 @@
 // (cudamat/cudamat.cu:1148-1258, 1733-1759, 2104-2118, 2192-2240; the axis sums replace
 // the reference's GEMV with a ones vector, cudamat/cudamat.py:724-748,1546-1577).
 // Warp-shuffle trees inside a block; HBM-bound: 4 bytes read per input element.
+#include <mutex>
+
 #include "common.cuh"
 
 using namespace b200;
@@ -541,8 +543,11 @@ float sum_all(cudamat* mat, int* err_code) {
 constexpr int kNoAllocScratchFloats = 32768;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 constexpr int kMaxDevices = 64;
-static float* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address per device ordinal
+// Device address of the array and SM count per device ordinal, looked up once per device under a
+// lock; the pointer is published last, so a thread that sees it also sees the SM count.
+static float* g_noalloc_ptr[kMaxDevices] = {nullptr};
 static int g_noalloc_sms[kMaxDevices] = {0};
+static std::mutex g_noalloc_mu;
 
 extern "C" int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult) {
   if (!mat->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
@@ -552,26 +557,34 @@ extern "C" int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, 
   if (numel(target) != (axis == 0 ? w : h)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if ((long)h * w == 0) return 0;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return set_error("cudaGetDevice failed");
-  if (!g_noalloc_ptr[dev]) {
-    // In host code the array's name is only a handle; the kernels need its device address.
-    float* ptr = nullptr;
-    if (cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
-      cudaGetLastError();
-      return set_error("cudaGetSymbolAddress(g_noalloc_scratch) failed");
+  if (cudaGetDevice(&dev) != cudaSuccess) return set_error("cudaGetDevice failed");
+  if (dev < 0 || dev >= kMaxDevices)
+    return set_error("add_sum_by_axis_noalloc: device ordinal beyond the 64 this entry point keeps addresses for");
+  float* part = nullptr;
+  int sms = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      // In host code the array's name is only a handle; the kernels need its device address.
+      float* ptr = nullptr;
+      if (cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
+        cudaGetLastError();
+        return set_error("cudaGetSymbolAddress(g_noalloc_scratch) failed");
+      }
+      int n = 0;
+      if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        return set_error("cudaDeviceGetAttribute(multiprocessor count) failed");
+      g_noalloc_sms[dev] = n;
+      g_noalloc_ptr[dev] = ptr;
     }
-    int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      return set_error("cudaDeviceGetAttribute(multiprocessor count) failed");
-    g_noalloc_sms[dev] = sms;
-    g_noalloc_ptr[dev] = ptr;
+    part = g_noalloc_ptr[dev];
+    sms = g_noalloc_sms[dev];
   }
   cudaStream_t st = stream_if_initialised();
-  const int sms = g_noalloc_sms[dev];
   if (axis == 0) {  // sums down the columns need no scratch
     const int blocks = w < sms * 8 ? w : sms * 8;
     k_colsum<<<blocks, 256, 0, st>>>(mat->data_device, target->data_device, h, w, mult, 1.0f);
-    return check_launch();
+    return check_launch_any_stream();
   }
   const int bx = (h + 31) / 32;
   int splits = (4 * sms + bx - 1) / bx;
@@ -582,15 +595,14 @@ extern "C" int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, 
   splits = (w + cps - 1) / cps;
   if (splits == 1) {
     k_rowsum<<<dim3(bx, 1), 32 * kRowLanes, 0, st>>>(mat->data_device, target->data_device, h, w, cps, mult, 1.0f, true);
-    return check_launch();
+    return check_launch_any_stream();
   }
   if ((long)splits * h > kNoAllocScratchFloats) {
     set_error("add_sum_by_axis_noalloc: the partial sums of this matrix (splits x rows floats) exceed the "
               "32768-float static scratch; use add_sum_by_axis");
     return ERROR_UNSUPPORTED;
   }
-  float* part = g_noalloc_ptr[dev];
   k_rowsum<<<dim3(bx, splits), 32 * kRowLanes, 0, st>>>(mat->data_device, part, h, w, cps, 1.0f, 0.0f, false);
   k_rowsum_finish<<<(h + 255) / 256, 256, 0, st>>>(part, target->data_device, h, splits, mult, 1.0f);
-  return check_launch();
+  return check_launch_any_stream();
 }

@@ -35,7 +35,20 @@ from .dbm import LINEAR, LOGISTIC, REPLICATED_SOFTMAX, Parameter
 
 class FusedRBM(object):
     def __init__(self, cm, V, H, batchsize, weight, hyperparams, edge_hyperparams=None, visible=LOGISTIC,
-                 binary_data=True, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0):
+                 binary_data=False, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0):
+        """binary_data: the caller states that every input is exactly 0 or 1 (or, for word counts, a
+        small integer): such data have no low part, so the products over them run one term shorter
+        and, for a big logistic model, on the scaled half-precision form.  Real-valued inputs
+        (grey levels in [0, 1], standardised features) must leave it False: with it set their low
+        parts would be dropped without notice.
+
+        With world_size > 1 the replicated-softmax model draws its multinomial samples from the
+        rank's own call numbers: its random stream then depends on the number of ranks (the Bernoulli
+        paths do not: they are indexed by global column only)."""
+        if visible == LINEAR and hyperparams.sample_input:
+            # the reference's linear layer has no draw (deepnet/linear_layer.py:24-27 is a no-op without
+            # learned precision), so its `sample` buffer would feed stale values upward
+            raise ValueError("sample_input with a linear visible layer is not supported")
         self.cm = cm
         self.V, self.H, self.B = V, H, batchsize
         self.visible = visible
@@ -79,6 +92,7 @@ class FusedRBM(object):
         self.v_neg, self.v_neg_aux, self.h_neg = z(V, B), za(V, B), z(H, B)
         self.data_aux = za(V, B)
         self.h_pos_aux, self.h_neg_aux = (za(H, B), za(H, B)) if getattr(self, "f16", False) else (None, None)
+        self.v_samp = self.v_samp_aux = None      # allocated when sample_input asks for visible draws
         self.loss_acc = z(1, 1)
         if visible == REPLICATED_SOFTMAX:
             # document lengths, length-normalised visible states (the statistics use state / NN,
@@ -96,6 +110,17 @@ class FusedRBM(object):
     def _act(self, layer_activation):
         return 1 if layer_activation == LOGISTIC else 0
 
+    def _gibbs_steps(self, step):
+        """deepnet/dbm.py:202-208: the step-up schedule adds a Gibbs step every step_up_cd_after updates."""
+        h = self.hyp
+        if 0 < h.start_step_up_cd_after < step:
+            return h.gibbs_steps + 1 + (step - h.start_step_up_cd_after) // h.step_up_cd_after
+        return h.gibbs_steps
+
+    def _sample_visible(self, step):
+        """deepnet/dbm.py:217-222: the visible layer feeds a draw upward instead of its means."""
+        return bool(self.hyp.sample_input) and self.hyp.sample_input_after <= step
+
     def _op(self, name, flops, nbytes, fn, *args, **kw):
         """Runs one kernel-launching call; with a timeline attached, brackets it with CUDA events."""
         self.kernel_launches += 1
@@ -111,7 +136,7 @@ class FusedRBM(object):
         """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host."""
         if self.visible == REPLICATED_SOFTMAX:
             return self._train_replicated_softmax(step, data)
-        cm, k = self.cm, self.hyp.gibbs_steps
+        cm, k = self.cm, self._gibbs_steps(step)
         V, H, B = self.V, self.H, self.B
         W, Wa, P = self.W, self.W_aux, cm.split_passes
         v0 = data
@@ -130,17 +155,25 @@ class FusedRBM(object):
         self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm,
                  P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux if sa else None),
                  out=self.h_pos, sample=self.h_samp, sample_aux=h_samp_aux, bias=self.bh, activation=1)
-        # negative phase: k Gibbs steps, visible mean fed upward (sample_input off)
+        # negative phase: k Gibbs steps; the visible means feed upward, or with sample_input (logistic
+        # visible units only) their Bernoulli draw, which costs one sampling call per step
+        draw_v = self._sample_visible(step) and self.visible == LOGISTIC
+        if draw_v and self.v_samp is None:
+            self.v_samp, self.v_samp_aux = cm.empty((V, B)), cm.empty_aux((V, B))
         for i in range(k):
             self._op("gemm_down", gf, 2 * vb, cm.fused_gemm,
                      P(W, self.h_samp, exact_b=True, a_aux=Wa, b_aux=h_samp_aux), out=self.v_neg,
-                     out_aux=v_neg_aux, bias=self.bv, activation=self._act(self.visible))
+                     out_aux=None if draw_v else v_neg_aux, sample=self.v_samp if draw_v else None,
+                     sample_aux=self.v_samp_aux if (draw_v and sa) else None, bias=self.bv,
+                     activation=self._act(self.visible))
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1          # add_sq_diff is two launches
             # the hidden means are only read after the last step (statistics); before that the draw suffices
-            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, P(W.T, self.v_neg, a_aux=Wa, b_aux=v_neg_aux),
+            up = (P(W.T, self.v_samp, exact_b=True, a_aux=Wa, b_aux=self.v_samp_aux if sa else None) if draw_v
+                  else P(W.T, self.v_neg, a_aux=Wa, b_aux=v_neg_aux))
+            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, up,
                      out=self.h_neg if i == k - 1 else None, sample=self.h_samp, sample_aux=h_samp_aux,
                      bias=self.bh, activation=1)
         # statistics: pos - neg in one product: the difference of two nearly equal products, so its
@@ -172,7 +205,7 @@ class FusedRBM(object):
         half-precision operands: states and data as x * 2^14 = hi + lo in fp16 (written by the
         producing epilogue, `split_f16` for the data), W as W * 2^e (written by the update kernel,
         which also keeps e); a product is hi.lo + lo.hi + hi.hi, 0/1 operands need hi only."""
-        cm, k = self.cm, self.hyp.gibbs_steps
+        cm, k = self.cm, self._gibbs_steps(step)
         V, H, B = self.V, self.H, self.B
         W, Wa, We, F = self.W, self.W_aux, self.W_exp, cm.f16_passes
         E = 14                                     # exponent of every state: values in [0, 1]
@@ -186,20 +219,27 @@ class FusedRBM(object):
         self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, F(W.T, Wa, v0, v0a, exact_b=True), out=self.h_pos,
                  out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                  **act)
+        draw_v = self._sample_visible(step)       # sample_input: the visible draw feeds upward (one more call per step)
+        if draw_v and self.v_samp is None:
+            self.v_samp, self.v_samp_aux = cm.empty((V, B)), cm.empty_aux((V, B))
         for i in range(k):
             last = i == k - 1
             # the fp32 visible means are read by the error of the first reconstruction and by the
-            # statistics after the last step; in between only their half-precision form is
+            # statistics after the last step; in between only their half-precision form is (and not
+            # even that when the draw feeds upward)
             self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, F(W, Wa, self.h_samp, self.h_samp_aux, exact_b=True),
-                     out=self.v_neg if (i == 0 or last) else None, out_aux=self.v_neg_aux, bias=self.bv, activation=1,
-                     **act)
+                     out=self.v_neg if (i == 0 or last) else None,
+                     out_aux=self.v_neg_aux if (last or not draw_v) else None,
+                     sample_aux=self.v_samp_aux if draw_v else None, bias=self.bv, activation=1, **act)
             if i == 0:
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
                 self.kernel_launches += 1
             # the hidden means (and their parts) are only read after the last step, by the statistics
             # (the next product reads the draw's half-precision plane; the fp32 draw is kept for the caller)
-            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, F(W.T, Wa, self.v_neg, self.v_neg_aux),
+            up = (F(W.T, Wa, self.v_samp, self.v_samp_aux, exact_b=True) if draw_v
+                  else F(W.T, Wa, self.v_neg, self.v_neg_aux))
+            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, up,
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
                      sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
@@ -231,9 +271,10 @@ class FusedRBM(object):
         and edge.py:222-246, on fused kernels.  Same random stream as the call-by-call driver:
         one call for the positive hidden draw, then per Gibbs step one call per document for the
         multinomial draw and one for the hidden draw."""
-        cm, k = self.cm, self.hyp.gibbs_steps
+        cm, k = self.cm, self._gibbs_steps(step)
         V, H, B = self.V, self.H, self.B
         W, Wa, P = self.W, self.W_aux, cm.split_passes   # the small state matrices' parts are derived in the kernel
+        draw_v = self._sample_visible(step)
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         lib = cm._lib
@@ -255,8 +296,12 @@ class FusedRBM(object):
             if i == 0:   # squared error between state / NN and the counts (replicated_softmax_layer.py:128-135)
                 self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat,
                                                                                 self.loss_acc.p_mat)))
-            self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
-            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, self.v_samp, exact_b=True, a_aux=Wa),
+            if draw_v:   # word counts drawn from the softmax feed upward
+                self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
+                up = P(W.T, self.v_samp, exact_b=True, a_aux=Wa)
+            else:        # sample_input off: the expected counts do (deepnet/dbm.py:222)
+                up = P(W.T, self.v_neg, a_aux=Wa)
+            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, up,
                      out=self.h_neg, sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
         pos = P(self.v0n, self.h_pos.T, terms="tf32")
         neg = P(self.v_negn, self.h_neg.T, negate=1, terms="tf32")

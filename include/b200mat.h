@@ -149,6 +149,8 @@ int add_scalar(cudamat* mat, float alpha, cudamat* target);                   /*
 /* ---- index operations: cudamat/cudamat.cu:2120-2150 ----------------------------------- */
 int selectRows(cudamat* source, cudamat* target, cudamat* indices);                         /* cudamat.cu:2120 (select_columns) */
 int swapColumns(cudamat* source, cudamat* target, cudamat* indices1, cudamat* indices2);   /* cudamat.cu:2138 */
+int copy_transpose(cudamat* source, cudamat* target);                                       /* cudamat.cu:271 */
+int normlimit_by_axis(cudamat* mat, cudamat* target, int axis, float norm);                 /* cudamat.cu:1289 (axis 0 only, as there) */
 
 /* ---- matrix product: cudamat/cudamat.cu:1671-1696 (cublasSgemm) ---------------------- */
 /* target = beta * target + alpha * op(mat1) . op(mat2); tcgen05 split-TF32 when the
@@ -262,6 +264,13 @@ int b200_event_record(void* ev);
 float b200_event_elapsed_ms(void* start, void* end);  /* blocks until `end`; < 0 on error */
 void b200_event_destroy(void* ev);
 int b200_read_status(void);               /* non-zero: a kernel's bounded wait gave up (blocks, clears) */
+/* Iterations a device-side wait may spin before its kernel gives up (default 2^24, one to two
+ * seconds; 0 restores the default).  No counterpart in the reference. */
+int b200_set_wait_limit(unsigned int iterations);
+/* Test hook, host side only: the next tensor-core product expects extra_bytes more per stage than
+ * its copies deliver, so one of its bounded waits must run out (status word set, kernel returns).
+ * No counterpart in the reference. */
+int b200_test_inject_stage_bytes(int extra_bytes);
 int b200_set_gemm_path(int path);         /* 0 auto, 1 tensor cores only, 2 CUDA cores only */
 int b200_set_dot_precision(int mode);     /* 0 fp32-grade split TF32 (default), 1 one TF32 pass */
 int set_rng_column_offset(int col0);      /* first global minibatch column of this process */

@@ -257,6 +257,28 @@ class EigenMatrix(object):
     def euclid_norm(self):
         return float(_lib.euclid_norm(self.p_mat))
 
+    def norm_limit(self, norm, axis, target=None):
+        """Columns whose Euclidean norm exceeds `norm` are scaled back to it.  eigenmat leaves this
+        unimplemented (eigenmat/eigenmat.cc:761-767 returns an error), so the cudamat kernel's
+        meaning is restated (cudamat/cudamat_kernels.cu:1068-1088): float32 sum of squares per
+        column, factor 1 when the norm is below the limit, else norm / length."""
+        if axis != 0:
+            raise EigenMatException("norm_limit is defined along axis 0 only (cudamat/cudamat.cu:1310)")
+        target = target or self
+        a = self.numpy_array
+        length = np.sqrt((a.astype(np.float32) ** 2).sum(axis=0, dtype=np.float32)).astype(np.float32)
+        f = np.where(length < np.float32(norm), np.float32(1), np.float32(norm) / length).astype(np.float32)
+        target.numpy_array[...] = a * f[None, :]
+        return target
+
+    def transpose(self, target=None):
+        """eigenmat/eigenmat.py:307-318 (copy_transpose): target = self' as a new dense matrix."""
+        h, w = self.numpy_array.shape
+        if target is None:
+            target = empty((w, h))
+        target.numpy_array[...] = self.numpy_array.T
+        return target
+
     def apply_softmax(self, target=None):
         target = target or self
         _check(_lib.apply_softmax(self.p_mat, target.p_mat))

@@ -36,7 +36,8 @@ def main():
     b = gb // world
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, b, cfg["edges"][0]["weight"], cfg["hyperparams"],
-                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"], world_size=world, rank=rank)
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"], world_size=world,
+                   rank=rank)
     data = cm.CUDAMatrix(cfg["data"])
     for step in range(3):
         s = step * gb + rank * b

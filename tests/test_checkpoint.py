@@ -140,7 +140,7 @@ def test_trained_rbm_survives_a_checkpoint(cm, tmp_path):
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     B = cfg["batchsize"]
     mk = lambda w: FusedRBM(cm, V, H, B, w, cfg["hyperparams"], edge_hyperparams=cfg["edges"][0].get("hyperparams"),
-                            seed=cfg["seed"])
+                            binary_data=True, seed=cfg["seed"])
     eng = mk(cfg["edges"][0]["weight"])
     data = cm.CUDAMatrix(cfg["data"])
     for step in range(3):

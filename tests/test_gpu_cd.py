@@ -110,6 +110,41 @@ def test_fused_engine_matches_oracle(cm, oracle, config, scale, cases, form, gib
     assert cm.read_status() == 0
 
 
+@pytest.mark.parametrize("form", ["derived", "bf16 aux", "f16"])
+@pytest.mark.parametrize("branch", ["sample_input", "step_up_cd"])
+def test_fused_engine_follows_the_step_schedules(cm, oracle, form, branch, monkeypatch):
+    """deepnet/dbm.py:202-208 (a Gibbs step more every step_up_cd_after updates) and :217-222 (the
+    visible layer feeds its Bernoulli draw upward): same random stream as the call-by-call driver."""
+    monkeypatch.setenv("B200_RBM_STATE_AUX", "0" if form == "derived" else "1")
+    monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
+    cases, steps = 300, 3
+    cfg = configs.build(0, cases=cases, dims_scale=0.25)
+    hyp = cfg["hyperparams"]
+    if branch == "sample_input":
+        hyp.sample_input, hyp.sample_input_after, hyp.gibbs_steps = True, 1, 2     # means at step 0, draws from step 1
+    else:
+        hyp.start_step_up_cd_after, hyp.step_up_cd_after = 1, 1                    # 1, 1, 3 Gibbs steps
+    B = cfg["batchsize"]
+    mo, lo = run_driver(oracle, cfg, cases, steps)
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], hyp, edge_hyperparams=cfg["edges"][0].get("hyperparams"),
+                   binary_data=True, seed=cfg["seed"])
+    data = cm.CUDAMatrix(cfg["data"])
+    lg = []
+    for step in range(steps):
+        eng.TrainOneBatch(step, data.slice(step * B, (step + 1) * B))
+        lg.append(eng.read_loss())
+    np.testing.assert_allclose(lg, lo, rtol=1e-5)
+    assert cm.CUDAMatrix.rnd_state.calls == oracle._Rng.calls                      # same number of sampling calls
+    assert relerr(get(eng.W), get(mo.edge[0].params["weight"])) < TOL
+    assert relerr(get(eng.h_neg), get(mo.GetLayerByName("h").state)) < TOL
+    assert relerr(get(eng.v_neg), get(mo.GetLayerByName("v").state)) < TOL
+    np.testing.assert_array_equal(get(eng.h_samp), get(mo.GetLayerByName("h").sample))
+    if branch == "sample_input" and form != "f16":                                 # (the f16 form keeps only the draw's 16-bit plane)
+        np.testing.assert_array_equal(get(eng.v_samp), get(mo.GetLayerByName("v").sample))
+    assert cm.read_status() == 0
+
+
 def test_half_precision_engine_from_zero_weights(cm, oracle, monkeypatch):
     """W's exponent follows the weights from nothing to their first values (the update gathers the
     largest |W| and writes the half-precision form with the exponent that fits it)."""
@@ -121,7 +156,7 @@ def test_half_precision_engine_from_zero_weights(cm, oracle, monkeypatch):
     mo, lo = run_driver(oracle, cfg, 300, steps)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
-                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"])
     assert eng.f16
     data = cm.CUDAMatrix(cfg["data"])
     lg = []
@@ -179,7 +214,7 @@ def test_fused_engine_replicated_softmax_matches_oracle(cm, oracle, scale):
     mo, lo = run_driver(oracle, cfg, cases, steps)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"], visible=dbm.REPLICATED_SOFTMAX,
-                   seed=cfg["seed"])
+                   binary_data=True, seed=cfg["seed"])
     data = cm.CUDAMatrix(cfg["data"])
     lg = []
     for step in range(steps):
@@ -252,7 +287,7 @@ def test_reconstruction_error_curve_within_two_percent(cm, oracle, form, monkeyp
     _, lo = run_driver(oracle, cfg, cases, steps)
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
-                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"])
     data = cm.CUDAMatrix(cfg["data"])
     lg = []
     for step in range(steps):
@@ -285,7 +320,7 @@ def test_full_size_properties(cm):
     p = rng.beta(0.3, 2.0, size=(V, 1)).astype(np.float32)
     x = (rng.random((V, B), dtype=np.float32) < p).astype(np.float32)
     hyp = dbm.Hyperparams(base_epsilon=0.05, initial_momentum=0.9, final_momentum=0.9, gibbs_steps=10)
-    eng = FusedRBM(cm, V, H, B, W, hyp, seed=3004)
+    eng = FusedRBM(cm, V, H, B, W, hyp, binary_data=True, seed=3004)
     assert eng.f16                       # at this size every product runs on scaled half-precision operands
     data = cm.CUDAMatrix(x)
     eng.TrainOneBatch(0, data)

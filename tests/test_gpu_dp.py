@@ -37,7 +37,7 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, monkeypatch):
     gb = cfg["batchsize"]
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, gb, cfg["edges"][0]["weight"], cfg["hyperparams"],
-                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), seed=cfg["seed"])
+                   edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"])
     assert eng.f16 == (form == "f16")
     data = cm.CUDAMatrix(cfg["data"])
     for step in range(3):

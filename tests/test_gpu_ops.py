@@ -204,3 +204,29 @@ def test_views_slices_reshape_and_errors(cm):
     g.overwrite(np.ones((20, 12)))
     assert (get(g) == 1).all()
     assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(33, 17), (500, 784), (1024, 4096), (1, 5)])
+def test_transpose_copy_and_norm_limit(cm, oracle, shape):
+    # cudamat/cudamat.py:422-433 (copy_transpose) and :1000-1016 (normlimit_by_axis, axis 0)
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(shape).astype(np.float32)
+    g = cm.CUDAMatrix(x)
+    np.testing.assert_array_equal(get(g.transpose()), x.T)
+    limit = float(np.median(np.sqrt((x.astype(np.float64) ** 2).sum(axis=0))))
+    got = get(g.norm_limit(limit, axis=0, target=cm.empty(shape)))
+    want = oracle.EigenMatrix(x).norm_limit(limit, axis=0, target=oracle.empty(shape)).asarray()
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-7)
+    lengths = np.sqrt((got.astype(np.float64) ** 2).sum(axis=0))
+    assert lengths.max() <= limit * (1 + 1e-5)
+    with pytest.raises(cm.CUDAMatException):
+        g.norm_limit(limit, axis=1)
+
+
+def test_ones_vector_is_filled_at_start_up(cm):
+    # cudamat/cudamat.py:1879-1885: callers take sums as products with CUDAMatrix.ones
+    assert cm.CUDAMatrix.ones is not None and cm.CUDAMatrix.ones.shape == (1024 * 256, 1)
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    s = cm.dot(cm.CUDAMatrix(x), cm.CUDAMatrix(np.ones((4, 1), np.float32)))
+    np.testing.assert_allclose(get(s).ravel(), x.sum(axis=1))
+    assert float(np.array(cm.CUDAMatrix.ones.asarray()).min()) == 1.0

@@ -260,3 +260,11 @@ def test_cd1_step_matches_the_reference_numpy_twin(oracle):
     assert np.abs(e.params["weight"].asarray() - twin["new"][0]).max() < 1e-6
     assert np.abs(lv.params["bias"].asarray() - twin["new"][1]).max() < 1e-6
     assert np.abs(lh.params["bias"].asarray() - twin["new"][2]).max() < 1e-6
+
+
+def test_norm_limit_follows_the_cudamat_kernel(oracle):
+    # cudamat/cudamat_kernels.cu:1068-1088: factor 1 below the limit, norm / length above it
+    x = np.array([[3, 0.3], [4, 0.4]], np.float32)
+    y = oracle.EigenMatrix(x).norm_limit(1.0, axis=0, target=oracle.empty((2, 2))).asarray()
+    np.testing.assert_allclose(y, np.array([[0.6, 0.3], [0.8, 0.4]], np.float32), rtol=1e-6)
+    np.testing.assert_array_equal(oracle.EigenMatrix(x).transpose().asarray(), x.T)
