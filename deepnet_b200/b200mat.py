@@ -476,6 +476,13 @@ class CUDAMatrix(object):
         _check(_lib.softmax_scaled(self.p_mat, scale.p_mat, target.p_mat))
         return target
 
+    def softmax_sample(self, state, sample=None, bias=None):
+        """state = softmax over each column of self (+ bias); sample = one categorical draw per column
+        as a one-hot (deepnet/softmax_layer.py:11-16 in one kernel, one sampling call)."""
+        _check(_lib.softmax_sample(CUDAMatrix.rnd_state_p, self.p_mat, bias.p_mat if bias is not None else None,
+                                   state.p_mat, sample.p_mat if sample is not None else None))
+        return state
+
     def sample_multinomial(self, nn, target, max_draws=1000):
         """target[:, i] = counts of int(nn[i]) draws from self[:, i] (replicated_softmax_layer.py:43-60 fused)."""
         _check(_lib.sample_multinomial(CUDAMatrix.rnd_state_p, self.p_mat, nn.p_mat, target.p_mat, ct.c_int(max_draws)))
@@ -889,3 +896,8 @@ def dp_check():
 
 def dp_destroy():
     _lib.dp_destroy()
+
+
+def dp_abort():
+    """Tears the communicator down without waiting for collectives in flight (a peer is gone)."""
+    _lib.dp_abort()

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restr
                                                             unsigned long long call0) {
   __shared__ float sv[4][8];
   __shared__ int si[4][8];
-  const int doc = blockIdx.y;
+  for (int doc = blockIdx.y; doc < w; doc += gridDim.y) {
   int ndraws = (int)nn[doc];
   if (ndraws > max_draws) ndraws = max_draws;
   const float* p = probs + (long)doc * h;
@@ -125,6 +125,83 @@ __global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restr
         atomicAdd(&counts[(long)doc * h + i], 1.0f);   // choose_max one-hot summed over the draws
       }
     }
+    __syncthreads();   // sv / si are reused by the next block of draws
+  }
+  }
+}
+
+// Column softmax and one categorical draw per column in one kernel: the label layer of a DBM
+// (deepnet/softmax_layer.py:11-16: apply_softmax, then perturb_prob_for_softmax_sampling and
+// choose_max(axis=0)).  state = softmax(pre) (optionally after adding a per-row bias), sample =
+// one-hot of argmax_r state[r] / (-log u[r]) with u the uniforms of element (r, global column) of
+// this sampling call, the first maximum winning: what the three calls give on the same stream.
+__global__ void __launch_bounds__(128) k_softmax_sample(const float* pre, const float* __restrict__ bias, float* state,
+                                                        float* sample, int h, int w, int col0, PhiloxKey key) {
+  __shared__ float red[4];
+  __shared__ int redi[4];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int c = blockIdx.x; c < w; c += gridDim.x) {
+    const float* col = pre + (long)c * h;
+    float* st = state + (long)c * h;
+    float mx = -INFINITY;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) mx = fmaxf(mx, col[r] + (bias ? bias[r] : 0.0f));
+    mx = warp_max_f(mx);
+    __syncthreads();
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    mx = warp_max_f(lane < nw ? red[lane] : -INFINITY);
+    float s = 0;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      const float e = expf(col[r] + (bias ? bias[r] : 0.0f) - mx);
+      st[r] = e;
+      s += e;
+    }
+    s = warp_sum_f(s);
+    __syncthreads();
+    if (lane == 0) red[wid] = s;
+    __syncthreads();
+    s = warp_sum_f(lane < nw ? red[lane] : 0.0f);
+    const int gc = c + col0;                       // global column: which Philox block and word
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      const float pr = st[r] / s;                  // apply_softmax divides (cudamat_kernels.cu:868)
+      st[r] = pr;
+      if (sample) {
+        const uint4 wd = philox4x32_10((uint32_t)r, (uint32_t)(gc >> 2), key);
+        const float v = -pr / logf(word_to_uniform(pick_word(wd, gc & 3)));
+        if (v > bv || (v == bv && r < bi)) {
+          bv = v;
+          bi = r;
+        }
+      }
+    }
+    if (!sample) continue;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (v2 > bv || (v2 == bv && i2 < bi)) {
+        bv = v2;
+        bi = i2;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      red[wid] = bv;
+      redi[wid] = bi;
+    }
+    __syncthreads();
+    bv = red[0];
+    bi = redi[0];
+    for (int q = 1; q < nw; q++)
+      if (red[q] > bv || (red[q] == bv && redi[q] < bi)) {
+        bv = red[q];
+        bi = redi[q];
+      }
+    if (bi == 0x7fffffff) bi = 0;                  // all-NaN column: the sequential scan keeps row 0
+    float* sm = sample + (long)c * h;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) sm[r] = r == bi ? 1.0f : 0.0f;
   }
 }
 
@@ -159,8 +236,31 @@ int sample_multinomial(rnd_struct* rnd_state, cudamat* probs, cudamat* nn, cudam
   rnd_state->calls += (unsigned long long)w;
   int groups = (max_draws + 3) / 4 + 1;
   if (groups > 64) groups = 64;
-  k_sample_multinomial<<<dim3(groups, w), 256, 0, stream()>>>(probs->data_device, nn->data_device, target->data_device,
+  k_sample_multinomial<<<dim3(groups, w < 65535 ? w : 65535), 256, 0, stream()>>>(probs->data_device, nn->data_device, target->data_device,
                                                               h, w, max_draws, rng_col0(), rnd_state->seed, call0);
+  return check_launch();
+}
+
+// state[:, j] = softmax(pre[:, j] (+ bias)); sample[:, j] = one categorical draw from it as a one-hot
+// column (sample may be null: activation only, no sampling call consumed).  pre and state may be
+// the same matrix.  One sampling call, the one perturb_prob_for_softmax_sampling would consume.
+int softmax_sample(rnd_struct* rnd_state, cudamat* pre, cudamat* bias, cudamat* state, cudamat* sample) {
+  if (!pre->on_device || !state->on_device || (sample && !sample->on_device) || (bias && !bias->on_device))
+    return ERROR_NOT_ON_DEVICE;
+  if (pre->is_trans || state->is_trans || (sample && sample->is_trans)) return ERROR_TRANSPOSED;
+  if (!same_shape(pre, state) || (sample && !same_shape(pre, sample))) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (bias && numel(bias) != pre->size[0]) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = pre->size[0], w = pre->size[1];
+  PhiloxKey key = make_philox_key(0, 0);
+  if (sample) {
+    if (!rnd_state) return ERROR_GENERIC;
+    key = make_philox_key(rnd_state->seed, rnd_state->calls);
+    rnd_state->calls += 1;
+  }
+  if ((long)h * w == 0) return 0;
+  k_softmax_sample<<<w < sm_count() * 16 ? w : sm_count() * 16, 128, 0, stream()>>>(
+      pre->data_device, bias ? bias->data_device : nullptr, state->data_device, sample ? sample->data_device : nullptr,
+      h, w, rng_col0(), key);
   return check_launch();
 }
 

@@ -18,7 +18,7 @@ benchmark configurations and are not restated.
 """
 import numpy as np
 
-LOGISTIC, LINEAR, REPLICATED_SOFTMAX = "LOGISTIC", "LINEAR", "REPLICATED_SOFTMAX"
+LOGISTIC, LINEAR, REPLICATED_SOFTMAX, SOFTMAX = "LOGISTIC", "LINEAR", "REPLICATED_SOFTMAX", "SOFTMAX"
 CD, PCD = "CD", "PCD"
 
 
@@ -293,7 +293,43 @@ class ReplicatedSoftmaxLayer(Layer):
         self.state.mult_by_row(self.NN)
 
 
-_LAYER_TYPES = {LOGISTIC: LogisticLayer, LINEAR: LinearLayer, REPLICATED_SOFTMAX: ReplicatedSoftmaxLayer}
+class SoftmaxLayer(Layer):
+    """deepnet/softmax_layer.py: one softmax over `numdims` labels per case (dimensions = 1, the
+    label layer of deepnet/examples/dbm/model.pbtxt:57-81).  As an input its data is a 1 x batch
+    row of label indices, expanded to one-hot columns (:35-36)."""
+    activation = SOFTMAX
+
+    def AllocateMemory(self, batchsize):
+        super(SoftmaxLayer, self).AllocateMemory(batchsize)
+        cm, n = self.cm, self.numdims
+        self.expansion_matrix = cm.CUDAMatrix(np.eye(n, dtype=np.float32))
+        self.deriv = cm.CUDAMatrix(np.zeros((n, batchsize), np.float32))
+        if self.is_input:
+            self.data = cm.CUDAMatrix(np.zeros((1, batchsize), np.float32))
+
+    def ApplyActivation(self):
+        """:11-12."""
+        self.state.apply_softmax()
+
+    def Sample(self):
+        """:14-16: one categorical draw per column by the exponential race, as a one-hot."""
+        self.state.perturb_prob_for_softmax_sampling(target=self.sample)
+        self.sample.choose_max(axis=0)
+
+    def GetData(self):
+        """:35-36."""
+        self.expansion_matrix.select_columns(self.data, target=self.state)
+
+    def GetLoss(self):
+        """:86-89 (SQUARED_LOSS): deriv = state - onehot(label) (apply_softmax_grad,
+        cudamat/cudamat_kernels.cu:819-825), error = its squared norm."""
+        self.expansion_matrix.select_columns(self.data, target=self.deriv)
+        self.state.subtract(self.deriv, target=self.deriv)
+        return self.deriv.euclid_norm() ** 2
+
+
+_LAYER_TYPES = {LOGISTIC: LogisticLayer, LINEAR: LinearLayer, REPLICATED_SOFTMAX: ReplicatedSoftmaxLayer,
+                SOFTMAX: SoftmaxLayer}
 
 
 class Edge(Parameter):

@@ -242,6 +242,12 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
  * share the array, so calls that overlap on the GPU race; issue them in order on one stream. */
 int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult);
 
+/* state[:, j] = softmax(pre[:, j] + bias); sample[:, j] = one categorical draw from it as a one-hot
+ * column: deepnet/softmax_layer.py:11-16 (apply_softmax, perturb_prob_for_softmax_sampling,
+ * choose_max(axis=0)) in one kernel on the same random stream.  bias and sample may be null
+ * (no sampling call is consumed without sample). */
+int softmax_sample(rnd_struct* rnd_state, cudamat* pre, cudamat* bias, cudamat* state, cudamat* sample);
+
 /* target[:, j] = scale[j] * softmax(mat[:, j]): the six calls of
  * deepnet/replicated_softmax_layer.py:12-21 (max, add_row_mult, exp, sum, divide, mult_by_row). */
 int softmax_scaled(cudamat* mat, cudamat* scale, cudamat* target);

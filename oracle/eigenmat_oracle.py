@@ -30,7 +30,9 @@ def build(force=False):
     so = os.path.join(_HERE, "liboracle.so")
     src = os.path.join(_HERE, "eigenmat_port.c")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
-        subprocess.check_call(["make", "-s", "-C", _HERE])
+        # the reference project, when present, sits next to this repository (or where DEEPNET_REFERENCE says)
+        ref = os.environ.get("DEEPNET_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
+        subprocess.check_call(["make", "-s", "-C", _HERE, "REF=" + (ref if os.path.isdir(ref) else "")])
     return so
 
 

@@ -49,4 +49,12 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        # do not leave the peer waiting in a collective this rank will never join
+        try:
+            from deepnet_b200 import b200mat
+            b200mat._lib.dp_abort()
+        finally:
+            raise

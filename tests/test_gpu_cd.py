@@ -375,3 +375,83 @@ def test_full_size_properties(cm):
     eng.TrainOneBatch(1, data)
     np.testing.assert_array_equal(get(eng.W), W1)
     assert cm.read_status() == 0
+
+
+def joint_dbm_spec(seed=11, cases=120, B=40, sizes=(64, 48, 40, 32), labels=10):
+    """A small DBM shaped like deepnet/examples/dbm/model.pbtxt: input - hidden1 - hidden2 - joint hidden,
+    with a softmax label layer (a second input) attached to the joint layer (:57-81, :138-140)."""
+    from deepnet_b200 import synthetic
+    rng = np.random.default_rng(seed)
+    V, H1, H2, J = sizes
+    hyp = dbm.Hyperparams(base_epsilon=0.01, initial_momentum=0.5, final_momentum=0.9, momentum_change_steps=100,
+                          apply_l2_decay=True, l2_decay=1e-4, mf_steps=5, gibbs_steps=5)
+    layers = [dict(name="input_layer", activation=dbm.LOGISTIC, numdims=V, is_input=True),
+              # an input layer feeds its means upward unless sample_input is set (deepnet/dbm.py:217-222)
+              dict(name="label_layer", activation=dbm.SOFTMAX, numdims=labels, is_input=True,
+                   hyperparams=hyp.copy(sample_input=True)),
+              dict(name="hidden1", activation=dbm.LOGISTIC, numdims=H1),
+              dict(name="hidden2", activation=dbm.LOGISTIC, numdims=H2),
+              dict(name="joint_hidden", activation=dbm.LOGISTIC, numdims=J)]
+    w = lambda r, c: (rng.standard_normal((r, c)) * 0.05).astype(np.float32)
+    edges = [dict(node1="input_layer", node2="hidden1", weight=w(V, H1)),
+             dict(node1="hidden1", node2="hidden2", weight=w(H1, H2)),
+             dict(node1="hidden2", node2="joint_hidden", weight=w(H2, J)),
+             dict(node1="label_layer", node2="joint_hidden", weight=w(labels, J))]
+    data, _ = synthetic.binary_data(V, cases, seed)
+    lab = rng.integers(0, labels, (1, cases)).astype(np.float32)
+    return dict(layers=layers, edges=edges, hyp=hyp, B=B, data=data, labels=lab, seed=seed)
+
+
+def run_joint_dbm(backend, spec, steps):
+    m = dbm.DBM(backend, spec["layers"], spec["edges"], spec["hyp"], spec["B"], dbm.PCD, seed=spec["seed"])
+    data, lab = backend.CUDAMatrix(spec["data"]), backend.CUDAMatrix(spec["labels"])
+    B, losses = spec["B"], []
+    for step in range(steps):
+        m.SetBatch([data.slice(step * B, (step + 1) * B), lab.slice(step * B, (step + 1) * B)])
+        losses.append(m.TrainOneBatch(step))
+    return m, losses
+
+
+def test_dbm_with_softmax_label_layer_matches_oracle(cm, oracle):
+    """deepnet/softmax_layer.py on the path: the label layer is clamped to one-hot labels in the
+    positive phase, reconstructed through a softmax, and drawn categorically in every Gibbs sweep."""
+    spec = joint_dbm_spec()
+    mg, lg = run_joint_dbm(cm, spec, 3)
+    mo, lo = run_joint_dbm(oracle, spec, 3)
+    np.testing.assert_allclose(lg, lo, rtol=1e-5)                     # both inputs' reconstruction errors
+    assert cm.CUDAMatrix.rnd_state.calls == oracle._Rng.calls
+    lab_g, lab_o = mg.GetLayerByName("label_layer"), mo.GetLayerByName("label_layer")
+    np.testing.assert_array_equal(get(lab_g.neg_sample), get(lab_o.neg_sample))       # categorical draws
+    assert np.array_equal(get(lab_g.neg_sample).sum(axis=0), np.ones(spec["B"]))      # one label per case
+    assert relerr(get(lab_g.neg_state), get(lab_o.neg_state)) < TOL                   # softmax probabilities
+    for eg, eo in zip(mg.edge, mo.edge):
+        assert relerr(get(eg.params["weight"]), get(eo.params["weight"])) < TOL, eg.name
+    for l_g, l_o in zip(mg.layer, mo.layer):
+        assert relerr(get(l_g.pos_state), get(l_o.pos_state)) < TOL, l_g.name
+        if l_g.name != "input_layer":
+            np.testing.assert_array_equal(get(l_g.neg_sample), get(l_o.neg_sample))
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("labels,B", [(10, 100), (1000, 37), (4, 5)])
+def test_fused_softmax_and_categorical_draw_match_the_call_sequence(cm, oracle, labels, B):
+    rng = np.random.default_rng(labels)
+    pre = (rng.standard_normal((labels, B)) * 2).astype(np.float32)
+    bias = rng.standard_normal((labels, 1)).astype(np.float32)
+    # the reference's calls on the oracle: add_col_vec, apply_softmax, perturb_prob, choose_max
+    oracle.EigenMatrix.init_random(9)
+    st = oracle.EigenMatrix(pre)
+    st.add_col_vec(oracle.EigenMatrix(bias))
+    st.apply_softmax()
+    smp = oracle.empty((labels, B))
+    st.perturb_prob_for_softmax_sampling(target=smp)
+    smp.choose_max(axis=0)
+    cm.CUDAMatrix.init_random(9)
+    g_state, g_smp = cm.empty((labels, B)), cm.empty((labels, B))
+    cm.CUDAMatrix(pre).softmax_sample(g_state, g_smp, bias=cm.CUDAMatrix(bias))
+    assert relerr(get(g_state), get(st)) < TOL
+    np.testing.assert_array_equal(get(g_smp), get(smp))
+    assert cm.CUDAMatrix.rnd_state.calls == 1
+    # activation only: no sampling call consumed
+    cm.CUDAMatrix(pre).softmax_sample(g_state, None)
+    assert cm.CUDAMatrix.rnd_state.calls == 1

@@ -25,8 +25,16 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, monkeypatch):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path)], env=env)
              for r in range(2)]
-    for p in procs:
-        assert p.wait(timeout=300) == 0
+    try:
+        codes = [p.wait(timeout=300) for p in procs]
+    finally:
+        # a rank that outlives a failed or timed-out peer would sit in its all-reduce on a shared
+        # GPU: no child is left behind, whatever happened above
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+                p.wait()
+    assert codes == [0, 0]
     r0, r1 = (np.load(os.path.join(tmp_path, "rank%d.npz" % r)) for r in range(2))
     assert int(r0["status"]) == 0 and int(r1["status"]) == 0
     assert np.array_equal(r0["W"], r1["W"])                 # replicas stay bit-identical

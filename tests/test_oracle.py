@@ -268,3 +268,32 @@ def test_norm_limit_follows_the_cudamat_kernel(oracle):
     y = oracle.EigenMatrix(x).norm_limit(1.0, axis=0, target=oracle.empty((2, 2))).asarray()
     np.testing.assert_allclose(y, np.array([[0.6, 0.3], [0.8, 0.4]], np.float32), rtol=1e-6)
     np.testing.assert_array_equal(oracle.EigenMatrix(x).transpose().asarray(), x.T)
+
+
+def test_softmax_label_layer_step_runs_on_the_oracle(oracle):
+    """The DBM with a softmax label layer (deepnet/softmax_layer.py) through the call-by-call driver:
+    one-hot clamping, softmax reconstruction summing to one, one categorical draw per case."""
+    from deepnet_b200 import dbm, synthetic
+    rng = np.random.default_rng(2)
+    V, H, L, B = 24, 16, 5, 12
+    hyp = dbm.Hyperparams(base_epsilon=0.05, mf_steps=2, gibbs_steps=2)
+    # an input layer feeds its means upward unless sample_input is set (deepnet/dbm.py:217-222)
+    layers = [dict(name="v", activation=dbm.LOGISTIC, numdims=V, is_input=True),
+              dict(name="y", activation=dbm.SOFTMAX, numdims=L, is_input=True, hyperparams=hyp.copy(sample_input=True)),
+              dict(name="h", activation=dbm.LOGISTIC, numdims=H)]
+    edges = [dict(node1="v", node2="h", weight=(rng.standard_normal((V, H)) * 0.1).astype(np.float32)),
+             dict(node1="y", node2="h", weight=(rng.standard_normal((L, H)) * 0.1).astype(np.float32))]
+    m = dbm.DBM(oracle, layers, edges, hyp, B, dbm.PCD, seed=4)
+    data, _ = synthetic.binary_data(V, B, 3)
+    lab = rng.integers(0, L, (1, B)).astype(np.float32)
+    m.SetBatch([oracle.CUDAMatrix(data), oracle.CUDAMatrix(lab)])
+    losses = m.TrainOneBatch(0)
+    assert len(losses) == 2 and all(np.isfinite(losses))
+    y = m.GetLayerByName("y")
+    onehot = np.zeros((L, B), np.float32)
+    onehot[lab[0].astype(int), np.arange(B)] = 1
+    # the positive state is the reconstruction at this point: columns of a softmax sum to one
+    np.testing.assert_allclose(y.pos_state.asarray().sum(axis=0), np.ones(B), rtol=1e-5)
+    assert abs(losses[1] - ((y.pos_state.asarray() - onehot) ** 2).sum()) < 1e-4
+    s = y.neg_sample.asarray()
+    assert set(np.unique(s)) <= {0.0, 1.0} and np.array_equal(s.sum(axis=0), np.ones(B))
