@@ -811,6 +811,11 @@ def set_dot_precision(mode):
     _lib.b200_set_dot_precision(ct.c_int(mode))
 
 
+def set_split_k(mode):
+    """Split-K of the tensor-core product: 0 automatic (default), 1 never, n > 1 always n splits."""
+    _lib.b200_set_split_k(ct.c_int(mode))
+
+
 def set_rng_column_offset(col0):
     _check(_lib.set_rng_column_offset(ct.c_int(col0)))
 

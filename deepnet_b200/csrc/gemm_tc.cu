@@ -99,6 +99,9 @@ struct TcParams {
   int num_stages;          // ring depth
   uint32_t stage_bytes;    // ring pitch
   int chunk_iters;         // k-blocks per TMEM accumulation chunk (128 products)
+  int splits;              // > 1: split-K: work item = (tile, split); split s multiplies k-blocks [ki*s/splits, ki*(s+1)/splits)
+                           //      of every group and stores its raw fp32 partial at epi.out + s * split_stride
+  long split_stride;       // floats between two partials
   int direct;              // 1: no group derives anything: the copies of both CTAs complete on the leader's `ready`
                            //    barrier and the converter warps stay out of the way
   GemmEpilogue epi;
@@ -427,7 +430,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int splits = p.splits;
+  const int num_tiles = p.tiles_m * p.tiles_n * splits;     // work items: every role walks the same list
   const uint32_t rank = kTwo ? cluster_ctarank() : 0u;        // 0 = leader of the pair
   const int first_tile = kTwo ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = kTwo ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -463,9 +467,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  int total_k_iters = 0;
-  for (int q = 0; q < p.ngroups; q++) total_k_iters += p.group[q].k_iters;
   const int kChunkIters = p.chunk_iters;
+  // k-blocks of group q that split s multiplies (all of them when the product is not split)
+  auto split_range = [&](int q, int s, int& kb0, int& kb1) {
+    const int ki = p.group[q].k_iters;
+    kb0 = (int)(((long)ki * s) / splits);
+    kb1 = (int)(((long)ki * (s + 1)) / splits);
+  };
+  auto item_k_iters = [&](int s) {
+    int n = 0;
+    for (int q = 0; q < p.ngroups; q++) {
+      int kb0, kb1;
+      split_range(q, s, kb0, kb1);
+      n += kb1 - kb0;
+    }
+    return n;
+  };
 
   // Every warpgroup (four warps) passes ONE setmaxnreg instruction, at the top of its branch.
   if (warp < kFirstConvWarp) {
@@ -482,13 +499,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       bool ok = true;
       long long t_empty = 0;
       const bool direct = p.direct != 0;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int w = first_tile; w < num_tiles && ok; w += tile_step) {
+        const int t = w / splits, sp = w - t * splits;
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * TILE_M + (int)rank * BM, n0 = tn * BN + (int)rank * BN_LOCAL;
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
-          const int k_iters = gr.k_iters;
+          int kb_first, kb_last;
+          split_range(q, sp, kb_first, kb_last);
           bool active[2];
           const CUtensorMap* map[2];
           int row0[2], mn[2];
@@ -505,7 +524,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             dst_off[c] = ld.smem_off + (ld.mn ? (uint32_t)(box * bk * 128) : 0u);
             mn[c] = ld.mn;
           }
-          for (int kb = 0; kb < k_iters; kb++) {
+          for (int kb = kb_first; kb < kb_last; kb++) {
             if (!TIMED_WAIT(t_empty, mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, spin_limit))) {
               ok = false;
               if (!abort_flag) atomicCAS(p.status, 0, 1);
@@ -576,11 +595,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
       const long long t_start = clock64();
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int w = first_tile; w < num_tiles && ok; w += tile_step) {
+        const int sp = w % splits;
+        const int total_k_iters = item_k_iters(sp);
         int in_tile = 0, in_chunk = 0;
         uint32_t fresh = 1;
         for (int q = 0; q < p.ngroups && ok; q++) {
           const TcGroup& gr = p.group[q];
+          int kb_first, kb_last;
+          split_range(q, sp, kb_first, kb_last);
           // The issuing thread must launch an MMA every ~70 ns to keep the tensor pipe busy, and what
           // it does between two k-blocks is not hidden behind the pipe: all per-product constants
           // live in registers, the k-loop only adds the stage address, and the common term lists
@@ -589,7 +612,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             constexpr int kNm = decltype(nm_c)::value;       // -1: count and kinds read from the group
             constexpr int kMask = decltype(mask_c)::value;   // bit i: term i is a bfloat16 product
             const int nm = kNm >= 0 ? kNm : gr.nmma;
-            const int k_iters = gr.k_iters;
+            const int k_iters = kb_last - kb_first;
             uint32_t a_lo[kMaxMma], b_lo[kMaxMma], a_hi[kMaxMma], b_hi[kMaxMma], a_adv[kMaxMma], b_adv[kMaxMma],
                 idesc[kMaxMma];
             bool f16[kMaxMma];
@@ -732,10 +755,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     uint32_t phase = 0;
     bool ok = !p.direct;   // nothing to derive anywhere: the copies report to the issuer themselves
     long long t_cfull = 0, t_conv = 0;
-    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+    for (int w = first_tile; w < num_tiles && ok; w += tile_step) {
+      const int sp = w % splits;
       for (int q = 0; q < p.ngroups && ok; q++) {
         const TcGroup& gr = p.group[q];
-        const int k_iters = gr.k_iters, nconv = gr.nconv;
+        int kb_first, kb_last;
+        split_range(q, sp, kb_first, kb_last);
+        const int k_iters = kb_last - kb_first, nconv = gr.nconv;
         const TcConv c0 = gr.conv[0], c1 = gr.conv[1];
         for (int kb = 0; kb < k_iters; kb++) {
           if (!TIMED_WAIT(t_cfull, mbar_wait(full_bar(stage), phase, &abort_flag, spin_limit))) {
@@ -824,10 +850,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
     const float aux_scale = exp2f((float)e.aux_exp);
     const uint16_t aux_one = e.aux_f16 ? __half_as_ushort(__float2half_rn(aux_scale)) : (uint16_t)0x3f80;
     const int pM = p.M, pN = p.N;
-    const int nchunks = (total_k_iters + kChunkIters - 1) / kChunkIters;
     bool ok = true;
     long long t_tfull = 0, t_epi = 0;
-    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+    for (int w = first_tile; w < num_tiles && ok; w += tile_step) {
+      const int t = w / splits, sp = w - t * splits;
+      const int nchunks = (item_k_iters(sp) + kChunkIters - 1) / kChunkIters;
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       float accum[COLS];
@@ -866,7 +893,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       const int nc = tn * BN + col_base;
       if (m < pM && nc < pN) {
         if (kEpi == kEpiPlain) {
-          float* const out = e.out + (long)nc * e.ldo + m;
+          float* const out = e.out + (long)sp * p.split_stride + (long)nc * e.ldo + m;
           const float alpha = e.alpha, beta = e.beta;
           const long ldo = e.ldo;
           const int ncols = pN - nc < COLS ? pN - nc : COLS;
@@ -1169,7 +1196,7 @@ int launch_tc(TcParams& p) {
   constexpr int TILE_M = kTwo ? 2 * BM : BM;
   p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.splits;   // work items
   if (!kTwo) {
     const int grid = tiles < sm_count() ? tiles : sm_count();
     kernel<<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
@@ -1192,6 +1219,40 @@ int launch_tc(TcParams& p) {
   return check_launch();
 }
 
+// Split-K: the partial products of the splits are summed in split order (the same bits every run)
+// and the epilogue runs once per element, on CUDA cores: one thread per row and block of four
+// columns, which share one Philox block exactly as the tensor-core epilogue assigns them.
+__global__ void __launch_bounds__(256) k_splitk_finish(const float* __restrict__ part, int splits, long stride, int M,
+                                                       int N, const GemmEpilogue e) {
+  const int nblk = (N + 3) >> 2;
+  const long items = (long)M * nblk;
+  const bool draw = e.sample != nullptr || e.sample_aux != nullptr;
+  for (long it = (long)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (long)gridDim.x * blockDim.x) {
+    const int b = (int)(it / M), m = (int)(it - (long)b * M);
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (draw) w = philox4x32_10((uint32_t)m, (uint32_t)(b + (e.col0 >> 2)), e.key);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = 4 * b + j;
+      if (n >= N) break;
+      const float* src = part + (long)n * M + m;
+      float acc = 0.0f;
+      for (int sp = 0; sp < splits; sp++) acc += src[(long)sp * stride];
+      epilogue_store(e, acc, m, n, word_to_uniform(pick_word(w, j)));
+    }
+  }
+}
+
+int g_split_mode = 0;   // 0: split when the tiles would leave most SMs idle; 1: never; n > 1: always n splits (tests)
+
+}  // namespace
+
+extern "C" int b200_set_split_k(int mode) {
+  g_split_mode = mode < 0 ? 0 : mode;
+  return 0;
+}
+
+namespace {
 }  // namespace
 
 bool gemm_tc_supported(const GemmProblem& g) {
@@ -1375,7 +1436,46 @@ int gemm_tc(const GemmProblem& g) {
   const int ck = chunk_k >= 16 ? chunk_k : (g.epi.activation == 1 ? 2048 : 128);
   p.chunk_iters = ck / bk < 1 ? 1 : ck / bk;
 
-  const GemmEpilogue& e = g.epi;
+  // Split-K: a product whose tiles would occupy less than half of the SMs and whose inner dimension
+  // is long is cut along K into work items (tile, split); every item stores its raw partial and a
+  // finishing kernel sums them and runs the epilogue.  (Configuration 1's down product, 1024 x 256
+  // with K = 4096, is 4 paired tiles = 8 SMs otherwise.)
+  p.splits = 1;
+  p.split_stride = 0;
+  {
+    const int tile_m = two ? 2 * BM : BM;
+    const int tiles = ((g.M + tile_m - 1) / tile_m) * ((g.N + BN - 1) / BN);
+    const int ctas = two ? 2 * tiles : tiles;
+    int min_ki = p.group[0].k_iters;
+    for (int gi = 1; gi < ngroups; gi++) min_ki = p.group[gi].k_iters < min_ki ? p.group[gi].k_iters : min_ki;
+    int want = 1;
+    if (g_split_mode == 0) {
+      if (ctas * 2 <= sm_count() && min_ki >= 8) {
+        want = sm_count() / ctas;
+        if (want > min_ki / 4) want = min_ki / 4;
+        if (want > 32) want = 32;
+      }
+    } else if (g_split_mode > 1) {
+      want = g_split_mode < min_ki ? g_split_mode : min_ki;
+    }
+    if (want > 1) {
+      float* ws = (float*)workspace(2, (size_t)want * g.M * g.N * sizeof(float));
+      if (!ws) return CUDA_ERROR;
+      p.splits = want;
+      p.split_stride = (long)g.M * g.N;
+      GemmEpilogue& pe = p.epi;       // the kernel stores raw partials; g.epi runs in the finishing kernel
+      pe.alpha = 1.0f;
+      pe.beta = 0.0f;
+      pe.bias = pe.col_scale = nullptr;
+      pe.activation = 0;
+      pe.out = ws;
+      pe.out_aux = pe.sample = pe.sample_aux = nullptr;
+      pe.scale_exp = nullptr;
+      pe.scale_exp_const = 0;
+      pe.ldo = g.M;
+    }
+  }
+  const GemmEpilogue& e = p.epi;
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
     epi = kEpiPlain;
@@ -1409,11 +1509,20 @@ int gemm_tc(const GemmProblem& g) {
     case kEpiLin: return launch_tc<BNV, kEpiLin, TWO>(p);             \
     default: return launch_tc<BNV, kEpiGeneric, TWO>(p);              \
   }
-  if (BN == 256 && two) { B200_TC_CASE(256, true) }
-  if (BN == 256) { B200_TC_CASE(256, false) }
-  if (BN == 128) { B200_TC_CASE(128, false) }
-  B200_TC_CASE(64, false)
+  auto launch = [&]() -> int {
+    if (BN == 256 && two) { B200_TC_CASE(256, true) }
+    if (BN == 256) { B200_TC_CASE(256, false) }
+    if (BN == 128) { B200_TC_CASE(128, false) }
+    B200_TC_CASE(64, false)
+  };
 #undef B200_TC_CASE
+  const int err = launch();
+  if (err || p.splits == 1) return err;
+  const long items = (long)g.M * ((g.N + 3) / 4);
+  long blocks = (items + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  k_splitk_finish<<<(int)blocks, 256, 0, stream()>>>(p.epi.out, p.splits, p.split_stride, g.M, g.N, g.epi);
+  return check_launch();
 }
 
 }  // namespace b200

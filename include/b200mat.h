@@ -279,6 +279,10 @@ int b200_set_wait_limit(unsigned int iterations);
 int b200_test_inject_stage_bytes(int extra_bytes);
 int b200_set_gemm_path(int path);         /* 0 auto, 1 tensor cores only, 2 CUDA cores only */
 int b200_set_dot_precision(int mode);     /* 0 fp32-grade split TF32 (default), 1 one TF32 pass */
+/* Split-K of the tensor-core product: 0 (default) = cut the inner dimension into work items when the
+ * output tiles alone would leave most SMs idle, 1 = never, n > 1 = always n splits.  No counterpart
+ * in the reference. */
+int b200_set_split_k(int mode);
 int set_rng_column_offset(int col0);      /* first global minibatch column of this process */
 void* b200_host_alloc(size_t bytes);      /* pinned host memory */
 void b200_host_free(void* p);
