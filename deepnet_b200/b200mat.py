@@ -748,6 +748,14 @@ def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activat
     with exponent aux_exp.  Replaces the dot / add_dot / add_col_vec / sigmoid /
     sample_bernoulli group of deepnet/dbm.py:88-105.
     """
+    f = _build_fused_gemm(passes, out, sample, bias, col_scale, activation, alpha, beta, out_aux, sample_aux, scale_exp,
+                          scale_exp_const, aux_f16, aux_exp)
+    _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))
+
+
+def _build_fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activation=0, alpha=1.0, beta=0.0,
+                      out_aux=None, sample_aux=None, scale_exp=None, scale_exp_const=0, aux_f16=False, aux_exp=0):
+    """The argument block of `fused_gemm` (it points into the matrices' handles: keep them alive)."""
     f = _FusedGemm()
     f.npass = len(passes)
     if not 0 < f.npass <= MAX_PASS:
@@ -767,7 +775,185 @@ def fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, activat
                     ("out_aux", out_aux), ("sample_aux", sample_aux), ("scale_exp", scale_exp)):
         if m is not None:
             setattr(f, name, m.p_mat)
-    _check(_lib.fused_gemm(CUDAMatrix.rnd_state_p, ct.byref(f)))
+    return f
+
+
+# -- one call per training step ---------------------------------------------------------
+# The operations a training step is made of, under one vocabulary with two executors: `Immediate`
+# issues each through its own library call as it is named; `Program` records them once and
+# replays the whole list from C with a single call per step (b200_run_program), which is what
+# the small configurations need: their kernels are shorter than a call from Python.
+(OP_FUSED_GEMM, OP_SUM_AXIS, OP_ADD_SUM_AXIS, OP_ROW_SUM_DIFF, OP_ADD_SQ_DIFF, OP_MOMENTUM_UPDATE, OP_SPLIT_F16,
+ OP_SPLIT_BF16, OP_ALLREDUCE, OP_SOFTMAX_SCALED, OP_SAMPLE_MULTINOMIAL, OP_DIV_BY_ROW, OP_ADD_SCALAR, OP_ASSIGN_SCALAR,
+ OP_COPY, OP_SAMPLE_BERNOULLI, OP_SOFTMAX_SAMPLE) = range(17)
+
+
+class _Op(ct.Structure):
+    _fields_ = [("kind", ct.c_int), ("i0", ct.c_int), ("i1", ct.c_int), ("i2", ct.c_int),
+                ("f0", ct.c_float), ("f1", ct.c_float), ("f2", ct.c_float), ("f3", ct.c_float), ("f4", ct.c_float),
+                ("m", ct.POINTER(cudamat) * 6), ("gemm", ct.POINTER(_FusedGemm))]
+
+
+_lib.b200_run_program.argtypes = [ct.POINTER(rnd_struct), ct.POINTER(_Op), ct.c_int, ct.POINTER(ct.c_int)]
+
+
+class Immediate(object):
+    """Issues every operation at once, one library call each."""
+
+    launches = {OP_FUSED_GEMM: 1}
+
+    def fused_gemm(self, passes, **kw):
+        fused_gemm(passes, **kw)
+
+    def sum(self, mat, axis, target):
+        sum(mat, axis, target)
+
+    def add_sums(self, target, mat, axis, mult=1.0):
+        target.add_sums(mat, axis, mult)
+
+    def row_sum_diff(self, a, b, target):
+        _check(_lib.row_sum_diff(a.p_mat, b.p_mat, target.p_mat))
+
+    def sq_diff(self, a, b, acc):
+        _check(_lib.add_sq_diff(a.p_mat, b.p_mat, acc.p_mat))
+
+    def momentum_update(self, w, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None, w_scale=None):
+        w.momentum_update(delta, grad, suff, inv_batch, momentum, eps, l2=l2, l1=l1, w_aux=w_aux, w_scale=w_scale)
+
+    def split_f16(self, x, aux, exp_dev=None, exp_const=0):
+        x.split_f16(aux, exp_dev, exp_const)
+
+    def split_bf16(self, x, aux):
+        x.split_bf16(aux)
+
+    def allreduce(self, mat):
+        dp_allreduce(mat)
+
+    def softmax_scaled(self, mat, scale, target):
+        mat.softmax_scaled(scale, target)
+
+    def sample_multinomial(self, probs, nn, target, max_draws=1000):
+        probs.sample_multinomial(nn, target, max_draws)
+
+    def div_by_row(self, mat, vec, target):
+        mat.div_by_row(vec, target)
+
+    def add_scalar(self, mat, val, target=None):
+        mat.add(val, target)
+
+    def assign_scalar(self, mat, val):
+        mat.assign(val)
+
+    def copy(self, src, dst):
+        dst.assign(src)
+
+    def sample_bernoulli(self, mat, target):
+        mat.sample_bernoulli(target)
+
+    def softmax_sample(self, pre, state, sample=None, bias=None):
+        pre.softmax_sample(state, sample, bias)
+
+
+class Program(object):
+    """Records the operations of a step (same methods as `Immediate`), then `run()` replays them
+    with one call.  Every method returns the index of the recorded operation; `set_floats`
+    changes the scalars of one (momentum and learning rate follow their schedules)."""
+
+    def __init__(self):
+        self._ops, self._keep, self._arr = [], [], None
+
+    def _add(self, kind, mats=(), ints=(), floats=(), gemm=None):
+        op = _Op()
+        op.kind = kind
+        for i, m in enumerate(mats):
+            if m is not None:
+                op.m[i] = m.p_mat
+                self._keep.append(m)
+        for name, v in zip(("i0", "i1", "i2"), ints):
+            setattr(op, name, int(v))
+        for name, v in zip(("f0", "f1", "f2", "f3", "f4"), floats):
+            setattr(op, name, float(v))
+        if gemm is not None:
+            op.gemm = ct.pointer(gemm)
+            self._keep.append(gemm)
+        self._ops.append(op)
+        self._arr = None
+        return len(self._ops) - 1
+
+    def fused_gemm(self, passes, **kw):
+        for p in passes:
+            self._keep.extend([p[0], p[1]])
+        self._keep.extend(v for v in kw.values() if isinstance(v, CUDAMatrix))
+        return self._add(OP_FUSED_GEMM, gemm=_build_fused_gemm(passes, **kw))
+
+    def sum(self, mat, axis, target):
+        return self._add(OP_SUM_AXIS, (mat, target), (axis,))
+
+    def add_sums(self, target, mat, axis, mult=1.0):
+        return self._add(OP_ADD_SUM_AXIS, (mat, target), (axis,), (mult,))
+
+    def row_sum_diff(self, a, b, target):
+        return self._add(OP_ROW_SUM_DIFF, (a, b, target))
+
+    def sq_diff(self, a, b, acc):
+        return self._add(OP_ADD_SQ_DIFF, (a, b, acc))
+
+    def momentum_update(self, w, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None, w_scale=None):
+        return self._add(OP_MOMENTUM_UPDATE, (w, delta, grad, suff, w_aux, w_scale), (), (inv_batch, momentum, eps, l2, l1))
+
+    def split_f16(self, x, aux, exp_dev=None, exp_const=0):
+        return self._add(OP_SPLIT_F16, (x, aux, exp_dev), (exp_const,))
+
+    def split_bf16(self, x, aux):
+        return self._add(OP_SPLIT_BF16, (x, aux))
+
+    def allreduce(self, mat):
+        return self._add(OP_ALLREDUCE, (mat,))
+
+    def softmax_scaled(self, mat, scale, target):
+        return self._add(OP_SOFTMAX_SCALED, (mat, scale, target))
+
+    def sample_multinomial(self, probs, nn, target, max_draws=1000):
+        return self._add(OP_SAMPLE_MULTINOMIAL, (probs, nn, target), (max_draws,))
+
+    def div_by_row(self, mat, vec, target):
+        return self._add(OP_DIV_BY_ROW, (mat, vec, target))
+
+    def add_scalar(self, mat, val, target=None):
+        return self._add(OP_ADD_SCALAR, (mat, target or mat), (), (val,))
+
+    def assign_scalar(self, mat, val):
+        return self._add(OP_ASSIGN_SCALAR, (mat,), (), (val,))
+
+    def copy(self, src, dst):
+        return self._add(OP_COPY, (src, dst))
+
+    def sample_bernoulli(self, mat, target):
+        return self._add(OP_SAMPLE_BERNOULLI, (mat, target))
+
+    def softmax_sample(self, pre, state, sample=None, bias=None):
+        return self._add(OP_SOFTMAX_SAMPLE, (pre, bias, state, sample))
+
+    def __len__(self):
+        return len(self._ops)
+
+    def _array(self):
+        if self._arr is None:
+            self._arr = (_Op * len(self._ops))(*self._ops)
+        return self._arr
+
+    def set_floats(self, index, **kw):
+        """kw: f0..f4 of operation `index` (momentum_update: f0 1/batch, f1 momentum, f2 epsilon, f3 l2, f4 l1)."""
+        op = self._array()[index]
+        for k, v in kw.items():
+            setattr(op, k, float(v))
+
+    def run(self):
+        failed = ct.c_int(-1)
+        err = _lib.b200_run_program(CUDAMatrix.rnd_state_p, self._array(), len(self._ops), ct.byref(failed))
+        if err:
+            e = generate_exception(err)
+            raise CUDAMatException("operation %d of the recorded step failed: %s" % (failed.value, e))
 
 
 # -- device / library control -----------------------------------------------------

@@ -491,21 +491,7 @@ float vdot(cudamat* mat1, cudamat* mat2, int* err_code) {
 }
 // acc[0] += sum((a - b)^2) without a host round trip: the squared reconstruction error of
 // deepnet/logistic_layer.py:48-52 (subtract + euclid_norm()**2) kept on the device.
-int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc) {
-  if (!a->on_device || !b->on_device || !acc->on_device) return ERROR_NOT_ON_DEVICE;
-  if (!same_shape(a, b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
-  if (numel(acc) < 1) return ERROR_INCOMPATIBLE_DIMENSIONS;
-  const long n = numel(a);
-  if (n == 0) return 0;
-  int blocks = (int)((n + 255) / 256);
-  const int cap = sm_count() * 8;
-  if (blocks > cap) blocks = cap;
-  double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
-  if (!part) return CUDA_ERROR;
-  k_scalar_partial<<<blocks, 256, 0, stream()>>>(a->data_device, b->data_device, n, 3, part + 1);
-  k_scalar_final<<<1, 256, 0, stream()>>>(part + 1, blocks, nullptr, acc->data_device);
-  return check_launch();
-}
+int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc);   // defined with its single-launch kernel below
 
 // Sum of all elements (cudamat/cudamat.py:719-721 computes it as a vdot with ones).
 float sum_all(cudamat* mat, int* err_code) {
@@ -606,3 +592,192 @@ extern "C" int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, 
   k_rowsum_finish<<<(h + 255) / 256, 256, 0, st>>>(part, target->data_device, h, splits, mult, 1.0f);
   return check_launch_any_stream();
 }
+
+// ---------------------------------------------------------------------------------------
+// Single-launch reductions for the training step.  Both split their input over many blocks and
+// let the block that finishes last fold the partial results, in a fixed order (the same bits
+// every run): no second launch, which at the small configurations costs more than the sums.
+namespace {
+
+// A counter per reduction group, zero between calls (the last block resets it).
+unsigned* ticket_counters(int n) {
+  static unsigned* ptr = nullptr;
+  static int cap = 0;
+  if (n > cap) {
+    const int want = n < 4096 ? 4096 : n;
+    unsigned* p = (unsigned*)workspace(3, (size_t)want * sizeof(unsigned));
+    if (!p) return nullptr;
+    if (cudaMemsetAsync(p, 0, (size_t)want * sizeof(unsigned), stream()) != cudaSuccess) return nullptr;
+    ptr = p;
+    cap = want;
+  }
+  return ptr;
+}
+
+// out[r] = sum_c a[r, c] - sum_c b[r, c].  Block = 32 row lanes x 8 column lanes, kVec rows per
+// lane (4 with 128-bit loads); blockIdx.y splits the columns.
+template <int kVec>
+__global__ void __launch_bounds__(32 * kRowLanes) k_rowsum_diff(const float* __restrict__ a, const float* __restrict__ b,
+                                                                float* __restrict__ part, unsigned* counters,
+                                                                float* __restrict__ out, int h, int w,
+                                                                int cols_per_split) {
+  __shared__ float smem[kRowLanes][32 * kVec + 1];
+  __shared__ bool is_last;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int r = (blockIdx.x * 32 + tx) * kVec;
+  const int c0 = blockIdx.y * cols_per_split;
+  const int c1 = min(w, c0 + cols_per_split);
+  float s[kVec];
+#pragma unroll
+  for (int v = 0; v < kVec; v++) s[v] = 0.0f;
+  if (r < h) {
+    for (int c = c0 + ty; c < c1; c += kRowLanes) {
+      const long o = (long)c * h + r;
+      if (kVec == 4) {
+        const float4 x = *reinterpret_cast<const float4*>(a + o), y = *reinterpret_cast<const float4*>(b + o);
+        s[0] += x.x - y.x; s[1 % kVec] += x.y - y.y; s[2 % kVec] += x.z - y.z; s[3 % kVec] += x.w - y.w;
+      } else {
+        s[0] += a[o] - b[o];
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < kVec; v++) smem[ty][tx * kVec + v] = s[v];
+  __syncthreads();
+  const int splits = gridDim.y;
+  // thread t < 32 * kVec owns row blockIdx.x * 32 * kVec + t of the block
+  const int row = blockIdx.x * 32 * kVec + threadIdx.x;
+  float tot = 0.0f;
+  if (threadIdx.x < 32 * kVec) {
+#pragma unroll
+    for (int j = 0; j < kRowLanes; j++) tot += smem[j][threadIdx.x];
+    if (row < h) {
+      if (splits == 1) out[row] = tot;
+      else part[(long)blockIdx.y * h + row] = tot;
+    }
+  }
+  if (splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&counters[blockIdx.x], 1u) == (unsigned)(splits - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x < 32 * kVec && row < h) {
+    float t = 0.0f;
+    for (int sp = 0; sp < splits; sp++) t += __ldcg(part + (long)sp * h + row);
+    out[row] = t;
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] = 0u;
+}
+
+// acc[0] += sum (a - b)^2: every block leaves a double, the last one folds them.
+__global__ void __launch_bounds__(256) k_sq_diff_acc(const float* __restrict__ a, const float* __restrict__ b, long n,
+                                                     double* __restrict__ part, unsigned* counter, float* acc) {
+  __shared__ double smem[32];
+  __shared__ bool is_last;
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
+  double s = 0;
+  long start = 0;
+  if ((((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+    const long n4 = n >> 2;
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    long i = tid;
+    for (; i + nth < n4; i += 2 * nth) {   // two independent 128-bit load pairs in flight per thread
+      const float4 x0 = a4[i], y0 = b4[i], x1 = a4[i + nth], y1 = b4[i + nth];
+      const float e0 = x0.x - y0.x, e1 = x0.y - y0.y, e2 = x0.z - y0.z, e3 = x0.w - y0.w;
+      const float f0 = x1.x - y1.x, f1 = x1.y - y1.y, f2 = x1.z - y1.z, f3 = x1.w - y1.w;
+      s += (double)((e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3)) + (double)((f0 * f0 + f1 * f1) + (f2 * f2 + f3 * f3));
+    }
+    for (; i < n4; i += nth) {
+      const float4 x = a4[i], y = b4[i];
+      const float d0 = x.x - y.x, d1 = x.y - y.y, d2 = x.z - y.z, d3 = x.w - y.w;
+      s += (double)(d0 * d0 + d1 * d1) + (double)(d2 * d2 + d3 * d3);
+    }
+    start = n4 << 2;
+  }
+  for (long i = start + tid; i < n; i += nth) {
+    const float d = a[i] - b[i];
+    s += (double)d * d;
+  }
+  s = block_sum(s, smem);
+  if (gridDim.x == 1) {
+    if (threadIdx.x == 0) *acc += (float)s;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    part[blockIdx.x] = s;
+    __threadfence();
+    is_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  double t = 0;
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) t += __ldcg(part + i);
+  t = block_sum(t, smem);
+  if (threadIdx.x == 0) {
+    *acc += (float)t;
+    *counter = 0u;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// acc[0] += sum((a - b)^2) without a host round trip: the squared reconstruction error of
+// deepnet/logistic_layer.py:48-52 (subtract + euclid_norm()**2) kept on the device; one launch.
+int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc) {
+  if (!a->on_device || !b->on_device || !acc->on_device) return ERROR_NOT_ON_DEVICE;
+  if (!same_shape(a, b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (numel(acc) < 1) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const long n = numel(a);
+  if (n == 0) return 0;
+  int blocks = (int)((n / 4 + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
+  unsigned* counter = ticket_counters(1);
+  if (!part || !counter) return CUDA_ERROR;
+  k_sq_diff_acc<<<blocks, 256, 0, stream()>>>(a->data_device, b->data_device, n, part + 1, counter, acc->data_device);
+  return check_launch();
+}
+
+// target = row sums of a minus row sums of b, in one launch: the bias statistics of a layer,
+// positive minus negative phase (deepnet/layer.py:202-213: sum(axis=1) then add_sums(axis=1, mult=-1)).
+int row_sum_diff(cudamat* a, cudamat* b, cudamat* target) {
+  if (!a->on_device || !b->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (a->is_trans || b->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(a, b) || numel(target) != a->size[0]) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int h = a->size[0], w = a->size[1];
+  if ((long)h * w == 0) return 0;
+  const bool vec4 = (h % 4 == 0) && (((uintptr_t)a->data_device | (uintptr_t)b->data_device) & 15) == 0;
+  const int rows_per_block = vec4 ? 128 : 32;
+  const int bx = (h + rows_per_block - 1) / rows_per_block;
+  int splits = (8 * sm_count() + bx - 1) / bx;
+  const int max_splits = (w + 31) / 32;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  const int cps = (w + splits - 1) / splits;
+  splits = (w + cps - 1) / cps;
+  float* part = nullptr;
+  unsigned* counters = nullptr;
+  if (splits > 1) {
+    part = (float*)workspace(0, (size_t)splits * h * sizeof(float));
+    counters = ticket_counters(bx + 1);
+    if (!part || !counters) return CUDA_ERROR;
+    counters += 1;   // slot 0 belongs to add_sq_diff
+  }
+  if (vec4)
+    k_rowsum_diff<4><<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(a->data_device, b->data_device, part, counters,
+                                                                       target->data_device, h, w, cps);
+  else
+    k_rowsum_diff<1><<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(a->data_device, b->data_device, part, counters,
+                                                                       target->data_device, h, w, cps);
+  return check_launch();
+}
+
+}  // extern "C"

@@ -26,6 +26,7 @@ own operand reads.
 With more than one rank the sufficient statistics of the ranks' minibatch shards are
 summed by one NCCL all-reduce of a packed buffer before the update.
 """
+import ctypes as ct
 import os
 
 import numpy as np
@@ -78,14 +79,23 @@ class FusedRBM(object):
             self.W_scale = cm.f16_scale_state(float(np.abs(w).max()))
             self.W_exp = self.W_scale.slice(0, 1)
             self.W.split_f16(self.W_aux, exp_dev=self.W_exp)
-        self.bv = cm.CUDAMatrix(np.zeros((V, 1), np.float32) if bias_v is None else np.asarray(bias_v, np.float32).reshape(V, 1))
-        self.bh = cm.CUDAMatrix(np.zeros((H, 1), np.float32) if bias_h is None else np.asarray(bias_h, np.float32).reshape(H, 1))
-        self.dW, self.dbv, self.dbh = z(V, H), z(V, 1), z(H, 1)
+        # both bias vectors, their update histories and their statistics are packed [b_v | b_h], so
+        # one kernel updates them
+        b0 = np.zeros((V + H, 1), np.float32)
+        if bias_v is not None:
+            b0[:V, 0] = np.asarray(bias_v, np.float32).ravel()
+        if bias_h is not None:
+            b0[V:, 0] = np.asarray(bias_h, np.float32).ravel()
+        self.b, self.db = cm.CUDAMatrix(b0), z(V + H, 1)
+        self.bv, self.bh = self.b.slice(0, V), self.b.slice(V, V + H)
+        self.dbv, self.dbh = self.db.slice(0, V), self.db.slice(V, V + H)
+        self.dW = z(V, H)
         # packed statistics [W | b_v | b_h]: one buffer, one all-reduce
         self.pack = z(V * H + V + H, 1)
         self.suff_W = self.pack.slice(0, V * H).reshape((V, H))
         self.suff_bv = self.pack.slice(V * H, V * H + V)
         self.suff_bh = self.pack.slice(V * H + V, V * H + V + H)
+        self.suff_b = self.pack.slice(V * H, V * H + V + H)
         B = batchsize
         za = lambda r, c: cm.empty_aux((r, c))
         self.h_pos, self.h_samp, self.h_samp_aux = z(H, B), z(H, B), za(H, B)
@@ -106,6 +116,11 @@ class FusedRBM(object):
         self._esched = Parameter(cm, self.ehyp)
         self.kernel_launches = 0
         self.timeline = None   # set to a list to record (name, flops, bytes, start, end) per launch
+        # the step is recorded once per (Gibbs steps, visible draw) and replayed with one library call;
+        # B200_RBM_PROGRAM=0 issues every operation through its own call instead
+        self.use_program = os.environ.get("B200_RBM_PROGRAM", "1") != "0"
+        self._programs = {}
+        self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
 
     def _act(self, layer_activation):
         return 1 if layer_activation == LOGISTIC else 0
@@ -121,10 +136,15 @@ class FusedRBM(object):
         """deepnet/dbm.py:217-222: the visible layer feeds a draw upward instead of its means."""
         return bool(self.hyp.sample_input) and self.hyp.sample_input_after <= step
 
-    def _op(self, name, flops, nbytes, fn, *args, **kw):
-        """Runs one kernel-launching call; with a timeline attached, brackets it with CUDA events."""
-        self.kernel_launches += 1
-        if self.timeline is None:
+    # launches behind one operation of the vocabulary (row and column sums: partial + finishing launch)
+    _LAUNCHES = dict(sum=2, add_sums=2)
+
+    def _op(self, X, name, flops, nbytes, method, *args, **kw):
+        """Names one operation of the step to the executor X (`Immediate` or a recording `Program`);
+        with a timeline attached, brackets the immediate call with CUDA events."""
+        self.kernel_launches += self._LAUNCHES.get(method, 1)
+        fn = getattr(X, method)
+        if self.timeline is None or isinstance(X, self.cm.Program):
             return fn(*args, **kw)
         e0 = self.cm.Event().record()
         r = fn(*args, **kw)
@@ -134,194 +154,178 @@ class FusedRBM(object):
 
     def TrainOneBatch(self, step, data):
         """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host."""
-        if self.visible == REPLICATED_SOFTMAX:
-            return self._train_replicated_softmax(step, data)
-        cm, k = self.cm, self._gibbs_steps(step)
+        cm = self.cm
+        k, draw_v = self._gibbs_steps(step), self._sample_visible(step)
+        if self.visible == LINEAR:
+            draw_v = False
+        mom, eps = self._sched.GetMomentumAndEpsilon(step)
+        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
+        eh = self.ehyp
+        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
+        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
+        sc = dict(mom=mom, eps=eps, emom=emom, eeps=eeps, l2=l2, l1=l1, inv_b=1.0 / (self.B * self.world_size))
+        if draw_v and self.v_samp is None:
+            self.v_samp, self.v_samp_aux = cm.empty((self.V, self.B)), cm.empty_aux((self.V, self.B))
+        body = (self._issue_replicated_softmax if self.visible == REPLICATED_SOFTMAX
+                else (self._issue_f16 if self.f16 else self._issue))
+        if not self.use_program or self.timeline is not None:
+            self.kernel_launches = 0
+            return body(cm.Immediate(), data, k, draw_v, sc)
+        key = (k, draw_v)
+        rec = self._programs.get(key)
+        if rec is None:
+            prog = cm.Program()
+            self.kernel_launches = 0
+            handles = body(prog, self._batch, k, draw_v, sc)
+            rec = self._programs[key] = (prog, handles, self.kernel_launches)
+        prog, (ub, uw), self.kernel_launches = rec
+        # the recorded step reads the minibatch through one handle: point it at this batch
+        ct.memmove(ct.byref(self._batch.mat), ct.byref(data.mat), ct.sizeof(data.mat))
+        self._batch.mat.owns_data = 0
+        self._batch_owner = data
+        prog.set_floats(ub, f0=sc["inv_b"], f1=mom, f2=eps)
+        prog.set_floats(uw, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
+        prog.run()
+
+    def _issue_updates(self, X, sc, wb, w_scale=None):
+        """All-reduce of the packed statistics, then the two updates (biases are not regularised,
+        deepnet/dbm.py:249).  Returns the operations whose scalars follow the schedules."""
+        V, H = self.V, self.H
+        if self.world_size > 1:
+            self._op(X, "allreduce", 0, 4.0 * (V * H + V + H), "allreduce", self.pack)
+        ub = self._op(X, "update_bias", 0, 20.0 * (V + H), "momentum_update", self.b, self.db, None, self.suff_b,
+                      sc["inv_b"], sc["mom"], sc["eps"])
+        uw = self._op(X, "update_W", 0, 6 * wb, "momentum_update", self.W, self.dW, None, self.suff_W, sc["inv_b"],
+                      sc["emom"], sc["eeps"], l2=sc["l2"], l1=sc["l1"], w_aux=self.W_aux, w_scale=w_scale)
+        return ub, uw
+
+    def _issue(self, X, data, k, draw_v, sc):
+        """CD-k with split-TF32 products (parts derived in the kernel, or bfloat16 parts from aux matrices)."""
+        cm = self.cm
         V, H, B = self.V, self.H, self.B
         W, Wa, P = self.W, self.W_aux, cm.split_passes
         v0 = data
-        self.kernel_launches = 0
         gf = 2.0 * V * H * B                      # algorithmic flops of one product
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
-        lib = cm._lib
         exact = self.binary_data                  # 0/1 data have no low part
-        # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
-        if self.f16:
-            return self._train_f16(step, data)
         sa = self.state_aux
         if sa:
-            self._op("split", 0, 2 * vb, v0.split_bf16, self.data_aux)
+            self._op(X, "split", 0, 2 * vb, "split_bf16", v0, self.data_aux)
         h_samp_aux, v_neg_aux = (self.h_samp_aux, self.v_neg_aux) if sa else (None, None)
-        self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm,
+        # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
+        self._op(X, "gemm_up", gf, 2.5 * hb, "fused_gemm",
                  P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux if sa else None),
                  out=self.h_pos, sample=self.h_samp, sample_aux=h_samp_aux, bias=self.bh, activation=1)
         # negative phase: k Gibbs steps; the visible means feed upward, or with sample_input (logistic
         # visible units only) their Bernoulli draw, which costs one sampling call per step
-        draw_v = self._sample_visible(step) and self.visible == LOGISTIC
-        if draw_v and self.v_samp is None:
-            self.v_samp, self.v_samp_aux = cm.empty((V, B)), cm.empty_aux((V, B))
         for i in range(k):
-            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm,
+            self._op(X, "gemm_down", gf, 2 * vb, "fused_gemm",
                      P(W, self.h_samp, exact_b=True, a_aux=Wa, b_aux=h_samp_aux), out=self.v_neg,
                      out_aux=None if draw_v else v_neg_aux, sample=self.v_samp if draw_v else None,
                      sample_aux=self.v_samp_aux if (draw_v and sa) else None, bias=self.bv,
                      activation=self._act(self.visible))
             if i == 0:
-                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
-                                                                                self.loss_acc.p_mat)))
-                self.kernel_launches += 1          # add_sq_diff is two launches
+                self._op(X, "sq_err", 0, 2 * vb, "sq_diff", self.v_neg, v0, self.loss_acc)
             # the hidden means are only read after the last step (statistics); before that the draw suffices
             up = (P(W.T, self.v_samp, exact_b=True, a_aux=Wa, b_aux=self.v_samp_aux if sa else None) if draw_v
                   else P(W.T, self.v_neg, a_aux=Wa, b_aux=v_neg_aux))
-            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, up,
+            self._op(X, "gemm_up", gf, 2.5 * hb, "fused_gemm", up,
                      out=self.h_neg if i == k - 1 else None, sample=self.h_samp, sample_aux=h_samp_aux,
                      bias=self.bh, activation=1)
         # statistics: pos - neg in one product: the difference of two nearly equal products, so its
-        # correction terms are TF32 products too; bias statistics by row sums
+        # correction terms are TF32 products too; bias statistics: row sums of pos - neg, one launch a layer
         pos = P(v0, self.h_pos.T, exact_a=exact, terms="tf32")
         neg = P(self.v_neg, self.h_neg.T, negate=1, terms="tf32")
-        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
-        self._op("row_sum", 0, vb, v0.sum, axis=1, target=self.suff_bv)
-        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_neg, axis=1, mult=-1.0)
-        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
-        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
-        self.kernel_launches += 4                  # each row sum is a partial + a finish launch
-        if self.world_size > 1:
-            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
-        inv_b = 1.0 / (self.B * self.world_size)
-        # updates (biases are not regularised, deepnet/dbm.py:249)
-        mom, eps = self._sched.GetMomentumAndEpsilon(step)
-        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
-        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
-        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
-        eh = self.ehyp
-        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
-        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1, w_aux=Wa)
+        self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W)
+        self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
+        self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
+        return self._issue_updates(X, sc, wb)
 
-    def _train_f16(self, step, data):
+    def _issue_f16(self, X, data, k, draw_v, sc):
         """The binary-data, logistic-units CD-k update with every big product on scaled
         half-precision operands: states and data as x * 2^14 = hi + lo in fp16 (written by the
         producing epilogue, `split_f16` for the data), W as W * 2^e (written by the update kernel,
         which also keeps e); a product is hi.lo + lo.hi + hi.hi, 0/1 operands need hi only."""
-        cm, k = self.cm, self._gibbs_steps(step)
+        cm = self.cm
         V, H, B = self.V, self.H, self.B
         W, Wa, We, F = self.W, self.W_aux, self.W_exp, cm.f16_passes
         E = 14                                     # exponent of every state: values in [0, 1]
         v0, v0a = data, self.data_aux
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
-        lib = cm._lib
         act = dict(scale_exp=We, scale_exp_const=E, aux_f16=True, aux_exp=E)
-        self._op("split", 0, 2 * vb, v0.split_f16, v0a, None, E)
+        self._op(X, "split", 0, 2 * vb, "split_f16", v0, v0a, None, E)
         # positive phase: h0 = sigmoid(W' v0 + b_h), its Bernoulli sample, and the parts of both
-        self._op("gemm_up", gf, 3.5 * hb, cm.fused_gemm, F(W.T, Wa, v0, v0a, exact_b=True), out=self.h_pos,
+        self._op(X, "gemm_up", gf, 3.5 * hb, "fused_gemm", F(W.T, Wa, v0, v0a, exact_b=True), out=self.h_pos,
                  out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                  **act)
-        draw_v = self._sample_visible(step)       # sample_input: the visible draw feeds upward (one more call per step)
-        if draw_v and self.v_samp is None:
-            self.v_samp, self.v_samp_aux = cm.empty((V, B)), cm.empty_aux((V, B))
         for i in range(k):
             last = i == k - 1
             # the fp32 visible means are read by the error of the first reconstruction and by the
             # statistics after the last step; in between only their half-precision form is (and not
-            # even that when the draw feeds upward)
-            self._op("gemm_down", gf, 2 * vb, cm.fused_gemm, F(W, Wa, self.h_samp, self.h_samp_aux, exact_b=True),
+            # even that when the draw feeds upward: sample_input, one more sampling call per step)
+            self._op(X, "gemm_down", gf, 2 * vb, "fused_gemm", F(W, Wa, self.h_samp, self.h_samp_aux, exact_b=True),
                      out=self.v_neg if (i == 0 or last) else None,
                      out_aux=self.v_neg_aux if (last or not draw_v) else None,
                      sample_aux=self.v_samp_aux if draw_v else None, bias=self.bv, activation=1, **act)
             if i == 0:
-                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_neg.p_mat, v0.p_mat,
-                                                                                self.loss_acc.p_mat)))
-                self.kernel_launches += 1
+                self._op(X, "sq_err", 0, 2 * vb, "sq_diff", self.v_neg, v0, self.loss_acc)
             # the hidden means (and their parts) are only read after the last step, by the statistics
             # (the next product reads the draw's half-precision plane; the fp32 draw is kept for the caller)
             up = (F(W.T, Wa, self.v_samp, self.v_samp_aux, exact_b=True) if draw_v
                   else F(W.T, Wa, self.v_neg, self.v_neg_aux))
-            self._op("gemm_up", gf, 2.5 * hb, cm.fused_gemm, up,
+            self._op(X, "gemm_up", gf, 2.5 * hb, "fused_gemm", up,
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
                      sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
         pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
         neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
-        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W, scale_exp_const=2 * E)
-        self._op("row_sum", 0, vb, v0.sum, axis=1, target=self.suff_bv)
-        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_neg, axis=1, mult=-1.0)
-        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
-        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
-        self.kernel_launches += 4
-        if self.world_size > 1:
-            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
-        inv_b = 1.0 / (self.B * self.world_size)
-        mom, eps = self._sched.GetMomentumAndEpsilon(step)
-        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
-        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
-        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
-        eh = self.ehyp
-        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
-        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1, w_aux=Wa, w_scale=self.W_scale)
+        self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W, scale_exp_const=2 * E)
+        self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
+        self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
         self.kernel_launches += 2                  # the exponent launch and the pass that writes W's aux
+        return self._issue_updates(X, sc, wb, w_scale=self.W_scale)
 
-    def _train_replicated_softmax(self, step, data):
-        """CD-k with a replicated-softmax visible layer (word-count columns) and sampled inputs:
-        the call sequence of deepnet/dbm.py:118-238 with replicated_softmax_layer.py:12-60,90-154
-        and edge.py:222-246, on fused kernels.  Same random stream as the call-by-call driver:
-        one call for the positive hidden draw, then per Gibbs step one call per document for the
-        multinomial draw and one for the hidden draw."""
-        cm, k = self.cm, self._gibbs_steps(step)
+    def _issue_replicated_softmax(self, X, data, k, draw_v, sc):
+        """CD-k with a replicated-softmax visible layer (word-count columns): the call sequence of
+        deepnet/dbm.py:118-238 with replicated_softmax_layer.py:12-60,90-154 and edge.py:222-246, on
+        fused kernels.  Same random stream as the call-by-call driver: one call for the positive
+        hidden draw, then per Gibbs step one call per document for the multinomial draw (with
+        sample_input) and one for the hidden draw."""
+        cm = self.cm
         V, H, B = self.V, self.H, self.B
         W, Wa, P = self.W, self.W_aux, cm.split_passes   # the small state matrices' parts are derived in the kernel
-        draw_v = self._sample_visible(step)
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
-        lib = cm._lib
-        self.kernel_launches = 0
         v0 = data                                              # integer counts: exact in TF32
         # GetData: NN = column sums + tiny; v0n = data / NN for the statistics
-        self._op("col_sum", 0, vb, v0.sum, axis=0, target=self.NN)
-        self._op("add_scalar", 0, 8.0 * B, self.NN.add, self.tiny)
-        self._op("div_by_row", 0, 2 * vb, v0.div_by_row, self.NN, target=self.v0n)
+        self._op(X, "col_sum", 0, vb, "sum", v0, 0, self.NN)
+        self._op(X, "add_scalar", 0, 8.0 * B, "add_scalar", self.NN, self.tiny)
+        self._op(X, "div_by_row", 0, 2 * vb, "div_by_row", v0, self.NN, self.v0n)
         # positive phase: hidden bias is scaled by the document length (deepnet/dbm.py:101-104)
-        self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, P(W.T, v0, exact_b=True, a_aux=Wa), out=self.h_pos,
+        self._op(X, "gemm_up", gf, 2 * hb, "fused_gemm", P(W.T, v0, exact_b=True, a_aux=Wa), out=self.h_pos,
                  sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
         for i in range(k):
             # visible: NN * softmax(W h + b_v)
-            self._op("gemm_down", gf, vb, cm.fused_gemm, P(W, self.h_samp, exact_b=True, a_aux=Wa), out=self.v_act,
+            self._op(X, "gemm_down", gf, vb, "fused_gemm", P(W, self.h_samp, exact_b=True, a_aux=Wa), out=self.v_act,
                      bias=self.bv, activation=0)
-            self._op("softmax", 0, 2 * vb, self.v_act.softmax_scaled, self.NN, target=self.v_neg)
-            self._op("div_by_row", 0, 2 * vb, self.v_neg.div_by_row, self.NN, target=self.v_negn)
+            self._op(X, "softmax", 0, 2 * vb, "softmax_scaled", self.v_act, self.NN, self.v_neg)
+            self._op(X, "div_by_row", 0, 2 * vb, "div_by_row", self.v_neg, self.NN, self.v_negn)
             if i == 0:   # squared error between state / NN and the counts (replicated_softmax_layer.py:128-135)
-                self._op("sq_err", 0, 2 * vb, lambda: cm._check(lib.add_sq_diff(self.v_negn.p_mat, v0.p_mat,
-                                                                                self.loss_acc.p_mat)))
+                self._op(X, "sq_err", 0, 2 * vb, "sq_diff", self.v_negn, v0, self.loss_acc)
             if draw_v:   # word counts drawn from the softmax feed upward
-                self._op("multinomial", 0, 2 * vb, self.v_neg.sample_multinomial, self.NN, self.v_samp)
+                self._op(X, "multinomial", 0, 2 * vb, "sample_multinomial", self.v_neg, self.NN, self.v_samp)
                 up = P(W.T, self.v_samp, exact_b=True, a_aux=Wa)
             else:        # sample_input off: the expected counts do (deepnet/dbm.py:222)
                 up = P(W.T, self.v_neg, a_aux=Wa)
-            self._op("gemm_up", gf, 2 * hb, cm.fused_gemm, up,
+            self._op(X, "gemm_up", gf, 2 * hb, "fused_gemm", up,
                      out=self.h_neg, sample=self.h_samp, bias=self.bh, col_scale=self.NN, activation=1)
         pos = P(self.v0n, self.h_pos.T, terms="tf32")
         neg = P(self.v_negn, self.h_neg.T, negate=1, terms="tf32")
-        self._op("gemm_stats", 2 * gf, wb, cm.fused_gemm, pos + neg, out=self.suff_W)
-        self._op("row_sum", 0, vb, self.v0n.sum, axis=1, target=self.suff_bv)
-        self._op("row_sum", 0, vb, self.suff_bv.add_sums, self.v_negn, axis=1, mult=-1.0)
-        self._op("row_sum", 0, hb, self.h_pos.sum, axis=1, target=self.suff_bh)
-        self._op("row_sum", 0, hb, self.suff_bh.add_sums, self.h_neg, axis=1, mult=-1.0)
-        if self.world_size > 1:
-            self._op("allreduce", 0, 4.0 * (V * H + V + H), cm.dp_allreduce, self.pack)
-        inv_b = 1.0 / (self.B * self.world_size)
-        mom, eps = self._sched.GetMomentumAndEpsilon(step)
-        self._op("update_bias", 0, 20.0 * V, self.bv.momentum_update, self.dbv, None, self.suff_bv, inv_b, mom, eps)
-        self._op("update_bias", 0, 20.0 * H, self.bh.momentum_update, self.dbh, None, self.suff_bh, inv_b, mom, eps)
-        emom, eeps = self._esched.GetMomentumAndEpsilon(step)
-        eh = self.ehyp
-        l2 = eh.l2_decay if eh.apply_l2_decay else 0.0
-        l1 = eh.l1_decay if (eh.apply_l1_decay and step > eh.apply_l1decay_after) else 0.0
-        self._op("update_W", 0, 6 * wb, W.momentum_update, self.dW, None, self.suff_W, inv_b, emom, eeps, l2=l2,
-                 l1=l1, w_aux=Wa)
+        self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W)
+        self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", self.v0n, self.v_negn, self.suff_bv)
+        self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
+        return self._issue_updates(X, sc, wb)
 
     def refresh_weight_aux(self):
         """Rebuilds the 16-bit parts of W after W was written from outside (a loaded checkpoint)."""

@@ -242,6 +242,10 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
  * share the array, so calls that overlap on the GPU race; issue them in order on one stream. */
 int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult);
 
+/* target = row sums of a minus row sums of b in one launch: a layer's bias statistics, positive minus
+ * negative phase (deepnet/layer.py:202-213: sum(axis=1), then add_sums(axis=1, mult=-1)). */
+int row_sum_diff(cudamat* a, cudamat* b, cudamat* target);
+
 /* state[:, j] = softmax(pre[:, j] + bias); sample[:, j] = one categorical draw from it as a one-hot
  * column: deepnet/softmax_layer.py:11-16 (apply_softmax, perturb_prob_for_softmax_sampling,
  * choose_max(axis=0)) in one kernel on the same random stream.  bias and sample may be null
@@ -300,6 +304,25 @@ int dp_allreduce(cudamat* mat);           /* in-place sum over ranks, on the lib
 int dp_check(void);
 int dp_destroy(void);
 int dp_abort(void);
+
+/* ---- a recorded training step: no counterpart in the reference ---------------------------- */
+/* The update of deepnet/dbm.py:268-274 is 10-60 library calls per minibatch; at the small
+ * configurations a call from the host language costs more than its kernel.  The caller records
+ * the calls once as an array of b200_op and replays them with one call.  kind selects the entry
+ * point (0 fused_gemm, 1 sum_by_axis, 2 add_sum_by_axis, 3 row_sum_diff, 4 add_sq_diff,
+ * 5 momentum_update, 6 split_f16, 7 split_bf16, 8 dp_allreduce, 9 softmax_scaled, 10 sample_multinomial,
+ * 11 div_by_row_vec, 12 add_scalar, 13 assign_scalar, 14 copy_on_device, 15 sample_bernoulli,
+ * 16 softmax_sample); m[], i0.., f0.. are its arguments in declaration order (matrices, then integers,
+ * then floats; gemm for kind 0).  Stops at the first failure: returns its code, *failed_at its index. */
+struct b200_fused_gemm;
+typedef struct b200_op {
+  int kind;
+  int i0, i1, i2;
+  float f0, f1, f2, f3, f4;
+  cudamat* m[6];
+  struct b200_fused_gemm* gemm;
+} b200_op;
+int b200_run_program(rnd_struct* rnd_state, b200_op* ops, int n, int* failed_at);
 
 #ifdef __cplusplus
 }

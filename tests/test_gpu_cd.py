@@ -161,6 +161,40 @@ def test_fused_engine_follows_the_step_schedules(cm, oracle, form, branch, monke
     assert cm.read_status() == 0
 
 
+@pytest.mark.parametrize("config,scale,cases", [(0, 0.25, 300), (2, 0.02, 200), (3, 0.1, 300)])
+def test_recorded_step_equals_the_call_by_call_step(cm, config, scale, cases, monkeypatch):
+    """The engines record their step once and replay it with one library call; issued operation by
+    operation instead (B200_RBM_PROGRAM=0) the same kernels run in the same order: identical bits."""
+    results = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("B200_RBM_PROGRAM", mode)
+        cfg = configs.build(config, cases=cases, dims_scale=scale)
+        B = cfg["batchsize"]
+        if config == 3:
+            from deepnet_b200.fused_dbm import FusedDBM
+            eng = FusedDBM(cm, [l["numdims"] for l in cfg["layers"]], B, [e["weight"] for e in cfg["edges"]],
+                           cfg["hyperparams"], seed=cfg["seed"])
+        else:
+            V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+            eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                           edge_hyperparams=cfg["edges"][0].get("hyperparams"), visible=cfg["layers"][0]["activation"],
+                           binary_data=True, seed=cfg["seed"])
+        assert eng.use_program == (mode == "1")
+        data = cm.CUDAMatrix(cfg["data"])
+        losses = []
+        for step in range(3):
+            s = (step % (cases // B)) * B
+            eng.TrainOneBatch(step, data.slice(s, s + B))
+            losses.append(eng.read_loss())
+        W = eng.W if isinstance(eng.W, list) else [eng.W]
+        results.append((losses, [get(w) for w in W], cm.CUDAMatrix.rnd_state.calls, eng.kernel_launches))
+    assert results[0][0] == results[1][0]
+    for a, b in zip(results[0][1], results[1][1]):
+        np.testing.assert_array_equal(a, b)
+    assert results[0][2] == results[1][2] and results[0][3] == results[1][3]
+    assert cm.read_status() == 0
+
+
 def test_half_precision_engine_from_zero_weights(cm, oracle, monkeypatch):
     """W's exponent follows the weights from nothing to their first values (the update gathers the
     largest |W| and writes the half-precision form with the exponent that fits it)."""

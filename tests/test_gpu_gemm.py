@@ -408,7 +408,9 @@ def test_long_same_sign_products_keep_the_bound(cm, k, form):
     dimensions of the path (8192 hidden units, a 10 000-word vocabulary), linear and logistic."""
     rng = np.random.default_rng(k)
     m, n = 256, 512
-    A = (rng.random((k, m)) * 0.02).astype(np.float32)            # stored k x m, used transposed (the up product)
+    # weights sized so that the same-sign sum stays a few units (a logistic unit's working range: at
+    # |sum| = 40 the 1e-5 absolute bound would be 2.5e-7 relative, below fp32 itself)
+    A = (rng.random((k, m)) * 0.002).astype(np.float32)           # stored k x m, used transposed (the up product)
     B = rng.random((k, n)).astype(np.float32)
     b = (-(A.astype(np.float64).T @ B).mean(axis=1, keepdims=True)).astype(np.float32)   # centres the logistic
     cm.set_gemm_path(1)
@@ -427,4 +429,77 @@ def test_long_same_sign_products_keep_the_bound(cm, k, form):
     pre = A.astype(np.float64).T @ B.astype(np.float64)
     assert relerr(get(lin), pre) < (4e-6 if form != "bf16" else TOL)
     assert np.abs(get(sig) - 1 / (1 + np.exp(-(pre + b)))).max() < TOL
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("splits", [2, 5, 16])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(500, 100, 784), (1024, 256, 4096), (132, 68, 1000)])
+def test_split_k_dot_matches_float64(cm, splits, ta, tb, m, n, k):
+    """The inner dimension cut into work items (tile, split) with a finishing kernel: what fills the
+    SMs when a product has few output tiles (config 1's down product is 1024 x 256 with K = 4096)."""
+    rng = np.random.default_rng(m + n + k + splits)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    cm.set_gemm_path(1)
+    cm.set_split_k(splits)
+    try:
+        out = cm.CUDAMatrix(rng.standard_normal((m, n)).astype(np.float32))
+        base = get(out)
+        out.add_dot(make(cm, A, ta), make(cm, B, tb), mult=0.5)          # beta = 1, alpha = 0.5 in the finishing kernel
+    finally:
+        cm.set_split_k(0)
+    want = base + 0.5 * (A.astype(np.float64) @ B.astype(np.float64))
+    assert relerr(get(out), want) < TOL
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("form", ["bf16", "f16"])
+def test_split_k_epilogue_equals_the_unsplit_one(cm, oracle, splits, form):
+    """Bias, logistic, Bernoulli draw and the 16-bit parts of result and draw behind a split product:
+    probabilities within rounding of the unsplit kernel's, the draw bit-exact against the oracle fed
+    the kernel's own probabilities, the parts exactly those of the stored result."""
+    rng = np.random.default_rng(40 + splits)
+    m, n, k = 500, 100, 2048
+    W = (rng.standard_normal((k, m)) * 0.05).astype(np.float32)
+    X = (rng.random((k, n)) < 0.3).astype(np.float32)
+    b = rng.standard_normal((m, 1)).astype(np.float32)
+    cm.set_gemm_path(1)
+    w, x, bias = cm.CUDAMatrix(W), cm.CUDAMatrix(X), cm.CUDAMatrix(b)
+    out, smp = cm.empty((m, n)), cm.empty((m, n))
+    out_aux, smp_aux = cm.empty_aux((m, n)), cm.empty_aux((m, n))
+    if form == "f16":
+        scale = cm.f16_scale_state(np.abs(W).max())
+        wa = w.split_f16(cm.empty_aux(W.shape), exp_dev=scale.slice(0, 1))
+        xa = x.split_f16(cm.empty_aux(X.shape), exp_const=14)
+        passes = cm.f16_passes(w.T, wa, x, xa, exact_b=True)
+        kw = dict(scale_exp=scale.slice(0, 1), scale_exp_const=14, aux_f16=True, aux_exp=14)
+    else:
+        wa, xa = w.split_bf16(cm.empty_aux(W.shape)), x.split_bf16(cm.empty_aux(X.shape))
+        passes = cm.split_passes(w.T, x, exact_b=True, a_aux=wa, b_aux=xa)
+        kw = {}
+    cm.CUDAMatrix.init_random(5)
+    oracle.EigenMatrix.init_random(5)
+    cm.set_split_k(splits)
+    try:
+        cm.fused_gemm(passes, out=out, sample=smp, out_aux=out_aux, sample_aux=smp_aux, bias=bias, activation=1, **kw)
+    finally:
+        cm.set_split_k(0)
+    got = get(out)
+    want = 1 / (1 + np.exp(-(W.astype(np.float64).T @ X + b)))
+    assert relerr(got, want) < TOL
+    want_s = get(oracle.EigenMatrix(got).sample_bernoulli(target=oracle.empty((m, n))))
+    np.testing.assert_array_equal(get(smp), want_s)
+    if form == "f16":
+        lo, hi = f16_planes(out_aux)
+        want_hi = (got * np.float32(2.0 ** 14)).astype(np.float16).astype(np.float32)
+        np.testing.assert_array_equal(hi, want_hi)
+        np.testing.assert_array_equal(lo, (got * np.float32(2.0 ** 14) - want_hi).astype(np.float16).astype(np.float32))
+        np.testing.assert_array_equal(f16_planes(smp_aux)[1], want_s * 2.0 ** 14)
+    else:
+        lo, bb = out_aux.planes()
+        np.testing.assert_array_equal(bb, bf16_round(got))
+        np.testing.assert_array_equal(lo, bf16_round(got - tf32_trunc(got)))
+        np.testing.assert_array_equal(smp_aux.planes()[1], want_s)
     assert cm.read_status() == 0

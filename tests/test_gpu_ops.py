@@ -230,3 +230,25 @@ def test_ones_vector_is_filled_at_start_up(cm):
     s = cm.dot(cm.CUDAMatrix(x), cm.CUDAMatrix(np.ones((4, 1), np.float32)))
     np.testing.assert_allclose(get(s).ravel(), x.sum(axis=1))
     assert float(np.array(cm.CUDAMatrix.ones.asarray()).min()) == 1.0
+
+
+@pytest.mark.parametrize("shape", [(8192, 4096), (500, 100), (33, 7), (784, 1), (4, 5000)])
+def test_single_launch_statistics(cm, oracle, shape):
+    # row_sum_diff = sum(axis=1) then add_sums(axis=1, mult=-1) (deepnet/layer.py:202-213); add_sq_diff twice in a row
+    rng = np.random.default_rng(shape[0])
+    a = rng.random(shape).astype(np.float32)
+    b = rng.random(shape).astype(np.float32)
+    ga, gb = cm.CUDAMatrix(a), cm.CUDAMatrix(b)
+    want = oracle.EigenMatrix(a).sum(axis=1)
+    want.add_sums(oracle.EigenMatrix(b), axis=1, mult=-1.0)
+    for _ in range(2):                     # the ticket counters are back at zero after every call
+        t = cm.empty((shape[0], 1))
+        cm._check(cm._lib.row_sum_diff(ga.p_mat, gb.p_mat, t.p_mat))
+        np.testing.assert_allclose(get(t), get(want), rtol=1e-5, atol=1e-5 * shape[1])
+    ref = a.astype(np.float64).sum(axis=1) - b.astype(np.float64).sum(axis=1)
+    np.testing.assert_allclose(get(t).ravel(), ref, rtol=1e-5, atol=2e-6 * shape[1])
+    acc = cm.empty((1, 1))
+    for _ in range(2):
+        cm._check(cm._lib.add_sq_diff(ga.p_mat, gb.p_mat, acc.p_mat))
+    sq = ((a.astype(np.float64) - b) ** 2).sum()
+    assert abs(float(get(acc)[0, 0]) - 2 * sq) < 1e-5 * 2 * sq
