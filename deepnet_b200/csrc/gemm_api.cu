@@ -91,8 +91,10 @@ __global__ void __launch_bounds__(256) k_split_aux(const float* x, uint16_t* aux
 }
 
 // aux matrix of x in scaled half-precision form (split_f16): scale = 2^(*exp_dev + exp_const).
+// `only_if` (optional): a device flag; the kernel returns at once when it is zero.
 __global__ void __launch_bounds__(256) k_split_f16(const float* x, uint16_t* aux, int rows, int lda, long n, bool vec,
-                                                   const float* exp_dev, int exp_const) {
+                                                   const float* exp_dev, int exp_const, const float* only_if) {
+  if (only_if && *only_if == 0.0f) return;
   const float scale = exp2f((exp_dev ? *exp_dev : 0.0f) + (float)exp_const);
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
@@ -150,15 +152,20 @@ __device__ __forceinline__ void update_one(float& w, float& d, float g, float su
   w = __fadd_rn(w, __fmul_rn(d, neps));
 }
 
-// kAux: 0 no aux, 1 bfloat16 parts, 2 scaled half-precision form.  For 2 this pass only gathers the
-// largest |w| of the new parameter into scale[2] (`scale` = {exponent, -, max |w| bits, -});
-// k_update_scale turns it into the exponent and k_split_f16 writes the aux with it.
+// kAux: 0 no aux, 1 bfloat16 parts, 2 scaled half-precision form.  For 2 the aux is written with
+// the exponent the parameter has carried so far (`scale` = {exponent, copy, max |w| bits, redo flag})
+// and the largest |w| of the new parameter is gathered into scale[2]; k_update_scale then checks
+// that this exponent still fits the new parameter (it does unless the weights grew eightfold or
+// shrank by more than half in one update) and only otherwise sets the flag that makes a second
+// pass (k_split_f16) rewrite the aux with a new exponent.  One pass over the weights in the
+// common case: 24 bytes per weight instead of 28.
 template <bool kHasGrad, int kAux>
 __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff,
                                                 uint16_t* w_aux, float* scale, int rows, int lda, long n, bool vec,
                                                 float ninv_batch, float momentum, float neps, float l2, float l1) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   float wmax = 0.0f;
+  const float f16_scale = kAux == 2 ? exp2f(scale[0]) : 1.0f;
   if (vec) {   // n % 4 == 0, and with an aux rows % 4 == 0: four consecutive elements share a column
     for (long i = tid; i < (n >> 2); i += nth) {
       float4 W = reinterpret_cast<float4*>(w)[i];
@@ -181,7 +188,16 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
         *reinterpret_cast<ushort4*>(dst) = L;
         *reinterpret_cast<ushort4*>(dst + lda) = B;
       }
-      if (kAux == 2) wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(W.x), fabsf(W.y))), fmaxf(fabsf(W.z), fabsf(W.w)));
+      if (kAux == 2) {
+        wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(W.x), fabsf(W.y))), fmaxf(fabsf(W.z), fabsf(W.w)));
+        const long e = i << 2, c = e / rows, r = e - c * rows;
+        ushort4 L, Hh;
+        split_f16(W.x, f16_scale, L.x, Hh.x); split_f16(W.y, f16_scale, L.y, Hh.y);
+        split_f16(W.z, f16_scale, L.z, Hh.z); split_f16(W.w, f16_scale, L.w, Hh.w);
+        uint16_t* dst = w_aux + c * 2 * lda + r;
+        *reinterpret_cast<ushort4*>(dst) = L;
+        *reinterpret_cast<ushort4*>(dst + lda) = Hh;
+      }
     }
   } else {
     for (long i = tid; i < n; i += nth) {
@@ -196,7 +212,14 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
         w_aux[c * 2 * lda + r] = L;
         w_aux[c * 2 * lda + lda + r] = B;
       }
-      if (kAux == 2) wmax = fmaxf(wmax, fabsf(W));
+      if (kAux == 2) {
+        wmax = fmaxf(wmax, fabsf(W));
+        const long c = i / rows, r = i - c * rows;
+        uint16_t L, Hh;
+        split_f16(W, f16_scale, L, Hh);
+        w_aux[c * 2 * lda + r] = L;
+        w_aux[c * 2 * lda + lda + r] = Hh;
+      }
     }
   }
   if (kAux == 2) {   // non-negative floats order like their bit patterns
@@ -205,13 +228,25 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
   }
 }
 
-// After an update in scaled half-precision form: the exponent that puts the largest |w| * 2^e at
-// or below 2^13 (the fp16 limit is just under 2^16), and the maximum starts over.  A parameter
-// that is all zero (or not finite) keeps its exponent.
+// After an update in scaled half-precision form.  The exponent wanted for the new parameter puts
+// the largest |w| * 2^e in (2^12, 2^13] (the fp16 limit is just under 2^16).  The aux was written
+// with the exponent carried so far; it stands while the largest scaled magnitude stays within
+// (2^11, 2^15].  Otherwise the wanted exponent is stored and scale[3] tells the second pass to
+// rewrite the aux.  The maximum starts over.  A parameter that is all zero (or not finite) keeps
+// its exponent.
 __global__ void k_update_scale(float* scale) {
   const float m = __uint_as_float(reinterpret_cast<unsigned*>(scale)[2]);
-  if (m > 0.0f && m < 3.0e38f) scale[0] = fminf(fmaxf(floorf(log2f(8192.0f / m)), -100.0f), 100.0f);
+  float redo = 0.0f;
+  if (m > 0.0f && m < 3.0e38f) {
+    const float want = fminf(fmaxf(floorf(log2f(8192.0f / m)), -100.0f), 100.0f);
+    const float d = scale[0] - want;
+    if (d < -1.0f || d > 2.0f) {
+      scale[0] = want;
+      redo = 1.0f;
+    }
+  }
   scale[1] = scale[0];
+  scale[3] = redo;
   reinterpret_cast<unsigned*>(scale)[2] = 0u;
 }
 
@@ -294,7 +329,7 @@ int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const) {
   if (blocks < 1) blocks = 1;
   k_split_f16<<<(int)blocks, 256, 0, stream()>>>(x->data_device, reinterpret_cast<uint16_t*>(aux->data_device), rows,
                                                  aux_rows(rows), n, vec, exp_dev ? exp_dev->data_device : nullptr,
-                                                 exp_const);
+                                                 exp_const, nullptr);
   return check_launch();
 }
 
@@ -432,10 +467,10 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 //   grad += suff * (-inv_batch); delta = momentum*delta + l2*w + l1*sign(w) + grad;
 //   w -= eps * delta; grad = 0; and, when w_aux is given, the aux matrix of the new w: its
 //   bfloat16 parts, or with w_scale (1 x 4 device matrix {exponent, -, max |w| bits, -}) its
-//   scaled half-precision form, with the exponent that fits the new w (the update gathers the
-//   largest |w|, then a second pass over w writes the aux).
+//   scaled half-precision form, written in the same pass with the exponent carried so far; a
+//   second pass rewrites it only when the new w no longer fits that exponent.
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
-// without grad and aux; +8 with grad, +4 with the bfloat16 aux, +8 with the half-precision one.
+// without grad and aux; +8 with grad, +4 with either aux (+8 more in an update that changes the exponent).
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
                     float inv_batch, float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
@@ -479,7 +514,8 @@ int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cu
   long sblocks = ((svec ? n / 4 : n) + 255) / 256;
   if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
   if (sblocks < 1) sblocks = 1;
-  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, aux_rows(rows), n, svec, sp, 0);
+  // (returns at once unless the exponent had to change)
+  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, aux_rows(rows), n, svec, sp, 0, sp + 3);
   return check_launch();
 }
 
