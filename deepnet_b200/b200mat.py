@@ -22,6 +22,9 @@ MAX_PASS = 8
 
 
 def _load():
+    alt = os.environ.get("B200MAT_LIBRARY")       # another build of the same library (instrumented, say)
+    if alt:
+        return ct.CDLL(alt)
     if not os.path.exists(_LIB_PATH):
         raise ImportError(
             "libb200mat.so is missing: build it with `python -m deepnet_b200.build` "
@@ -954,6 +957,41 @@ class Program(object):
         if err:
             e = generate_exception(err)
             raise CUDAMatException("operation %d of the recorded step failed: %s" % (failed.value, e))
+
+
+# -- device-resident data feed -----------------------------------------------------------
+_lib.feed_permutation_at.restype = ct.c_uint
+_lib.feed_permutation_at.argtypes = [ct.c_uint, ct.c_uint, ct.c_uint, ct.c_uint]
+
+
+def feed_pack(array):
+    """A (dims x cases) 0/1 host array as a device matrix of one bit per value: ceil(dims / 32) x cases
+    32-bit words, bit r % 32 of word r // 32 of a column = row r (see `feed_gather`)."""
+    a = np.asarray(array)
+    dims, n = a.shape
+    if not np.isin(a, (0, 1)).all():
+        raise ValueError("only 0/1 data can be stored one bit per value")
+    words = (dims + 31) // 32
+    bits = np.zeros((n, words * 32), np.uint8)
+    bits[:, :dims] = a.T
+    packed = np.packbits(bits, axis=1, bitorder="little").view("<u4")            # cases x words
+    # the words travel as float32 storage (same-type copies keep every bit); they are never read as floats
+    return CUDAMatrix(np.ascontiguousarray(packed.T).view(np.float32))
+
+
+def feed_gather(src, packed, dims, key, shuffle, start, out, mean=None, std=None, out_aux=None, aux_mode=0, aux_exp=0):
+    """out = stored columns perm(start ..) of the data set `src` (see include/b200mat.h); key = (lo, hi)."""
+    _check(_lib.feed_gather(src.p_mat, ct.c_int(int(bool(packed))), ct.c_int(dims), ct.c_uint(key[0] & 0xffffffff),
+                            ct.c_uint(key[1] & 0xffffffff), ct.c_int(int(bool(shuffle))), ct.c_int(int(start)),
+                            mean.p_mat if mean is not None else None, std.p_mat if std is not None else None,
+                            out.p_mat, out_aux.p_mat if out_aux is not None else None, ct.c_int(aux_mode),
+                            ct.c_int(aux_exp)))
+    return out
+
+
+def feed_permutation(n, key):
+    """The stored column read at every position of the epoch keyed `key`, as the device evaluates it."""
+    return np.array([_lib.feed_permutation_at(i, n, key[0] & 0xffffffff, key[1] & 0xffffffff) for i in range(n)], np.int64)
 
 
 # -- device / library control -----------------------------------------------------

@@ -27,7 +27,9 @@
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, drains
 // and frees its tensor memory and returns.
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
+#include <time.h>
 
 #include <mutex>
 #include <type_traits>
@@ -1275,7 +1277,27 @@ bool gemm_tc_supported(const GemmProblem& g) {
   return encode_fn() != nullptr;
 }
 
+#ifdef B200_HOST_TIMING
+// Debug build only: where the host time of a product goes (printed when the process exits).
+struct HostTimes {
+  double setup = 0, launch = 0;
+  long calls = 0;
+  static double now() {
+    timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    return t.tv_sec * 1e6 + t.tv_nsec * 1e-3;
+  }
+  ~HostTimes() {
+    if (calls) fprintf(stderr, "gemm_tc host time per call: set-up %.2f us, launch %.2f us (%ld calls)\n", setup / calls, launch / calls, calls);
+  }
+};
+static HostTimes g_host_times;
+#endif
+
 int gemm_tc(const GemmProblem& g) {
+#ifdef B200_HOST_TIMING
+  const double t_begin = HostTimes::now();
+#endif
   if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
   static int pair_mode = -1;   // B200_GEMM_2CTA=0 keeps one CTA per tile
@@ -1516,7 +1538,15 @@ int gemm_tc(const GemmProblem& g) {
     B200_TC_CASE(64, false)
   };
 #undef B200_TC_CASE
+#ifdef B200_HOST_TIMING
+  const double t_launch = HostTimes::now();
   const int err = launch();
+  g_host_times.setup += t_launch - t_begin;
+  g_host_times.launch += HostTimes::now() - t_launch;
+  g_host_times.calls++;
+#else
+  const int err = launch();
+#endif
   if (err || p.splits == 1) return err;
   const long items = (long)g.M * ((g.N + 3) / 4);
   long blocks = (items + 255) / 256;

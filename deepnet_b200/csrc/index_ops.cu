@@ -175,3 +175,129 @@ int normlimit_by_axis(cudamat* mat, cudamat* target, int axis, float norm) {
 }
 
 }  // extern "C"
+
+// ---- device-resident data feed -------------------------------------------------------------
+// The data set stays on the device as one (dims x cases) matrix per modality, either fp32 or,
+// for 0/1 data, one bit per value (32 rows per 32-bit word: a million 8192-dimensional binary
+// cases take 1 GB instead of 33).  A minibatch is GATHERED: output column j is stored column
+// perm(start + j), where perm is a keyed bijection of [0, cases) evaluated on the fly (a Feistel
+// network on ceil(log2 cases) bits, walked until it lands inside the range), so an epoch's shuffle
+// costs nothing and moves no data (the reference swaps columns in place after drawing the
+// permutation on the host, deepnet/datahandler.py:364-375).  The same pass applies the
+// mean / standard-deviation normalisation (datahandler.py:299-306) and writes, when asked, the
+// 16-bit parts of the minibatch that the products read.
+namespace {
+
+__host__ __device__ inline uint32_t feed_mix(uint32_t r, uint32_t k) {
+  uint32_t h = r * 0x9E3779B1u + k;
+  h ^= h >> 15;
+  h *= 0x85EBCA77u;
+  h ^= h >> 13;
+  h *= 0xC2B2AE3Du;
+  h ^= h >> 16;
+  return h;
+}
+constexpr int kFeedRounds = 6;
+// Bijection of [0, n): alternating unbalanced Feistel rounds on `bits` bits (2^(bits-1) < n <= 2^bits,
+// bits >= 2), repeated while the image falls outside [0, n) (fewer than two passes on average).
+__host__ __device__ inline uint32_t feed_perm(uint32_t i, uint32_t n, uint32_t bits, uint32_t key_lo, uint32_t key_hi) {
+  const uint32_t a = bits >> 1, b = bits - a;
+  const uint32_t mask_a = (1u << a) - 1u, mask_b = (1u << b) - 1u;
+  uint32_t x = i;
+  do {
+    uint32_t L = x >> a, R = x & mask_a;
+    for (int round = 0; round < kFeedRounds; round++) {
+      const uint32_t k = key_lo * 0x9E3779B9u + key_hi * 0x85EBCA6Bu + (uint32_t)round * 0xC2B2AE35u;
+      if ((round & 1) == 0) L ^= feed_mix(R, k) & mask_b;
+      else R ^= feed_mix(L, k) & mask_a;
+    }
+    x = (L << a) | R;
+  } while (x >= n);
+  return x;
+}
+inline uint32_t feed_bits(uint32_t n) {
+  uint32_t bits = 2;
+  while (bits < 32 && (1ull << bits) < n) bits++;
+  return bits;
+}
+
+// One block per output column.  kPacked: the source holds one bit per value.
+template <bool kPacked>
+__global__ void __launch_bounds__(256) k_feed_gather(const float* __restrict__ src, int h, int src_ld, uint32_t n,
+                                                     uint32_t bits, uint32_t key_lo, uint32_t key_hi, int shuffle,
+                                                     uint32_t start, int count, const float* __restrict__ mean,
+                                                     const float* __restrict__ stdv, float* __restrict__ out,
+                                                     uint16_t* __restrict__ aux, int lda, int aux_mode, float aux_scale) {
+  for (int j = blockIdx.x; j < count; j += gridDim.x) {
+    const uint32_t pos = start + (uint32_t)j;
+    const uint32_t c = shuffle ? feed_perm(pos, n, bits, key_lo, key_hi) : pos;
+    const float* col = src + (size_t)c * src_ld;
+    float* o = out + (size_t)j * h;
+    uint16_t* a0 = aux ? aux + (size_t)j * 2 * lda : nullptr;
+    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+      float x;
+      if (kPacked) x = (float)((__float_as_uint(col[r >> 5]) >> (r & 31)) & 1u);
+      else x = col[r];
+      if (mean) x = __fdiv_rn(__fadd_rn(x, -mean[r]), stdv[r]);    // add_col_mult(mean, -1), then div_by_col(std)
+      o[r] = x;
+      if (aux_mode == 2) {
+        uint16_t lo, hi;
+        split_f16(x, aux_scale, lo, hi);
+        a0[r] = lo;
+        a0[lda + r] = hi;
+      } else if (aux_mode == 1) {
+        uint16_t lo, b16;
+        split_aux(x, lo, b16);
+        a0[r] = lo;
+        a0[lda + r] = b16;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// out (h x count) = columns perm(start .. start + count - 1) of the stored data set `src`
+// (h x n fp32, or with packed != 0 ceil(h / 32) x n words of 32 rows each), normalised with
+// mean / std (h x 1 each, or both null), plus the aux matrix of the minibatch (aux_mode 0 none,
+// 1 bfloat16 parts, 2 scaled half-precision form with exponent aux_exp).  shuffle = 0 reads the
+// columns in stored order.  No counterpart in the reference (its GPUCache slices and swaps).
+int feed_gather(cudamat* src, int packed, int h, unsigned int key_lo, unsigned int key_hi, int shuffle, int start,
+                cudamat* mean, cudamat* stdv, cudamat* out, cudamat* out_aux, int aux_mode, int aux_exp) {
+  if (!src->on_device || !out->on_device || (out_aux && !out_aux->on_device)) return ERROR_NOT_ON_DEVICE;
+  if ((mean && !mean->on_device) || (stdv && !stdv->on_device)) return ERROR_NOT_ON_DEVICE;
+  if (src->is_trans || out->is_trans) return ERROR_TRANSPOSED;
+  if ((mean == nullptr) != (stdv == nullptr)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  const int n = src->size[1], count = out->size[1];
+  if (h <= 0 || out->size[0] != h || src->size[0] != (packed ? (h + 31) / 32 : h)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (start < 0 || count < 0 || (long)start + count > n) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (mean && (numel(mean) != h || numel(stdv) != h)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (aux_mode < 0 || aux_mode > 2 || (aux_mode != 0) != (out_aux != nullptr)) return ERROR_UNSUPPORTED;
+  if (out_aux && (out_aux->size[0] != aux_rows(h) || out_aux->size[1] != count)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (count == 0) return 0;
+  const int blocks = count < sm_count() * 8 ? count : sm_count() * 8;
+  uint16_t* ap = out_aux ? reinterpret_cast<uint16_t*>(out_aux->data_device) : nullptr;
+  const float scale = exp2f((float)aux_exp);
+  const uint32_t bits = feed_bits((uint32_t)n);
+  if (packed)
+    k_feed_gather<true><<<blocks, 256, 0, stream()>>>(src->data_device, h, src->size[0], (uint32_t)n, bits, key_lo, key_hi,
+                                                     shuffle, (uint32_t)start, count, mean ? mean->data_device : nullptr,
+                                                     stdv ? stdv->data_device : nullptr, out->data_device, ap,
+                                                     aux_rows(h), aux_mode, scale);
+  else
+    k_feed_gather<false><<<blocks, 256, 0, stream()>>>(src->data_device, h, src->size[0], (uint32_t)n, bits, key_lo, key_hi,
+                                                      shuffle, (uint32_t)start, count, mean ? mean->data_device : nullptr,
+                                                      stdv ? stdv->data_device : nullptr, out->data_device, ap,
+                                                      aux_rows(h), aux_mode, scale);
+  return check_launch();
+}
+
+// The stored column that position `pos` of an epoch keyed (key_lo, key_hi) reads, for n cases
+// (what feed_gather evaluates on the device; host-side, for callers that need the order).
+unsigned int feed_permutation_at(unsigned int pos, unsigned int n, unsigned int key_lo, unsigned int key_hi) {
+  return feed_perm(pos, n, feed_bits(n), key_lo, key_hi);
+}
+
+}  // extern "C"

@@ -1,127 +1,95 @@
-"""Device-resident data feed: the GPU cache of the reference's data pipeline.
+"""Device-resident data feed: what the reference's GPU cache does for the training loop
+(`GPUCache`, deepnet/datahandler.py:259-416: the data set in device memory, minibatches cut from
+it, a shuffle per epoch, mean / standard-deviation normalisation and additive Gaussian noise on
+the device), built for a GPU that holds the whole data set.
 
-Restates `GPUCache` of deepnet/datahandler.py:259-416 over a `cm` backend: the data set
-(or a chunk of it) lives in one (dims x cases) device matrix per modality, a minibatch
-is a column slice (a view, no copy), an epoch ends with an in-place shuffle by
-`swap_columns` on disjoint index halves, and mean / standard-deviation normalisation and
-additive Gaussian noise run on the device.  The parent (disk and host caches of the
-reference, datahandler.py:14-257) is reduced to a host array that is cut into chunks of
-`capacity` cases; image translations (datahandler.py:340-362) are not restated.
+Differences in design, not in what the trainer sees:
+  * 0/1 data are stored one bit per value (`cm.feed_pack`): configuration 4's million
+    8192-dimensional cases take 1 GB, not 33, and a minibatch that has to cross PCIe is 4 MB, not 134.
+  * nothing is shuffled in place.  An epoch has a key; position p of the epoch reads stored column
+    perm_key(p), a bijection the gather kernel evaluates on the fly (`cm.feed_gather`).  The host
+    draws no permutation and uploads no index vectors (the reference shuffles a host index array
+    and swaps columns, datahandler.py:364-375).
+  * normalisation is applied while gathering, to the minibatch only; the stored data stay raw.
+  * the gather also writes the 16-bit parts of the minibatch that the tensor-core products read
+    (otherwise a separate pass over the minibatch at the start of every update).
+Every modality of a case (data, labels) shares the epoch's key, so they stay aligned.
+Image translations (datahandler.py:340-362) are not on the contrastive-divergence path and are left out.
 """
 import numpy as np
 
 
-class HostSource(object):
-    """Parent of the device cache: hands out consecutive chunks of host arrays (cases x dims)."""
-
-    def __init__(self, arrays, randomize=False, seed=0):
-        self.arrays = [np.asarray(a, dtype=np.float32) for a in arrays]
-        self.num_data = len(self.arrays)
-        self.datasize = self.arrays[0].shape[0]
-        self._maxpos = self.datasize
-        self._pos = 0
-        self.randomize = randomize
-        self.rng = np.random.RandomState(seed)
-
-    def Get(self, n):
-        if self._pos >= self.datasize:
-            self._pos = 0
-            if self.randomize:
-                perm = self.rng.permutation(self.datasize)
-                self.arrays = [a[perm] for a in self.arrays]
-        end = min(self._pos + n, self.datasize)
-        out = [a[self._pos:end] for a in self.arrays]
-        self._pos = end
-        return out
-
-
-class GPUCache(object):
-    """deepnet/datahandler.py:259-416."""
-
-    def __init__(self, cm, parent, capacity, randomize=False, add_noise=None, sigma=0.01, seed=0):
+class DeviceFeed(object):
+    def __init__(self, cm, arrays, randomize=False, binary=None, add_noise=None, sigma=0.01, seed=0, aux_mode=0, aux_exp=14):
+        """arrays: host arrays (cases x dims), one per modality, as the reference's caches hold them.
+        binary[i]: store modality i one bit per value (default: detect 0/1 data).  aux_mode: 16-bit
+        parts written beside modality 0 (0 none, 1 bfloat16 parts, 2 scaled half precision)."""
         self.cm = cm
-        self.parent = parent
-        self.num_data = parent.num_data
-        self._maxpos = min(int(capacity), parent._maxpos)
-        self._pos = 0
-        self.datasize = 0
-        self.randomize = randomize
-        self.data = [None] * self.num_data
-        self.empty = True
-        self.allocated_memory_size = [0] * self.num_data
-        self.normalize = [False] * self.num_data
-        self.means = [None] * self.num_data
-        self.stds = [None] * self.num_data
+        self.num_data = len(arrays)
+        self.datasize = int(np.asarray(arrays[0]).shape[0])
+        self.randomize, self.seed, self.epoch = randomize, int(seed), 0
         self.add_noise = add_noise or [False] * self.num_data
         self.sigma = sigma
-        self.rng = np.random.RandomState(seed)   # the reference shuffles with numpy's global generator
+        self.aux_mode, self.aux_exp = aux_mode, aux_exp
+        self.dims, self.packed, self.data = [], [], []
+        for i, a in enumerate(arrays):
+            a = np.asarray(a, np.float32)
+            assert a.shape[0] == self.datasize
+            is_bits = bool(np.isin(a, (0, 1)).all()) if binary is None else bool(binary[i])
+            self.dims.append(a.shape[1])
+            self.packed.append(is_bits)
+            self.data.append(cm.feed_pack(a.T) if is_bits else cm.CUDAMatrix(a.T))
+        self.means = [None] * self.num_data
+        self.stds = [None] * self.num_data
+        self._pos = 0
+        self._out = {}          # (modality, batch size) -> output buffers, reused
 
     def SetDataStats(self, i, mean, std):
-        """:377-383 (statistics passed in instead of read from a stats file)."""
-        self.normalize[i] = True
-        self.means[i] = self.cm.CUDAMatrix(np.asarray(mean, np.float32).reshape(-1, 1))
-        self.stds[i] = self.cm.CUDAMatrix(1e-10 + np.asarray(std, np.float32).reshape(-1, 1))
+        """datahandler.py:377-383 (statistics passed in instead of read from a stats file)."""
+        cm = self.cm
+        self.means[i] = cm.CUDAMatrix(np.asarray(mean, np.float32).reshape(-1, 1))
+        self.stds[i] = cm.CUDAMatrix((1e-10 + np.asarray(std, np.float32)).astype(np.float32).reshape(-1, 1))
 
-    def Normalize(self):
-        """:299-306."""
-        for i, batch in enumerate(self.data):
-            if self.normalize[i]:
-                batch.add_col_mult(self.means[i], mult=-1.0)
-                batch.div_by_col(self.stds[i])
+    def key(self):
+        return (self.seed, self.epoch)
 
-    def LoadData(self):
-        """:308-333: pull the next chunk from the parent, reuse the device buffer when it fits."""
-        data_cpu = self.parent.Get(self._maxpos)
-        datasize = data_cpu[0].shape[0]
-        assert datasize <= self._maxpos
-        self.datasize = datasize
-        for i, d in enumerate(data_cpu):
-            mat = d.T
-            size = mat.shape[0] * mat.shape[1]
-            if size != self.allocated_memory_size[i]:
-                if self.data[i] is not None:
-                    self.data[i].free_device_memory()
-                self.data[i] = self.cm.CUDAMatrix(mat)
-                self.allocated_memory_size[i] = size
-            else:
-                self.data[i].overwrite(mat)
-        self.Normalize()
+    def order(self):
+        """Stored case read at each position of the current epoch."""
+        if not self.randomize:
+            return np.arange(self.datasize)
+        return self.cm.feed_permutation(self.datasize, self.key())
 
-    def ShuffleData(self):
-        """:364-375: in-place shuffle, columns indices1[k] and indices2[k] change places."""
-        indices = np.arange(self.datasize)
-        self.rng.shuffle(indices)
-        half = self.datasize // 2
-        if half == 0:
-            return
-        indices1 = self.cm.CUDAMatrix(indices[:half].reshape(1, -1))
-        indices2 = self.cm.CUDAMatrix(indices[half:2 * half].reshape(1, -1))
-        for d in self.data:
-            d.swap_columns(indices1, indices2, target=d)
-        indices1.free_device_memory()
-        indices2.free_device_memory()
+    def _buffers(self, i, count):
+        buf = self._out.get((i, count))
+        if buf is None:
+            cm = self.cm
+            aux = cm.empty_aux((self.dims[i], count)) if (i == 0 and self.aux_mode) else None
+            buf = self._out[(i, count)] = (cm.empty((self.dims[i], count)), aux)
+        return buf
 
     def Get(self, batchsize, get_last_piece=False):
-        """:385-416: the next `batchsize` cases as column-slice views; short tails are skipped."""
-        skip = False
+        """The next `batchsize` cases of every modality as (dims x batch) device matrices; an epoch
+        that ends with fewer is cut short (or, with get_last_piece, returns them), then the next
+        epoch starts with a new key (datahandler.py:385-416).  The matrices are reused by the
+        next call with the same batch size."""
         if self._pos == self.datasize:
             self._pos = 0
-        if self._pos == 0:
-            if self.empty or self._maxpos < self.parent._maxpos:
-                self.LoadData()
-                self.empty = False
-            if self.randomize and self._maxpos == self.parent._maxpos:
-                self.ShuffleData()
-        start = self._pos
-        end = self._pos + batchsize
+            self.epoch += 1
+        start, end = self._pos, self._pos + batchsize
         if end > self.datasize:
             end = self.datasize
-            skip = not get_last_piece
+            if not get_last_piece or end == start:
+                self._pos = self.datasize
+                return self.Get(batchsize, get_last_piece=get_last_piece)
         self._pos = end
-        if skip:
-            return self.Get(batchsize, get_last_piece=get_last_piece)
-        batch = [d.slice(start, end) for d in self.data]
+        batch = []
         for i in range(self.num_data):
+            out, aux = self._buffers(i, end - start)
+            self.cm.feed_gather(self.data[i], self.packed[i], self.dims[i], self.key(), self.randomize, start, out,
+                                mean=self.means[i], std=self.stds[i], out_aux=aux, aux_mode=self.aux_mode if aux else 0,
+                                aux_exp=self.aux_exp)
             if self.add_noise[i]:
-                batch[i].sample_gaussian(mult=self.sigma)
+                out.sample_gaussian(mult=self.sigma)          # datahandler.py:335-337
+            batch.append(out)
+        self.last_aux = self._buffers(0, end - start)[1]
         return batch

@@ -121,6 +121,8 @@ class FusedRBM(object):
         self.use_program = os.environ.get("B200_RBM_PROGRAM", "1") != "0"
         self._programs = {}
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
+        self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
+        self._given_aux = None
 
     def _act(self, layer_activation):
         return 1 if layer_activation == LOGISTIC else 0
@@ -152,8 +154,10 @@ class FusedRBM(object):
         self.timeline.append((name, flops, nbytes, e0, e1))
         return r
 
-    def TrainOneBatch(self, step, data):
-        """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host."""
+    def TrainOneBatch(self, step, data, data_aux=None):
+        """One CD-k update on `data` (V x B device matrix).  Nothing returns to the host.
+        data_aux: the 16-bit parts of `data` in the form this engine's products read (the data
+        feed writes them while gathering the minibatch); without it the step begins by splitting."""
         cm = self.cm
         k, draw_v = self._gibbs_steps(step), self._sample_visible(step)
         if self.visible == LINEAR:
@@ -168,21 +172,27 @@ class FusedRBM(object):
             self.v_samp, self.v_samp_aux = cm.empty((self.V, self.B)), cm.empty_aux((self.V, self.B))
         body = (self._issue_replicated_softmax if self.visible == REPLICATED_SOFTMAX
                 else (self._issue_f16 if self.f16 else self._issue))
+        if data_aux is not None and not (self.state_aux and self.visible != REPLICATED_SOFTMAX):
+            data_aux = None                      # this engine derives the parts of the data in its kernels
+        self._given_aux = data_aux
         if not self.use_program or self.timeline is not None:
             self.kernel_launches = 0
             return body(cm.Immediate(), data, k, draw_v, sc)
-        key = (k, draw_v)
+        key = (k, draw_v, data_aux is not None)
         rec = self._programs.get(key)
         if rec is None:
             prog = cm.Program()
             self.kernel_launches = 0
+            self._given_aux = self._batch_aux if data_aux is not None else None
             handles = body(prog, self._batch, k, draw_v, sc)
             rec = self._programs[key] = (prog, handles, self.kernel_launches)
         prog, (ub, uw), self.kernel_launches = rec
         # the recorded step reads the minibatch through one handle: point it at this batch
-        ct.memmove(ct.byref(self._batch.mat), ct.byref(data.mat), ct.sizeof(data.mat))
-        self._batch.mat.owns_data = 0
-        self._batch_owner = data
+        for view, m in ((self._batch, data), (self._batch_aux, data_aux)):
+            if m is not None:
+                ct.memmove(ct.byref(view.mat), ct.byref(m.mat), ct.sizeof(m.mat))
+                view.mat.owns_data = 0
+        self._batch_owner = (data, data_aux)
         prog.set_floats(ub, f0=sc["inv_b"], f1=mom, f2=eps)
         prog.set_floats(uw, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
         prog.run()
@@ -209,12 +219,13 @@ class FusedRBM(object):
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         exact = self.binary_data                  # 0/1 data have no low part
         sa = self.state_aux
-        if sa:
-            self._op(X, "split", 0, 2 * vb, "split_bf16", v0, self.data_aux)
+        v0a = self._given_aux if self._given_aux is not None else self.data_aux
+        if sa and self._given_aux is None:
+            self._op(X, "split", 0, 2 * vb, "split_bf16", v0, v0a)
         h_samp_aux, v_neg_aux = (self.h_samp_aux, self.v_neg_aux) if sa else (None, None)
         # positive phase: h0 = sigmoid(W' v0 + b_h), and its Bernoulli sample
         self._op(X, "gemm_up", gf, 2.5 * hb, "fused_gemm",
-                 P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=self.data_aux if sa else None),
+                 P(W.T, v0, exact_b=exact, a_aux=Wa, b_aux=v0a if sa else None),
                  out=self.h_pos, sample=self.h_samp, sample_aux=h_samp_aux, bias=self.bh, activation=1)
         # negative phase: k Gibbs steps; the visible means feed upward, or with sample_input (logistic
         # visible units only) their Bernoulli draw, which costs one sampling call per step
@@ -250,11 +261,12 @@ class FusedRBM(object):
         V, H, B = self.V, self.H, self.B
         W, Wa, We, F = self.W, self.W_aux, self.W_exp, cm.f16_passes
         E = 14                                     # exponent of every state: values in [0, 1]
-        v0, v0a = data, self.data_aux
+        v0, v0a = data, (self._given_aux if self._given_aux is not None else self.data_aux)
         gf = 2.0 * V * H * B
         vb, hb, wb = 4.0 * V * B, 4.0 * H * B, 4.0 * V * H
         act = dict(scale_exp=We, scale_exp_const=E, aux_f16=True, aux_exp=E)
-        self._op(X, "split", 0, 2 * vb, "split_f16", v0, v0a, None, E)
+        if self._given_aux is None:
+            self._op(X, "split", 0, 2 * vb, "split_f16", v0, v0a, None, E)
         # positive phase: h0 = sigmoid(W' v0 + b_h), its Bernoulli sample, and the parts of both
         self._op(X, "gemm_up", gf, 3.5 * hb, "fused_gemm", F(W.T, Wa, v0, v0a, exact_b=True), out=self.h_pos,
                  out_aux=self.h_pos_aux, sample=self.h_samp, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,

@@ -149,6 +149,15 @@ int add_scalar(cudamat* mat, float alpha, cudamat* target);                   /*
 /* ---- index operations: cudamat/cudamat.cu:2120-2150 ----------------------------------- */
 int selectRows(cudamat* source, cudamat* target, cudamat* indices);                         /* cudamat.cu:2120 (select_columns) */
 int swapColumns(cudamat* source, cudamat* target, cudamat* indices1, cudamat* indices2);   /* cudamat.cu:2138 */
+/* Device-resident data feed (no counterpart in the reference, whose GPUCache slices a device matrix
+ * and swaps columns after drawing a permutation on the host, deepnet/datahandler.py:364-416):
+ * out (h x count) = stored columns perm(start ..) of src (h x n fp32; or, packed != 0, one bit per
+ * value, ceil(h / 32) x n words), perm a keyed bijection of [0, n) evaluated on the device,
+ * normalised with mean / std (or both null), with the minibatch's aux matrix (aux_mode 0 none,
+ * 1 bfloat16 parts, 2 scaled half precision with exponent aux_exp). */
+int feed_gather(cudamat* src, int packed, int h, unsigned int key_lo, unsigned int key_hi, int shuffle, int start,
+                cudamat* mean, cudamat* stdv, cudamat* out, cudamat* out_aux, int aux_mode, int aux_exp);
+unsigned int feed_permutation_at(unsigned int pos, unsigned int n, unsigned int key_lo, unsigned int key_hi);
 int copy_transpose(cudamat* source, cudamat* target);                                       /* cudamat.cu:271 */
 int normlimit_by_axis(cudamat* mat, cudamat* target, int axis, float norm);                 /* cudamat.cu:1289 (axis 0 only, as there) */
 

@@ -463,3 +463,60 @@ def reference_r4_uni(seed, n):
     f.restype = ct.c_float
     state = ct.c_ulong(seed)
     return np.array([f(ct.byref(state)) for _ in range(n)], dtype=np.float32)
+
+
+# ---- device-resident data feed: CPU twin of feed_pack / feed_gather / feed_permutation ----------
+# (the reference's GPUCache, deepnet/datahandler.py:259-416, shuffles with a host-drawn permutation;
+# the feed evaluates a keyed Feistel bijection instead, restated here in numpy uint32 arithmetic)
+def _feed_mix(r, k):
+    h = (r * np.uint32(0x9E3779B1) + k).astype(np.uint32)
+    h ^= h >> np.uint32(15)
+    h = (h * np.uint32(0x85EBCA77)).astype(np.uint32)
+    h ^= h >> np.uint32(13)
+    h = (h * np.uint32(0xC2B2AE3D)).astype(np.uint32)
+    h ^= h >> np.uint32(16)
+    return h
+
+
+def feed_permutation(n, key, rounds=6):
+    bits = 2
+    while bits < 32 and (1 << bits) < n:
+        bits += 1
+    a = bits >> 1
+    b = bits - a
+    mask_a, mask_b = np.uint32((1 << a) - 1), np.uint32((1 << b) - 1)
+    klo, khi = np.uint32(key[0] & 0xffffffff), np.uint32(key[1] & 0xffffffff)
+    x = np.arange(n, dtype=np.uint32)
+    todo = np.ones(n, bool)
+    with np.errstate(over="ignore"):
+        while todo.any():
+            L, R = x[todo] >> np.uint32(a), x[todo] & mask_a
+            for rnd in range(rounds):
+                k = np.uint32(klo * np.uint32(0x9E3779B9) + khi * np.uint32(0x85EBCA6B) + np.uint32(rnd) * np.uint32(0xC2B2AE35))
+                if rnd % 2 == 0:
+                    L = L ^ (_feed_mix(R, k) & mask_b)
+                else:
+                    R = R ^ (_feed_mix(L, k) & mask_a)
+            x[todo] = (L << np.uint32(a)) | R
+            todo = x >= n
+    return x.astype(np.int64)
+
+
+def feed_pack(array):
+    """Keeps the 0/1 data as they are (the packing is a storage detail of the device library)."""
+    a = np.asarray(array, np.float32)
+    if not np.isin(a, (0, 1)).all():
+        raise ValueError("only 0/1 data can be stored one bit per value")
+    return EigenMatrix(a)
+
+
+def feed_gather(src, packed, dims, key, shuffle, start, out, mean=None, std=None, out_aux=None, aux_mode=0, aux_exp=0):
+    n, count = src.numpy_array.shape[1], out.numpy_array.shape[1]
+    cols = np.arange(start, start + count)
+    if shuffle:
+        cols = feed_permutation(n, key)[cols]
+    x = src.numpy_array[:, cols].astype(np.float32)
+    if mean is not None:
+        x = ((x + (-mean.numpy_array.reshape(-1, 1))) / std.numpy_array.reshape(-1, 1)).astype(np.float32)
+    out.numpy_array[...] = x
+    return out

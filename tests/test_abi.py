@@ -16,7 +16,7 @@ LIB = os.path.join(ROOT, "deepnet_b200", "libb200mat.so")
 def declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"^\s*(?:const\s+)?(?:int|void|float|char)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
+    names = re.findall(r"^\s*(?:const\s+)?(?:unsigned\s+)?(?:int|void|float|char)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
     return sorted(set(names))
 
 
