@@ -486,6 +486,12 @@ class CUDAMatrix(object):
                                    state.p_mat, sample.p_mat if sample is not None else None))
         return state
 
+    def sample_energy_softmax(self, target, ndraws):
+        """target = counts over ndraws Gumbel-max draws per column from the softmax with energies self
+        (deepnet/ais.py:16-30 in one kernel; consumes ndraws sampling calls)."""
+        _check(_lib.sample_energy_softmax(CUDAMatrix.rnd_state_p, self.p_mat, target.p_mat, ct.c_int(int(ndraws))))
+        return target
+
     def sample_multinomial(self, nn, target, max_draws=1000):
         """target[:, i] = counts of int(nn[i]) draws from self[:, i] (replicated_softmax_layer.py:43-60 fused)."""
         _check(_lib.sample_multinomial(CUDAMatrix.rnd_state_p, self.p_mat, nn.p_mat, target.p_mat, ct.c_int(max_draws)))

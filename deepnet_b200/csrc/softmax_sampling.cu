@@ -205,6 +205,78 @@ __global__ void __launch_bounds__(128) k_softmax_sample(const float* pre, const 
   }
 }
 
+// D independent Gumbel-max draws per column from the energies of a softmax, counted per row: the
+// loop of deepnet/ais.py:16-30 (SampleEnergySoftmax: for each of D draws,
+// perturb_energy_for_softmax_sampling then choose_max_and_accumulate) as one kernel.  Draw d of
+// column c takes the uniform of element (row, global column) of sampling call (calls + d): what
+// the call-by-call loop draws, so both give the same counts.  grid = (blocks of 4 columns, draw
+// groups); a block races one draw of its 4 columns (the 4 words of a Philox block) over all rows.
+__global__ void __launch_bounds__(256) k_sample_energy_softmax(const float* __restrict__ energy, float* counts, int h,
+                                                               int w, int ndraws, int col0, unsigned long long seed,
+                                                               unsigned long long call0) {
+  __shared__ float sv[4][8];
+  __shared__ int si[4][8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int first_blk = col0 >> 2, nblk = ((col0 + w - 1) >> 2) - first_blk + 1;
+  for (int b = blockIdx.x; b < nblk; b += gridDim.x) {
+    const int blk = first_blk + b;
+    for (int d = blockIdx.y; d < ndraws; d += gridDim.y) {
+      const PhiloxKey key = make_philox_key(seed, call0 + (unsigned long long)d);
+      float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      int bi[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+      for (int r = threadIdx.x; r < h; r += blockDim.x) {
+        const uint4 wd = philox4x32_10((uint32_t)r, (uint32_t)blk, key);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int c = (blk << 2) + j - col0;
+          if (c < 0 || c >= w) continue;
+          const float v = energy[(long)c * h + r] - logf(-logf(word_to_uniform(pick_word(wd, j))));   // cudamat_kernels.cu:240-251
+          if (v > bv[j] || (v == bv[j] && r < bi[j])) {
+            bv[j] = v;
+            bi[j] = r;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float v2 = __shfl_xor_sync(0xffffffffu, bv[j], o);
+          const int i2 = __shfl_xor_sync(0xffffffffu, bi[j], o);
+          if (v2 > bv[j] || (v2 == bv[j] && i2 < bi[j])) {
+            bv[j] = v2;
+            bi[j] = i2;
+          }
+        }
+      }
+      __syncthreads();
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          sv[j][wid] = bv[j];
+          si[j][wid] = bi[j];
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x < 4) {
+        const int j = threadIdx.x, c = (blk << 2) + j - col0;
+        if (c >= 0 && c < w) {
+          float v = sv[j][0];
+          int i = si[j][0];
+          for (int q = 1; q < (int)(blockDim.x >> 5); q++)
+            if (sv[j][q] > v || (sv[j][q] == v && si[j][q] < i)) {
+              v = sv[j][q];
+              i = si[j][q];
+            }
+          if (i == 0x7fffffff) i = 0;
+          atomicAdd(&counts[(long)c * h + i], 1.0f);
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -261,6 +333,30 @@ int softmax_sample(rnd_struct* rnd_state, cudamat* pre, cudamat* bias, cudamat* 
   k_softmax_sample<<<w < sm_count() * 16 ? w : sm_count() * 16, 128, 0, stream()>>>(
       pre->data_device, bias ? bias->data_device : nullptr, state->data_device, sample ? sample->data_device : nullptr,
       h, w, rng_col0(), key);
+  return check_launch();
+}
+
+// target[:, c] = counts over `ndraws` Gumbel-max draws from the softmax whose energies are
+// energy[:, c] (deepnet/ais.py:16-30).  Consumes ndraws sampling calls.
+int sample_energy_softmax(rnd_struct* rnd_state, cudamat* energy, cudamat* target, int ndraws) {
+  if (!energy->on_device || !target->on_device) return ERROR_NOT_ON_DEVICE;
+  if (energy->is_trans || target->is_trans) return ERROR_TRANSPOSED;
+  if (!same_shape(energy, target)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (ndraws < 0) return ERROR_UNSUPPORTED;
+  const int h = energy->size[0], w = energy->size[1];
+  if ((long)h * w == 0) return 0;
+  if (cudaMemsetAsync(target->data_device, 0, (size_t)h * w * sizeof(float), stream()) != cudaSuccess)
+    return set_error("cudaMemsetAsync failed");
+  const unsigned long long call0 = rnd_state->calls;
+  rnd_state->calls += (unsigned long long)ndraws;
+  if (ndraws == 0) return 0;
+  const int col0 = rng_col0();
+  const int nblk = ((col0 + w - 1) >> 2) - (col0 >> 2) + 1;
+  int gy = ndraws < 64 ? ndraws : 64;
+  int gx = nblk;
+  if ((long)gx * gy > 65535L * 4) gx = (int)(65535L * 4 / gy);
+  k_sample_energy_softmax<<<dim3(gx, gy), 256, 0, stream()>>>(energy->data_device, target->data_device, h, w, ndraws, col0,
+                                                            rnd_state->seed, call0);
   return check_launch();
 }
 

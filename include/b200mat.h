@@ -255,6 +255,11 @@ int add_sum_by_axis_noalloc(cudamat* mat, cudamat* target, int axis, float mult)
  * negative phase (deepnet/layer.py:202-213: sum(axis=1), then add_sums(axis=1, mult=-1)). */
 int row_sum_diff(cudamat* a, cudamat* b, cudamat* target);
 
+/* target[:, c] = counts over ndraws Gumbel-max draws from the softmax with energies energy[:, c]:
+ * the loop of deepnet/ais.py:16-30 (perturb_energy_for_softmax_sampling + choose_max_and_accumulate
+ * per draw) in one kernel on the same random stream (ndraws sampling calls). */
+int sample_energy_softmax(rnd_struct* rnd_state, cudamat* energy, cudamat* target, int ndraws);
+
 /* state[:, j] = softmax(pre[:, j] + bias); sample[:, j] = one categorical draw from it as a one-hot
  * column: deepnet/softmax_layer.py:11-16 (apply_softmax, perturb_prob_for_softmax_sampling,
  * choose_max(axis=0)) in one kernel on the same random stream.  bias and sample may be null
