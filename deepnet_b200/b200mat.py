@@ -1133,6 +1133,12 @@ def dp_destroy():
     _lib.dp_destroy()
 
 
+def dp_wait(timeout_ms=30000):
+    """Blocks until the enqueued work (all-reduces included) is done; a collective that does not
+    complete within timeout_ms (a peer never joined) is aborted and raises."""
+    _check(_lib.dp_wait(ct.c_int(int(timeout_ms))))
+
+
 def dp_abort():
     """Tears the communicator down without waiting for collectives in flight (a peer is gone)."""
     _lib.dp_abort()

@@ -6,6 +6,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+#include <time.h>
 
 #include "common.cuh"
 
@@ -115,6 +116,41 @@ int dp_check() {
   if (r != ncclSuccess) return nccl_fail(r);
   if (st != ncclSuccess && st != ncclInProgress) return nccl_fail(st);
   return 0;
+}
+
+// Host-side watchdog for the collectives: waits until everything enqueued on the library stream
+// (all-reduces included) has completed, polling the communicator for asynchronous errors.  After
+// timeout_ms without completion (a peer that never joined) the communicator is aborted, which
+// ends its kernels, and ERROR_NCCL is returned; the stream is usable again afterwards.
+int dp_wait(int timeout_ms) {
+  timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  for (;;) {
+    const cudaError_t q = cudaStreamQuery(stream());
+    if (q == cudaSuccess) return 0;
+    if (q != cudaErrorNotReady) return set_error(cudaGetErrorString(q));
+    if (g_comm) {
+      ncclResult_t st = ncclSuccess;
+      if (api.CommGetAsyncError(g_comm, &st) == ncclSuccess && st != ncclSuccess && st != ncclInProgress) {
+        api.CommAbort(g_comm);
+        g_comm = nullptr;
+        return nccl_fail(st);
+      }
+    }
+    timespec t1;
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double ms = (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6;
+    if (ms > timeout_ms) {
+      if (g_comm) {
+        api.CommAbort(g_comm);
+        g_comm = nullptr;
+      }
+      set_error("dp_wait: the collectives did not complete in time; the communicator was aborted");
+      return ERROR_NCCL;
+    }
+    timespec nap = {0, 50000};
+    nanosleep(&nap, nullptr);
+  }
 }
 
 int dp_destroy() {

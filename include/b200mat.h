@@ -318,6 +318,9 @@ int dp_allreduce(cudamat* mat);           /* in-place sum over ranks, on the lib
 int dp_check(void);
 int dp_destroy(void);
 int dp_abort(void);
+/* Waits (at most timeout_ms) for the work enqueued on the library stream, collectives included; on
+ * time-out or an asynchronous NCCL error aborts the communicator and returns ERROR_NCCL. */
+int dp_wait(int timeout_ms);
 
 /* ---- a recorded training step: no counterpart in the reference ---------------------------- */
 /* The update of deepnet/dbm.py:268-274 is 10-60 library calls per minibatch; at the small

@@ -42,6 +42,7 @@ def main():
     for step in range(3):
         s = step * gb + rank * b
         eng.TrainOneBatch(step, data.slice(s, s + b))
+    cm.dp_wait(20000)        # bounded: a peer that never joined would end here with an error, not a hang
     cm.dp_check()
     np.savez(os.path.join(tmp, "rank%d.npz" % rank), W=np.array(eng.W.asarray()), hs=np.array(eng.h_samp.asarray()),
              loss=eng.read_loss(), status=cm.read_status())
