@@ -49,7 +49,8 @@ class rnd_struct(ct.Structure):
 class _Pass(ct.Structure):
     _fields_ = [("a", ct.POINTER(cudamat)), ("b", ct.POINTER(cudamat)), ("negate", ct.c_int),
                 ("a_part", ct.c_int), ("b_part", ct.c_int),
-                ("a_aux", ct.POINTER(cudamat)), ("b_aux", ct.POINTER(cudamat))]
+                ("a_aux", ct.POINTER(cudamat)), ("b_aux", ct.POINTER(cudamat)),
+                ("a_row0", ct.c_int), ("a_rows", ct.c_int), ("b_row0", ct.c_int), ("b_rows", ct.c_int)]
 
 
 class _FusedGemm(ct.Structure):
@@ -617,18 +618,19 @@ def b16(x, aux=None):
     return Part(x, PART_B16, aux)
 
 
-def f16_passes(a, a_aux, b, b_aux, negate=0, exact_a=False, exact_b=False):
+def f16_passes(a, a_aux, b, b_aux, negate=0, exact_a=False, exact_b=False, a_rows=None, b_rows=None):
     """The terms of a . b over aux matrices in scaled half-precision form (`split_f16`): with
     x * 2^e = hi + lo,  a . b * 2^(ea + eb) ~= hi(a).lo(b) + lo(a).hi(b) + hi(a).hi(b), three
     half-precision products (no TF32 term, no fp32 operand read), below 2^-21 per term.  The
     caller passes the exponent sum to `fused_gemm` (scale_exp / scale_exp_const).  exact_a /
     exact_b: that operand is exact in fp16 (0/1 data and samples), its lo plane is not read."""
+    win = dict(a_rows=a_rows, b_rows=b_rows) if (a_rows or b_rows) else None   # (first stored row, count): see fused_gemm
     p = []
     if not exact_b:
-        p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16LO, b_aux), negate))
+        p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16LO, b_aux), negate, win))
     if not exact_a:
-        p.append((Part(a, PART_F16LO, a_aux), Part(b, PART_F16HI, b_aux), negate))
-    p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16HI, b_aux), negate))
+        p.append((Part(a, PART_F16LO, a_aux), Part(b, PART_F16HI, b_aux), negate, win))
+    p.append((Part(a, PART_F16HI, a_aux), Part(b, PART_F16HI, b_aux), negate, win))
     return p
 
 
@@ -640,7 +642,8 @@ def f16_scale_state(max_abs):
     return CUDAMatrix(np.array([[e, e, 0.0, 0.0]], np.float32))
 
 
-def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16", a_aux=None, b_aux=None):
+def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16", a_aux=None, b_aux=None, a_rows=None,
+                 b_rows=None):
     """The terms of a . b at fp32 grade, small terms first.  terms="bf16": the corrections are
     bfloat16 products, lo16(a).b16(b) + b16(a).lo16(b) (twice the TF32 rate; 2^-18 per term);
     terms="tf32": TF32 products lo32(a).b + a.lo32(b) (2^-20 per term: for products whose
@@ -649,19 +652,20 @@ def split_passes(a, b, negate=0, exact_a=False, exact_b=False, terms="bf16", a_a
     a_aux / b_aux: AuxMatrix of a / b (of the untransposed matrix): the bfloat16 parts are read
     from it instead of being derived in the kernel, which the big products need to run at the
     tensor pipe's rate."""
+    win = dict(a_rows=a_rows, b_rows=b_rows) if (a_rows or b_rows) else None
     p = []
     if terms == "bf16":
         if not exact_a:
-            p.append((lo16(a, a_aux), b16(b, b_aux), negate))
+            p.append((lo16(a, a_aux), b16(b, b_aux), negate, win))
         if not exact_b:
-            p.append((b16(a, a_aux), lo16(b, b_aux), negate))
-        p.append((Part(a, PART_X, a_aux), Part(b, PART_X, b_aux), negate))
+            p.append((b16(a, a_aux), lo16(b, b_aux), negate, win))
+        p.append((Part(a, PART_X, a_aux), Part(b, PART_X, b_aux), negate, win))
     else:
         if not exact_a:
-            p.append((lo32(a), b, negate))
+            p.append((lo32(a), b, negate, win))
         if not exact_b:
-            p.append((a, lo32(b), negate))
-        p.append((a, b, negate))
+            p.append((a, lo32(b), negate, win))
+        p.append((a, b, negate, win))
     return p
 
 
@@ -778,6 +782,12 @@ def _build_fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, 
             if is_part and op.aux is not None:
                 setattr(f.passes[i], side + "_aux", op.aux.p_mat)
         f.passes[i].negate = int(p[2]) if len(p) > 2 else 0
+        if len(p) > 3 and p[3]:      # row windows: dict(a_rows=(first, count), b_rows=(first, count))
+            for side in ("a", "b"):
+                win = p[3].get(side + "_rows")
+                if win:
+                    setattr(f.passes[i], side + "_row0", int(win[0]))
+                    setattr(f.passes[i], side + "_rows", int(win[1]))
     f.alpha, f.beta, f.activation = alpha, beta, activation
     f.scale_exp_const, f.aux_f16, f.aux_exp = int(scale_exp_const), int(bool(aux_f16)), int(aux_exp)
     for name, m in (("bias", bias), ("col_scale", col_scale), ("out", out), ("sample", sample),
@@ -794,7 +804,8 @@ def _build_fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, 
 # the small configurations need: their kernels are shorter than a call from Python.
 (OP_FUSED_GEMM, OP_SUM_AXIS, OP_ADD_SUM_AXIS, OP_ROW_SUM_DIFF, OP_ADD_SQ_DIFF, OP_MOMENTUM_UPDATE, OP_SPLIT_F16,
  OP_SPLIT_BF16, OP_ALLREDUCE, OP_SOFTMAX_SCALED, OP_SAMPLE_MULTINOMIAL, OP_DIV_BY_ROW, OP_ADD_SCALAR, OP_ASSIGN_SCALAR,
- OP_COPY, OP_SAMPLE_BERNOULLI, OP_SOFTMAX_SAMPLE) = range(17)
+ OP_COPY, OP_SAMPLE_BERNOULLI, OP_SOFTMAX_SAMPLE, OP_MOMENTUM_UPDATE_COLUMNS, OP_ALLREDUCE_BEGIN, OP_ALLREDUCE_END,
+ OP_SM_LIMIT) = range(21)
 
 
 class _Op(ct.Structure):
@@ -829,6 +840,13 @@ class Immediate(object):
     def momentum_update(self, w, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None, w_scale=None):
         w.momentum_update(delta, grad, suff, inv_batch, momentum, eps, l2=l2, l1=l1, w_aux=w_aux, w_scale=w_scale)
 
+    def momentum_update_columns(self, w, delta, grad, suff, col0, ncols, inv_batch, momentum, eps, l2=0.0, l1=0.0,
+                                w_aux=None, w_scale=None):
+        p = lambda m: m.p_mat if m is not None else None
+        _check(_lib.momentum_update_columns(w.p_mat, delta.p_mat, p(grad), suff.p_mat, p(w_aux), p(w_scale), ct.c_int(col0),
+                                            ct.c_int(ncols), ct.c_float(inv_batch), ct.c_float(momentum), ct.c_float(eps),
+                                            ct.c_float(l2), ct.c_float(l1)))
+
     def split_f16(self, x, aux, exp_dev=None, exp_const=0):
         x.split_f16(aux, exp_dev, exp_const)
 
@@ -837,6 +855,15 @@ class Immediate(object):
 
     def allreduce(self, mat):
         dp_allreduce(mat)
+
+    def allreduce_begin(self, mat, slot):
+        _check(_lib.dp_allreduce_begin(mat.p_mat, ct.c_int(slot)))
+
+    def allreduce_end(self, slot):
+        _check(_lib.dp_allreduce_end(ct.c_int(slot)))
+
+    def sm_limit(self, sms):
+        _check(_lib.b200_set_sm_limit(ct.c_int(sms)))
 
     def softmax_scaled(self, mat, scale, target):
         mat.softmax_scaled(scale, target)
@@ -909,6 +936,20 @@ class Program(object):
 
     def momentum_update(self, w, delta, grad, suff, inv_batch, momentum, eps, l2=0.0, l1=0.0, w_aux=None, w_scale=None):
         return self._add(OP_MOMENTUM_UPDATE, (w, delta, grad, suff, w_aux, w_scale), (), (inv_batch, momentum, eps, l2, l1))
+
+    def momentum_update_columns(self, w, delta, grad, suff, col0, ncols, inv_batch, momentum, eps, l2=0.0, l1=0.0,
+                                w_aux=None, w_scale=None):
+        return self._add(OP_MOMENTUM_UPDATE_COLUMNS, (w, delta, grad, suff, w_aux, w_scale), (col0, ncols),
+                         (inv_batch, momentum, eps, l2, l1))
+
+    def allreduce_begin(self, mat, slot):
+        return self._add(OP_ALLREDUCE_BEGIN, (mat,), (slot,))
+
+    def allreduce_end(self, slot):
+        return self._add(OP_ALLREDUCE_END, (), (slot,))
+
+    def sm_limit(self, sms):
+        return self._add(OP_SM_LIMIT, (), (sms,))
 
     def split_f16(self, x, aux, exp_dev=None, exp_const=0):
         return self._add(OP_SPLIT_F16, (x, aux, exp_dev), (exp_const,))
@@ -1039,6 +1080,15 @@ def set_gemm_path(path):
 def set_dot_precision(mode):
     """0: fp32-grade split-TF32 `dot` (default); 1: one TF32 pass."""
     _lib.b200_set_dot_precision(ct.c_int(mode))
+
+
+def set_sm_limit(sms):
+    """SMs the library's kernels size their grids for (0 = all of the device)."""
+    _check(_lib.b200_set_sm_limit(ct.c_int(int(sms))))
+
+
+def sm_count():
+    return _lib.b200_sm_count()
 
 
 def set_split_k(mode):

@@ -61,9 +61,11 @@ cudaStream_t stream() {
   return g_stream;
 }
 cudaStream_t stream_if_initialised() { return g_stream; }
+static int g_sm_limit = 0;
 int sm_count() {
   ensure_init();
-  return g_sm_count > 0 ? g_sm_count : 148;
+  const int n = g_sm_count > 0 ? g_sm_count : 148;
+  return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
 int rng_col0() { return g_col0; }
 int* status_word() {
@@ -143,6 +145,15 @@ int cublas_init() {
 // the kernel gives up, records where in the status word (b200_read_status) and returns.  The
 // default, 2^24, is one to two seconds; 0 restores it.  Failure-detection tests set a few
 // thousand iterations (milliseconds) so that a wait that cannot complete ends quickly.
+// SMs the library's kernels size their grids for (0 = all of the device).  The data-parallel step
+// leaves a few SMs to the all-reduce that runs beside its statistics products: the persistent
+// tensor-core kernel otherwise holds every SM until it ends.
+int b200_sm_count() { return sm_count(); }
+int b200_set_sm_limit(int sms) {
+  g_sm_limit = sms > 0 ? sms : 0;
+  return 0;
+}
+
 int b200_set_wait_limit(unsigned int iterations) {
   g_wait_limit = iterations ? iterations : (1u << 24);
   return 0;

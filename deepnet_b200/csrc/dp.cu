@@ -108,6 +108,55 @@ int dp_allreduce(cudamat* mat) {
   return 0;
 }
 
+}  // extern "C"
+
+namespace {
+
+// The same all-reduce on a side stream, so that it runs beside the kernels that follow on the
+// library stream: `begin` makes the side stream wait for what has been enqueued so far (the product
+// that filled this buffer) and starts the all-reduce there; `end` makes the library stream wait for
+// it.  The statistics of an update are reduced panel by panel this way while the next panel is
+// still being multiplied.  slot = 0..7, one pending all-reduce each.
+constexpr int kSlots = 8;
+cudaStream_t g_side = nullptr;
+cudaEvent_t g_ready[kSlots] = {nullptr}, g_done[kSlots] = {nullptr};
+
+int ensure_side_stream() {
+  if (g_side) return 0;
+  if (cudaStreamCreateWithFlags(&g_side, cudaStreamNonBlocking) != cudaSuccess) return set_error("side stream creation failed");
+  for (int i = 0; i < kSlots; i++)
+    if (cudaEventCreateWithFlags(&g_ready[i], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&g_done[i], cudaEventDisableTiming) != cudaSuccess)
+      return set_error("event creation failed");
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dp_allreduce_begin(cudamat* mat, int slot) {
+  if (!mat->on_device) return ERROR_NOT_ON_DEVICE;
+  if (slot < 0 || slot >= kSlots) return ERROR_UNSUPPORTED;
+  if (g_nranks == 1) return 0;
+  if (!g_comm) return set_error("dp_allreduce_begin before dp_init");
+  int err = ensure_side_stream();
+  if (err) return err;
+  if (cudaEventRecord(g_ready[slot], stream()) != cudaSuccess || cudaStreamWaitEvent(g_side, g_ready[slot], 0) != cudaSuccess)
+    return set_error("dp_allreduce_begin: event hand-over failed");
+  ncclResult_t r = api.AllReduce(mat->data_device, mat->data_device, (size_t)numel(mat), ncclFloat, ncclSum, g_comm, g_side);
+  if (r != ncclSuccess) return nccl_fail(r);
+  if (cudaEventRecord(g_done[slot], g_side) != cudaSuccess) return set_error("dp_allreduce_begin: cudaEventRecord failed");
+  return 0;
+}
+
+int dp_allreduce_end(int slot) {
+  if (slot < 0 || slot >= kSlots) return ERROR_UNSUPPORTED;
+  if (g_nranks == 1 || !g_side) return 0;
+  if (cudaStreamWaitEvent(stream(), g_done[slot], 0) != cudaSuccess) return set_error("dp_allreduce_end failed");
+  return 0;
+}
+
 // Polls the communicator for an asynchronous error (a peer that died, a timeout).
 int dp_check() {
   if (!g_comm) return 0;

@@ -40,6 +40,8 @@ struct GemmOperand {
   int part;
   const float* aux;   // aux matrix of the same matrix (or null: bfloat16 parts are derived from ptr)
   int lda;            // floats per column of aux
+  int row0;           // first stored row of the window the product reads (its length is M or N): a panel of the
+                      // output rows (a, not transposed) or columns (b, transposed) without copying the operand
 };
 
 // One term of the sum: op(a) is M x k, op(b) is k x N.

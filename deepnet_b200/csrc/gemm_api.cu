@@ -22,6 +22,7 @@ inline GemmOperand operand(const cudamat* m, int part, const cudamat* aux = null
   o.part = part;
   o.aux = aux ? aux->data_device : nullptr;
   o.lda = aux ? aux->size[0] : 0;
+  o.row0 = 0;
   return o;
 }
 // An aux handle holds aux_rows(rows) x cols floats.
@@ -263,6 +264,10 @@ struct b200_pass {
   int a_part, b_part;
   cudamat* a_aux;
   cudamat* b_aux;
+  // Row windows of the STORED matrices (0, 0 = all rows): a_rows > 0 restricts a (not transposed) to
+  // rows [a_row0, a_row0 + a_rows), a panel of the output's rows; b_rows > 0 restricts b (transposed)
+  // likewise, a panel of the output's columns.  Offsets are multiples of 8.
+  int a_row0, a_rows, b_row0, b_rows;
 };
 // out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale)
 struct b200_fused_gemm {
@@ -338,12 +343,17 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
   GemmProblem g;
   g.npass = f->npass;
   g.tf32_operands = 1;
-  g.M = lead(f->pass[0].a);
-  g.N = nonlead(f->pass[0].b);
+  g.M = f->pass[0].a_rows > 0 ? f->pass[0].a_rows : lead(f->pass[0].a);
+  g.N = f->pass[0].b_rows > 0 ? f->pass[0].b_rows : nonlead(f->pass[0].b);
   for (int q = 0; q < f->npass; q++) {
     const cudamat *a = f->pass[q].a, *b = f->pass[q].b;
+    const b200_pass& ps = f->pass[q];
     if (!a->on_device || !b->on_device) return ERROR_NOT_ON_DEVICE;
-    if (lead(a) != g.M || nonlead(b) != g.N || nonlead(a) != lead(b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+    // a window selects rows of the stored matrix that run along M (a as stored) or N (b transposed)
+    if (ps.a_rows > 0 && (a->is_trans || ps.a_row0 < 0 || (ps.a_row0 & 7) || ps.a_row0 + ps.a_rows > a->size[0])) return ERROR_UNSUPPORTED;
+    if (ps.b_rows > 0 && (!b->is_trans || ps.b_row0 < 0 || (ps.b_row0 & 7) || ps.b_row0 + ps.b_rows > b->size[0])) return ERROR_UNSUPPORTED;
+    const int m_q = ps.a_rows > 0 ? ps.a_rows : lead(a), n_q = ps.b_rows > 0 ? ps.b_rows : nonlead(b);
+    if (m_q != g.M || n_q != g.N || nonlead(a) != lead(b)) return ERROR_INCOMPATIBLE_DIMENSIONS;
     const int pa = f->pass[q].a_part, pb = f->pass[q].b_part;
     if (pa < 0 || pa >= kNumParts || pb < 0 || pb >= kNumParts) return ERROR_UNSUPPORTED;
     // both operands of a term of one kind: fp32-wide, bfloat16, or scaled half precision (aux only)
@@ -353,6 +363,8 @@ int fused_gemm(rnd_struct* rnd_state, b200_fused_gemm* f) {
     if ((xa && !aux_shape_ok(xa, a)) || (xb && !aux_shape_ok(xb, b))) return ERROR_INCOMPATIBLE_DIMENSIONS;
     g.pass[q].a = operand(a, pa, xa);
     g.pass[q].b = operand(b, pb, xb);
+    if (ps.a_rows > 0) g.pass[q].a.row0 = ps.a_row0;
+    if (ps.b_rows > 0) g.pass[q].b.row0 = ps.b_row0;
     g.pass[q].k = nonlead(a);
     g.pass[q].negate = f->pass[q].negate;
   }
@@ -471,52 +483,72 @@ int dot(cudamat* mat1, cudamat* mat2, cudamat* target, float beta, float alpha) 
 //   second pass rewrites it only when the new w no longer fits that exponent.
 // grad may be null (treated as zero and not written).  20 bytes of traffic per element
 // without grad and aux; +8 with grad, +4 with either aux (+8 more in an update that changes the exponent).
-int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
-                    float inv_batch, float momentum, float eps, float l2, float l1) {
+// The update restricted to columns [col0, col0 + ncols) of the parameter (and of delta, grad, suff,
+// w_aux): the statistics of a data-parallel update arrive panel by panel (each after its own
+// all-reduce) and every panel is updated as it arrives.  In scaled half-precision form all panels
+// use the exponent carried so far; the check of that exponent against the new parameter (and, if it
+// no longer fits, the rewrite of the whole aux) runs with the panel that ends at the last column.
+int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                            int col0, int ncols, float inv_batch, float momentum, float eps, float l2, float l1) {
   if (!w->on_device || !delta->on_device || !suff->on_device) return ERROR_NOT_ON_DEVICE;
   if (!same_shape(w, delta) || !same_shape(w, suff)) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (grad && (!grad->on_device || !same_shape(w, grad))) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (w_aux && (w->is_trans || !aux_shape_ok(w_aux, w))) return ERROR_INCOMPATIBLE_DIMENSIONS;
   if (w_scale && (!w_aux || !w_scale->on_device || numel(w_scale) < 4)) return ERROR_INCOMPATIBLE_DIMENSIONS;
-  const long n = numel(w);
-  if (n == 0) return 0;
-  uintptr_t bits = (uintptr_t)w->data_device | (uintptr_t)delta->data_device | (uintptr_t)suff->data_device;
-  if (grad) bits |= (uintptr_t)grad->data_device;
-  if (w_aux) bits |= (uintptr_t)w_aux->data_device;
+  if (w->is_trans && !(col0 == 0 && ncols == w->size[1])) return ERROR_TRANSPOSED;
+  if (col0 < 0 || ncols < 0 || col0 + ncols > w->size[1]) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const int rows = w->size[0];
-  const bool vec = (bits & 15) == 0 && n % 4 == 0 && (!w_aux || rows % 4 == 0);
-  long blocks = ((vec ? n / 4 : n) + 255) / 256;
-  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
-  if (blocks < 1) blocks = 1;
-  float* gp = grad ? grad->data_device : nullptr;
-  uint16_t* ap = w_aux ? reinterpret_cast<uint16_t*>(w_aux->data_device) : nullptr;
+  const long n = (long)rows * ncols, first = (long)rows * col0;
+  const bool last_panel = col0 + ncols == w->size[1];
   float* sp = w_scale ? w_scale->data_device : nullptr;
+  uint16_t* ap = w_aux ? reinterpret_cast<uint16_t*>(w_aux->data_device) : nullptr;
   const int mode = !w_aux ? 0 : (w_scale ? 2 : 1);
-#define LAUNCH_UPDATE(G, A)                                                                                       \
-  k_update<G, A><<<(int)blocks, 256, 0, stream()>>>(w->data_device, delta->data_device, gp, suff->data_device, ap, \
-                                                    sp, rows, aux_rows(rows), n, vec, -inv_batch, momentum, -eps, l2, l1)
-  if (grad) {
-    if (mode == 2) LAUNCH_UPDATE(true, 2);
-    else if (mode == 1) LAUNCH_UPDATE(true, 1);
-    else LAUNCH_UPDATE(true, 0);
-  } else {
-    if (mode == 2) LAUNCH_UPDATE(false, 2);
-    else if (mode == 1) LAUNCH_UPDATE(false, 1);
-    else LAUNCH_UPDATE(false, 0);
-  }
+  const int lda = aux_rows(rows);
+  if (n > 0) {
+    float *wp = w->data_device + first, *dp = delta->data_device + first, *gp = grad ? grad->data_device + first : nullptr;
+    const float* sfp = suff->data_device + first;
+    uint16_t* app = ap ? ap + (long)col0 * 2 * lda : nullptr;
+    uintptr_t bits = (uintptr_t)wp | (uintptr_t)dp | (uintptr_t)sfp;
+    if (gp) bits |= (uintptr_t)gp;
+    if (app) bits |= (uintptr_t)app;
+    const bool vec = (bits & 15) == 0 && n % 4 == 0 && (!w_aux || rows % 4 == 0);
+    long blocks = ((vec ? n / 4 : n) + 255) / 256;
+    if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+    if (blocks < 1) blocks = 1;
+#define LAUNCH_UPDATE(G, A)                                                                                  \
+  k_update<G, A><<<(int)blocks, 256, 0, stream()>>>(wp, dp, gp, sfp, app, sp, rows, lda, n, vec, -inv_batch, \
+                                                    momentum, -eps, l2, l1)
+    if (grad) {
+      if (mode == 2) LAUNCH_UPDATE(true, 2);
+      else if (mode == 1) LAUNCH_UPDATE(true, 1);
+      else LAUNCH_UPDATE(true, 0);
+    } else {
+      if (mode == 2) LAUNCH_UPDATE(false, 2);
+      else if (mode == 1) LAUNCH_UPDATE(false, 1);
+      else LAUNCH_UPDATE(false, 0);
+    }
 #undef LAUNCH_UPDATE
-  int err = check_launch();
-  if (err || mode != 2) return err;
+    const int err = check_launch();
+    if (err) return err;
+  }
+  if (mode != 2 || !last_panel) return 0;
   k_update_scale<<<1, 1, 0, stream()>>>(sp);
-  err = check_launch();
+  int err = check_launch();
   if (err) return err;
+  const long total = numel(w);
+  if (total == 0) return 0;
   const bool svec = (rows % 4 == 0) && ((((uintptr_t)w->data_device) & 15) == 0);
-  long sblocks = ((svec ? n / 4 : n) + 255) / 256;
+  long sblocks = ((svec ? total / 4 : total) + 255) / 256;
   if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
   if (sblocks < 1) sblocks = 1;
   // (returns at once unless the exponent had to change)
-  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, aux_rows(rows), n, svec, sp, 0, sp + 3);
+  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, lda, total, svec, sp, 0, sp + 3);
   return check_launch();
+}
+
+int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                    float inv_batch, float momentum, float eps, float l2, float l1) {
+  return momentum_update_columns(w, delta, grad, suff, w_aux, w_scale, 0, w->size[1], inv_batch, momentum, eps, l2, l1);
 }
 
 }  // extern "C"

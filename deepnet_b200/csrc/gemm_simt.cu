@@ -15,6 +15,7 @@ __device__ __forceinline__ float as_operand(float x, int tf32) {
 }
 // Element (r, c) of the stored matrix, as the part the term reads.
 __device__ __forceinline__ float element(const GemmOperand& o, int r, int c, int tf32) {
+  r += o.row0;
   if (o.part >= kPartLo16 && o.aux) {
     const long w = (long)c * 2 * o.lda + ((o.part == kPartB16 || o.part == kPartF16Hi) ? o.lda : 0) + r;
     const uint16_t bits = reinterpret_cast<const uint16_t*>(o.aux)[w];

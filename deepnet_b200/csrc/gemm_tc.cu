@@ -1107,7 +1107,8 @@ bool make_map(CUtensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint6
 
 // TMA needs a 16-byte aligned base and column stride.
 inline bool tma_ok(const GemmOperand& o) {
-  return (o.ld % 4 == 0) && (((uintptr_t)o.ptr & 15) == 0) && (!o.aux || (o.lda % 8 == 0 && ((uintptr_t)o.aux & 15) == 0));
+  return (o.ld % 4 == 0) && (((uintptr_t)(o.ptr + o.row0) & 15) == 0) &&
+         (!o.aux || (o.lda % 8 == 0 && ((uintptr_t)o.aux & 15) == 0 && o.row0 % 8 == 0));
 }
 
 // Shared-memory matrix descriptor, upper 32 bits: stride byte offset (bits 32-45, in
@@ -1142,7 +1143,7 @@ TcTile tile_view(bool mn, bool bf16, int bk, uint32_t smem_off) {
 }
 
 inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
-  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.aux == b.aux && a.lda == b.lda;
+  return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.aux == b.aux && a.lda == b.lda && a.row0 == b.row0;
 }
 
 static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
@@ -1383,7 +1384,7 @@ int gemm_tc(const GemmProblem& g) {
       const bool from_aux = src[o]->aux != nullptr;
       if (!(want[o][kPartX] || want[o][kPartLo32] || (!from_aux && (want[o][kPartLo16] || want[o][kPartB16])))) continue;
       x_off[o] = off;
-      if (!add_load(o, src[o]->ptr, (uint64_t)src[o]->ld, false))
+      if (!add_load(o, src[o]->ptr + src[o]->row0, (uint64_t)src[o]->ld, false))
         return set_error("cuTensorMapEncodeTiled failed for an operand");
       tile_of[o][kPartX] = ntiles;
       tg.tile[ntiles++] = tile_view(mn[o], false, bk, off);
@@ -1393,7 +1394,8 @@ int gemm_tc(const GemmProblem& g) {
       if (!src[o]->aux) continue;
       for (int part = kPartLo16; part < kNumParts; part++) {
         if (!want[o][part]) continue;
-        const uint16_t* plane = reinterpret_cast<const uint16_t*>(src[o]->aux) + (part_plane(part) ? src[o]->lda : 0);
+        const uint16_t* plane =
+            reinterpret_cast<const uint16_t*>(src[o]->aux) + (part_plane(part) ? src[o]->lda : 0) + src[o]->row0;
         if (!add_load(o, plane, (uint64_t)(2 * src[o]->lda), true))
           return set_error("cuTensorMapEncodeTiled failed for an aux plane");
         tile_of[o][part] = ntiles;

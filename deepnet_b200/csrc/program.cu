@@ -19,6 +19,11 @@ int row_sum_diff(cudamat* a, cudamat* b, cudamat* target);
 int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc);
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
                     float inv_batch, float momentum, float eps, float l2, float l1);
+int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                            int col0, int ncols, float inv_batch, float momentum, float eps, float l2, float l1);
+int dp_allreduce_begin(cudamat* mat, int slot);
+int dp_allreduce_end(int slot);
+int b200_set_sm_limit(int sms);
 int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const);
 int split_bf16(cudamat* x, cudamat* aux);
 int dp_allreduce(cudamat* mat);
@@ -50,6 +55,10 @@ enum {
   B200_OP_COPY = 14,           // m0 source, m1 target
   B200_OP_SAMPLE_BERNOULLI = 15,   // m0 mat, m1 target
   B200_OP_SOFTMAX_SAMPLE = 16, // m0 pre, m1 bias?, m2 state, m3 sample?
+  B200_OP_MOMENTUM_UPDATE_COLUMNS = 17,  // as 5, on columns [i0, i0 + i1)
+  B200_OP_ALLREDUCE_BEGIN = 18,   // m0, i0 slot
+  B200_OP_ALLREDUCE_END = 19,     // i0 slot
+  B200_OP_SM_LIMIT = 20,          // i0 SMs the following kernels size their grids for (0 = all)
   B200_OP_COUNT
 };
 
@@ -87,6 +96,12 @@ extern "C" int b200_run_program(rnd_struct* rnd_state, b200_op* ops, int n, int*
       case B200_OP_COPY: err = copy_on_device(o.m[0], o.m[1]); break;
       case B200_OP_SAMPLE_BERNOULLI: err = sample_bernoulli(rnd_state, o.m[0], o.m[1]); break;
       case B200_OP_SOFTMAX_SAMPLE: err = softmax_sample(rnd_state, o.m[0], o.m[1], o.m[2], o.m[3]); break;
+      case B200_OP_MOMENTUM_UPDATE_COLUMNS:
+        err = momentum_update_columns(o.m[0], o.m[1], o.m[2], o.m[3], o.m[4], o.m[5], o.i0, o.i1, o.f0, o.f1, o.f2, o.f3, o.f4);
+        break;
+      case B200_OP_ALLREDUCE_BEGIN: err = dp_allreduce_begin(o.m[0], o.i0); break;
+      case B200_OP_ALLREDUCE_END: err = dp_allreduce_end(o.i0); break;
+      case B200_OP_SM_LIMIT: err = b200_set_sm_limit(o.i0); break;
       default: break;
     }
     if (err) {

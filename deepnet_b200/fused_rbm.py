@@ -120,6 +120,10 @@ class FusedRBM(object):
         # B200_RBM_PROGRAM=0 issues every operation through its own call instead
         self.use_program = os.environ.get("B200_RBM_PROGRAM", "1") != "0"
         self._programs = {}
+        # data parallel, big model: statistics, all-reduce and update run in this many column panels of W
+        # with the all-reduce beside the next panel's product, which leaves it these SMs
+        self.dp_panels = int(os.environ.get("B200_DP_PANELS", "4"))
+        self.dp_reserved_sms = int(os.environ.get("B200_DP_RESERVED_SMS", "12"))
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
         self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
         self._given_aux = None
@@ -139,7 +143,7 @@ class FusedRBM(object):
         return bool(self.hyp.sample_input) and self.hyp.sample_input_after <= step
 
     # launches behind one operation of the vocabulary (row and column sums: partial + finishing launch)
-    _LAUNCHES = dict(sum=2, add_sums=2)
+    _LAUNCHES = dict(sum=2, add_sums=2, sm_limit=0, allreduce_end=0)
 
     def _op(self, X, name, flops, nbytes, method, *args, **kw):
         """Names one operation of the step to the executor X (`Immediate` or a recording `Program`);
@@ -194,7 +198,8 @@ class FusedRBM(object):
                 view.mat.owns_data = 0
         self._batch_owner = (data, data_aux)
         prog.set_floats(ub, f0=sc["inv_b"], f1=mom, f2=eps)
-        prog.set_floats(uw, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
+        for op in (uw if isinstance(uw, list) else [uw]):
+            prog.set_floats(op, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
         prog.run()
 
     def _issue_updates(self, X, sc, wb, w_scale=None):
@@ -290,13 +295,44 @@ class FusedRBM(object):
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
                      sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
-        pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
-        neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
-        self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W, scale_exp_const=2 * E)
+        panels = self.dp_panels if (self.world_size > 1 and H % (8 * self.dp_panels) == 0) else 1
+        if panels == 1:
+            pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
+            neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
+            self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W, scale_exp_const=2 * E)
+            self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
+            self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
+            self.kernel_launches += 2                  # the exponent launch and the pass that writes W's aux
+            return self._issue_updates(X, sc, wb, w_scale=self.W_scale)
+        # Data parallel: the statistics are multiplied, all-reduced and applied in column panels of W.
+        # Panel p's all-reduce runs on a side stream while panel p + 1 multiplies (the persistent
+        # product kernel leaves it a few SMs), and each panel is updated as its sum arrives, so
+        # the exchange hides behind the product instead of standing between product and update.
+        Hc = H // panels
+        self._op(X, "sm_limit", 0, 0, "sm_limit", max(cm.sm_count() - self.dp_reserved_sms, 2))
+        for p in range(panels):
+            win = (p * Hc, Hc)
+            pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True, b_rows=win)
+            neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1, b_rows=win)
+            panel = self.suff_W.slice(p * Hc, (p + 1) * Hc)
+            self._op(X, "gemm_stats", 2 * gf / panels, wb / panels, "fused_gemm", pos + neg, out=panel,
+                     scale_exp_const=2 * E)
+            self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", panel, p)
+        self._op(X, "sm_limit", 0, 0, "sm_limit", 0)
         self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
         self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
-        self.kernel_launches += 2                  # the exponent launch and the pass that writes W's aux
-        return self._issue_updates(X, sc, wb, w_scale=self.W_scale)
+        self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_b, panels)
+        uw = []
+        for p in range(panels):
+            self._op(X, "allreduce_end", 0, 0, "allreduce_end", p)
+            uw.append(self._op(X, "update_W", 0, 6 * wb / panels, "momentum_update_columns", self.W, self.dW, None,
+                               self.suff_W, p * Hc, Hc, sc["inv_b"], sc["emom"], sc["eeps"], l2=sc["l2"], l1=sc["l1"],
+                               w_aux=self.W_aux, w_scale=self.W_scale))
+        self._op(X, "allreduce_end", 0, 0, "allreduce_end", panels)
+        ub = self._op(X, "update_bias", 0, 20.0 * (V + H), "momentum_update", self.b, self.db, None, self.suff_b,
+                      sc["inv_b"], sc["mom"], sc["eps"])
+        self.kernel_launches += 2
+        return ub, uw
 
     def _issue_replicated_softmax(self, X, data, k, draw_v, sc):
         """CD-k with a replicated-softmax visible layer (word-count columns): the call sequence of

@@ -206,6 +206,10 @@ typedef struct b200_pass {
   int a_part, b_part;
   cudamat* a_aux;
   cudamat* b_aux;
+  /* row windows of the stored matrices (0, 0 = all rows; offsets multiples of 8): a_rows > 0 restricts
+   * a (not transposed) to rows [a_row0, a_row0 + a_rows), a panel of the output's rows; b_rows > 0
+   * restricts b (transposed) likewise, a panel of the output's columns */
+  int a_row0, a_rows, b_row0, b_rows;
 } b200_pass;
 
 /* out = act(alpha * sum_p (+/-) op(a_p).op(b_p) + beta * out + bias (x) col_scale).
@@ -240,6 +244,11 @@ int split_tf32(cudamat* x, cudamat* hi, cudamat* lo);
  * fits the new w) its scaled half-precision form.  grad, w_aux, w_scale may be NULL. */
 int momentum_update(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
                     float inv_batch, float momentum, float eps, float l2, float l1);
+/* The same on columns [col0, col0 + ncols) of the parameter: statistics that arrive panel by panel
+ * (each after its own all-reduce) are applied as they arrive; the exponent check of the scaled
+ * half-precision form runs with the panel that ends at the last column. */
+int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* suff, cudamat* w_aux, cudamat* w_scale,
+                            int col0, int ncols, float inv_batch, float momentum, float eps, float l2, float l1);
 
 /* Has no counterpart in the reference.  add_sum_by_axis for callers that must never reach
  * cudaMalloc (a host that gave the whole device to its own memory pool, or a loop that cannot
@@ -291,6 +300,10 @@ int b200_read_status(void);               /* non-zero: a kernel's bounded wait g
 /* Iterations a device-side wait may spin before its kernel gives up (default 2^24, one to two
  * seconds; 0 restores the default).  No counterpart in the reference. */
 int b200_set_wait_limit(unsigned int iterations);
+/* SMs the library's kernels size their grids for (0 = all): leaves room for an all-reduce that runs
+ * beside the persistent tensor-core kernel.  No counterpart in the reference. */
+int b200_set_sm_limit(int sms);
+int b200_sm_count(void);                  /* SMs in force (the device's, or the limit) */
 /* Test hook, host side only: the next tensor-core product expects extra_bytes more per stage than
  * its copies deliver, so one of its bounded waits must run out (status word set, kernel returns).
  * No counterpart in the reference. */
@@ -318,6 +331,11 @@ int dp_allreduce(cudamat* mat);           /* in-place sum over ranks, on the lib
 int dp_check(void);
 int dp_destroy(void);
 int dp_abort(void);
+/* The all-reduce on a side stream, beside the kernels that follow on the library stream: begin waits
+ * for what is enqueued so far and starts it (slot 0..7, one pending all-reduce each); end makes the
+ * library stream wait for it. */
+int dp_allreduce_begin(cudamat* mat, int slot);
+int dp_allreduce_end(int slot);
 /* Waits (at most timeout_ms) for the work enqueued on the library stream, collectives included; on
  * time-out or an asynchronous NCCL error aborts the communicator and returns ERROR_NCCL. */
 int dp_wait(int timeout_ms);
@@ -329,7 +347,8 @@ int dp_wait(int timeout_ms);
  * point (0 fused_gemm, 1 sum_by_axis, 2 add_sum_by_axis, 3 row_sum_diff, 4 add_sq_diff,
  * 5 momentum_update, 6 split_f16, 7 split_bf16, 8 dp_allreduce, 9 softmax_scaled, 10 sample_multinomial,
  * 11 div_by_row_vec, 12 add_scalar, 13 assign_scalar, 14 copy_on_device, 15 sample_bernoulli,
- * 16 softmax_sample); m[], i0.., f0.. are its arguments in declaration order (matrices, then integers,
+ * 16 softmax_sample, 17 momentum_update_columns, 18 dp_allreduce_begin, 19 dp_allreduce_end,
+ * 20 b200_set_sm_limit); m[], i0.., f0.. are its arguments in declaration order (matrices, then integers,
  * then floats; gemm for kind 0).  Stops at the first failure: returns its code, *failed_at its index. */
 struct b200_fused_gemm;
 typedef struct b200_op {

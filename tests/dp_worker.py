@@ -13,6 +13,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     rank, world, tmp = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    scale = float(sys.argv[4]) if len(sys.argv) > 4 else 0.5
     from deepnet_b200 import b200mat as cm
     from deepnet_b200 import configs
     from deepnet_b200.fused_rbm import FusedRBM
@@ -31,7 +32,7 @@ def main():
     with open(idfile, "rb") as f:
         uid = f.read()
     cm.dp_init(uid, world, rank)
-    cfg = configs.build(0, cases=400, dims_scale=0.5)
+    cfg = configs.build(0, cases=400, dims_scale=scale)
     gb = cfg["batchsize"]                       # global minibatch, split evenly over the ranks
     b = gb // world
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]

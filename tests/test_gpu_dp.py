@@ -14,16 +14,18 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("form", ["derived", "f16"])
-def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, monkeypatch):
+@pytest.mark.parametrize("form,scale", [("derived", 0.5), ("f16", 0.5), ("f16", 0.512)])
+def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, monkeypatch):
     if cm._lib.b200_device_count() < 2:
         pytest.skip("needs two GPUs")
     # "f16": the operand form of the big model (aux matrices in scaled half precision, W's exponent
-    # kept on each replica by its update kernel), forced here at test size
+    # kept on each replica by its update kernel), forced here at test size; at scale 0.512 the hidden
+    # layer has 256 units, which the data-parallel step cuts into 4 column panels of W (statistics,
+    # side-stream all-reduce and update per panel), as it does at full size
     monkeypatch.setenv("B200_RBM_STATE_AUX", "1" if form == "f16" else "0")
     monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path)], env=env)
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path), str(scale)], env=env)
              for r in range(2)]
     try:
         codes = [p.wait(timeout=300) for p in procs]
@@ -41,7 +43,7 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, monkeypatch):
 
     from deepnet_b200 import configs
     from deepnet_b200.fused_rbm import FusedRBM
-    cfg = configs.build(0, cases=400, dims_scale=0.5)
+    cfg = configs.build(0, cases=400, dims_scale=scale)
     gb = cfg["batchsize"]
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, gb, cfg["edges"][0]["weight"], cfg["hyperparams"],

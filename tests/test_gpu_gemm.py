@@ -508,3 +508,67 @@ def test_split_k_epilogue_equals_the_unsplit_one(cm, oracle, splits, form):
         np.testing.assert_array_equal(lo, bf16_round(got - tf32_trunc(got)))
         np.testing.assert_array_equal(smp_aux.planes()[1], want_s)
     assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("form", ["f16", "tf32", "bf16 aux"])
+def test_row_windows_give_the_panels_of_the_full_product(cm, path, form):
+    """A term may read a window of the stored rows of a (a panel of the output's rows) or of a
+    transposed b (a panel of its columns): how the data-parallel step cuts its statistics product
+    v h' into column panels of W without copying h.  Every panel equals the full product's."""
+    rng = np.random.default_rng(50)
+    M, N, K = 384, 512, 640
+    A = rng.random((M, K)).astype(np.float32)                  # stored M x K: op(a) = a
+    Bt = rng.random((N, K)).astype(np.float32)                 # stored N x K, used transposed: op(b) = b'
+    cm.set_gemm_path(path)
+    a, bt = cm.CUDAMatrix(A), cm.CUDAMatrix(Bt)
+    if form == "f16":
+        xa, xb = a.split_f16(cm.empty_aux(A.shape), exp_const=14), bt.split_f16(cm.empty_aux(Bt.shape), exp_const=14)
+        passes = lambda **w: cm.f16_passes(a, xa, bt.T, xb, **w)
+        kw = dict(scale_exp_const=28)
+    elif form == "bf16 aux":
+        xa, xb = a.split_bf16(cm.empty_aux(A.shape)), bt.split_bf16(cm.empty_aux(Bt.shape))
+        passes = lambda **w: cm.split_passes(a, bt.T, a_aux=xa, b_aux=xb, **w)
+        kw = {}
+    else:
+        passes = lambda **w: cm.split_passes(a, bt.T, terms="tf32", **w)
+        kw = {}
+    full = cm.empty((M, N))
+    cm.fused_gemm(passes(), out=full, **kw)
+    want = get(full)
+    assert relerr(want, A.astype(np.float64) @ Bt.astype(np.float64).T) < TOL
+    cols = cm.empty((M, N))
+    for n0 in range(0, N, 128):                                # column panels: windows of b's stored rows
+        cm.fused_gemm(passes(b_rows=(n0, 128)), out=cols.slice(n0, n0 + 128), **kw)
+    np.testing.assert_array_equal(get(cols), want)
+    for m0, rows in ((0, 128), (128, 256)):                    # row panels: windows of a's stored rows
+        part = cm.empty((rows, N))
+        cm.fused_gemm(passes(a_rows=(m0, rows)), out=part, **kw)
+        np.testing.assert_array_equal(get(part), want[m0:m0 + rows])
+    with pytest.raises(cm.CUDAMatException):                   # a window must start on a multiple of 8 rows
+        cm.fused_gemm(passes(b_rows=(4, 128)), out=cols.slice(0, 128), **kw)
+    assert cm.read_status() == 0
+
+
+@pytest.mark.parametrize("mode", ["plain", "bf16", "f16"])
+def test_momentum_update_by_column_panels_equals_the_whole_update(cm, mode):
+    rng = np.random.default_rng(51)
+    shape = (256, 96)
+    w0 = (rng.standard_normal(shape) * 0.01).astype(np.float32)
+    d0 = (rng.standard_normal(shape) * 0.001).astype(np.float32)
+    s0 = rng.standard_normal(shape).astype(np.float32)
+    out = []
+    for panels in (1, 3):
+        w, d, s = cm.CUDAMatrix(w0), cm.CUDAMatrix(d0), cm.CUDAMatrix(s0)
+        aux = cm.empty_aux(shape) if mode != "plain" else None
+        scale = cm.f16_scale_state(np.abs(w0).max()) if mode == "f16" else None
+        if mode == "f16":
+            w.split_f16(aux, exp_dev=scale.slice(0, 1))
+        X = cm.Immediate()
+        step = shape[1] // panels
+        for p in range(panels):
+            X.momentum_update_columns(w, d, None, s, p * step, step, 1.0 / 10, 0.5, 0.1, l2=2e-4, w_aux=aux, w_scale=scale)
+        out.append((get(w), get(d), get(aux) if aux is not None else None, get(scale) if scale is not None else None))
+    for a, b in zip(out[0], out[1]):
+        if a is not None:
+            np.testing.assert_array_equal(a, b)
