@@ -348,7 +348,10 @@ struct TcConfig {
 //   kEpiSigSample  kEpiSig plus sample = Bernoulli(out)
 //   kEpiLin        out = alpha * acc + bias
 //   kEpiGeneric    every option tested at run time
-enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSig = 2, kEpiSigSample = 3, kEpiLin = 4 };
+//   kEpiPartial    kEpiPlain for one split of a split-K product: raw partial sums to the workspace
+//                  (the only variant that carries the work-item bookkeeping of split-K)
+enum { kEpiPlain = 0, kEpiGeneric = 1, kEpiSig = 2, kEpiSigSample = 3, kEpiLin = 4, kEpiPartial = 5 };
+__host__ __device__ constexpr bool epi_is_plain(int e) { return e == kEpiPlain || e == kEpiPartial; }
 
 // Two packed bfloat16 (round to nearest even): `lo` goes to the lower address.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -432,7 +435,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int splits = p.splits;
+  const int splits = (kEpi == kEpiPartial) ? p.splits : 1;
   const int num_tiles = p.tiles_m * p.tiles_n * splits;     // work items: every role walks the same list
   const uint32_t rank = kTwo ? cluster_ctarank() : 0u;        // 0 = leader of the pair
   const int first_tile = kTwo ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
@@ -610,9 +613,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           // it does between two k-blocks is not hidden behind the pipe: all per-product constants
           // live in registers, the k-loop only adds the stage address, and the common term lists
           // (count and which terms are bfloat16 known at compile time) run as straight-line code.
-          auto run_group = [&](auto nm_c, auto mask_c) {
+          auto run_group = [&](auto nm_c, auto mask_c, auto steps_c) {
             constexpr int kNm = decltype(nm_c)::value;       // -1: count and kinds read from the group
             constexpr int kMask = decltype(mask_c)::value;   // bit i: term i is a bfloat16 product
+            constexpr int kSteps16 = decltype(steps_c)::value;   // 16-bit MMAs (K = 16) per term and k-block: bk / 16
             const int nm = kNm >= 0 ? kNm : gr.nmma;
             const int k_iters = kb_last - kb_first;
             uint32_t a_lo[kMaxMma], b_lo[kMaxMma], a_hi[kMaxMma], b_hi[kMaxMma], a_adv[kMaxMma], b_adv[kMaxMma],
@@ -665,9 +669,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
                 if (i < nm) {
                   const uint32_t al = a_lo[i] + sb, bl = b_lo[i] + sb;
                   if (f16[i]) {
-                    // bfloat16: K = 16 per instruction, two instructions per k-block of 32
+                    // 16-bit operands: K = 16 per instruction, bk / 16 instructions per k-block
 #pragma unroll
-                    for (int j = 0; j < 2; j++) {
+                    for (int j = 0; j < kSteps16; j++) {
                       const uint64_t a_desc = ((uint64_t)a_hi[i] << 32) | (uint64_t)(al + j * a_adv[i]);
                       const uint64_t b_desc = ((uint64_t)b_hi[i] << 32) | (uint64_t)(bl + j * b_adv[i]);
                       const uint32_t accumulate = (i == 0 && j == 0) ? (fresh ^ 1u) : 1u;
@@ -716,14 +720,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           for (int i = 0; i < gr.nmma; i++) mask |= (gr.mma[i].f16 != 0 ? 1 : 0) << i;
           using std::integral_constant;
           const int shape = gr.nmma * 16 + mask;
-          if (shape == 3 * 16 + 7) run_group(integral_constant<int, 3>{}, integral_constant<int, 7>{});        // three half-precision terms
-          else if (shape == 2 * 16 + 3) run_group(integral_constant<int, 2>{}, integral_constant<int, 3>{});   // two
-          else if (shape == 3 * 16 + 3) run_group(integral_constant<int, 3>{}, integral_constant<int, 3>{});   // lo16.b16, b16.lo16, x.x
-          else if (shape == 2 * 16 + 1) run_group(integral_constant<int, 2>{}, integral_constant<int, 1>{});   // lo16.b16, x.x
-          else if (shape == 3 * 16) run_group(integral_constant<int, 3>{}, integral_constant<int, 0>{});       // three TF32 terms
-          else if (shape == 2 * 16) run_group(integral_constant<int, 2>{}, integral_constant<int, 0>{});
-          else if (shape == 1 * 16) run_group(integral_constant<int, 1>{}, integral_constant<int, 0>{});
-          else run_group(integral_constant<int, -1>{}, integral_constant<int, 0>{});
+          using S2 = integral_constant<int, 2>;
+          using S4 = integral_constant<int, 4>;
+          if (bk == 64) {   // every term on 16-bit planes
+            if (shape == 3 * 16 + 7) run_group(integral_constant<int, 3>{}, integral_constant<int, 7>{}, S4{});
+            else if (shape == 2 * 16 + 3) run_group(integral_constant<int, 2>{}, integral_constant<int, 3>{}, S4{});
+            else if (shape == 1 * 16 + 1) run_group(integral_constant<int, 1>{}, integral_constant<int, 1>{}, S4{});
+            else run_group(integral_constant<int, -1>{}, integral_constant<int, 0>{}, S4{});
+          }
+          else if (shape == 3 * 16 + 7) run_group(integral_constant<int, 3>{}, integral_constant<int, 7>{}, S2{});        // three half-precision terms
+          else if (shape == 2 * 16 + 3) run_group(integral_constant<int, 2>{}, integral_constant<int, 3>{}, S2{});   // two
+          else if (shape == 3 * 16 + 3) run_group(integral_constant<int, 3>{}, integral_constant<int, 3>{}, S2{});   // lo16.b16, b16.lo16, x.x
+          else if (shape == 2 * 16 + 1) run_group(integral_constant<int, 2>{}, integral_constant<int, 1>{}, S2{});   // lo16.b16, x.x
+          else if (shape == 3 * 16) run_group(integral_constant<int, 3>{}, integral_constant<int, 0>{}, S2{});       // three TF32 terms
+          else if (shape == 2 * 16) run_group(integral_constant<int, 2>{}, integral_constant<int, 0>{}, S2{});
+          else if (shape == 1 * 16) run_group(integral_constant<int, 1>{}, integral_constant<int, 0>{}, S2{});
+          else run_group(integral_constant<int, -1>{}, integral_constant<int, 0>{}, S2{});
         }
       }
 #ifdef B200_GEMM_TIMING
@@ -894,7 +906,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       const int m = tm * TILE_M + (int)rank * BM + wq * 32 + lane;
       const int nc = tn * BN + col_base;
       if (m < pM && nc < pN) {
-        if (kEpi == kEpiPlain) {
+        if (epi_is_plain(kEpi)) {
           float* const out = e.out + (long)sp * p.split_stride + (long)nc * e.ldo + m;
           const float alpha = e.alpha, beta = e.beta;
           const long ldo = e.ldo;
@@ -910,7 +922,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
         }
       }
-      if (kEpi != kEpiPlain) {
+      if (!epi_is_plain(kEpi)) {
         // Activation epilogues leave through shared memory and TMA stores.  Per-thread global
         // stores (three arrays, 128 columns, 32 KB apart) cost 55 us per tile here against 7 us
         // for the arithmetic; a batch of four columns (one Philox block) is staged as
@@ -1135,7 +1147,7 @@ TcTile tile_view(bool mn, bool bf16, int bk, uint32_t smem_off) {
     t.desc_lo = ((uint32_t)(bk * 128) >> 4) << 16;   // distance between column blocks = bk rows x 128 B
     t.adv = (bf16 ? 2048u : 1024u) >> 4;             // one MMA reads 16 (bfloat16) or 8 (fp32) rows of 128 B
   } else {
-    t.desc_hi = bf16 ? kDescHiK16 : kDescHiK32;
+    t.desc_hi = (bf16 && bk == 32) ? kDescHiK16 : kDescHiK32;   // 64 16-bit elements of K are a 128-byte row too
     t.desc_lo = 1u << 16;                            // leading byte offset is unused for swizzled K-major tiles
     t.adv = 32u >> 4;                                // one MMA reads 32 bytes of K inside the swizzled row
   }
@@ -1205,7 +1217,8 @@ int launch_tc(TcParams& p) {
     kernel<<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
     return check_launch();
   }
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  if (pairs > sm_count() / 2) pairs = sm_count() / 2;   // an SM limit in force (b200_set_sm_limit) leaves the rest free
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreadsTc);
@@ -1312,9 +1325,21 @@ int gemm_tc(const GemmProblem& g) {
   // pairs of CTAs (cta_group::2) on 256-row tiles when the product has at least two row tiles
   const bool two = pair_mode != 0 && BN == 256 && g.M > BM;
   const int BN_LOCAL = two ? BN / 2 : BN;      // rows of B staged per CTA
-  // 32 elements of K per k-block (one 128-byte swizzle row of floats); 16 doubles the stage count
-  // but measured slower (64-byte rows, twice the MMA and TMA issues)
-  const int bk = 32;
+  // Elements of K per k-block: 32 (one 128-byte swizzle row of floats; 16 doubles the stage count but
+  // measured slower: 64-byte rows, twice the MMA and TMA issues).  When every term reads 16-bit planes
+  // from aux matrices (no fp32 tile, nothing derived) a k-block is 64 elements: again 128-byte rows,
+  // four MMAs per term and k-block, half the barrier round trips and copies per flop.
+  static int wide16 = -1;
+  if (wide16 < 0) {
+    const char* wv = getenv("B200_GEMM_BK64");
+    wide16 = wv ? atoi(wv) : 1;
+  }
+  bool all16 = wide16 != 0;
+  for (int q = 0; q < g.npass && all16; q++) {
+    const GemmPass& ps = g.pass[q];
+    all16 = part_is_16bit(ps.a.part) && part_is_16bit(ps.b.part) && ps.a.aux && ps.b.aux;
+  }
+  const int bk = all16 ? 64 : 32;
   TcParams p;
   p.M = g.M;
   p.N = g.N;
@@ -1375,7 +1400,7 @@ int gemm_tc(const GemmProblem& g) {
       const bool ok = mn[o] ? make_map(&p.maps[nmaps], ptr, (uint64_t)extent[o], (uint64_t)f.k, ld,
                                        (uint32_t)l.box_rows, (uint32_t)bk, bf16 ? 0 : 1, bf16)
                             : make_map(&p.maps[nmaps], ptr, (uint64_t)f.k, (uint64_t)extent[o], ld, (uint32_t)bk,
-                                       (uint32_t)rows[o], bf16 ? 2 : 0, bf16);
+                                       (uint32_t)rows[o], (bf16 && bk == 32) ? 2 : 0, bf16);
       nmaps++;
       return ok;
     };
@@ -1502,14 +1527,14 @@ int gemm_tc(const GemmProblem& g) {
   const GemmEpilogue& e = p.epi;
   int epi = kEpiGeneric;
   if (!e.bias && e.activation == 0 && !e.sample && !e.out_aux && !e.sample_aux && e.out) {
-    epi = kEpiPlain;
+    epi = p.splits > 1 ? kEpiPartial : kEpiPlain;
   } else if (e.bias && !e.col_scale && e.beta == 0.0f && (e.out || e.sample || e.out_aux || e.sample_aux)) {
     if (e.activation == 1 && (e.sample || e.sample_aux)) epi = kEpiSigSample;
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;
   }
   for (int i = 0; i < kOutArrays; i++) p.out_map[i] = -1;
-  if (epi != kEpiPlain) {
+  if (!epi_is_plain(epi)) {
     // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns: M x N floats
     // with columns ldo apart, or one bfloat16 plane of an aux matrix (columns 2 ld_aux bfloat16
     // apart, plane 1 starting ld_aux bfloat16 into the column)
@@ -1528,6 +1553,7 @@ int gemm_tc(const GemmProblem& g) {
 #define B200_TC_CASE(BNV, TWO)                                        \
   switch (epi) {                                                      \
     case kEpiPlain: return launch_tc<BNV, kEpiPlain, TWO>(p);         \
+    case kEpiPartial: return launch_tc<BNV, kEpiPartial, TWO>(p);     \
     case kEpiSig: return launch_tc<BNV, kEpiSig, TWO>(p);             \
     case kEpiSigSample: return launch_tc<BNV, kEpiSigSample, TWO>(p); \
     case kEpiLin: return launch_tc<BNV, kEpiLin, TWO>(p);             \

@@ -120,9 +120,13 @@ class FusedRBM(object):
         # B200_RBM_PROGRAM=0 issues every operation through its own call instead
         self.use_program = os.environ.get("B200_RBM_PROGRAM", "1") != "0"
         self._programs = {}
-        # data parallel, big model: statistics, all-reduce and update run in this many column panels of W
-        # with the all-reduce beside the next panel's product, which leaves it these SMs
-        self.dp_panels = int(os.environ.get("B200_DP_PANELS", "4"))
+        # data parallel, big model: the all-reduce and the update (and with B200_DP_PANEL_PRODUCTS the
+        # statistics product, which then leaves the all-reduce some SMs) can run in column panels of W,
+        # the all-reduce on a side stream.  Measured on two B200s neither form changed the time of an
+        # update (the panel products run 40 % slower than the one product; the update is too short
+        # to matter), so one all-reduce between product and update stays the default.
+        self.dp_panels = int(os.environ.get("B200_DP_PANELS", "1"))
+        self.dp_panel_products = os.environ.get("B200_DP_PANEL_PRODUCTS", "0") != "0"
         self.dp_reserved_sms = int(os.environ.get("B200_DP_RESERVED_SMS", "12"))
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
         self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
@@ -295,7 +299,7 @@ class FusedRBM(object):
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
                      sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
-        panels = self.dp_panels if (self.world_size > 1 and H % (8 * self.dp_panels) == 0) else 1
+        panels = self.dp_panels if (self.world_size > 1 and 1 < self.dp_panels < 8 and H % (8 * self.dp_panels) == 0) else 1
         if panels == 1:
             pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
             neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
@@ -309,16 +313,24 @@ class FusedRBM(object):
         # product kernel leaves it a few SMs), and each panel is updated as its sum arrives, so
         # the exchange hides behind the product instead of standing between product and update.
         Hc = H // panels
-        self._op(X, "sm_limit", 0, 0, "sm_limit", max(cm.sm_count() - self.dp_reserved_sms, 2))
-        for p in range(panels):
-            win = (p * Hc, Hc)
-            pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True, b_rows=win)
-            neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1, b_rows=win)
-            panel = self.suff_W.slice(p * Hc, (p + 1) * Hc)
-            self._op(X, "gemm_stats", 2 * gf / panels, wb / panels, "fused_gemm", pos + neg, out=panel,
-                     scale_exp_const=2 * E)
-            self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", panel, p)
-        self._op(X, "sm_limit", 0, 0, "sm_limit", 0)
+        if self.dp_panel_products:
+            self._op(X, "sm_limit", 0, 0, "sm_limit", max(cm.sm_count() - self.dp_reserved_sms, 2))
+            for p in range(panels):
+                win = (p * Hc, Hc)
+                pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True, b_rows=win)
+                neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1, b_rows=win)
+                panel = self.suff_W.slice(p * Hc, (p + 1) * Hc)
+                self._op(X, "gemm_stats", 2 * gf / panels, wb / panels, "fused_gemm", pos + neg, out=panel,
+                         scale_exp_const=2 * E)
+                self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", panel, p)
+            self._op(X, "sm_limit", 0, 0, "sm_limit", 0)
+        else:
+            # one product on every SM, then the all-reduce in panels beside the panels' updates
+            pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
+            neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
+            self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W, scale_exp_const=2 * E)
+            for p in range(panels):
+                self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_W.slice(p * Hc, (p + 1) * Hc), p)
         self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
         self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
         self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_b, panels)

@@ -25,6 +25,8 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, monkeypatch):
     monkeypatch.setenv("B200_RBM_STATE_AUX", "1" if form == "f16" else "0")
     monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    if scale == 0.512:
+        env.update(B200_DP_PANELS="4", B200_DP_PANEL_PRODUCTS="1")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path), str(scale)], env=env)
              for r in range(2)]
     try:
