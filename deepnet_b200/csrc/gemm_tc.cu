@@ -106,6 +106,10 @@ struct TcParams {
   long split_stride;       // floats between two partials
   int direct;              // 1: no group derives anything: the copies of both CTAs complete on the leader's `ready`
                            //    barrier and the converter warps stay out of the way
+  int store16;             // 1: the epilogue's only outputs are 16-bit planes (the draw's, or the result's two): every
+                           //    thread stores them straight to global memory (64 bytes per warp and column); no
+                           //    staging, barriers or TMA stores, whose latency otherwise keeps the epilogue warps
+                           //    from draining the next tile's first chunk in time
   GemmEpilogue epi;
   int out_map[kOutArrays];   // tensor maps (indices into maps) of the outputs stored by TMA; -1 = absent
   int* status;
@@ -969,6 +973,32 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           }
           uint4 w = make_uint4(0, 0, 0, 0);
           if (draw) w = philox4x32_10((uint32_t)m, cblk0 + g4, key);
+          if (p.store16) {
+            uint16_t* const ob = reinterpret_cast<uint16_t*>(e.out_aux);
+            uint16_t* const sb = reinterpret_cast<uint16_t*>(e.sample_aux);
+            const long lda2 = 2L * e.ld_aux;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (!row_ok || c0 + j >= pN) continue;
+              const long word = (long)(c0 + j) * lda2 + m;
+              if (has_aux) {
+                uint16_t lo16, b16;
+                if (e.aux_f16) {
+                  split_f16(x[j], aux_scale, lo16, b16);
+                } else {
+                  lo16 = (uint16_t)pack_bf16(tf32_rest(x[j]), 0.0f);
+                  b16 = (uint16_t)pack_bf16(x[j], 0.0f);
+                }
+                ob[word] = lo16;
+                ob[word + e.ld_aux] = b16;
+              }
+              if (has_smp_aux) {
+                const bool on = word_to_uniform(pick_word(w, j)) < x[j];
+                sb[word + e.ld_aux] = (uint16_t)(on ? aux_one : 0);
+              }
+            }
+            continue;
+          }
           // buffer (g4 & 1) is free once the stores of batch g4 - 2 have read it (the leader waited)
           named_bar_sync(1 + hf, 128);
           const uint32_t buf = group_base + (uint32_t)(g4 & 1) * kBufBytes;
@@ -1010,7 +1040,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
             tma_store_wait_read<1>();               // the other buffer's stores have read it
           }
         }
-        if (leader) tma_store_wait_all();           // results are in memory before the kernel can end
+        if (leader && !p.store16) tma_store_wait_all();   // results are in memory before the kernel can end
       }
 #ifdef B200_GEMM_TIMING
       t_epi += clock64() - t_e0;
@@ -1533,6 +1563,12 @@ int gemm_tc(const GemmProblem& g) {
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;
   }
+  static int store16_mode = -1;
+  if (store16_mode < 0) {
+    const char* sv = getenv("B200_EPI_STORE16");
+    store16_mode = sv ? atoi(sv) : 1;
+  }
+  p.store16 = store16_mode != 0 && !epi_is_plain(epi) && !e.out && !e.sample && (e.out_aux || e.sample_aux);
   for (int i = 0; i < kOutArrays; i++) p.out_map[i] = -1;
   if (!epi_is_plain(epi)) {
     // outputs of the activation epilogues, stored as boxes of 128 rows x 4 columns: M x N floats
