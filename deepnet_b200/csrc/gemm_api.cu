@@ -32,8 +32,13 @@ inline bool aux_shape_ok(const cudamat* aux, const cudamat* m) {
 
 int run(const GemmProblem& g) {
   if (g_path == 2) return gemm_simt(g);
-  if (gemm_tc_supported(g)) return gemm_tc(g);
-  if (g_path == 1) return ERROR_UNSUPPORTED;
+  if (gemm_tc_supported(g)) {
+    const int r = gemm_tc(g);
+    // (a product with more operand pairs or tiles than one tensor-core launch carries)
+    if (r != ERROR_UNSUPPORTED || g_path == 1) return r;
+  } else if (g_path == 1) {
+    return ERROR_UNSUPPORTED;
+  }
   return gemm_simt(g);
 }
 

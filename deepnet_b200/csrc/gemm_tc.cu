@@ -60,11 +60,13 @@ struct TcTile {
   uint32_t smem_off;       // byte offset of the tile inside a stage
 };
 // One operand tile of a k-block as TMA loads it: fp32, or one bfloat16 plane of an aux matrix.
+// (The parameter block travels with every launch: small types keep it under 4 KB, above which a
+// launch costs about twice as much on the host.)
 struct TcLoad {
-  int map;                 // index into TcParams::maps
-  int mn;                  // 1: M/N is the contiguous direction in memory (loaded as boxes of 128 bytes x bk)
-  int is_a;
-  int box_rows;            // rows of M/N per box of an MN-major tile: 32 floats or 64 bfloat16
+  uint8_t map;             // index into TcParams::maps
+  uint8_t mn;              // 1: M/N is the contiguous direction in memory (loaded as boxes of 128 bytes x bk)
+  uint8_t is_a;
+  uint8_t box_rows;        // rows of M/N per box of an MN-major tile: 32 floats or 64 bfloat16
   uint32_t smem_off;
 };
 // The parts derived from a loaded tile (offsets inside the stage, kNoTile = not wanted).
@@ -75,8 +77,8 @@ struct TcConv {
   int is_a;
 };
 struct TcMma {
-  int a, b;                // tiles of the group
-  int f16;                 // 0: kind::tf32 (K = 8 per instruction), 1: kind::f16 on bfloat16 (K = 16)
+  uint8_t a, b;            // tiles of the group
+  uint8_t f16;             // 0: kind::tf32 (K = 8 per instruction), 1: kind::f16 on bfloat16 (K = 16)
   uint32_t idesc;          // tcgen05 instruction descriptor (carries the negate bit)
 };
 // A group = the terms over one pair of fp32 operands (and so one K range).  Each k-block stages
@@ -92,9 +94,12 @@ struct TcGroup {
   TcMma mma[kMaxMma];
 };
 
+constexpr int kMaxGroups = 4;   // pairs of operand matrices in one product (a DBM layer update and the statistics have two)
+constexpr int kMaxMaps = 16;    // tensor maps: operand tiles as loaded, then the outputs an activation epilogue stores
+
 struct TcParams {
-  CUtensorMap maps[2 * kMaxPass + kOutArrays];   // operands (fp32, aux planes; at most two per term), then the outputs an activation epilogue stores
-  TcGroup group[kMaxPass];
+  CUtensorMap maps[kMaxMaps];
+  TcGroup group[kMaxGroups];
   int ngroups;
   int M, N, tiles_m, tiles_n;
   int bk;                  // floats of K per k-block: 32 or 16
@@ -1188,7 +1193,7 @@ inline bool same_operand(const GemmOperand& a, const GemmOperand& b) {
   return a.ptr == b.ptr && a.ld == b.ld && a.trans == b.trans && a.aux == b.aux && a.lda == b.lda && a.row0 == b.row0;
 }
 
-static_assert(sizeof(TcParams) <= 8192, "kernel parameter block");
+static_assert(sizeof(TcParams) <= 4096, "kernel parameter block");
 
 // Host-side failure injection for the bounded waits: the next tensor-core product is told to
 // expect this many more bytes per stage than its copies deliver, so the stage's barrier can
@@ -1384,6 +1389,7 @@ int gemm_tc(const GemmProblem& g) {
 
   // ---- group consecutive terms over the same two fp32 matrices (at most kMaxMma of them)
   int ngroups = 0, nmaps = 0;
+  bool map_overflow = false;   // more operand tiles than the parameter block has tensor maps for
   uint32_t stage_bytes = 0;
   const GemmPass* first_of[kMaxPass];
   for (int q = 0; q < g.npass; q++) {
@@ -1395,6 +1401,7 @@ int gemm_tc(const GemmProblem& g) {
         continue;
       }
     }
+    if (ngroups == kMaxGroups) return ERROR_UNSUPPORTED;   // more operand pairs than one launch carries
     first_of[ngroups] = &ps;
     p.group[ngroups].nmma = 1;
     ngroups++;
@@ -1420,6 +1427,10 @@ int gemm_tc(const GemmProblem& g) {
     int ntiles = 0;
     tg.nload = tg.nconv = 0;
     auto add_load = [&](int o, const void* ptr, uint64_t ld, bool bf16) {
+      if (nmaps >= kMaxMaps - kOutArrays) {
+        map_overflow = true;
+        return false;
+      }
       TcLoad& l = tg.load[tg.nload++];
       l.map = nmaps;
       l.mn = mn[o];
@@ -1440,7 +1451,7 @@ int gemm_tc(const GemmProblem& g) {
       if (!(want[o][kPartX] || want[o][kPartLo32] || (!from_aux && (want[o][kPartLo16] || want[o][kPartB16])))) continue;
       x_off[o] = off;
       if (!add_load(o, src[o]->ptr + src[o]->row0, (uint64_t)src[o]->ld, false))
-        return set_error("cuTensorMapEncodeTiled failed for an operand");
+        return map_overflow ? ERROR_UNSUPPORTED : set_error("cuTensorMapEncodeTiled failed for an operand");
       tile_of[o][kPartX] = ntiles;
       tg.tile[ntiles++] = tile_view(mn[o], false, bk, off);
       off += (uint32_t)rows[o] * bk * 4;
@@ -1452,7 +1463,7 @@ int gemm_tc(const GemmProblem& g) {
         const uint16_t* plane =
             reinterpret_cast<const uint16_t*>(src[o]->aux) + (part_plane(part) ? src[o]->lda : 0) + src[o]->row0;
         if (!add_load(o, plane, (uint64_t)(2 * src[o]->lda), true))
-          return set_error("cuTensorMapEncodeTiled failed for an aux plane");
+          return map_overflow ? ERROR_UNSUPPORTED : set_error("cuTensorMapEncodeTiled failed for an aux plane");
         tile_of[o][part] = ntiles;
         tg.tile[ntiles++] = tile_view(mn[o], true, bk, off);
         off += (uint32_t)rows[o] * bk * 2;
@@ -1528,8 +1539,13 @@ int gemm_tc(const GemmProblem& g) {
     int min_ki = p.group[0].k_iters;
     for (int gi = 1; gi < ngroups; gi++) min_ki = p.group[gi].k_iters < min_ki ? p.group[gi].k_iters : min_ki;
     int want = 1;
+    static int min_ki_to_split = -1;   // a split costs a second (finishing) launch: only long inner dimensions repay it
+    if (min_ki_to_split < 0) {
+      const char* mv = getenv("B200_SPLITK_MIN_KI");
+      min_ki_to_split = mv ? atoi(mv) : 8;
+    }
     if (g_split_mode == 0) {
-      if (ctas * 2 <= sm_count() && min_ki >= 8) {
+      if (ctas * 2 <= sm_count() && min_ki >= min_ki_to_split) {
         want = sm_count() / ctas;
         if (want > min_ki / 4) want = min_ki / 4;
         if (want > 32) want = 32;
