@@ -37,6 +37,7 @@ UNIT = "examples/s"
 # DRAM bytes read + written by one launch of the dominant kernel (the up half-step product of
 # configuration 4) in the ncu capture of this build; other workloads were not captured.
 UP_PRODUCT_DRAM_BYTES_C4 = 1.31e9
+RAMP_SECONDS = 0.6     # load applied before the warm-up updates so that the GPU is at its steady clocks
 
 
 def measured_peaks():
@@ -61,6 +62,8 @@ class ClockSampler(object):
         self.proc = None
 
     def start(self):
+        if os.environ.get("B200_BENCH_SAMPLER") == "none":
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
@@ -98,6 +101,11 @@ class ClockSampler(object):
                         reasons.add(n)
         med = float(np.median(clocks)) if clocks else None
         return dict(sm_mhz=med, sm_max_mhz=smax, reasons=sorted(reasons), samples=len(clocks))
+
+
+def ramp_updates(config):
+    """Updates that make up about RAMP_SECONDS of load at each configuration's speed."""
+    return 30 if config == 4 else 1000
 
 
 def make_engine(cm, cfg, world, rank):
@@ -156,10 +164,12 @@ def small_config_line(cm, config, steps, warmup):
     cm.set_rng_column_offset(0)
     eng = make_engine(cm, cfg, 1, 0)
     batches = [cm.CUDAMatrix(cfg["data"][:, i * B:(i + 1) * B]) for i in range(pool)]
-    for s in range(warmup):
+    ramp = ramp_updates(config)
+    for s in range(ramp + warmup):
         eng.TrainOneBatch(s, batches[s % pool])
-    ms, launches = time_updates(cm, eng, batches, warmup, steps, Group(cm, 1, 0))
-    loss = eng.read_loss() / ((steps + warmup) * B)
+    eng.read_loss()
+    ms, launches = time_updates(cm, eng, batches, ramp + warmup, steps, Group(cm, 1, 0))
+    loss = eng.read_loss() / (steps * B)
     per = ms / steps
     return dict(workload=cfg["name"], value=round(B / (per * 1e-3), 1), unit=UNIT, ms_per_step=round(per, 4),
                 steps=steps, algorithmic_tflops=round(configs.flops_per_example(config) * B / (per * 1e-3) / 1e12, 3),
@@ -222,15 +232,24 @@ def run_ours(args):
 
     # ---- device-resident inputs: the headline ------------------------------------------
     dev_batches = [cm.CUDAMatrix(cfg["data"][:, i * B:(i + 1) * B]) for i in range(pool)]
-    for s in range(args.warmup):
-        eng.TrainOneBatch(s, dev_batches[s % pool])
-    eng.read_loss()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.3)                  # the sampler is running before the GPU is (an idle GPU has to ramp up again)
+    # A GPU that comes out of idle needs about half a second of load before its clocks and power
+    # management settle: the first 10-20 updates of configuration 4 run 5-7 % slower than the
+    # steady state (21.0 against 19.7 ms measured with 3 and with 25 updates before the timed ones).
+    # So the engine first runs about RAMP_SECONDS of updates, then the W warm-up updates, then the timed ones.
+    ramp = ramp_updates(config)          # the same count on every rank (each update is a collective when N > 1)
+    for r in range(ramp):
+        eng.TrainOneBatch(r, dev_batches[r % pool])
+        if r % 8 == 7:
+            cm.cuda_sync_threads()
+    for s in range(args.warmup):         # warm-up directly before the timed region
+        eng.TrainOneBatch(ramp + s, dev_batches[s % pool])
+    eng.read_loss()
     t_wall0 = time.time()
-    ms, launches = time_updates(cm, eng, dev_batches, args.warmup, args.steps, group)
+    ms, launches = time_updates(cm, eng, dev_batches, ramp + args.warmup, args.steps, group)
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     loss = eng.read_loss() / (args.steps * B)
@@ -242,7 +261,7 @@ def run_ours(args):
     g0, g1 = cm.Event(), cm.Event()
     g0.record()
     for s in range(args.steps):
-        eng.TrainOneBatch(args.warmup + args.steps + s, dev_batches[s % pool])
+        eng.TrainOneBatch(ramp + args.warmup + args.steps + s, dev_batches[s % pool])
     g1.record()
     inst_ms = g0.elapsed_ms(g1)
     timeline, eng.timeline = eng.timeline, None
@@ -320,7 +339,7 @@ def run_ours(args):
         if s + 1 < e2e_steps:                               # next batch travels during this step
             cm.prefetch_fence()
             stage[(s + 1) & 1].prefetch_from_pinned(host[(s + 1) & 1][1], nbytes)
-        eng.TrainOneBatch(args.warmup + 2 * args.steps + s, stage[s & 1])
+        eng.TrainOneBatch(ramp + args.warmup + 2 * args.steps + s, stage[s & 1])
         eng.read_loss()                                     # device -> host, every step
     f1.record()
     e2e_ms = group.max(f0.elapsed_ms(f1))
@@ -342,7 +361,7 @@ def run_ours(args):
                    warmup=args.warmup, ms_per_step=round(ms / args.steps, 4), higher_is_better=True, scaling="weak",
                    vs_baseline=None, dtype="f32", data="synthetic",
                    config=dict(workload=cfg["name"], visible=V, hidden=H, batch_per_gpu=B, global_batch=B * world,
-                               gibbs_steps=k, parallelism="dp%d" % world,
+                               gibbs_steps=k, parallelism="dp%d" % world, ramp_up_updates=ramp,
                                cache="working set (weights 268 MB x3, states) exceeds the 126 MB L2; no flush needed"
                                if config == 4 else "small working set: L2-resident, as in training"),
                    clocks=clocks, gpu_launches=launches,
