@@ -127,6 +127,8 @@ class FusedRBM(object):
         # to matter), so one all-reduce between product and update stays the default.
         self.dp_panels = int(os.environ.get("B200_DP_PANELS", "1"))
         self.dp_panel_products = os.environ.get("B200_DP_PANEL_PRODUCTS", "0") != "0"
+        cols = os.environ.get("B200_DP_PANEL_COLS", "")          # e.g. "5888,2304": unequal panels
+        self.dp_panel_cols = [int(c) for c in cols.split(",")] if cols else None
         self.dp_reserved_sms = int(os.environ.get("B200_DP_RESERVED_SMS", "12"))
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
         self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
@@ -299,7 +301,16 @@ class FusedRBM(object):
                      out=self.h_neg if last else None, out_aux=self.h_neg_aux if last else None,
                      sample=self.h_samp if last else None, sample_aux=self.h_samp_aux, bias=self.bh, activation=1,
                      **act)
-        panels = self.dp_panels if (self.world_size > 1 and 1 < self.dp_panels < 8 and H % (8 * self.dp_panels) == 0) else 1
+        # column panels of W as (first column, columns): equal ones, or the widths asked for
+        bounds = []
+        if self.world_size > 1:
+            widths = self.dp_panel_cols or ([H // self.dp_panels] * self.dp_panels if self.dp_panels > 1 else [])
+            if 1 < len(widths) < 8 and sum(widths) == H and all(w > 0 and w % 8 == 0 for w in widths):
+                first = 0
+                for w in widths:
+                    bounds.append((first, w))
+                    first += w
+        panels = len(bounds) if bounds else 1
         if panels == 1:
             pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
             neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
@@ -312,15 +323,15 @@ class FusedRBM(object):
         # Panel p's all-reduce runs on a side stream while panel p + 1 multiplies (the persistent
         # product kernel leaves it a few SMs), and each panel is updated as its sum arrives, so
         # the exchange hides behind the product instead of standing between product and update.
-        Hc = H // panels
         if self.dp_panel_products:
-            self._op(X, "sm_limit", 0, 0, "sm_limit", max(cm.sm_count() - self.dp_reserved_sms, 2))
-            for p in range(panels):
-                win = (p * Hc, Hc)
+            for p, (c0, nc) in enumerate(bounds):
+                if p == 1:   # from the second panel on an all-reduce runs beside the product
+                    self._op(X, "sm_limit", 0, 0, "sm_limit", max(cm.sm_count() - self.dp_reserved_sms, 2))
+                win = (c0, nc)
                 pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True, b_rows=win)
                 neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1, b_rows=win)
-                panel = self.suff_W.slice(p * Hc, (p + 1) * Hc)
-                self._op(X, "gemm_stats", 2 * gf / panels, wb / panels, "fused_gemm", pos + neg, out=panel,
+                panel = self.suff_W.slice(c0, c0 + nc)
+                self._op(X, "gemm_stats", 2 * gf * nc / H, wb * nc / H, "fused_gemm", pos + neg, out=panel,
                          scale_exp_const=2 * E)
                 self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", panel, p)
             self._op(X, "sm_limit", 0, 0, "sm_limit", 0)
@@ -329,16 +340,16 @@ class FusedRBM(object):
             pos = F(v0, v0a, self.h_pos.T, self.h_pos_aux, exact_a=True)
             neg = F(self.v_neg, self.v_neg_aux, self.h_neg.T, self.h_neg_aux, negate=1)
             self._op(X, "gemm_stats", 2 * gf, wb, "fused_gemm", pos + neg, out=self.suff_W, scale_exp_const=2 * E)
-            for p in range(panels):
-                self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_W.slice(p * Hc, (p + 1) * Hc), p)
+            for p, (c0, nc) in enumerate(bounds):
+                self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_W.slice(c0, c0 + nc), p)
         self._op(X, "row_sum", 0, 2 * vb, "row_sum_diff", v0, self.v_neg, self.suff_bv)
         self._op(X, "row_sum", 0, 2 * hb, "row_sum_diff", self.h_pos, self.h_neg, self.suff_bh)
         self._op(X, "allreduce_begin", 0, 0, "allreduce_begin", self.suff_b, panels)
         uw = []
-        for p in range(panels):
+        for p, (c0, nc) in enumerate(bounds):
             self._op(X, "allreduce_end", 0, 0, "allreduce_end", p)
-            uw.append(self._op(X, "update_W", 0, 6 * wb / panels, "momentum_update_columns", self.W, self.dW, None,
-                               self.suff_W, p * Hc, Hc, sc["inv_b"], sc["emom"], sc["eeps"], l2=sc["l2"], l1=sc["l1"],
+            uw.append(self._op(X, "update_W", 0, 6 * wb * nc / H, "momentum_update_columns", self.W, self.dW, None,
+                               self.suff_W, c0, nc, sc["inv_b"], sc["emom"], sc["eeps"], l2=sc["l2"], l1=sc["l1"],
                                w_aux=self.W_aux, w_scale=self.W_scale))
         self._op(X, "allreduce_end", 0, 0, "allreduce_end", panels)
         ub = self._op(X, "update_bias", 0, 20.0 * (V + H), "momentum_update", self.b, self.db, None, self.suff_b,
