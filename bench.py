@@ -108,7 +108,7 @@ def ramp_updates(config):
     return 30 if config == 4 else 1000
 
 
-def make_engine(cm, cfg, world, rank):
+def make_engine(cm, cfg, world, rank, group=None):
     from deepnet_b200.fused_rbm import FusedRBM
     if len(cfg["layers"]) > 2:
         from deepnet_b200.fused_dbm import FusedDBM
@@ -121,7 +121,7 @@ def make_engine(cm, cfg, world, rank):
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     return FusedRBM(cm, V, H, cfg["batchsize"], cfg["edges"][0]["weight"], cfg["hyperparams"],
                     edge_hyperparams=cfg["edges"][0].get("hyperparams"), visible=cfg["layers"][0]["activation"],
-                    binary_data=cfg["binary"], seed=cfg["seed"], world_size=world, rank=rank)
+                    binary_data=cfg["binary"], seed=cfg["seed"], world_size=world, rank=rank, group=group)
 
 
 def workload(config, cases, data_seed=None):
@@ -228,7 +228,7 @@ def run_ours(args):
     if config in (2, 3):
         pool = 2
         cfg["data"] = cfg["data"][:, :pool * B]
-    eng = make_engine(cm, cfg, world, rank)
+    eng = make_engine(cm, cfg, world, rank, group)
 
     # ---- device-resident inputs: the headline ------------------------------------------
     dev_batches = [cm.CUDAMatrix(cfg["data"][:, i * B:(i + 1) * B]) for i in range(pool)]
@@ -362,6 +362,8 @@ def run_ours(args):
                    vs_baseline=None, dtype="f32", data="synthetic",
                    config=dict(workload=cfg["name"], visible=V, hidden=H, batch_per_gpu=B, global_batch=B * world,
                                gibbs_steps=k, parallelism="dp%d" % world, ramp_up_updates=ramp,
+                               exchange=("none" if world == 1 else ("peer-memory reduce + update kernel" if getattr(eng, "dp_peer", False)
+                                                                    else "NCCL all-reduce")),
                                cache="working set (weights 268 MB x3, states) exceeds the 126 MB L2; no flush needed"
                                if config == 4 else "small working set: L2-resident, as in training"),
                    clocks=clocks, gpu_launches=launches,
@@ -371,6 +373,8 @@ def run_ours(args):
         if replicas_identical is not None:
             out["replicas_identical"] = replicas_identical
     group.barrier()
+    if getattr(eng, "dp_peer", False):
+        cm.dp_peer_close()
     group.close()
     if rank == 0 and world == 1 and config == 4 and not args.no_other_configs:
         # the other configurations of the benchmark set, a few updates each (1 GPU)

@@ -805,13 +805,14 @@ def _build_fused_gemm(passes, out=None, sample=None, bias=None, col_scale=None, 
 (OP_FUSED_GEMM, OP_SUM_AXIS, OP_ADD_SUM_AXIS, OP_ROW_SUM_DIFF, OP_ADD_SQ_DIFF, OP_MOMENTUM_UPDATE, OP_SPLIT_F16,
  OP_SPLIT_BF16, OP_ALLREDUCE, OP_SOFTMAX_SCALED, OP_SAMPLE_MULTINOMIAL, OP_DIV_BY_ROW, OP_ADD_SCALAR, OP_ASSIGN_SCALAR,
  OP_COPY, OP_SAMPLE_BERNOULLI, OP_SOFTMAX_SAMPLE, OP_MOMENTUM_UPDATE_COLUMNS, OP_ALLREDUCE_BEGIN, OP_ALLREDUCE_END,
- OP_SM_LIMIT) = range(21)
+ OP_SM_LIMIT, OP_DP_PEER_UPDATE) = range(22)
 
 
 class _Op(ct.Structure):
     _fields_ = [("kind", ct.c_int), ("i0", ct.c_int), ("i1", ct.c_int), ("i2", ct.c_int),
                 ("f0", ct.c_float), ("f1", ct.c_float), ("f2", ct.c_float), ("f3", ct.c_float), ("f4", ct.c_float),
-                ("m", ct.POINTER(cudamat) * 6), ("gemm", ct.POINTER(_FusedGemm))]
+                ("f5", ct.c_float), ("f6", ct.c_float), ("f7", ct.c_float),
+                ("m", ct.POINTER(cudamat) * 8), ("gemm", ct.POINTER(_FusedGemm))]
 
 
 _lib.b200_run_program.argtypes = [ct.POINTER(rnd_struct), ct.POINTER(_Op), ct.c_int, ct.POINTER(ct.c_int)]
@@ -865,6 +866,12 @@ class Immediate(object):
     def sm_limit(self, sms):
         _check(_lib.b200_set_sm_limit(ct.c_int(sms)))
 
+    def dp_peer_update(self, w, delta, w_aux, w_scale, pack, b, db, inv_batch, mom_b, eps_b, mom_w, eps_w, l2=0.0, l1=0.0):
+        p = lambda m: m.p_mat if m is not None else None
+        _check(_lib.dp_peer_update(w.p_mat, delta.p_mat, p(w_aux), p(w_scale), pack.p_mat, b.p_mat, db.p_mat,
+                                   ct.c_float(inv_batch), ct.c_float(mom_b), ct.c_float(eps_b), ct.c_float(mom_w),
+                                   ct.c_float(eps_w), ct.c_float(l2), ct.c_float(l1)))
+
     def softmax_scaled(self, mat, scale, target):
         mat.softmax_scaled(scale, target)
 
@@ -907,7 +914,7 @@ class Program(object):
                 self._keep.append(m)
         for name, v in zip(("i0", "i1", "i2"), ints):
             setattr(op, name, int(v))
-        for name, v in zip(("f0", "f1", "f2", "f3", "f4"), floats):
+        for name, v in zip(("f0", "f1", "f2", "f3", "f4", "f5", "f6", "f7"), floats):
             setattr(op, name, float(v))
         if gemm is not None:
             op.gemm = ct.pointer(gemm)
@@ -950,6 +957,10 @@ class Program(object):
 
     def sm_limit(self, sms):
         return self._add(OP_SM_LIMIT, (), (sms,))
+
+    def dp_peer_update(self, w, delta, w_aux, w_scale, pack, b, db, inv_batch, mom_b, eps_b, mom_w, eps_w, l2=0.0, l1=0.0):
+        return self._add(OP_DP_PEER_UPDATE, (w, delta, w_aux, w_scale, pack, b, db), (),
+                         (inv_batch, mom_b, eps_b, mom_w, eps_w, l2, l1))
 
     def split_f16(self, x, aux, exp_dev=None, exp_const=0):
         return self._add(OP_SPLIT_F16, (x, aux, exp_dev), (exp_const,))
@@ -1181,6 +1192,28 @@ def dp_check():
 
 def dp_destroy():
     _lib.dp_destroy()
+
+
+def dp_peer_setup(group, pack, w, w_aux):
+    """Maps every rank's statistics, parameter, its 16-bit planes and flag array into this process
+    (CUDA IPC) for `dp_peer_update`.  group: a `rendezvous.Group` (the handles travel through it)."""
+    n = _lib.dp_peer_handle_bytes()
+    mine = b""
+    for m in (pack, w, w_aux):
+        buf = ct.create_string_buffer(n)
+        if m is not None:
+            _check(_lib.dp_peer_export(m.p_mat, buf))
+        mine += buf.raw
+    buf = ct.create_string_buffer(n)
+    _check(_lib.dp_peer_export_flags(buf))
+    mine += buf.raw
+    everyone = b"".join(group.exchange("peer_handles", mine))
+    _check(_lib.dp_peer_setup(ct.c_int(group.world), ct.c_int(group.rank), ct.c_char_p(everyone), pack.p_mat, w.p_mat,
+                              w_aux.p_mat if w_aux is not None else None))
+
+
+def dp_peer_close():
+    _lib.dp_peer_close()
 
 
 def dp_wait(timeout_ms=30000):

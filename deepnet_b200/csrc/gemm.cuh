@@ -80,6 +80,10 @@ struct GemmProblem {
   GemmEpilogue epi;
 };
 
+// aux = x * 2^(*exp_dev) as two fp16 planes, written only when *only_if != 0 (a device flag): the
+// second pass of an update whose exponent had to change.
+int rewrite_f16_planes_if(const float* x, uint16_t* aux, int rows, long n, const float* exp_dev, const float* only_if);
+
 int gemm_simt(const GemmProblem& g);
 // Returns ERROR_UNSUPPORTED when an operand is not addressable by TMA (leading
 // dimension not a multiple of 4 floats or base not 16-byte aligned).

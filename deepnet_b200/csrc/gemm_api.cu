@@ -258,6 +258,18 @@ __global__ void k_update_scale(float* scale) {
 
 }  // namespace
 
+namespace b200 {
+int rewrite_f16_planes_if(const float* x, uint16_t* aux, int rows, long n, const float* exp_dev, const float* only_if) {
+  if (n == 0) return 0;
+  const bool svec = (rows % 4 == 0) && ((((uintptr_t)x) & 15) == 0);
+  long sblocks = ((svec ? n / 4 : n) + 255) / 256;
+  if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
+  if (sblocks < 1) sblocks = 1;
+  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(x, aux, rows, aux_rows(rows), n, svec, exp_dev, 0, only_if);
+  return check_launch();
+}
+}  // namespace b200
+
 // One term of a fused product: op(a) is M x k, op(b) is k x N (handles carry is_trans).
 // a_part / b_part choose what of each fp32 matrix the term multiplies (kPartX, kPartLo32:
 // a TF32 product; kPartLo16, kPartB16: a bfloat16 product); both of one width.  a_aux / b_aux:

@@ -24,6 +24,8 @@ int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* 
 int dp_allreduce_begin(cudamat* mat, int slot);
 int dp_allreduce_end(int slot);
 int b200_set_sm_limit(int sms);
+int dp_peer_update(cudamat* w, cudamat* delta, cudamat* w_aux, cudamat* w_scale, cudamat* pack, cudamat* b, cudamat* db,
+                   float inv_batch, float mom_b, float eps_b, float mom_w, float eps_w, float l2, float l1);
 int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const);
 int split_bf16(cudamat* x, cudamat* aux);
 int dp_allreduce(cudamat* mat);
@@ -59,14 +61,15 @@ enum {
   B200_OP_ALLREDUCE_BEGIN = 18,   // m0, i0 slot
   B200_OP_ALLREDUCE_END = 19,     // i0 slot
   B200_OP_SM_LIMIT = 20,          // i0 SMs the following kernels size their grids for (0 = all)
+  B200_OP_DP_PEER_UPDATE = 21,    // m0 w, m1 delta, m2 w_aux?, m3 w_scale?, m4 pack, m5 b, m6 db; f0 inv_batch, f1 mom_b, f2 eps_b, f3 mom_w, f4 eps_w, f5 l2, f6 l1
   B200_OP_COUNT
 };
 
 struct b200_op {
   int kind;
   int i0, i1, i2;
-  float f0, f1, f2, f3, f4;
-  cudamat* m[6];
+  float f0, f1, f2, f3, f4, f5, f6, f7;
+  cudamat* m[8];
   b200_fused_gemm* gemm;
 };
 
@@ -102,6 +105,9 @@ extern "C" int b200_run_program(rnd_struct* rnd_state, b200_op* ops, int n, int*
       case B200_OP_ALLREDUCE_BEGIN: err = dp_allreduce_begin(o.m[0], o.i0); break;
       case B200_OP_ALLREDUCE_END: err = dp_allreduce_end(o.i0); break;
       case B200_OP_SM_LIMIT: err = b200_set_sm_limit(o.i0); break;
+      case B200_OP_DP_PEER_UPDATE:
+        err = dp_peer_update(o.m[0], o.m[1], o.m[2], o.m[3], o.m[4], o.m[5], o.m[6], o.f0, o.f1, o.f2, o.f3, o.f4, o.f5, o.f6);
+        break;
       default: break;
     }
     if (err) {

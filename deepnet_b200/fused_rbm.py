@@ -36,7 +36,7 @@ from .dbm import LINEAR, LOGISTIC, REPLICATED_SOFTMAX, Parameter
 
 class FusedRBM(object):
     def __init__(self, cm, V, H, batchsize, weight, hyperparams, edge_hyperparams=None, visible=LOGISTIC,
-                 binary_data=False, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0):
+                 binary_data=False, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0, group=None):
         """binary_data: the caller states that every input is exactly 0 or 1 (or, for word counts, a
         small integer): such data have no low part, so the products over them run one term shorter
         and, for a big logistic model, on the scaled half-precision form.  Real-valued inputs
@@ -45,7 +45,12 @@ class FusedRBM(object):
 
         With world_size > 1 the replicated-softmax model draws its multinomial samples from the
         rank's own call numbers: its random stream then depends on the number of ranks (the Bernoulli
-        paths do not: they are indexed by global column only)."""
+        paths do not: they are indexed by global column only).
+
+        group: the `rendezvous.Group` of the ranks.  With it the exchange and the update of a data-parallel
+        step run as one pass over peer memory (`dp_peer_update`: every rank reduces and updates its own
+        columns of W and stores them into every replica) instead of an NCCL all-reduce followed by the
+        update; B200_DP_PEER=0 keeps NCCL."""
         if visible == LINEAR and hyperparams.sample_input:
             # the reference's linear layer has no draw (deepnet/linear_layer.py:24-27 is a no-op without
             # learned precision), so its `sample` buffer would feed stale values upward
@@ -130,6 +135,12 @@ class FusedRBM(object):
         cols = os.environ.get("B200_DP_PANEL_COLS", "")          # e.g. "5888,2304": unequal panels
         self.dp_panel_cols = [int(c) for c in cols.split(",")] if cols else None
         self.dp_reserved_sms = int(os.environ.get("B200_DP_RESERVED_SMS", "12"))
+        self.dp_peer = False
+        if (world_size > 1 and group is not None and visible != REPLICATED_SOFTMAX and H % world_size == 0 and V % 4 == 0
+                and os.environ.get("B200_DP_PEER", "1") != "0"):
+            cm.dp_peer_setup(group, self.pack, self.W, self.W_aux)
+            self.dp_peer = True
+            self._peer_group = group       # the first update starts with a host barrier: ranks may finish set-up seconds apart
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
         self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
         self._given_aux = None
@@ -169,6 +180,9 @@ class FusedRBM(object):
         data_aux: the 16-bit parts of `data` in the form this engine's products read (the data
         feed writes them while gathering the minibatch); without it the step begins by splitting."""
         cm = self.cm
+        if self.dp_peer and self._peer_group is not None:
+            self._peer_group.barrier()
+            self._peer_group = None
         k, draw_v = self._gibbs_steps(step), self._sample_visible(step)
         if self.visible == LINEAR:
             draw_v = False
@@ -203,15 +217,23 @@ class FusedRBM(object):
                 ct.memmove(ct.byref(view.mat), ct.byref(m.mat), ct.sizeof(m.mat))
                 view.mat.owns_data = 0
         self._batch_owner = (data, data_aux)
-        prog.set_floats(ub, f0=sc["inv_b"], f1=mom, f2=eps)
-        for op in (uw if isinstance(uw, list) else [uw]):
-            prog.set_floats(op, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
+        if isinstance(ub, tuple):       # the peer-memory update: one operation carries every scalar
+            prog.set_floats(ub[1], f0=sc["inv_b"], f1=mom, f2=eps, f3=emom, f4=eeps, f5=l2, f6=l1)
+        else:
+            prog.set_floats(ub, f0=sc["inv_b"], f1=mom, f2=eps)
+            for op in (uw if isinstance(uw, list) else [uw]):
+                prog.set_floats(op, f0=sc["inv_b"], f1=emom, f2=eeps, f3=l2, f4=l1)
         prog.run()
 
     def _issue_updates(self, X, sc, wb, w_scale=None):
         """All-reduce of the packed statistics, then the two updates (biases are not regularised,
         deepnet/dbm.py:249).  Returns the operations whose scalars follow the schedules."""
         V, H = self.V, self.H
+        if self.dp_peer:
+            # exchange + update of every parameter in one pass over peer memory (no NCCL)
+            u = self._op(X, "peer_update", 0, 6 * wb, "dp_peer_update", self.W, self.dW, self.W_aux, w_scale, self.pack,
+                         self.b, self.db, sc["inv_b"], sc["mom"], sc["eps"], sc["emom"], sc["eeps"], l2=sc["l2"], l1=sc["l1"])
+            return ("peer", u), None
         if self.world_size > 1:
             self._op(X, "allreduce", 0, 4.0 * (V * H + V + H), "allreduce", self.pack)
         ub = self._op(X, "update_bias", 0, 20.0 * (V + H), "momentum_update", self.b, self.db, None, self.suff_b,
@@ -303,7 +325,7 @@ class FusedRBM(object):
                      **act)
         # column panels of W as (first column, columns): equal ones, or the widths asked for
         bounds = []
-        if self.world_size > 1:
+        if self.world_size > 1 and not self.dp_peer:
             widths = self.dp_panel_cols or ([H // self.dp_panels] * self.dp_panels if self.dp_panels > 1 else [])
             if 1 < len(widths) < 8 and sum(widths) == H and all(w > 0 and w % 8 == 0 for w in widths):
                 first = 0

@@ -25,9 +25,10 @@ class Group(object):
     def __init__(self, cm, world, rank, timeout=120.0, path=None):
         self.cm, self.world, self.rank = cm, world, rank
         self._slots = None
+        self._path = path or _id_path()
         if world == 1:
             return
-        path = path or _id_path()
+        path = self._path
         if rank == 0:
             uid = cm.dp_unique_id()
             with open(path + ".tmp", "wb") as f:
@@ -59,6 +60,30 @@ class Group(object):
         self._slots.overwrite(v)
         self.cm.dp_allreduce(self._slots)
         return [float(t) for t in np.array(self._slots.asarray())[0, :self.world]]
+
+    def exchange(self, tag, payload, timeout=120.0):
+        """Every rank contributes some bytes; returns all ranks' contributions in rank order."""
+        if self.world == 1:
+            return [payload]
+        base = "%s_%s_" % (self._path, tag)
+        with open(base + "%d.tmp" % self.rank, "wb") as f:
+            f.write(payload)
+        os.rename(base + "%d.tmp" % self.rank, base + str(self.rank))
+        out = []
+        deadline = time.time() + timeout
+        for r in range(self.world):
+            while not os.path.exists(base + str(r)):
+                if time.time() > deadline:
+                    raise RuntimeError("rank %d: rank %d published no %s within %.0f s" % (self.rank, r, tag, timeout))
+                time.sleep(0.01)
+            with open(base + str(r), "rb") as f:
+                out.append(f.read())
+        self.gather(0.0)                             # everyone has read everything
+        try:
+            os.remove(base + str(self.rank))
+        except OSError:
+            pass
+        return out
 
     def barrier(self):
         self.cm.cuda_sync_threads()

@@ -334,6 +334,22 @@ int dp_abort(void);
 /* The all-reduce on a side stream, beside the kernels that follow on the library stream: begin waits
  * for what is enqueued so far and starts it (slot 0..7, one pending all-reduce each); end makes the
  * library stream wait for it. */
+/* The exchange and the update of a data-parallel step as one pass over peer memory, without NCCL:
+ * rank r owns the columns [r H/G, (r+1) H/G) of W; once every rank's statistics are complete it reads
+ * the G partial statistics of its columns (plain loads over NVLink), applies the momentum / decay
+ * update to its shard and stores the new shard and its 16-bit planes into every rank's copy of W.
+ * Bring-up: every rank exports {pack, W, W_aux, flags} (dp_peer_export / dp_peer_export_flags,
+ * dp_peer_handle_bytes() bytes each), the ranks exchange them by any host channel and call
+ * dp_peer_setup with all of them in rank order; then dp_peer_update once per update on every rank
+ * (pack = [W statistics | b_v | b_h] of this rank, b / db the packed biases and their history).
+ * Waits are bounded (b200_set_wait_limit; b200_read_status tells).  H must be a multiple of G. */
+int dp_peer_handle_bytes(void);
+int dp_peer_export(cudamat* m, char* handle_out);
+int dp_peer_export_flags(char* handle_out);
+int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cudamat* w, cudamat* w_aux);
+int dp_peer_update(cudamat* w, cudamat* delta, cudamat* w_aux, cudamat* w_scale, cudamat* pack, cudamat* b, cudamat* db,
+                   float inv_batch, float mom_b, float eps_b, float mom_w, float eps_w, float l2, float l1);
+int dp_peer_close(void);
 int dp_allreduce_begin(cudamat* mat, int slot);
 int dp_allreduce_end(int slot);
 /* Waits (at most timeout_ms) for the work enqueued on the library stream, collectives included; on
@@ -348,14 +364,14 @@ int dp_wait(int timeout_ms);
  * 5 momentum_update, 6 split_f16, 7 split_bf16, 8 dp_allreduce, 9 softmax_scaled, 10 sample_multinomial,
  * 11 div_by_row_vec, 12 add_scalar, 13 assign_scalar, 14 copy_on_device, 15 sample_bernoulli,
  * 16 softmax_sample, 17 momentum_update_columns, 18 dp_allreduce_begin, 19 dp_allreduce_end,
- * 20 b200_set_sm_limit); m[], i0.., f0.. are its arguments in declaration order (matrices, then integers,
+ * 20 b200_set_sm_limit, 21 dp_peer_update); m[], i0.., f0.. are its arguments in declaration order (matrices, then integers,
  * then floats; gemm for kind 0).  Stops at the first failure: returns its code, *failed_at its index. */
 struct b200_fused_gemm;
 typedef struct b200_op {
   int kind;
   int i0, i1, i2;
-  float f0, f1, f2, f3, f4;
-  cudamat* m[6];
+  float f0, f1, f2, f3, f4, f5, f6, f7;
+  cudamat* m[8];
   struct b200_fused_gemm* gemm;
 } b200_op;
 int b200_run_program(rnd_struct* rnd_state, b200_op* ops, int n, int* failed_at);

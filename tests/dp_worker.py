@@ -19,26 +19,15 @@ def main():
     from deepnet_b200.fused_rbm import FusedRBM
     cm.cuda_set_device(rank)
     cm.cublas_init()
-    idfile = os.path.join(tmp, "nccl_id")
-    if rank == 0:
-        with open(idfile + ".tmp", "wb") as f:
-            f.write(cm.dp_unique_id())
-        os.rename(idfile + ".tmp", idfile)
-    deadline = time.time() + 60
-    while not os.path.exists(idfile):
-        if time.time() > deadline:
-            raise SystemExit("rank %d: no NCCL id after 60 s" % rank)
-        time.sleep(0.05)
-    with open(idfile, "rb") as f:
-        uid = f.read()
-    cm.dp_init(uid, world, rank)
+    from deepnet_b200.rendezvous import Group
+    group = Group(cm, world, rank, timeout=60, path=os.path.join(tmp, "nccl_id"))
     cfg = configs.build(0, cases=400, dims_scale=scale)
     gb = cfg["batchsize"]                       # global minibatch, split evenly over the ranks
     b = gb // world
     V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
     eng = FusedRBM(cm, V, H, b, cfg["edges"][0]["weight"], cfg["hyperparams"],
                    edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"], world_size=world,
-                   rank=rank)
+                   rank=rank, group=group)
     data = cm.CUDAMatrix(cfg["data"])
     for step in range(3):
         s = step * gb + rank * b
@@ -46,7 +35,9 @@ def main():
     cm.dp_wait(20000)        # bounded: a peer that never joined would end here with an error, not a hang
     cm.dp_check()
     np.savez(os.path.join(tmp, "rank%d.npz" % rank), W=np.array(eng.W.asarray()), hs=np.array(eng.h_samp.asarray()),
-             loss=eng.read_loss(), status=cm.read_status())
+             loss=eng.read_loss(), status=cm.read_status(), peer=int(eng.dp_peer))
+    group.barrier()          # nobody unmaps a peer's memory while another rank may still write to it
+    cm.dp_peer_close()
     cm.dp_destroy()          # leaves only after its last collective has completed
 
 

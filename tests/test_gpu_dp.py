@@ -14,8 +14,9 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("form,scale", [("derived", 0.5), ("f16", 0.5), ("f16", 0.512)])
-def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, monkeypatch):
+@pytest.mark.parametrize("form,scale,peer", [("derived", 0.5, 0), ("f16", 0.5, 0), ("f16", 0.512, 0), ("derived", 0.512, 1),
+                                             ("f16", 0.512, 1)])
+def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, peer, monkeypatch):
     if cm._lib.b200_device_count() < 2:
         pytest.skip("needs two GPUs")
     # "f16": the operand form of the big model (aux matrices in scaled half precision, W's exponent
@@ -24,8 +25,10 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, monkeypatch):
     # side-stream all-reduce and update per panel), as it does at full size
     monkeypatch.setenv("B200_RBM_STATE_AUX", "1" if form == "f16" else "0")
     monkeypatch.setenv("B200_RBM_F16", "1" if form == "f16" else "0")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    if scale == 0.512:
+    # peer = 1: the exchange and the update run as one pass over peer memory (plain loads and stores,
+    # bounded flag waits) instead of an NCCL all-reduce followed by the update
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_DP_PEER=str(peer))
+    if scale == 0.512 and not peer:
         env.update(B200_DP_PANELS="4", B200_DP_PANEL_PRODUCTS="1")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path), str(scale)], env=env)
              for r in range(2)]
@@ -41,6 +44,7 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, monkeypatch):
     assert codes == [0, 0]
     r0, r1 = (np.load(os.path.join(tmp_path, "rank%d.npz" % r)) for r in range(2))
     assert int(r0["status"]) == 0 and int(r1["status"]) == 0
+    assert int(r0["peer"]) == peer and int(r1["peer"]) == peer
     assert np.array_equal(r0["W"], r1["W"])                 # replicas stay bit-identical
 
     from deepnet_b200 import configs
