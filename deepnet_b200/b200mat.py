@@ -1122,6 +1122,12 @@ def set_wait_limit(iterations):
     _check(_lib.b200_set_wait_limit(ct.c_uint(int(iterations))))
 
 
+def set_dependent_launch(on):
+    """Programmatic dependent launch of the step's kernels (on by default): a kernel is scheduled
+    while its predecessor drains and touches global memory only after that one has completed."""
+    _check(_lib.b200_set_dependent_launch(1 if on else 0))
+
+
 class Event(object):
     """A CUDA event on the library stream: e.record(); ...; start.elapsed_ms(end)."""
 

@@ -52,6 +52,34 @@ int* status_word();                    // device int: non-zero after a bounded w
 bool initialised();                    // the library stream and status word exist (tries to create them)
 uint32_t wait_limit();                 // iterations a bounded device-side wait may spin (b200_set_wait_limit)
 
+bool dependent_launch_enabled();       // b200_set_dependent_launch / B200_DEPENDENT_LAUNCH (default on)
+
+// Programmatic dependent launch.  A kernel started with launch_dependent() may be scheduled while
+// the kernel before it on the stream is still running (its blocks become resident, run their
+// prologue and then block in grid_dependency_wait() until the predecessor has completed and its
+// writes are visible).  RULE: every kernel launched this way calls grid_dependency_wait() on every
+// thread before its first access to global memory; grid_dependents_launch() (optional, at the top)
+// lets the successor be scheduled before this kernel's blocks exit.  Both are no-ops in a kernel
+// that was launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline long numel(const cudamat* m) { return (long)m->size[0] * m->size[1]; }
 inline bool same_shape(const cudamat* a, const cudamat* b) {
   return a->size[0] == b->size[0] && a->size[1] == b->size[1];

@@ -3,6 +3,7 @@
 // One process drives one GPU; every operation is enqueued on one library stream and
 // the host only blocks where the reference API returns data to it.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -21,6 +22,7 @@ static void* g_ws[8] = {nullptr};
 static size_t g_ws_bytes[8] = {0};
 static std::mutex g_mu;
 
+static int g_dependent_launch = -1;        // programmatic dependent launch of the hot kernels: -1 = read the environment
 static uint32_t g_wait_limit = 1u << 24;   // iterations of a bounded device-side wait: ~1-2 s
 
 // Creates the library stream and the device status word.  A failure (a device with no memory left,
@@ -77,6 +79,13 @@ bool initialised() {
   return g_stream != nullptr;
 }
 uint32_t wait_limit() { return g_wait_limit; }
+bool dependent_launch_enabled() {
+  if (g_dependent_launch < 0) {
+    const char* e = getenv("B200_DEPENDENT_LAUNCH");
+    g_dependent_launch = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_dependent_launch != 0;
+}
 
 int set_error(const char* msg) {
   if (msg != g_err) snprintf(g_err, sizeof(g_err), "%s", msg);
@@ -151,6 +160,14 @@ int cublas_init() {
 int b200_sm_count() { return sm_count(); }
 int b200_set_sm_limit(int sms) {
   g_sm_limit = sms > 0 ? sms : 0;
+  return 0;
+}
+
+// Programmatic dependent launch of the hot kernels (a kernel is scheduled while its predecessor on
+// the stream drains; it touches global memory only after the predecessor has completed): on by
+// default, B200_DEPENDENT_LAUNCH=0 or this call with 0 turns it off.  No counterpart in the reference.
+int b200_set_dependent_launch(int on) {
+  g_dependent_launch = on ? 1 : 0;
   return 0;
 }
 

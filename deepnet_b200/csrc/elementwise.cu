@@ -24,6 +24,8 @@ inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 template <class F>
 __global__ void __launch_bounds__(kThreads) k_map1(const float* a, float* t, long n, bool vec,
                                                    F f) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
     const long n4 = n >> 2;
@@ -40,6 +42,8 @@ __global__ void __launch_bounds__(kThreads) k_map1(const float* a, float* t, lon
 
 template <class F>
 __global__ void __launch_bounds__(kThreads) k_map2(const float* a, const float* b, float* t, long n, bool vec, F f) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
     const long n4 = n >> 2;
@@ -56,6 +60,8 @@ __global__ void __launch_bounds__(kThreads) k_map2(const float* a, const float* 
 }
 
 __global__ void __launch_bounds__(kThreads) k_fill(float* __restrict__ t, long n, bool vec, float v) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
     const long n4 = n >> 2;
@@ -71,6 +77,8 @@ __global__ void __launch_bounds__(kThreads) k_fill(float* __restrict__ t, long n
 // One thread handles 4 consecutive rows of one column when h % 4 == 0.
 template <bool kByRow, class F>
 __global__ void __launch_bounds__(kThreads) k_bcast(const float* m, const float* v, float* t, int h, int w, bool vec, F f) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
     const int h4 = h >> 2;
@@ -104,7 +112,8 @@ int map1(cudamat* mat, cudamat* target, F f) {
   const long n = numel(mat);
   if (n == 0) return 0;
   const bool vec = aligned16(mat->data_device) && aligned16(target->data_device);
-  k_map1<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, stream()>>>(mat->data_device, target->data_device, n, vec, f);
+  (void)launch_dependent(k_map1<F>, dim3(grid_for(vec ? (n + 3) / 4 : n)), dim3(kThreads), 0, stream(), mat->data_device,
+                         target->data_device, n, vec, f);
   return check_launch();
 }
 
@@ -116,8 +125,8 @@ int map2(cudamat* mat1, cudamat* mat2, cudamat* target, F f) {
   const long n = numel(mat1);
   if (n == 0) return 0;
   const bool vec = aligned16(mat1->data_device) && aligned16(mat2->data_device) && aligned16(target->data_device);
-  k_map2<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, stream()>>>(mat1->data_device, mat2->data_device,
-                                                                   target->data_device, n, vec, f);
+  (void)launch_dependent(k_map2<F>, dim3(grid_for(vec ? (n + 3) / 4 : n)), dim3(kThreads), 0, stream(), mat1->data_device,
+                         mat2->data_device, target->data_device, n, vec, f);
   return check_launch();
 }
 
@@ -135,8 +144,8 @@ int bcast(cudamat* mat, cudamat* vec, cudamat* target, F f) {
   const bool v4 = (h % 4 == 0) && aligned16(mat->data_device) && aligned16(target->data_device) &&
                   aligned16(vec->data_device);
   const long items = v4 ? (long)(h / 4) * w : (long)h * w;
-  k_bcast<kByRow><<<grid_for(items), kThreads, 0, stream()>>>(mat->data_device, vec->data_device, target->data_device, h,
-                                                             w, v4, f);
+  (void)launch_dependent(k_bcast<kByRow, F>, dim3(grid_for(items)), dim3(kThreads), 0, stream(), mat->data_device,
+                         vec->data_device, target->data_device, h, w, v4, f);
   return check_launch();
 }
 
@@ -259,7 +268,7 @@ int assign_scalar(cudamat* mat, float alpha) {
   const long n = numel(mat);
   if (n == 0) return 0;
   const bool vec = aligned16(mat->data_device);
-  k_fill<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, stream()>>>(mat->data_device, n, vec, alpha);
+  (void)launch_dependent(k_fill, dim3(grid_for(vec ? (n + 3) / 4 : n)), dim3(kThreads), 0, stream(), mat->data_device, n, vec, alpha);
   return check_launch();
 }
 int mult_by_scalar(cudamat* mat, float alpha, cudamat* target) { return map1(mat, target, FMulS{alpha}); }

@@ -45,6 +45,8 @@ int run(const GemmProblem& g) {
 // hi may be null: the tensor core itself drops the low 13 mantissa bits of an fp32
 // operand, so the matrix x can stand in for its own high part and only lo is stored.
 __global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float* lo, long n, bool vec) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {
     const long n4 = n >> 2;
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(256) k_split(const float* x, float* hi, float*
 // aux matrix of x (rows x cols, contiguous columns): both bfloat16 planes in one pass.
 __global__ void __launch_bounds__(256) k_split_aux(const float* x, uint16_t* aux, int rows, int lda, long n,
                                                    bool vec) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   if (vec) {   // rows % 4 == 0: four consecutive elements share a column
     for (long i = tid; i < (n >> 2); i += nth) {
@@ -100,6 +104,8 @@ __global__ void __launch_bounds__(256) k_split_aux(const float* x, uint16_t* aux
 // `only_if` (optional): a device flag; the kernel returns at once when it is zero.
 __global__ void __launch_bounds__(256) k_split_f16(const float* x, uint16_t* aux, int rows, int lda, long n, bool vec,
                                                    const float* exp_dev, int exp_const, const float* only_if) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   if (only_if && *only_if == 0.0f) return;
   const float scale = exp2f((exp_dev ? *exp_dev : 0.0f) + (float)exp_const);
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
@@ -132,7 +138,9 @@ int launch_split_aux(const float* x, float* aux, int rows, long n) {
   long blocks = ((vec ? n / 4 : n) + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
   if (blocks < 1) blocks = 1;
-  k_split_aux<<<(int)blocks, 256, 0, stream()>>>(x, reinterpret_cast<uint16_t*>(aux), rows, aux_rows(rows), n, vec);
+  if (launch_dependent(k_split_aux, dim3((unsigned)blocks), dim3(256), 0, stream(), x, reinterpret_cast<uint16_t*>(aux), rows,
+                       aux_rows(rows), n, vec) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 
@@ -141,7 +149,7 @@ int launch_split(const float* x, float* hi, float* lo, long n) {
   const bool vec = (((uintptr_t)x | (uintptr_t)hi | (uintptr_t)lo) & 15) == 0;
   long blocks = ((vec ? (n + 3) / 4 : n) + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
-  k_split<<<(int)blocks, 256, 0, stream()>>>(x, hi, lo, n, vec);
+  (void)launch_dependent(k_split, dim3((unsigned)blocks), dim3(256), 0, stream(), x, hi, lo, n, vec);
   return check_launch();
 }
 
@@ -169,6 +177,8 @@ template <bool kHasGrad, int kAux>
 __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* grad, const float* suff,
                                                 uint16_t* w_aux, float* scale, int rows, int lda, long n, bool vec,
                                                 float ninv_batch, float momentum, float neps, float l2, float l1) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   float wmax = 0.0f;
   const float f16_scale = kAux == 2 ? exp2f(scale[0]) : 1.0f;
@@ -241,6 +251,8 @@ __global__ void __launch_bounds__(256) k_update(float* w, float* delta, float* g
 // rewrite the aux.  The maximum starts over.  A parameter that is all zero (or not finite) keeps
 // its exponent.
 __global__ void k_update_scale(float* scale) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const float m = __uint_as_float(reinterpret_cast<unsigned*>(scale)[2]);
   float redo = 0.0f;
   if (m > 0.0f && m < 3.0e38f) {
@@ -265,7 +277,9 @@ int rewrite_f16_planes_if(const float* x, uint16_t* aux, int rows, long n, const
   long sblocks = ((svec ? n / 4 : n) + 255) / 256;
   if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
   if (sblocks < 1) sblocks = 1;
-  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(x, aux, rows, aux_rows(rows), n, svec, exp_dev, 0, only_if);
+  if (launch_dependent(k_split_f16, dim3((unsigned)sblocks), dim3(256), 0, stream(), x, aux, rows, aux_rows(rows), n, svec,
+                       exp_dev, 0, only_if) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 }  // namespace b200
@@ -349,9 +363,10 @@ int split_f16(cudamat* x, cudamat* aux, cudamat* exp_dev, int exp_const) {
   long blocks = ((vec ? n / 4 : n) + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
   if (blocks < 1) blocks = 1;
-  k_split_f16<<<(int)blocks, 256, 0, stream()>>>(x->data_device, reinterpret_cast<uint16_t*>(aux->data_device), rows,
-                                                 aux_rows(rows), n, vec, exp_dev ? exp_dev->data_device : nullptr,
-                                                 exp_const, nullptr);
+  if (launch_dependent(k_split_f16, dim3((unsigned)blocks), dim3(256), 0, stream(), x->data_device,
+                       reinterpret_cast<uint16_t*>(aux->data_device), rows, aux_rows(rows), n, vec,
+                       exp_dev ? exp_dev->data_device : nullptr, exp_const, nullptr) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 
@@ -532,9 +547,9 @@ int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* 
     long blocks = ((vec ? n / 4 : n) + 255) / 256;
     if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
     if (blocks < 1) blocks = 1;
-#define LAUNCH_UPDATE(G, A)                                                                                  \
-  k_update<G, A><<<(int)blocks, 256, 0, stream()>>>(wp, dp, gp, sfp, app, sp, rows, lda, n, vec, -inv_batch, \
-                                                    momentum, -eps, l2, l1)
+#define LAUNCH_UPDATE(G, A)                                                                                          \
+  (void)launch_dependent(k_update<G, A>, dim3((unsigned)blocks), dim3(256), 0, stream(), wp, dp, gp, sfp, app, sp, rows, lda, n, \
+                         vec, -inv_batch, momentum, -eps, l2, l1)
     if (grad) {
       if (mode == 2) LAUNCH_UPDATE(true, 2);
       else if (mode == 1) LAUNCH_UPDATE(true, 1);
@@ -549,7 +564,7 @@ int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* 
     if (err) return err;
   }
   if (mode != 2 || !last_panel) return 0;
-  k_update_scale<<<1, 1, 0, stream()>>>(sp);
+  (void)launch_dependent(k_update_scale, dim3(1), dim3(1), 0, stream(), sp);
   int err = check_launch();
   if (err) return err;
   const long total = numel(w);
@@ -559,7 +574,8 @@ int momentum_update_columns(cudamat* w, cudamat* delta, cudamat* grad, cudamat* 
   if (sblocks > (long)sm_count() * 8) sblocks = (long)sm_count() * 8;
   if (sblocks < 1) sblocks = 1;
   // (returns at once unless the exponent had to change)
-  k_split_f16<<<(int)sblocks, 256, 0, stream()>>>(w->data_device, ap, rows, lda, total, svec, sp, 0, sp + 3);
+  (void)launch_dependent(k_split_f16, dim3((unsigned)sblocks), dim3(256), 0, stream(), w->data_device, ap, rows, lda, total, svec,
+                         sp, 0, sp + 3);
   return check_launch();
 }
 

@@ -443,6 +443,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  grid_dependents_launch();   // the next kernel of the stream may be scheduled as SMs free up
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int splits = (kEpi == kEpiPartial) ? p.splits : 1;
   const int num_tiles = p.tiles_m * p.tiles_n * splits;     // work items: every role walks the same list
@@ -480,6 +481,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   if (kTwo) cluster_sync();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // Everything above (barriers, TMEM) touched no global memory and may have run while the previous
+  // kernel of the stream was still finishing; operands, biases and outputs are touched only from here on.
+  grid_dependency_wait();
 
   const int kChunkIters = p.chunk_iters;
   // k-blocks of group q that split s multiplies (all of them when the product is not split)
@@ -1249,7 +1253,8 @@ int launch_tc(TcParams& p) {
   const int tiles = p.tiles_m * p.tiles_n * p.splits;   // work items
   if (!kTwo) {
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kernel<<<grid, kThreadsTc, Cfg::kSmemBytes, stream()>>>(p);
+    if (launch_dependent(kernel, dim3(grid), dim3(kThreadsTc), Cfg::kSmemBytes, stream(), p) != cudaSuccess)
+      return set_error(cudaGetErrorString(cudaGetLastError()));
     return check_launch();
   }
   int pairs = tiles < max_pairs ? tiles : max_pairs;
@@ -1259,13 +1264,15 @@ int launch_tc(TcParams& p) {
   cfg.blockDim = dim3(kThreadsTc);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream();
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = dependent_launch_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
@@ -1275,6 +1282,8 @@ int launch_tc(TcParams& p) {
 // columns, which share one Philox block exactly as the tensor-core epilogue assigns them.
 __global__ void __launch_bounds__(256) k_splitk_finish(const float* __restrict__ part, int splits, long stride, int M,
                                                        int N, const GemmEpilogue e) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int nblk = (N + 3) >> 2;
   const long items = (long)M * nblk;
   const bool draw = e.sample != nullptr || e.sample_aux != nullptr;
@@ -1631,7 +1640,9 @@ int gemm_tc(const GemmProblem& g) {
   const long items = (long)g.M * ((g.N + 3) / 4);
   long blocks = (items + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
-  k_splitk_finish<<<(int)blocks, 256, 0, stream()>>>(p.epi.out, p.splits, p.split_stride, g.M, g.N, g.epi);
+  if (launch_dependent(k_splitk_finish, dim3((unsigned)blocks), dim3(256), 0, stream(), p.epi.out, p.splits, p.split_stride,
+                       g.M, g.N, g.epi) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 

@@ -623,6 +623,8 @@ __global__ void __launch_bounds__(32 * kRowLanes) k_rowsum_diff(const float* __r
                                                                 int cols_per_split) {
   __shared__ float smem[kRowLanes][32 * kVec + 1];
   __shared__ bool is_last;
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int r = (blockIdx.x * 32 + tx) * kVec;
   const int c0 = blockIdx.y * cols_per_split;
@@ -676,6 +678,8 @@ __global__ void __launch_bounds__(256) k_sq_diff_acc(const float* __restrict__ a
                                                      double* __restrict__ part, unsigned* counter, float* acc) {
   __shared__ double smem[32];
   __shared__ bool is_last;
+  grid_dependents_launch();
+  grid_dependency_wait();
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long)gridDim.x * blockDim.x;
   double s = 0;
   long start = 0;
@@ -742,7 +746,9 @@ int add_sq_diff(cudamat* a, cudamat* b, cudamat* acc) {
   double* part = (double*)workspace(1, (size_t)(blocks + 1) * sizeof(double));
   unsigned* counter = ticket_counters(1);
   if (!part || !counter) return CUDA_ERROR;
-  k_sq_diff_acc<<<blocks, 256, 0, stream()>>>(a->data_device, b->data_device, n, part + 1, counter, acc->data_device);
+  if (launch_dependent(k_sq_diff_acc, dim3(blocks), dim3(256), 0, stream(), a->data_device, b->data_device, n, part + 1, counter,
+                       acc->data_device) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 
@@ -771,12 +777,9 @@ int row_sum_diff(cudamat* a, cudamat* b, cudamat* target) {
     if (!part || !counters) return CUDA_ERROR;
     counters += 1;   // slot 0 belongs to add_sq_diff
   }
-  if (vec4)
-    k_rowsum_diff<4><<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(a->data_device, b->data_device, part, counters,
-                                                                       target->data_device, h, w, cps);
-  else
-    k_rowsum_diff<1><<<dim3(bx, splits), 32 * kRowLanes, 0, stream()>>>(a->data_device, b->data_device, part, counters,
-                                                                       target->data_device, h, w, cps);
+  const cudaError_t e = launch_dependent(vec4 ? k_rowsum_diff<4> : k_rowsum_diff<1>, dim3(bx, splits), dim3(32 * kRowLanes), 0,
+                                         stream(), a->data_device, b->data_device, part, counters, target->data_device, h, w, cps);
+  if (e != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
   return check_launch();
 }
 

@@ -15,6 +15,8 @@ enum RngOp { kUniform = 0, kNormal, kBernoulli, kBernoulliTanh, kGaussianAdd, kP
 template <int kOp>
 __global__ void __launch_bounds__(256) k_rng(const float* src, float* dst, int h, int w, int col0, PhiloxKey key,
                                              float p0, float p1) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   // global column blocks covered by this matrix: [col0 >> 2, (col0 + w - 1) >> 2]
   const int blk0 = col0 >> 2;
   const int nblk = ((col0 + w - 1) >> 2) - blk0 + 1;
@@ -66,7 +68,8 @@ int launch(rnd_struct* rnd, cudamat* mat, cudamat* target, float p0 = 0, float p
   const long items = (long)h * (((col0 + w - 1) >> 2) - (col0 >> 2) + 1);
   long blocks = (items + 255) / 256;
   if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
-  k_rng<kOp><<<(int)blocks, 256, 0, stream()>>>(mat->data_device, target->data_device, h, w, col0, key, p0, p1);
+  (void)launch_dependent(k_rng<kOp>, dim3((unsigned)blocks), dim3(256), 0, stream(), mat->data_device, target->data_device, h, w,
+                         col0, key, p0, p1);
   return check_launch();
 }
 

@@ -29,6 +29,8 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 __global__ void __launch_bounds__(256) k_softmax_scaled(const float* m, const float* __restrict__ scale, float* t,
                                                         int h, int w) {
   __shared__ float red[32];
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int c = blockIdx.x; c < w; c += gridDim.x) {
     const float* col = m + (long)c * h;
@@ -64,6 +66,8 @@ __global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restr
                                                             unsigned long long call0) {
   __shared__ float sv[4][8];
   __shared__ int si[4][8];
+  grid_dependents_launch();
+  grid_dependency_wait();
   for (int doc = blockIdx.y; doc < w; doc += gridDim.y) {
   int ndraws = (int)nn[doc];
   if (ndraws > max_draws) ndraws = max_draws;
@@ -139,6 +143,8 @@ __global__ void __launch_bounds__(128) k_softmax_sample(const float* pre, const 
                                                         float* sample, int h, int w, int col0, PhiloxKey key) {
   __shared__ float red[4];
   __shared__ int redi[4];
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int c = blockIdx.x; c < w; c += gridDim.x) {
     const float* col = pre + (long)c * h;
@@ -288,8 +294,8 @@ int softmax_scaled(cudamat* mat, cudamat* scale, cudamat* target) {
   if (!same_shape(mat, target) || numel(scale) != mat->size[1]) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const int h = mat->size[0], w = mat->size[1];
   if ((long)h * w == 0) return 0;
-  k_softmax_scaled<<<w < sm_count() * 8 ? w : sm_count() * 8, 256, 0, stream()>>>(mat->data_device, scale->data_device,
-                                                                                 target->data_device, h, w);
+  (void)launch_dependent(k_softmax_scaled, dim3(w < sm_count() * 8 ? w : sm_count() * 8), dim3(256), 0, stream(), mat->data_device,
+                         scale->data_device, target->data_device, h, w);
   return check_launch();
 }
 
@@ -308,8 +314,8 @@ int sample_multinomial(rnd_struct* rnd_state, cudamat* probs, cudamat* nn, cudam
   rnd_state->calls += (unsigned long long)w;
   int groups = (max_draws + 3) / 4 + 1;
   if (groups > 64) groups = 64;
-  k_sample_multinomial<<<dim3(groups, w < 65535 ? w : 65535), 256, 0, stream()>>>(probs->data_device, nn->data_device, target->data_device,
-                                                              h, w, max_draws, rng_col0(), rnd_state->seed, call0);
+  (void)launch_dependent(k_sample_multinomial, dim3(groups, w < 65535 ? w : 65535), dim3(256), 0, stream(), probs->data_device,
+                         nn->data_device, target->data_device, h, w, max_draws, rng_col0(), rnd_state->seed, call0);
   return check_launch();
 }
 
@@ -330,9 +336,9 @@ int softmax_sample(rnd_struct* rnd_state, cudamat* pre, cudamat* bias, cudamat* 
     rnd_state->calls += 1;
   }
   if ((long)h * w == 0) return 0;
-  k_softmax_sample<<<w < sm_count() * 16 ? w : sm_count() * 16, 128, 0, stream()>>>(
-      pre->data_device, bias ? bias->data_device : nullptr, state->data_device, sample ? sample->data_device : nullptr,
-      h, w, rng_col0(), key);
+  (void)launch_dependent(k_softmax_sample, dim3(w < sm_count() * 16 ? w : sm_count() * 16), dim3(128), 0, stream(),
+                         pre->data_device, bias ? bias->data_device : nullptr, state->data_device,
+                         sample ? sample->data_device : nullptr, h, w, rng_col0(), key);
   return check_launch();
 }
 

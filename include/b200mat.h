@@ -300,6 +300,10 @@ int b200_read_status(void);               /* non-zero: a kernel's bounded wait g
 /* Iterations a device-side wait may spin before its kernel gives up (default 2^24, one to two
  * seconds; 0 restores the default).  No counterpart in the reference. */
 int b200_set_wait_limit(unsigned int iterations);
+/* Programmatic dependent launch of the step's kernels (each is scheduled while its predecessor on
+ * the stream drains and touches global memory only after that one has completed): on by default;
+ * 0 turns it off (so does B200_DEPENDENT_LAUNCH=0).  No counterpart in the reference. */
+int b200_set_dependent_launch(int on);
 /* SMs the library's kernels size their grids for (0 = all): leaves room for an all-reduce that runs
  * beside the persistent tensor-core kernel.  No counterpart in the reference. */
 int b200_set_sm_limit(int sms);

@@ -195,6 +195,43 @@ def test_recorded_step_equals_the_call_by_call_step(cm, config, scale, cases, mo
     assert cm.read_status() == 0
 
 
+@pytest.mark.parametrize("config,scale,cases,form", [(0, 1.0, 400, None), (1, 0.25, 512, None), (2, 0.02, 200, None),
+                                                     (3, 0.25, 300, None), (0, 0.5, 300, "f16")])
+def test_dependent_launch_changes_no_bit(cm, config, scale, cases, form, monkeypatch):
+    """With programmatic dependent launch every kernel of the step is scheduled while its predecessor
+    drains and waits for it before touching memory: 20 updates give the bits of ordinary launches."""
+    if form:
+        monkeypatch.setenv("B200_RBM_STATE_AUX", "1")
+        monkeypatch.setenv("B200_RBM_F16", "1")
+    results = []
+    try:
+        for on in (True, False):
+            cm.set_dependent_launch(on)
+            cfg = configs.build(config, cases=cases, dims_scale=scale)
+            B = cfg["batchsize"]
+            if config == 3:
+                from deepnet_b200.fused_dbm import FusedDBM
+                eng = FusedDBM(cm, [l["numdims"] for l in cfg["layers"]], B, [e["weight"] for e in cfg["edges"]],
+                               cfg["hyperparams"], seed=cfg["seed"])
+            else:
+                V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+                eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                               edge_hyperparams=cfg["edges"][0].get("hyperparams"),
+                               visible=cfg["layers"][0]["activation"], binary_data=True, seed=cfg["seed"])
+            data = cm.CUDAMatrix(cfg["data"])
+            for step in range(20):
+                s = (step % (cases // B)) * B
+                eng.TrainOneBatch(step, data.slice(s, s + B))
+            W = eng.W if isinstance(eng.W, list) else [eng.W]
+            results.append((eng.read_loss(), [get(w) for w in W]))
+    finally:
+        cm.set_dependent_launch(True)
+    assert results[0][0] == results[1][0]
+    for a, b in zip(results[0][1], results[1][1]):
+        np.testing.assert_array_equal(a, b)
+    assert cm.read_status() == 0
+
+
 def test_half_precision_engine_from_zero_weights(cm, oracle, monkeypatch):
     """W's exponent follows the weights from nothing to their first values (the update gathers the
     largest |W| and writes the half-precision form with the exponent that fits it)."""
