@@ -1202,20 +1202,34 @@ def dp_destroy():
 
 def dp_peer_setup(group, pack, w, w_aux):
     """Maps every rank's statistics, parameter, its 16-bit planes and flag array into this process
-    (CUDA IPC) for `dp_peer_update`.  group: a `rendezvous.Group` (the handles travel through it)."""
+    (CUDA IPC) for `dp_peer_update`.  group: a `rendezvous.Group` (the handles travel through it).
+    Returns True when EVERY rank has mapped every peer; otherwise every rank has closed what it
+    opened and gets False (the ranks agree, so that all of them fall back to the all-reduce)."""
     n = _lib.dp_peer_handle_bytes()
     mine = b""
-    for m in (pack, w, w_aux):
+    try:
+        for m in (pack, w, w_aux):
+            buf = ct.create_string_buffer(n)
+            if m is not None:
+                _check(_lib.dp_peer_export(m.p_mat, buf))
+            mine += buf.raw
         buf = ct.create_string_buffer(n)
-        if m is not None:
-            _check(_lib.dp_peer_export(m.p_mat, buf))
+        _check(_lib.dp_peer_export_flags(buf))
         mine += buf.raw
-    buf = ct.create_string_buffer(n)
-    _check(_lib.dp_peer_export_flags(buf))
-    mine += buf.raw
-    everyone = b"".join(group.exchange("peer_handles", mine))
-    _check(_lib.dp_peer_setup(ct.c_int(group.world), ct.c_int(group.rank), ct.c_char_p(everyone), pack.p_mat, w.p_mat,
-                              w_aux.p_mat if w_aux is not None else None))
+    except CUDAMatException:
+        mine = b""                              # told to the peers through the exchange itself
+    payloads = group.exchange("peer_handles", mine)
+    failed = 0.0
+    if any(len(x) != 4 * n for x in payloads):
+        failed = 1.0
+    else:
+        err = _lib.dp_peer_setup(ct.c_int(group.world), ct.c_int(group.rank), ct.c_char_p(b"".join(payloads)), pack.p_mat,
+                                 w.p_mat, w_aux.p_mat if w_aux is not None else None)
+        failed = 1.0 if err else 0.0
+    if group.max(failed) > 0:
+        _lib.dp_peer_close()
+        return False
+    return True
 
 
 def dp_peer_close():

@@ -48,6 +48,7 @@ int check_launch_any_stream();         // the same for entry points that also ru
 int set_error(const char* msg);        // records msg, returns CUDA_ERROR
 int rng_col0();                        // first global column of this process's minibatch shard
 void* workspace(int slot, size_t bytes);  // grow-only cached device scratch, slot 0..7
+void* workspace_zeroed(int slot, size_t bytes);  // the same, cleared when first handed out or regrown (counters left at zero by their users)
 int* status_word();                    // device int: non-zero after a bounded wait gave up
 bool initialised();                    // the library stream and status word exist (tries to create them)
 uint32_t wait_limit();                 // iterations a bounded device-side wait may spin (b200_set_wait_limit)

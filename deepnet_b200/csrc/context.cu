@@ -20,6 +20,7 @@ static int* g_status = nullptr;
 static char g_err[512] = "";
 static void* g_ws[8] = {nullptr};
 static size_t g_ws_bytes[8] = {0};
+static bool g_ws_fresh[8] = {false};   // allocated since it was last cleared (workspace_zeroed)
 static std::mutex g_mu;
 
 static int g_dependent_launch = -1;        // programmatic dependent launch of the hot kernels: -1 = read the environment
@@ -122,7 +123,22 @@ void* workspace(int slot, size_t bytes) {
     want = bytes;
   }
   g_ws_bytes[slot] = want;
+  g_ws_fresh[slot] = true;
   return g_ws[slot];
+}
+
+// The same, all zero when first handed out (and again after it had to grow): counters that their
+// users leave at zero between calls.
+void* workspace_zeroed(int slot, size_t bytes) {
+  void* p = workspace(slot, bytes);
+  if (p && g_ws_fresh[slot]) {
+    if (cudaMemsetAsync(p, 0, g_ws_bytes[slot], g_stream) != cudaSuccess) {
+      set_error("workspace clear failed");
+      return nullptr;
+    }
+    g_ws_fresh[slot] = false;
+  }
+  return p;
 }
 
 }  // namespace b200
@@ -183,6 +199,7 @@ int cublas_shutdown() {
     if (g_ws[i]) cudaFree(g_ws[i]);
     g_ws[i] = nullptr;
     g_ws_bytes[i] = 0;
+    g_ws_fresh[i] = false;
   }
   return 0;
 }

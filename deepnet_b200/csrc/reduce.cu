@@ -601,17 +601,7 @@ namespace {
 
 // A counter per reduction group, zero between calls (the last block resets it).
 unsigned* ticket_counters(int n) {
-  static unsigned* ptr = nullptr;
-  static int cap = 0;
-  if (n > cap) {
-    const int want = n < 4096 ? 4096 : n;
-    unsigned* p = (unsigned*)workspace(3, (size_t)want * sizeof(unsigned));
-    if (!p) return nullptr;
-    if (cudaMemsetAsync(p, 0, (size_t)want * sizeof(unsigned), stream()) != cudaSuccess) return nullptr;
-    ptr = p;
-    cap = want;
-  }
-  return ptr;
+  return (unsigned*)workspace_zeroed(3, (size_t)(n < 4096 ? 4096 : n) * sizeof(unsigned));
 }
 
 // out[r] = sum_c a[r, c] - sum_c b[r, c].  Block = 32 row lanes x 8 column lanes, kVec rows per

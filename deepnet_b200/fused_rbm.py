@@ -138,9 +138,9 @@ class FusedRBM(object):
         self.dp_peer = False
         if (world_size > 1 and group is not None and visible != REPLICATED_SOFTMAX and H % world_size == 0 and V % 4 == 0
                 and os.environ.get("B200_DP_PEER", "1") != "0"):
-            cm.dp_peer_setup(group, self.pack, self.W, self.W_aux)
-            self.dp_peer = True
-            self._peer_group = group       # the first update starts with a host barrier: ranks may finish set-up seconds apart
+            # (False on every rank when any of them could not map a peer: all keep the NCCL all-reduce)
+            self.dp_peer = cm.dp_peer_setup(group, self.pack, self.W, self.W_aux)
+            self._peer_group = group if self.dp_peer else None   # the first update starts with a host barrier: ranks may finish set-up seconds apart
         self._batch = cm.CUDAMatrix._from_mat(cm.cudamat())   # the recorded step's view of the current minibatch
         self._batch_aux = cm.CUDAMatrix._from_mat(cm.cudamat())   # ... and of its 16-bit parts, when the caller has them
         self._given_aux = None

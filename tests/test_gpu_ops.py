@@ -252,3 +252,23 @@ def test_single_launch_statistics(cm, oracle, shape):
         cm._check(cm._lib.add_sq_diff(ga.p_mat, gb.p_mat, acc.p_mat))
     sq = ((a.astype(np.float64) - b) ** 2).sum()
     assert abs(float(get(acc)[0, 0]) - 2 * sq) < 1e-5 * 2 * sq
+
+
+def test_single_launch_statistics_after_a_shutdown(cm):
+    """cublas_shutdown frees the library's scratch, the ticket counters of the single-launch
+    reductions with it; the next call gets new, zeroed ones (no pointer kept from before)."""
+    rng = np.random.default_rng(9)
+    a = rng.random((512, 300)).astype(np.float32)
+    b = rng.random((512, 300)).astype(np.float32)
+    ga, gb = cm.CUDAMatrix(a), cm.CUDAMatrix(b)
+    ref = a.astype(np.float64).sum(axis=1) - b.astype(np.float64).sum(axis=1)
+    for cycle in range(2):
+        t, acc = cm.empty((512, 1)), cm.empty((1, 1))
+        acc.assign(0)
+        cm._check(cm._lib.row_sum_diff(ga.p_mat, gb.p_mat, t.p_mat))
+        cm._check(cm._lib.add_sq_diff(ga.p_mat, gb.p_mat, acc.p_mat))
+        np.testing.assert_allclose(get(t).ravel(), ref, rtol=1e-5, atol=1e-3)
+        sq = ((a.astype(np.float64) - b) ** 2).sum()
+        assert abs(float(get(acc)[0, 0]) - sq) < 1e-5 * sq
+        cm.cublas_shutdown()
+        cm.cublas_init()
