@@ -1201,8 +1201,9 @@ def dp_destroy():
 
 
 def dp_peer_setup(group, pack, w, w_aux):
-    """Maps every rank's statistics, parameter, its 16-bit planes and flag array into this process
-    (CUDA IPC) for `dp_peer_update`.  group: a `rendezvous.Group` (the handles travel through it).
+    """Maps every rank's statistics, parameter, its 16-bit planes, flag array and receive buffer into
+    this process (CUDA IPC) for `dp_peer_update`; from here on the product whose result is the
+    statistics area of `pack` delivers its column panels to their owners' receive buffers.  group: a `rendezvous.Group` (the handles travel through it).
     Returns True when EVERY rank has mapped every peer; otherwise every rank has closed what it
     opened and gets False (the ranks agree, so that all of them fall back to the all-reduce)."""
     n = _lib.dp_peer_handle_bytes()
@@ -1216,11 +1217,14 @@ def dp_peer_setup(group, pack, w, w_aux):
         buf = ct.create_string_buffer(n)
         _check(_lib.dp_peer_export_flags(buf))
         mine += buf.raw
+        buf = ct.create_string_buffer(n)
+        _check(_lib.dp_peer_export_recv(ct.c_long(w.shape[0] * w.shape[1]), buf))
+        mine += buf.raw
     except CUDAMatException:
         mine = b""                              # told to the peers through the exchange itself
     payloads = group.exchange("peer_handles", mine)
     failed = 0.0
-    if any(len(x) != 4 * n for x in payloads):
+    if any(len(x) != 5 * n for x in payloads):
         failed = 1.0
     else:
         err = _lib.dp_peer_setup(ct.c_int(group.world), ct.c_int(group.rank), ct.c_char_p(b"".join(payloads)), pack.p_mat,
@@ -1234,6 +1238,11 @@ def dp_peer_setup(group, pack, w, w_aux):
 
 def dp_peer_close():
     _lib.dp_peer_close()
+
+
+def dp_peer_mode():
+    """0: not set up; 1: the owners fetch the statistics panels; 2: the statistics product delivers them."""
+    return _lib.dp_peer_mode()
 
 
 def dp_wait(timeout_ms=30000):

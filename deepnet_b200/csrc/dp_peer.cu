@@ -2,9 +2,12 @@
 //
 // With NCCL the update of a data-parallel step is: all-reduce of the packed statistics (every rank
 // ends up with all 268 MB of sums), then every rank applies the same update to its whole copy of W.
-// Here rank r owns the columns [r H/G, (r+1) H/G) of W.  Once every rank's statistics are in place,
-// r reads the G partial statistics of its columns (its own from local memory, the others' with
-// plain loads over NVLink), adds them in rank order, applies the momentum / decay update to its
+// Here rank r owns the columns [r H/G, (r+1) H/G) of W.  The statistics product itself delivers every
+// column panel to its owner: its epilogue stores the tiles of panel q into slot r of rank q's receive
+// buffer with plain stores over NVLink while the product runs (set_product_scatter in gemm_tc.cu; when
+// H/G is not a whole number of 256-column tiles the owners fetch the panels with plain loads instead).
+// Once every rank's statistics are in place, r adds the G partial statistics of its columns in rank
+// order (all of them in its own memory), applies the momentum / decay update to its
 // shard of W and of the update history, and stores the new shard (and its 16-bit planes) into EVERY
 // rank's copy of W with plain stores.  Each rank moves (G-1)/G of the statistics in and (G-1)/G
 // of W + planes out, in both directions of its links at once, instead of the all-reduce's two
@@ -17,6 +20,7 @@
 // bounded (b200_set_wait_limit); on expiry the kernel records a status word and returns.
 // No multimem, no TMA, no library kernel touches peer memory: plain ld / st in this file only.
 // The reference has no multi-GPU layer; nothing here has a counterpart there.
+#include <stdlib.h>
 #include <string.h>
 
 #include "gemm.cuh"
@@ -34,13 +38,18 @@ struct PeerCtx {
   float* w[kMaxRanks] = {nullptr};         // every rank's copy of W
   uint16_t* aux[kMaxRanks] = {nullptr};    // ... and of W's 16-bit planes (or null)
   int* flags[kMaxRanks] = {nullptr};       // every rank's flag array
+  float* recv[kMaxRanks] = {nullptr};      // every rank's receive buffer: G slots (one per sender) of one column panel each
+  float* own_recv = nullptr;
+  long recv_floats = 0;
+  bool push = false;                       // the statistics product delivers the panels (else the owners fetch them)
   int* own_flags = nullptr;
   unsigned* ticket = nullptr;
   int epoch = 0;
-  bool open[kMaxRanks][4] = {};
+  bool open[kMaxRanks][5] = {};
 } g;
 
 struct PeerPtrs {
+  const float* stat[kMaxRanks];   // rank q's statistics of THIS rank's panel, indexed like W (element e of W at stat[q][e])
   float* pack[kMaxRanks];
   float* w[kMaxRanks];
   uint16_t* aux[kMaxRanks];
@@ -113,7 +122,7 @@ __global__ void __launch_bounds__(256) k_peer_reduce_update(PeerPtrs pp, int nra
     const long e = first + (i << 2);
     float4 S = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < nranks; q++) {                        // rank order: the same sum whoever computes it
-      const float4 s = *reinterpret_cast<const float4*>(pp.pack[q] + e);
+      const float4 s = *reinterpret_cast<const float4*>(pp.stat[q] + e);
       S.x += s.x; S.y += s.y; S.z += s.z; S.w += s.w;
     }
     float4 W = *reinterpret_cast<const float4*>(pp.w[rank] + e);
@@ -200,9 +209,11 @@ __global__ void k_peer_finish(PeerPtrs pp, int nranks, int rank, int epoch, floa
   reinterpret_cast<unsigned*>(scale_state)[2] = 0u;
 }
 
-PeerPtrs ptrs() {
+PeerPtrs ptrs(long first, long shard) {
   PeerPtrs pp;
   for (int q = 0; q < kMaxRanks; q++) {
+    // delivered: slot q of the own receive buffer holds rank q's panel (shard floats); fetched: rank q's whole statistics
+    pp.stat[q] = g.push ? (g.own_recv ? g.own_recv + (long)q * shard - first : nullptr) : g.pack[q];
     pp.pack[q] = g.pack[q];
     pp.w[q] = g.w[q];
     pp.aux[q] = g.aux[q];
@@ -241,11 +252,36 @@ int dp_peer_export_flags(char* handle_out) {
   return 0;
 }
 
-// handles: for every rank q (in rank order) four handles {pack, W, W_aux, flags} as exported by that
-// rank (W_aux all zero when there is none).  Own entries are taken from the matrices passed here.
+// The receive buffer of this rank (created here: `floats` = elements of W; G slots of one column panel
+// each, slot r written by rank r's statistics product), exported like a matrix.
+int dp_peer_export_recv(long floats, char* handle_out) {
+  if (floats <= 0) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (g.own_recv && g.recv_floats != floats) {
+    cudaFree(g.own_recv);
+    g.own_recv = nullptr;
+  }
+  if (!g.own_recv) {
+    if (cudaMalloc(&g.own_recv, (size_t)floats * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      g.own_recv = nullptr;
+      return set_error("dp_peer: receive buffer allocation failed");
+    }
+    g.recv_floats = floats;
+  }
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, g.own_recv) != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+
+// handles: for every rank q (in rank order) five handles {pack, W, W_aux, flags, receive buffer} as
+// exported by that rank (W_aux all zero when there is none).  Own entries are taken from the matrices
+// passed here.  From here on the product whose result is the statistics area of `pack` (its first
+// rows(W) x cols(W) floats) delivers its column panels to their owners.
 int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cudamat* w, cudamat* w_aux) {
   if (nranks < 2 || nranks > kMaxRanks || rank < 0 || rank >= nranks) return ERROR_UNSUPPORTED;
-  if (!pack->on_device || !w->on_device || (w_aux && !w_aux->on_device) || !g.own_flags) return ERROR_NOT_ON_DEVICE;
+  if (!pack->on_device || !w->on_device || (w_aux && !w_aux->on_device) || !g.own_flags || !g.own_recv) return ERROR_NOT_ON_DEVICE;
+  if (g.recv_floats != numel(w) || w->size[1] % nranks != 0) return ERROR_INCOMPATIBLE_DIMENSIONS;
   const size_t hb = sizeof(cudaIpcMemHandle_t);
   g.nranks = nranks;
   g.rank = rank;
@@ -255,13 +291,14 @@ int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cuda
       g.w[q] = w->data_device;
       g.aux[q] = w_aux ? reinterpret_cast<uint16_t*>(w_aux->data_device) : nullptr;
       g.flags[q] = g.own_flags;
+      g.recv[q] = g.own_recv;
       continue;
     }
-    void* p[4] = {nullptr, nullptr, nullptr, nullptr};
-    for (int k = 0; k < 4; k++) {
+    void* p[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    for (int k = 0; k < 5; k++) {
       if (k == 2 && !w_aux) continue;
       cudaIpcMemHandle_t h;
-      memcpy(&h, handles + ((size_t)q * 4 + k) * hb, hb);
+      memcpy(&h, handles + ((size_t)q * 5 + k) * hb, hb);
       if (cudaIpcOpenMemHandle(&p[k], h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
         return set_error(cudaGetErrorString(cudaGetLastError()));
       g.open[q][k] = true;
@@ -270,9 +307,20 @@ int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cuda
     g.w[q] = (float*)p[1];
     g.aux[q] = (uint16_t*)p[2];
     g.flags[q] = (int*)p[3];
+    g.recv[q] = (float*)p[4];
   }
   g.epoch = 0;
-  return 0;
+  // whole 256-column tiles per panel: the statistics product delivers them; otherwise the owners fetch
+  const int cols = w->size[1] / nranks;
+  const long shard = (long)w->size[0] * cols;
+  const char* pv = getenv("B200_DP_PEER_PUSH");      // 0: the owners fetch (measurements)
+  g.push = cols % 256 == 0 && (!pv || atoi(pv) != 0);
+  if (g.push) {
+    float* targets[kMaxRanks];
+    for (int q = 0; q < nranks; q++) targets[q] = g.recv[q] + (long)rank * shard;   // this rank's slot at owner q
+    return set_product_scatter(pack->data_device, targets, nranks, cols);
+  }
+  return set_product_scatter(nullptr, nullptr, 0, 0);
 }
 
 // One data-parallel update without NCCL: statistics -> parameters on every rank (see the top of this
@@ -289,7 +337,7 @@ int dp_peer_update(cudamat* w, cudamat* delta, cudamat* w_aux, cudamat* w_scale,
   const int mode = !w_aux ? 0 : (w_scale ? 2 : 1);
   const long shard = (long)rows * (cols / g.nranks), first = shard * g.rank;
   const int epoch = ++g.epoch;
-  const PeerPtrs pp = ptrs();
+  const PeerPtrs pp = ptrs(first, shard);
   // waits on other ranks get sixteen times the limit of a wait inside one kernel (about half a
   // minute by default): a rank may be late by a host hiccup, which an in-kernel wait never sees
   const unsigned long long lim64 = (unsigned long long)wait_limit() * 16ull;
@@ -311,11 +359,16 @@ int dp_peer_update(cudamat* w, cudamat* delta, cudamat* w_aux, cudamat* w_scale,
   return rewrite_f16_planes_if(w->data_device, reinterpret_cast<uint16_t*>(w_aux->data_device), rows, numel(w), sp, sp + 3);
 }
 
+// 0: not set up; 1: the owners fetch the statistics panels; 2: the statistics product delivers them.
+int dp_peer_mode() { return g.nranks < 2 ? 0 : (g.push ? 2 : 1); }
+
 int dp_peer_close() {
+  set_product_scatter(nullptr, nullptr, 0, 0);
+  g.push = false;
   for (int q = 0; q < g.nranks; q++) {
     if (q == g.rank) continue;
-    void* p[4] = {g.pack[q], g.w[q], g.aux[q], g.flags[q]};
-    for (int k = 0; k < 4; k++)
+    void* p[5] = {g.pack[q], g.w[q], g.aux[q], g.flags[q], g.recv[q]};
+    for (int k = 0; k < 5; k++)
       if (g.open[q][k] && p[k]) {
         cudaIpcCloseMemHandle(p[k]);
         g.open[q][k] = false;

@@ -84,6 +84,11 @@ struct GemmProblem {
 // second pass of an update whose exponent had to change.
 int rewrite_f16_planes_if(const float* x, uint16_t* aux, int rows, long n, const float* exp_dev, const float* only_if);
 
+// From now on a tensor-core product whose result is `match` stores columns [q * cols, (q + 1) * cols)
+// of it to out[q] instead (same row layout), q < n; n = 0 ends it.  The data-parallel step registers
+// the peers' receive buffers here, so that its statistics reach their owners while the product runs.
+int set_product_scatter(const float* match, float* const* out, int n, int cols);
+bool product_is_scattered(const float* out);
 int gemm_simt(const GemmProblem& g);
 // Returns ERROR_UNSUPPORTED when an operand is not addressable by TMA (leading
 // dimension not a multiple of 4 floats or base not 16-byte aligned).

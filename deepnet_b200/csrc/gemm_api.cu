@@ -31,6 +31,7 @@ inline bool aux_shape_ok(const cudamat* aux, const cudamat* m) {
 }
 
 int run(const GemmProblem& g) {
+  if (product_is_scattered(g.epi.out)) return gemm_tc(g);   // (fails loudly when the tensor-core kernel cannot take it)
   if (g_path == 2) return gemm_simt(g);
   if (gemm_tc_supported(g)) {
     const int r = gemm_tc(g);

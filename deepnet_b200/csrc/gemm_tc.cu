@@ -95,6 +95,7 @@ struct TcGroup {
 };
 
 constexpr int kMaxGroups = 4;   // pairs of operand matrices in one product (a DBM layer update and the statistics have two)
+constexpr int kMaxScatter = 8;
 constexpr int kMaxMaps = 16;    // tensor maps: operand tiles as loaded, then the outputs an activation epilogue stores
 
 struct TcParams {
@@ -116,6 +117,12 @@ struct TcParams {
                            //    staging, barriers or TMA stores, whose latency otherwise keeps the epilogue warps
                            //    from draining the next tile's first chunk in time
   GemmEpilogue epi;
+  // Column panels of a plain result delivered to other GPUs (scatter_cols > 0): columns
+  // [q * scatter_cols, (q + 1) * scatter_cols) go to scatter[q] (columns ldo apart, as epi.out) with
+  // plain stores, over NVLink when scatter[q] is peer memory: the reduce-scatter of the data-parallel
+  // statistics happens while the product runs (dp_peer.cu).  A tile never straddles two panels.
+  float* scatter[kMaxScatter];
+  int scatter_cols;
   int out_map[kOutArrays];   // tensor maps (indices into maps) of the outputs stored by TMA; -1 = absent
   int* status;
   uint32_t spin_limit;       // iterations a wait may spin before the kernel gives up (b200_set_wait_limit)
@@ -920,7 +927,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       const int nc = tn * BN + col_base;
       if (m < pM && nc < pN) {
         if (epi_is_plain(kEpi)) {
-          float* const out = e.out + (long)sp * p.split_stride + (long)nc * e.ldo + m;
+          float* out = e.out + (long)sp * p.split_stride + (long)nc * e.ldo + m;
+          if (kEpi == kEpiPlain && p.scatter_cols > 0) {
+            const int owner = nc / p.scatter_cols;
+            out = p.scatter[owner] + (long)(nc - owner * p.scatter_cols) * e.ldo + m;
+          }
           const float alpha = e.alpha, beta = e.beta;
           const long ldo = e.ldo;
           const int ncols = pN - nc < COLS ? pN - nc : COLS;
@@ -1362,11 +1373,29 @@ struct HostTimes {
 static HostTimes g_host_times;
 #endif
 
+// Scatter registration (dp_peer.cu): products whose result is `match` deliver column panels to `out`.
+static const float* g_scatter_match = nullptr;
+static float* g_scatter_out[kMaxScatter] = {nullptr};
+static int g_scatter_n = 0, g_scatter_cols = 0;
+
+int set_product_scatter(const float* match, float* const* out, int n, int cols) {
+  if (n < 0 || n > kMaxScatter || (n > 0 && (!match || cols <= 0))) return ERROR_UNSUPPORTED;
+  g_scatter_match = n > 0 ? match : nullptr;
+  g_scatter_n = n;
+  g_scatter_cols = n > 0 ? cols : 0;
+  for (int i = 0; i < n; i++) g_scatter_out[i] = out[i];
+  return 0;
+}
+
+bool product_is_scattered(const float* out) { return g_scatter_n > 0 && out != nullptr && out == g_scatter_match; }
+
 int gemm_tc(const GemmProblem& g) {
 #ifdef B200_HOST_TIMING
   const double t_begin = HostTimes::now();
 #endif
-  if (!gemm_tc_supported(g)) return ERROR_UNSUPPORTED;
+  const bool scatter = g_scatter_n > 0 && g.epi.out != nullptr && g.epi.out == g_scatter_match;
+  if (!gemm_tc_supported(g))
+    return scatter ? set_error("a product whose result is scattered to peers must run on the tensor cores") : ERROR_UNSUPPORTED;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
   static int pair_mode = -1;   // B200_GEMM_2CTA=0 keeps one CTA per tile
   static int chunk_k = 0;
@@ -1572,6 +1601,7 @@ int gemm_tc(const GemmProblem& g) {
     } else if (g_split_mode > 1) {
       want = g_split_mode < min_ki ? g_split_mode : min_ki;
     }
+    if (scatter) want = 1;   // a partial is not a result: the panels go out whole
     if (want > 1) {
       float* ws = (float*)workspace(2, (size_t)want * g.M * g.N * sizeof(float));
       if (!ws) return CUDA_ERROR;
@@ -1597,6 +1627,14 @@ int gemm_tc(const GemmProblem& g) {
     if (e.activation == 1 && (e.sample || e.sample_aux)) epi = kEpiSigSample;
     else if (e.activation == 1 && !e.sample && !e.sample_aux) epi = kEpiSig;
     else if (e.activation == 0 && !e.sample && !e.sample_aux) epi = kEpiLin;
+  }
+  p.scatter_cols = 0;
+  if (scatter) {
+    // whole tiles per panel, the plain epilogue, no split (a partial is not a result), nothing added to old contents
+    if (epi != kEpiPlain || p.splits != 1 || e.beta != 0.0f || g.N != g_scatter_n * g_scatter_cols || g_scatter_cols % BN != 0)
+      return set_error("a product whose result is scattered to peers must be plain, unsplit, with whole tiles per panel");
+    for (int i = 0; i < g_scatter_n; i++) p.scatter[i] = g_scatter_out[i];
+    p.scatter_cols = g_scatter_cols;
   }
   static int store16_mode = -1;
   if (store16_mode < 0) {

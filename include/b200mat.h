@@ -338,22 +338,29 @@ int dp_abort(void);
 /* The all-reduce on a side stream, beside the kernels that follow on the library stream: begin waits
  * for what is enqueued so far and starts it (slot 0..7, one pending all-reduce each); end makes the
  * library stream wait for it. */
-/* The exchange and the update of a data-parallel step as one pass over peer memory, without NCCL:
- * rank r owns the columns [r H/G, (r+1) H/G) of W; once every rank's statistics are complete it reads
- * the G partial statistics of its columns (plain loads over NVLink), applies the momentum / decay
- * update to its shard and stores the new shard and its 16-bit planes into every rank's copy of W.
- * Bring-up: every rank exports {pack, W, W_aux, flags} (dp_peer_export / dp_peer_export_flags,
- * dp_peer_handle_bytes() bytes each), the ranks exchange them by any host channel and call
- * dp_peer_setup with all of them in rank order; then dp_peer_update once per update on every rank
- * (pack = [W statistics | b_v | b_h] of this rank, b / db the packed biases and their history).
- * Waits are bounded (b200_set_wait_limit; b200_read_status tells).  H must be a multiple of G. */
+/* The exchange and the update of a data-parallel step over peer memory, without NCCL: rank r owns the
+ * columns [r H/G, (r+1) H/G) of W.  The statistics product itself (the fused_gemm whose result is the
+ * first rows(W) x cols(W) floats of `pack`) delivers every column panel to its owner: its epilogue
+ * stores the tiles of panel q into rank q's receive buffer with plain stores over NVLink while the
+ * product runs (when H/G is not a multiple of 256 the owners fetch the panels with plain loads
+ * instead).  Once every rank's statistics are complete the owner adds the G partial statistics of its
+ * columns, applies the momentum / decay update to its shard and stores the new shard and its 16-bit
+ * planes into every rank's copy of W.
+ * Bring-up: every rank exports {pack, W, W_aux, flags, receive buffer} (dp_peer_export,
+ * dp_peer_export_flags, dp_peer_export_recv(elements of W, ...); dp_peer_handle_bytes() bytes each), the
+ * ranks exchange them by any host channel and call dp_peer_setup with all of them in rank order; then
+ * dp_peer_update once per update on every rank (pack = [W statistics | b_v | b_h] of this rank, b / db
+ * the packed biases and their history).  Waits are bounded (b200_set_wait_limit; b200_read_status
+ * tells).  H must be a multiple of G. */
 int dp_peer_handle_bytes(void);
 int dp_peer_export(cudamat* m, char* handle_out);
 int dp_peer_export_flags(char* handle_out);
+int dp_peer_export_recv(long floats, char* handle_out);
 int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cudamat* w, cudamat* w_aux);
 int dp_peer_update(cudamat* w, cudamat* delta, cudamat* w_aux, cudamat* w_scale, cudamat* pack, cudamat* b, cudamat* db,
                    float inv_batch, float mom_b, float eps_b, float mom_w, float eps_w, float l2, float l1);
 int dp_peer_close(void);
+int dp_peer_mode(void);                  /* 0 not set up, 1 owners fetch the panels, 2 the statistics product delivers them */
 int dp_allreduce_begin(cudamat* mat, int slot);
 int dp_allreduce_end(int slot);
 /* Waits (at most timeout_ms) for the work enqueued on the library stream, collectives included; on

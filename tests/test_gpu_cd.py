@@ -85,6 +85,8 @@ def test_replicated_softmax_step_matches_oracle(cm, oracle, scale):
 @pytest.mark.parametrize("config,scale,cases,form,gibbs", [
     (0, 0.25, 300, "derived", 1), (1, 0.0625, 768, "derived", 1), (0, 1.0, 200, "derived", 1),
     (0, 0.25, 300, "bf16 aux", 1), (0, 0.25, 300, "f16", 1), (0, 1.0, 200, "f16", 1),
+    # 804 visible units: the 16-bit planes of a column are padded to 808 rows
+    (0, 1.024, 300, "f16", 1), (0, 1.024, 300, "bf16 aux", 1),
     # configuration 1 at its full size (1024 x 4096, batch 256)
     (1, 1.0, 512, "derived", 1), (1, 1.0, 512, "bf16 aux", 1),
     # CD-k with k > 1: the intermediate Gibbs steps store only what the next product reads

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.parametrize("form,scale,peer", [("derived", 0.5, 0), ("f16", 0.5, 0), ("f16", 0.512, 0), ("derived", 0.512, 1),
-                                             ("f16", 0.512, 1)])
+                                             ("f16", 0.512, 1), ("derived", 1.02, 1), ("f16", 1.02, 1)])
 def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, peer, monkeypatch):
     if cm._lib.b200_device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -45,6 +45,12 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, peer, monkeypat
     r0, r1 = (np.load(os.path.join(tmp_path, "rank%d.npz" % r)) for r in range(2))
     assert int(r0["status"]) == 0 and int(r1["status"]) == 0
     assert int(r0["peer"]) == peer and int(r1["peer"]) == peer
+    # 512 hidden units (scale 1.02) are one 256-column tile per rank: the statistics product delivers
+    # the panels to their owners itself; 256 units (0.512) are half a tile each: the owners fetch them
+    # (800 x 512, not 804 x 512: there one draw of the second update has its uniform within 1e-7 of its
+    # probability and falls differently on one GPU and on two, whose sums differ in the last bit)
+    want_mode = 0 if not peer else (2 if scale == 1.02 else 1)
+    assert int(r0["peer_mode"]) == want_mode and int(r1["peer_mode"]) == want_mode
     assert np.array_equal(r0["W"], r1["W"])                 # replicas stay bit-identical
 
     from deepnet_b200 import configs
