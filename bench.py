@@ -376,9 +376,9 @@ def run_ours(args):
                    roofline=roofline, kernels=kernels, mean_sq_error_per_case=round(loss, 4), device_status=status)
         if replicas_identical is not None:
             out["replicas_identical"] = replicas_identical
+    if hasattr(eng, "close"):
+        eng.close(group)                 # (peer-memory exchange: unmapped only when no rank can still store into a replica)
     group.barrier()
-    if getattr(eng, "dp_peer", False):
-        cm.dp_peer_close()
     group.close()
     if rank == 0 and world == 1 and config == 4 and not args.no_other_configs:
         # the other configurations of the benchmark set, a few updates each (1 GPU)

@@ -470,3 +470,16 @@ class FusedRBM(object):
         if reset:
             self.loss_acc.assign(0)
         return v
+
+    def close(self, group=None):
+        """Ends the peer-memory exchange (if this engine set it up): waits for the enqueued work, meets
+        the other ranks (nobody unmaps a replica while a peer may still store into it; pass the group
+        for that), unmaps the peers and stops the delivery of the statistics panels.  Call it before
+        the engine's matrices are freed; the all-reduce form needs no closing."""
+        if not self.dp_peer:
+            return
+        self.cm.cuda_sync_threads()
+        if group is not None:
+            group.barrier()
+        self.cm.dp_peer_close()
+        self.dp_peer = False

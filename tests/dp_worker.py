@@ -36,8 +36,7 @@ def main():
     cm.dp_check()
     np.savez(os.path.join(tmp, "rank%d.npz" % rank), W=np.array(eng.W.asarray()), hs=np.array(eng.h_samp.asarray()),
              loss=eng.read_loss(), status=cm.read_status(), peer=int(eng.dp_peer), peer_mode=cm.dp_peer_mode())
-    group.barrier()          # nobody unmaps a peer's memory while another rank may still write to it
-    cm.dp_peer_close()
+    eng.close(group)         # nobody unmaps a peer's memory while another rank may still write to it
     cm.dp_destroy()          # leaves only after its last collective has completed
 
 
