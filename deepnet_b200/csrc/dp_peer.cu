@@ -309,7 +309,11 @@ int dp_peer_setup(int nranks, int rank, const char* handles, cudamat* pack, cuda
     g.flags[q] = (int*)p[3];
     g.recv[q] = (float*)p[4];
   }
+  // a second set-up in one process starts from clean flags (the peers write into them only after the
+  // host barrier that precedes the first update, and the previous user closed behind a barrier)
   g.epoch = 0;
+  if (cudaMemset(g.own_flags, 0, kFlagInts * sizeof(int)) != cudaSuccess || cudaMemset(g.ticket, 0, sizeof(unsigned)) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
   // whole 256-column tiles per panel: the statistics product delivers them; otherwise the owners fetch
   const int cols = w->size[1] / nranks;
   const long shard = (long)w->size[0] * cols;
