@@ -344,7 +344,10 @@ def run_ours(args):
             cm.prefetch_fence()
             stage[(s + 1) & 1].prefetch_from_pinned(host[(s + 1) & 1][1], nbytes)
         eng.TrainOneBatch(ramp + args.warmup + 2 * args.steps + s, stage[s & 1])
-        eng.read_loss()                                     # device -> host, every step
+        eng.loss_begin(s & 1)                               # device -> host, every step, behind the update
+        if s > 0:
+            eng.loss_end((s - 1) & 1)                       # the previous update's loss has arrived
+    eng.loss_end((e2e_steps - 1) & 1)
     f1.record()
     e2e_ms = group.max(f0.elapsed_ms(f1))
     e2e_value = e2e_steps * B * world / (e2e_ms * 1e-3)
@@ -379,7 +382,10 @@ def run_ours(args):
                 stagep[(s + 1) & 1].prefetch_from_pinned(hostp[(s + 1) & 1][1], pbytes)
             cm.feed_gather(stagep[s & 1], True, V, (0, 0), False, 0, batch, out_aux=batch_aux, aux_mode=2, aux_exp=14)
             eng.TrainOneBatch(ramp + args.warmup + 3 * args.steps + s, batch, batch_aux)
-            eng.read_loss()
+            eng.loss_begin(s & 1)
+            if s > 0:
+                eng.loss_end((s - 1) & 1)
+        eng.loss_end((e2e_steps - 1) & 1)
         p1.record()
         pms = group.max(p0.elapsed_ms(p1))
         e2e_packed = dict(value=round(e2e_steps * B * world / (pms * 1e-3), 1), unit=UNIT, h2d_bytes_per_step=pbytes,

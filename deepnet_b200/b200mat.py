@@ -1165,6 +1165,16 @@ def host_alloc(shape):
     return arr, ptr
 
 
+def readback_begin(src, host_ptr, nbytes, slot=0):
+    """Starts a device-to-host copy of `src` into pinned host memory, ordered after the work enqueued so
+    far, without blocking (slot 0..7); `readback_wait(slot)` blocks until it has landed."""
+    _check(_lib.b200_readback_begin(src.p_mat, ct.c_void_p(host_ptr), ct.c_size_t(nbytes), ct.c_int(slot)))
+
+
+def readback_wait(slot=0):
+    _check(_lib.b200_readback_wait(ct.c_int(slot)))
+
+
 def prefetch_wait():
     _check(_lib.b200_prefetch_wait())
 

@@ -385,6 +385,36 @@ int b200_prefetch_fence() {
   return 0;
 }
 
+// Device-to-host read-back that does not stall the issuing thread: the copy is ordered after the
+// work enqueued so far on the library stream and runs on a stream of its own (slot 0..7, one pending
+// read-back each); b200_readback_wait blocks until the copy of that slot has landed.  `dst` is pinned
+// host memory (b200_host_alloc); `src` must not be rewritten before the copy has run - read back a
+// copy of a value that later work changes.  No counterpart in the reference.
+static cudaStream_t g_rb_stream = nullptr;
+static cudaEvent_t g_rb_ready[8] = {nullptr}, g_rb_done[8] = {nullptr};
+int b200_readback_begin(cudamat* src, void* dst, size_t bytes, int slot) {
+  if (!src->on_device) return ERROR_NOT_ON_DEVICE;
+  if (slot < 0 || slot >= 8 || !dst) return ERROR_UNSUPPORTED;
+  if (bytes > (size_t)numel(src) * sizeof(float)) return ERROR_INCOMPATIBLE_DIMENSIONS;
+  if (!initialised()) return CUDA_ERROR;
+  if (!g_rb_stream && cudaStreamCreateWithFlags(&g_rb_stream, cudaStreamNonBlocking) != cudaSuccess)
+    return set_error("read-back stream creation failed");
+  if (!g_rb_ready[slot] && (cudaEventCreateWithFlags(&g_rb_ready[slot], cudaEventDisableTiming) != cudaSuccess ||
+                            cudaEventCreateWithFlags(&g_rb_done[slot], cudaEventDisableTiming) != cudaSuccess))
+    return set_error("read-back event creation failed");
+  if (cudaEventRecord(g_rb_ready[slot], stream()) != cudaSuccess ||
+      cudaStreamWaitEvent(g_rb_stream, g_rb_ready[slot], 0) != cudaSuccess ||
+      cudaMemcpyAsync(dst, src->data_device, bytes, cudaMemcpyDeviceToHost, g_rb_stream) != cudaSuccess ||
+      cudaEventRecord(g_rb_done[slot], g_rb_stream) != cudaSuccess)
+    return set_error(cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
+int b200_readback_wait(int slot) {
+  if (slot < 0 || slot >= 8 || !g_rb_done[slot]) return ERROR_UNSUPPORTED;
+  if (cudaEventSynchronize(g_rb_done[slot]) != cudaSuccess) return set_error(cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
+
 void* b200_host_alloc(size_t bytes) {
   void* p = nullptr;
   if (cudaMallocHost(&p, bytes) != cudaSuccess) {

@@ -15,9 +15,10 @@ import os
 import numpy as np
 
 from .dbm import Parameter
+from .fused_rbm import LossReadback
 
 
-class FusedDBM(object):
+class FusedDBM(LossReadback):
     def __init__(self, cm, sizes, batchsize, weights, hyperparams, seed=0):
         """sizes = [visible, hidden1, ...]; weights[i] is sizes[i] x sizes[i+1]."""
         self.cm, self.sizes, self.B, self.hyp = cm, list(sizes), batchsize, hyperparams

@@ -34,7 +34,28 @@ import numpy as np
 from .dbm import LINEAR, LOGISTIC, REPLICATED_SOFTMAX, Parameter
 
 
-class FusedRBM(object):
+class LossReadback(object):
+    """The accumulated loss of an engine (`self.loss_acc`) read back without stalling the thread that
+    issues the updates: `loss_begin(slot)` after an update copies the accumulator aside, clears it and
+    starts a device-to-host copy behind the enqueued work; `loss_end(slot)` - an update or more later -
+    returns the value.  Two slots let the loss of update n travel while update n + 1 is issued."""
+
+    def loss_begin(self, slot=0):
+        cm = self.cm
+        if getattr(self, "_loss_host", None) is None:
+            self._loss_host = cm.host_alloc((8, 1))
+            self._loss_dev = cm.empty((1, 8))
+        keep = self._loss_dev.slice(slot, slot + 1)
+        keep.assign(self.loss_acc)
+        self.loss_acc.assign(0)
+        cm.readback_begin(keep, self._loss_host[1] + 4 * slot, 4, slot)
+
+    def loss_end(self, slot=0):
+        self.cm.readback_wait(slot)
+        return float(self._loss_host[0][slot, 0])
+
+
+class FusedRBM(LossReadback):
     def __init__(self, cm, V, H, batchsize, weight, hyperparams, edge_hyperparams=None, visible=LOGISTIC,
                  binary_data=False, bias_v=None, bias_h=None, seed=0, world_size=1, rank=0, group=None):
         """binary_data: the caller states that every input is exactly 0 or 1 (or, for word counts, a

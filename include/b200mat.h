@@ -325,6 +325,10 @@ int copy_from_host_ptr(cudamat* mat, const float* src, size_t bytes);  /* async 
 int b200_prefetch(cudamat* mat, const float* src, size_t bytes);       /* H2D on a second (copy) stream */
 int b200_prefetch_wait(void);             /* library stream waits for the copies started so far */
 int b200_prefetch_fence(void);            /* later copies wait for work already enqueued */
+/* Device-to-host read-back on a stream of its own, ordered after the work enqueued so far (slot 0..7,
+ * one pending read-back each); dst is pinned host memory; b200_readback_wait blocks until it has landed. */
+int b200_readback_begin(cudamat* src, void* dst, size_t bytes, int slot);
+int b200_readback_wait(int slot);
 
 /* Data parallelism over NCCL: one process per GPU. */
 int dp_unique_id(char* out128);

@@ -544,3 +544,29 @@ def test_fused_softmax_and_categorical_draw_match_the_call_sequence(cm, oracle, 
     # activation only: no sampling call consumed
     cm.CUDAMatrix(pre).softmax_sample(g_state, None)
     assert cm.CUDAMatrix.rnd_state.calls == 1
+
+
+def test_loss_read_back_behind_the_updates(cm):
+    """loss_begin / loss_end hand back every update's loss one update later, without a blocking read
+    in between: the same numbers as read_loss after each update."""
+    cfg = configs.build(0, cases=400, dims_scale=0.25)
+    B = cfg["batchsize"]
+    V, H = cfg["layers"][0]["numdims"], cfg["layers"][1]["numdims"]
+    data_host = cfg["data"]
+    want, got = [], []
+    for mode in ("blocking", "behind"):
+        eng = FusedRBM(cm, V, H, B, cfg["edges"][0]["weight"], cfg["hyperparams"],
+                       edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"])
+        data = cm.CUDAMatrix(data_host)
+        for step in range(4):
+            eng.TrainOneBatch(step, data.slice(step * B, (step + 1) * B))
+            if mode == "blocking":
+                want.append(eng.read_loss())
+            else:
+                eng.loss_begin(step & 1)
+                if step > 0:
+                    got.append(eng.loss_end((step - 1) & 1))
+        if mode == "behind":
+            got.append(eng.loss_end(3 & 1))
+    assert got == want
+    assert cm.read_status() == 0
