@@ -29,6 +29,24 @@ def main():
                    edge_hyperparams=cfg["edges"][0].get("hyperparams"), binary_data=True, seed=cfg["seed"], world_size=world,
                    rank=rank, group=group)
     data = cm.CUDAMatrix(cfg["data"])
+    if len(sys.argv) > 5 and sys.argv[5] == "absent":
+        # Failure detection: rank 1 is alive but never enqueues its update (it left between updates, no
+        # kernel of its in flight).  Rank 0's update waits for rank 1's statistics with a short limit,
+        # gives up by itself and leaves a status word; its context stays usable.
+        status, usable = 0, True
+        if rank == 1:
+            group.barrier()                     # (the host barrier that opens rank 0's first update)
+        else:
+            cm.set_wait_limit(20000)            # peer waits: sixteen times that, a fraction of a second
+            eng.TrainOneBatch(0, data.slice(0, b))
+            status = cm.read_status()           # blocks until the kernels have returned by themselves
+            cm.set_wait_limit(0)
+            a = np.random.default_rng(0).standard_normal((64, 64)).astype(np.float32)
+            usable = bool(np.allclose(np.array(cm.dot(cm.CUDAMatrix(a), cm.CUDAMatrix(a)).asarray()), a @ a, atol=1e-3))
+        np.savez(os.path.join(tmp, "rank%d.npz" % rank), status=status, usable=usable, peer=int(eng.dp_peer))
+        eng.close(group)
+        cm.dp_destroy()
+        return
     for step in range(3):
         s = step * gb + rank * b
         eng.TrainOneBatch(step, data.slice(s, s + b))

@@ -71,3 +71,26 @@ def test_two_gpu_shards_match_one_gpu(cm, tmp_path, form, scale, peer, monkeypat
     assert np.array_equal(np.concatenate([r0["hs"], r1["hs"]], axis=1), hs)
     total = eng.read_loss()
     assert abs(float(r0["loss"]) + float(r1["loss"]) - total) < 1e-5 * total
+
+
+def test_a_rank_that_does_not_join_makes_the_peer_wait_run_out(cm, tmp_path):
+    """Failure detection without a fault: rank 1 stays alive but never enqueues its update; rank 0's
+    update waits for rank 1's statistics under a short limit, its kernels return by themselves, the
+    status word says which wait gave up (21: statistics never became ready) and the context still works."""
+    if cm._lib.b200_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_DP_PEER="1")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), str(r), "2", str(tmp_path), "1.02", "absent"],
+                              env=env) for r in range(2)]
+    try:
+        codes = [p.wait(timeout=300) for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+                p.wait()
+    assert codes == [0, 0]
+    r0 = np.load(os.path.join(tmp_path, "rank0.npz"))
+    assert int(r0["peer"]) == 1
+    assert int(r0["status"]) in (21, 22)
+    assert bool(r0["usable"])
