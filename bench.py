@@ -13,7 +13,7 @@ instrumentation).  `e2e` feeds every update from pinned host memory and reads th
 
 `--impl reference` times the CPU restatement of the reference's eigenmat path (the
 oracle: the reference's own C++ needs Eigen, which is not available, so it cannot be
-built) on the host cores, on a bounded sample of the same workload, in a child process
+built) on the host cores, on a bounded sample of the same workload (the same batch and layer sizes, a few updates), in a child process
 whose thread count is set explicitly.  Prints ONE JSON line on rank 0.
 """
 import argparse
@@ -485,9 +485,13 @@ def cpu_arm(config, sample_batch, steps, warmup, threads):
     return r
 
 
-def cpu_sample_batch(config):
+def cpu_sample_batch(config, one_thread=False):
+    """The configuration's own minibatch (4096 cases at config 4: one CD-10 update is 12.6 TFLOP, a quarter
+    of a minute on 16 host threads); the single-thread figure of config 4 is taken on 256 cases."""
     from deepnet_b200 import configs
-    return 256 if config == 4 else configs.build(config, cases=4)["batchsize"]
+    if config == 4:
+        return 256 if one_thread else 4096
+    return configs.build(config, cases=4)["batchsize"]
 
 
 def run_reference(args):
@@ -541,16 +545,17 @@ def main():
         return
     if args.gpus == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
-        sample_batch = cpu_sample_batch(args.config)
-        r = cpu_arm(args.config, sample_batch, 1, 1, cores)
-        one = cpu_arm(args.config, sample_batch, 1, 1 if args.config != 4 else 0, 1)
-        what = "1 timed CD-%d update at batch %d (full layer sizes)" % (r["gibbs_steps"], sample_batch)
+        sample_batch, one_batch = cpu_sample_batch(args.config), cpu_sample_batch(args.config, one_thread=True)
+        warm = 0 if args.config == 4 else 1          # (one update of config 4 is already 15-35 s of CPU work)
+        r = cpu_arm(args.config, sample_batch, 1, warm, cores)
+        one = cpu_arm(args.config, one_batch, 1, warm, 1)
+        what = "1 timed CD-%d update at batch %%d (full layer sizes)" % r["gibbs_steps"]
         out["cpu_baseline"] = dict(
             value=round(r["rate"], 2), unit=UNIT, cores=r["threads"], kind="port",
-            sample="%s, %.1f s on %d threads" % (what, r["dt"], r["threads"]),
+            sample="%s, %.1f s on %d threads" % (what % sample_batch, r["dt"], r["threads"]),
             # the reference's own build never enables OpenMP (eigenmat/Makefile): its path runs on one thread
             one_thread=dict(value=round(one["rate"], 2), unit=UNIT, cores=one["threads"],
-                            sample="%s, %.1f s on 1 thread" % (what, one["dt"])))
+                            sample="%s, %.1f s on 1 thread" % (what % one_batch, one["dt"])))
     print(json.dumps(out), flush=True)
 
 
