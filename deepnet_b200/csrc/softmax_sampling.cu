@@ -79,7 +79,13 @@ __global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restr
   for (int blk = first_blk + blockIdx.x; ndraws > 0 && blk <= last_blk; blk += gridDim.x) {
     float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     int bi[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
-    for (int r = threadIdx.x; r < h; r += blockDim.x) {
+    // The first words are raced in full; the best value any thread has then seen is a lower bound of
+    // the winner's, and most of the remaining words cannot reach it: v = -p / log u > bound needs
+    // -log u < p / bound, and -log u >= 1 - u, so a word with 1 - u >= (p / bound)(1 + 2e-6) is out
+    // without its logarithm and division (the margin covers the rounding of either side; ties are
+    // never skipped).  What is raced in full, and its outcome, are those of the plain loop.
+    const int seed_rows = h < 2 * (int)blockDim.x ? h : 2 * (int)blockDim.x;
+    for (int r = threadIdx.x; r < seed_rows; r += blockDim.x) {
       const uint4 wd = philox4x32_10((uint32_t)r, (uint32_t)blk, key);
       const float pr = p[r];
       const float u[4] = {word_to_uniform(wd.x), word_to_uniform(wd.y), word_to_uniform(wd.z), word_to_uniform(wd.w)};
@@ -89,6 +95,47 @@ __global__ void __launch_bounds__(256) k_sample_multinomial(const float* __restr
         if (v > bv[j] || (v == bv[j] && r < bi[j])) {
           bv[j] = v;
           bi[j] = r;
+        }
+      }
+    }
+    float inv[4];                                 // (1 + 2e-6) / bound, or 0: no usable bound for this draw
+    {
+      float lb[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        lb[j] = bv[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lb[j] = fmaxf(lb[j], __shfl_xor_sync(0xffffffffu, lb[j], o));
+      }
+      __syncthreads();                            // (sv is free: the previous block of draws has been read)
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) sv[j][wid] = lb[j];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float m = sv[j][0];
+        for (int k = 1; k < (int)(blockDim.x >> 5); k++) m = fmaxf(m, sv[j][k]);
+        inv[j] = (m > 0.0f && m < INFINITY) ? 1.000002f / m : 0.0f;
+      }
+      __syncthreads();                            // sv is written again below
+    }
+    for (int r = seed_rows + threadIdx.x; r < h; r += blockDim.x) {
+      const uint4 wd = philox4x32_10((uint32_t)r, (uint32_t)blk, key);
+      const float pr = p[r];
+      const float u[4] = {word_to_uniform(wd.x), word_to_uniform(wd.y), word_to_uniform(wd.z), word_to_uniform(wd.w)};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (inv[j] > 0.0f && 1.0f - u[j] >= pr * inv[j]) continue;   // cannot reach the bound (NaN compares false: raced)
+        const float v = -pr / logf(u[j]);
+        if (v > bv[j] || (v == bv[j] && r < bi[j])) {
+          bv[j] = v;
+          bi[j] = r;
+          if (v > 0.0f && v < INFINITY) {            // a better bound of this thread's own
+            const float c = 1.000002f / v;
+            if (inv[j] == 0.0f || c < inv[j]) inv[j] = c;
+          }
         }
       }
     }
