@@ -496,8 +496,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
   // k-blocks of group q that split s multiplies (all of them when the product is not split)
   auto split_range = [&](int q, int s, int& kb0, int& kb1) {
     const int ki = p.group[q].k_iters;
-    kb0 = (int)(((long)ki * s) / splits);
-    kb1 = (int)(((long)ki * (s + 1)) / splits);
+    kb0 = (int)(((unsigned)ki * (unsigned)s) / (unsigned)splits);          // (k-blocks x splits stays far below 2^32)
+    kb1 = (int)(((unsigned)ki * (unsigned)(s + 1)) / (unsigned)splits);
   };
   auto item_k_iters = [&](int s) {
     int n = 0;
@@ -935,14 +935,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
           const float alpha = e.alpha, beta = e.beta;
           const long ldo = e.ldo;
           const int ncols = pN - nc < COLS ? pN - nc : COLS;
-          if (beta == 0.0f) {
+          // a real loop over batches of 16 columns (the accumulator registers shifted down after each):
+          // a product of one tile runs this code once, straight from a cold instruction cache
+#pragma unroll 1
+          for (int go = 0; go < COLS / 16; go++) {
+            float* const o16 = out + (long)(16 * go) * ldo;
+            const int left = ncols - 16 * go;
+            if (beta == 0.0f) {
 #pragma unroll
-            for (int j = 0; j < COLS; j++)
-              if (j < ncols) out[j * ldo] = alpha * accum[j];
-          } else {
+              for (int j = 0; j < 16; j++)
+                if (j < left) o16[j * ldo] = alpha * accum[j];
+            } else {
 #pragma unroll
-            for (int j = 0; j < COLS; j++)
-              if (j < ncols) out[j * ldo] = alpha * accum[j] + beta * out[j * ldo];
+              for (int j = 0; j < 16; j++)
+                if (j < left) o16[j * ldo] = alpha * accum[j] + beta * o16[j * ldo];
+            }
+#pragma unroll
+            for (int i = 0; i + 16 < COLS; i++) accum[i] = accum[i + 16];
           }
         }
       }
