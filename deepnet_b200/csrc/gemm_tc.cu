@@ -1085,6 +1085,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) k_gemm_tc(const __grid_constant
       t_epi += clock64() - t_e0;
 #endif
     }
+    // tiles delivered to other GPUs: this thread's stores are performed system-wide before it leaves (once
+    // per launch; a fence per tile held the epilogue, and with it the issuer, for 0.24 ms per product)
+    if (kEpi == kEpiPlain && p.scatter_cols > 0) __threadfence_system();
 #ifdef B200_GEMM_TIMING
     if (p.dbg && threadIdx.x == 32 * kFirstEpiWarp) {
       p.dbg[blockIdx.x * 8 + 4] = (unsigned long long)t_tfull;
